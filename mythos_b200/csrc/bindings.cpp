@@ -1,0 +1,360 @@
+// Python binding of the sm_100a kernel library. Thin on purpose: tensors are checked
+// (device, dtype, contiguity of the innermost dimension), outputs are allocated by the Python
+// side, and every launch goes to torch's current CUDA stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "kernels/api.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void chk(const Tensor& t, c10::ScalarType dt, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == dt, name, " has dtype ", t.scalar_type(), ", expected ", dt);
+}
+void chk_c(const Tensor& t, c10::ScalarType dt, const char* name) {
+  chk(t, dt, name);
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+const void* cptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+void* mptr(OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+int* status_ptr(const OptTensor& s) {
+  if (!s.has_value()) return nullptr;
+  chk_c(*s, torch::kInt32, "status");
+  return s->data_ptr<int>();
+}
+
+constexpr auto BF16 = torch::kBFloat16;
+constexpr auto F32 = torch::kFloat32;
+constexpr auto I32 = torch::kInt32;
+constexpr auto U8 = torch::kUInt8;
+
+// out[M,N] (+)= alpha * op(a) * op(b)^T. a: [M,K] or, with a_mn, [K,M]; b: [N,K] or, with b_mn, [K,N].
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, int64_t epi, double alpha,
+          const OptTensor& status) {
+  chk(a, BF16, "a");
+  chk(b, BF16, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2, "gemm: operands must be 2-D");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm: innermost stride must be 1");
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: contraction sizes differ: ", K, " vs ", Kb);
+  TORCH_CHECK(out.size(0) == M && out.size(1) == N, "gemm: output shape mismatch");
+  chk(out, epi == mb::EPI_BF16 ? BF16 : F32, "out");
+  c10::cuda::CUDAGuard guard(a.device());
+  mb::gemm_bf16(a.data_ptr(), a.stride(0), a_mn, b.data_ptr(), b.stride(0), b_mn, out.data_ptr(), out.stride(0),
+                (int)M, (int)N, (int)K, (int)epi, (float)alpha, status_ptr(status), cur_stream());
+}
+
+void rmsnorm_fwd(const Tensor& x, const OptTensor& residual, const Tensor& gamma, Tensor& y, OptTensor resid_out,
+                 OptTensor rstd, double eps) {
+  chk_c(x, BF16, "x");
+  chk_c(gamma, BF16, "gamma");
+  chk_c(y, BF16, "y");
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::rmsnorm_fwd(x.data_ptr(), cptr(residual), gamma.data_ptr(), y.data_ptr(), mptr(resid_out),
+                  rstd.has_value() ? rstd->data_ptr<float>() : nullptr, (int)rows, (int)dim, (float)eps, cur_stream());
+}
+
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const Tensor& rstd, Tensor& dx,
+                 Tensor& dgamma_partial, Tensor& dgamma, bool accumulate) {
+  chk_c(dy, BF16, "dy");
+  chk_c(x, BF16, "x");
+  chk_c(gamma, BF16, "gamma");
+  chk_c(rstd, F32, "rstd");
+  chk_c(dx, BF16, "dx");
+  chk_c(dgamma_partial, F32, "dgamma_partial");
+  chk_c(dgamma, F32, "dgamma");
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  const int64_t n_partial = dgamma_partial.size(0);
+  TORCH_CHECK(dgamma_partial.size(1) == dim, "rmsnorm_bwd: partial buffer must be [n_partial, dim]");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                  dgamma_partial.data_ptr<float>(), (int)rows, (int)dim, (int)n_partial, cur_stream());
+  mb::rmsnorm_bwd_reduce(dgamma_partial.data_ptr<float>(), dgamma.data_ptr<float>(), (int)n_partial, (int)dim,
+                         accumulate, cur_stream());
+}
+
+void layernorm_fwd(const Tensor& x, const Tensor& gamma, const OptTensor& beta, Tensor& y, double eps) {
+  chk_c(x, BF16, "x");
+  chk_c(gamma, BF16, "gamma");
+  chk_c(y, BF16, "y");
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::layernorm_fwd(x.data_ptr(), gamma.data_ptr(), cptr(beta), y.data_ptr(), (int)rows, (int)dim, (float)eps,
+                    cur_stream());
+}
+
+// x: [tokens, heads, head_dim] view (heads/head_dim contiguous, arbitrary token stride), rotated in place.
+void rope(Tensor& x, const Tensor& pos, double theta, bool inverse) {
+  chk(x, BF16, "x");
+  chk_c(pos, I32, "pos");
+  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: x must be [tokens, heads, head_dim]");
+  TORCH_CHECK(pos.numel() == x.size(0), "rope: one position per token");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::rope_apply(x.data_ptr(), pos.data_ptr<int>(), (int)x.size(0), (int)x.size(1), (int)x.size(2), x.stride(0),
+                 (float)theta, inverse, cur_stream());
+}
+
+void swiglu_fused_fwd(const Tensor& gate_up, Tensor& out) {
+  chk_c(gate_up, BF16, "gate_up");
+  chk_c(out, BF16, "out");
+  const int64_t ffn = gate_up.size(-1) / 2, rows = gate_up.numel() / (2 * ffn);
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::swiglu_fused_fwd(gate_up.data_ptr(), out.data_ptr(), rows, (int)ffn, cur_stream());
+}
+void swiglu_fused_bwd(const Tensor& gate_up, const Tensor& dout, Tensor& dgate_up) {
+  chk_c(gate_up, BF16, "gate_up");
+  chk_c(dout, BF16, "dout");
+  chk_c(dgate_up, BF16, "dgate_up");
+  const int64_t ffn = gate_up.size(-1) / 2, rows = gate_up.numel() / (2 * ffn);
+  c10::cuda::CUDAGuard guard(dout.device());
+  mb::swiglu_fused_bwd(gate_up.data_ptr(), dout.data_ptr(), dgate_up.data_ptr(), rows, (int)ffn, cur_stream());
+}
+void swiglu_fwd(const Tensor& gate, const Tensor& up, Tensor& out) {
+  chk_c(gate, BF16, "gate");
+  chk_c(up, BF16, "up");
+  chk_c(out, BF16, "out");
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), cur_stream());
+}
+void swiglu_bwd(const Tensor& gate, const Tensor& up, const Tensor& dout, Tensor& dgate, Tensor& dup) {
+  chk_c(gate, BF16, "gate");
+  chk_c(up, BF16, "up");
+  chk_c(dout, BF16, "dout");
+  chk_c(dgate, BF16, "dgate");
+  chk_c(dup, BF16, "dup");
+  c10::cuda::CUDAGuard guard(dout.device());
+  mb::swiglu_bwd(gate.data_ptr(), up.data_ptr(), dout.data_ptr(), dgate.data_ptr(), dup.data_ptr(), gate.numel(),
+                 cur_stream());
+}
+void relu2_fwd(const Tensor& x, Tensor& out) {
+  chk_c(x, BF16, "x");
+  chk_c(out, BF16, "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::relu2_fwd(x.data_ptr(), out.data_ptr(), x.numel(), cur_stream());
+}
+void relu2_bwd(const Tensor& x, const Tensor& dout, Tensor& dx) {
+  chk_c(x, BF16, "x");
+  chk_c(dout, BF16, "dout");
+  chk_c(dx, BF16, "dx");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::relu2_bwd(x.data_ptr(), dout.data_ptr(), dx.data_ptr(), x.numel(), cur_stream());
+}
+void act_fwd(const Tensor& x, Tensor& out, int64_t kind) {
+  chk_c(x, BF16, "x");
+  chk_c(out, BF16, "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::act_fwd(x.data_ptr(), out.data_ptr(), x.numel(), (int)kind, cur_stream());
+}
+void add(const Tensor& a, const Tensor& b, Tensor& out) {
+  chk_c(a, BF16, "a");
+  chk_c(b, BF16, "b");
+  chk_c(out, BF16, "out");
+  c10::cuda::CUDAGuard guard(a.device());
+  mb::add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream());
+}
+void softmax_rows(const Tensor& x, Tensor& y) {
+  chk_c(x, BF16, "x");
+  chk_c(y, BF16, "y");
+  const int64_t cols = x.size(-1);
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::softmax_rows(x.data_ptr(), y.data_ptr(), (int)(x.numel() / cols), (int)cols, cur_stream());
+}
+
+void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
+  chk_c(ids, I32, "ids");
+  chk_c(table, BF16, "table");
+  chk_c(out, BF16, "out");
+  c10::cuda::CUDAGuard guard(table.device());
+  mb::embedding_fwd(ids.data_ptr<int>(), table.data_ptr(), out.data_ptr(), (int)ids.numel(), (int)table.size(1),
+                    (int)table.size(0), cur_stream());
+}
+void embedding_bwd(const Tensor& ids, const Tensor& dout, Tensor& dtable) {
+  chk_c(ids, I32, "ids");
+  chk_c(dout, BF16, "dout");
+  chk_c(dtable, F32, "dtable");
+  c10::cuda::CUDAGuard guard(dout.device());
+  mb::embedding_bwd(ids.data_ptr<int>(), dout.data_ptr(), dtable.data_ptr<float>(), (int)ids.numel(),
+                    (int)dtable.size(1), (int)dtable.size(0), cur_stream());
+}
+
+void cross_entropy_fwd_bwd(Tensor& logits, const Tensor& targets, Tensor& losses, double grad_scale) {
+  chk(logits, BF16, "logits");
+  chk_c(targets, I32, "targets");
+  chk_c(losses, F32, "losses");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "cross_entropy: logits must be [rows, vocab]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  mb::cross_entropy_fwd_bwd(logits.data_ptr(), targets.data_ptr<int>(), losses.data_ptr<float>(), (int)logits.size(0),
+                            (int)logits.size(1), logits.stride(0), (float)grad_scale, cur_stream());
+}
+void cross_entropy_fwd(const Tensor& logits, const Tensor& targets, Tensor& losses) {
+  chk(logits, BF16, "logits");
+  chk_c(targets, I32, "targets");
+  chk_c(losses, F32, "losses");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "cross_entropy: logits must be [rows, vocab]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  mb::cross_entropy_fwd(logits.data_ptr(), targets.data_ptr<int>(), losses.data_ptr<float>(), (int)logits.size(0),
+                        (int)logits.size(1), logits.stride(0), cur_stream());
+}
+
+void adamw_step(Tensor& p, Tensor& m, Tensor& v, const Tensor& g, OptTensor p_bf16, double lr, double beta1,
+                double beta2, double eps, double weight_decay, int64_t step, double grad_scale,
+                const OptTensor& clip_coef) {
+  chk_c(p, F32, "p");
+  chk_c(m, F32, "m");
+  chk_c(v, F32, "v");
+  chk_c(g, F32, "g");
+  mb::AdamWArgs a;
+  a.lr = (float)lr;
+  a.beta1 = (float)beta1;
+  a.beta2 = (float)beta2;
+  a.eps = (float)eps;
+  a.weight_decay = (float)weight_decay;
+  a.bc1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.bc2 = (float)(1.0 - std::pow(beta2, (double)step));
+  a.grad_scale = (float)grad_scale;
+  c10::cuda::CUDAGuard guard(p.device());
+  mb::adamw_step(p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(), mptr(p_bf16),
+                 p.numel(), a, clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr, cur_stream());
+}
+void sumsq(const Tensor& x, Tensor& out) {
+  chk_c(x, F32, "x");
+  chk_c(out, F32, "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::sumsq_f32(x.data_ptr<float>(), x.numel(), out.data_ptr<float>(), cur_stream());
+}
+void oil_fake_quant(const Tensor& w, const Tensor& codebooks, const OptTensor& cb_map, int64_t bs, OptTensor w_bf16,
+                    OptTensor idx) {
+  chk_c(w, F32, "w");
+  chk_c(codebooks, F32, "codebooks");
+  c10::cuda::CUDAGuard guard(w.device());
+  mb::oil_fake_quant(w.data_ptr<float>(), codebooks.data_ptr<float>(),
+                     cb_map.has_value() ? cb_map->data_ptr<int>() : nullptr, (int)codebooks.size(-1), (int)bs,
+                     w.numel(), mptr(w_bf16), idx.has_value() ? idx->data_ptr<uint8_t>() : nullptr, cur_stream());
+}
+void i2s_fake_quant(const Tensor& w, int64_t bs, OptTensor w_bf16, OptTensor trits, OptTensor scales) {
+  chk_c(w, F32, "w");
+  c10::cuda::CUDAGuard guard(w.device());
+  mb::i2s_fake_quant(w.data_ptr<float>(), (int)bs, w.numel(), mptr(w_bf16),
+                     trits.has_value() ? trits->data_ptr<uint8_t>() : nullptr,
+                     scales.has_value() ? scales->data_ptr<float>() : nullptr, cur_stream());
+}
+void cast_f32_to_bf16(const Tensor& x, Tensor& y) {
+  chk_c(x, F32, "x");
+  chk_c(y, BF16, "y");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::cast_f32_to_bf16(x.data_ptr<float>(), y.data_ptr(), x.numel(), cur_stream());
+}
+void cast_bf16_to_f32(const Tensor& x, Tensor& y, bool accumulate) {
+  chk_c(x, BF16, "x");
+  chk_c(y, F32, "y");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::cast_bf16_to_f32(x.data_ptr(), y.data_ptr<float>(), x.numel(), accumulate, cur_stream());
+}
+void oil_codebook_stats(const Tensor& w, const Tensor& idx, const OptTensor& cb_map, int64_t cb_size, int64_t bs,
+                        Tensor& counts, Tensor& sums) {
+  chk_c(w, F32, "w");
+  chk_c(idx, U8, "idx");
+  chk_c(counts, F32, "counts");
+  chk_c(sums, F32, "sums");
+  c10::cuda::CUDAGuard guard(w.device());
+  mb::oil_codebook_stats(w.data_ptr<float>(), idx.data_ptr<uint8_t>(),
+                         cb_map.has_value() ? cb_map->data_ptr<int>() : nullptr, (int)cb_size, (int)bs, w.numel(),
+                         counts.data_ptr<float>(), sums.data_ptr<float>(), cur_stream());
+}
+
+// q: [B,S,H,D] view, k/v: [B,S,Hkv,D] views (last two dims contiguous, batch stride = S * token stride).
+void flash_attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, bool causal,
+                    double scale, const OptTensor& status) {
+  chk(q, BF16, "q");
+  chk(k, BF16, "k");
+  chk(v, BF16, "v");
+  chk(o, BF16, "o");
+  chk_c(lse, F32, "lse");
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && o.dim() == 4, "flash_attn: tensors must be [B,S,H,D]");
+  const int64_t B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+  auto ok_view = [&](const Tensor& t) {
+    return t.stride(3) == 1 && t.stride(2) == D && t.stride(0) == t.stride(1) * S;
+  };
+  TORCH_CHECK(ok_view(q) && ok_view(k) && ok_view(v) && ok_view(o), "flash_attn: unsupported strides");
+  TORCH_CHECK(k.stride(1) == v.stride(1), "flash_attn: k and v must share a token stride");
+  c10::cuda::CUDAGuard guard(q.device());
+  mb::flash_attn_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), (int)B,
+                             (int)S, (int)H, (int)Hkv, (int)D, q.stride(1), k.stride(1), o.stride(1), causal,
+                             (float)scale, status_ptr(status), cur_stream());
+}
+
+void flash_attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& dout,
+                    const Tensor& lse, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& dq_accum, Tensor& delta,
+                    bool causal, double scale, const OptTensor& status) {
+  chk(q, BF16, "q");
+  chk(k, BF16, "k");
+  chk(v, BF16, "v");
+  chk_c(o, BF16, "o");
+  chk_c(dout, BF16, "dout");
+  chk_c(lse, F32, "lse");
+  chk(dq, BF16, "dq");
+  chk(dk, BF16, "dk");
+  chk(dv, BF16, "dv");
+  chk_c(dq_accum, F32, "dq_accum");
+  chk_c(delta, F32, "delta");
+  const int64_t B = q.size(0), S = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+  auto ok_view = [&](const Tensor& t) {
+    return t.stride(3) == 1 && t.stride(2) == D && t.stride(0) == t.stride(1) * S;
+  };
+  TORCH_CHECK(ok_view(q) && ok_view(k) && ok_view(v) && ok_view(dq) && ok_view(dk) && ok_view(dv),
+              "flash_attn_bwd: unsupported strides");
+  TORCH_CHECK(k.stride(1) == v.stride(1) && dk.stride(1) == dv.stride(1),
+              "flash_attn_bwd: k/v and dk/dv must share a token stride");
+  TORCH_CHECK(dq_accum.numel() >= B * S * H * D && delta.numel() >= B * H * S, "flash_attn_bwd: scratch too small");
+  c10::cuda::CUDAGuard guard(q.device());
+  mb::flash_attn_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
+                             lse.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                             dq_accum.data_ptr<float>(), delta.data_ptr<float>(), (int)B, (int)S, (int)H, (int)Hkv,
+                             (int)D, q.stride(1), k.stride(1), dq.stride(1), dk.stride(1), causal, (float)scale,
+                             status_ptr(status), cur_stream());
+}
+
+int64_t launch_count() { return mb::launch_count(); }
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "mythos_b200 sm_100a kernels";
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("rope", &rope);
+  m.def("swiglu_fused_fwd", &swiglu_fused_fwd);
+  m.def("swiglu_fused_bwd", &swiglu_fused_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("relu2_fwd", &relu2_fwd);
+  m.def("relu2_bwd", &relu2_bwd);
+  m.def("act_fwd", &act_fwd);
+  m.def("add", &add);
+  m.def("softmax_rows", &softmax_rows);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);
+  m.def("cross_entropy_fwd", &cross_entropy_fwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("sumsq", &sumsq);
+  m.def("oil_fake_quant", &oil_fake_quant);
+  m.def("i2s_fake_quant", &i2s_fake_quant);
+  m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
+  m.def("cast_bf16_to_f32", &cast_bf16_to_f32);
+  m.def("oil_codebook_stats", &oil_codebook_stats);
+  m.def("flash_attn_fwd", &flash_attn_fwd);
+  m.def("flash_attn_bwd", &flash_attn_bwd);
+  m.def("launch_count", &launch_count);
+}

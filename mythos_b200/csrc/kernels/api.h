@@ -1,0 +1,102 @@
+// Raw-pointer launch API of the sm_100a kernel library. No framework types appear here:
+// the torch binding (bindings.cpp) and the C ABI both sit on top of these functions.
+// All launchers are asynchronous on `stream`, bump the library's launch counter and throw
+// std::invalid_argument / mb::CudaError on bad arguments or launch failure.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mb {
+
+// ---- GEMM epilogues
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_F32_ATOMIC = 3 };
+
+// C[M,N] (+)= alpha * A * B^T on tcgen05 tensor cores. a_mn / b_mn: operand is stored
+// transposed ([K,M] / [K,N] row-major). lda/ldb/ldc are row strides in elements.
+// `status` (device int, may be null) receives a non-zero code if a bounded wait expires.
+void gemm_bf16(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
+               long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream);
+
+// ---- normalisation (norm.cu)
+void rmsnorm_fwd(const void* x, const void* residual, const void* gamma, void* y, void* resid_out, float* rstd,
+                 int rows, int dim, float eps, cudaStream_t stream);
+void rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, void* dx, float* dgamma_partial,
+                 int rows, int dim, int n_partial, cudaStream_t stream);
+void rmsnorm_bwd_reduce(const float* dgamma_partial, float* dgamma, int n_partial, int dim, bool accumulate,
+                        cudaStream_t stream);
+void layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int rows, int dim, float eps,
+                   cudaStream_t stream);
+
+// ---- rotary embedding, half-split pairs (d, d + D/2) (rope.cu)
+// x: [tokens, heads, head_dim] bf16 in place; pos: [tokens] int32; inverse = backward pass.
+void rope_apply(void* x, const int* pos, int tokens, int heads, int head_dim, long long token_stride, float theta,
+                bool inverse, cudaStream_t stream);
+
+// ---- activations / pointwise (act.cu)
+void swiglu_fwd(const void* gate, const void* up, void* out, long long n, cudaStream_t stream);
+void swiglu_bwd(const void* gate, const void* up, const void* dout, void* dgate, void* dup, long long n,
+                cudaStream_t stream);
+// gate/up interleaved in one [rows, 2*ffn] buffer (gate = cols [0,ffn), up = cols [ffn,2ffn))
+void swiglu_fused_fwd(const void* gate_up, void* out, long long rows, int ffn, cudaStream_t stream);
+void swiglu_fused_bwd(const void* gate_up, const void* dout, void* dgate_up, long long rows, int ffn,
+                      cudaStream_t stream);
+void relu2_fwd(const void* x, void* out, long long n, cudaStream_t stream);
+void relu2_bwd(const void* x, const void* dout, void* dx, long long n, cudaStream_t stream);
+enum : int { ACT_RELU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SIGMOID = 4, ACT_TANH = 5 };
+void act_fwd(const void* x, void* out, long long n, int kind, cudaStream_t stream);
+void add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
+void softmax_rows(const void* x, void* y, int rows, int cols, cudaStream_t stream);
+
+// ---- embedding (embed.cu)
+void embedding_fwd(const int* ids, const void* table, void* out, int tokens, int dim, int vocab, cudaStream_t stream);
+void embedding_bwd(const int* ids, const void* dout, float* dtable, int tokens, int dim, int vocab, cudaStream_t stream);
+
+// ---- cross-entropy: per-row loss + in-place gradient (ce.cu)
+// logits [rows, vocab] bf16 is overwritten with (softmax - onehot) * grad_scale; losses [rows] fp32.
+void cross_entropy_fwd_bwd(void* logits, const int* targets, float* losses, int rows, int vocab, long long ld,
+                           float grad_scale, cudaStream_t stream);
+void cross_entropy_fwd(const void* logits, const int* targets, float* losses, int rows, int vocab, long long ld,
+                       cudaStream_t stream);
+
+// ---- optimizer + STE fake-quant (optim.cu, quant.cu)
+struct AdamWArgs {
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale;
+};
+// p/m/v fp32 master state, g fp32 gradient (scaled by grad_scale and, when clip_coef is non-null,
+// by *clip_coef read on the device); optional bf16 shadow copy of p written to p_bf16.
+void adamw_step(float* p, float* m, float* v, const float* g, void* p_bf16, long long n, AdamWArgs a,
+                const float* clip_coef, cudaStream_t stream);
+void sumsq_f32(const float* x, long long n, float* out_accum, cudaStream_t stream);
+// Nearest-centroid fake quantisation through sorted codebooks.
+// w fp32 [n]; block b (bs weights) uses codebook cb_map[b] (or b when cb_map is null) of
+// `cb_size` ascending fp32 centroids. Outputs: bf16 dequantised weight and/or u8 indices.
+void oil_fake_quant(const float* w, const float* codebooks, const int* cb_map, int cb_size, int bs, long long n,
+                    void* w_bf16, uint8_t* idx, cudaStream_t stream);
+// I2_S ternary: per-block absmean scale, trit = clamp(round(w/scale), -1, 1).
+void i2s_fake_quant(const float* w, int bs, long long n, void* w_bf16, uint8_t* trits, float* scales,
+                    cudaStream_t stream);
+void cast_f32_to_bf16(const float* x, void* y, long long n, cudaStream_t stream);
+void cast_bf16_to_f32(const void* x, float* y, long long n, bool accumulate, cudaStream_t stream);
+// Codebook EMA statistics: counts[cb, k] += 1, sums[cb, k] += w for each weight's centroid.
+void oil_codebook_stats(const float* w, const uint8_t* idx, const int* cb_map, int cb_size, int bs, long long n,
+                        float* counts, float* sums, cudaStream_t stream);
+
+// ---- flash attention, training (attention.cu)
+// q,k,v,o: [batch, seq, heads, head_dim] bf16 (k/v with kv_heads); lse: [batch, heads, seq] fp32.
+void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq, int heads,
+                    int kv_heads, int head_dim, bool causal, float scale, int* status, cudaStream_t stream);
+void flash_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq,
+                            int heads, int kv_heads, int head_dim, long long q_tok_stride, long long kv_tok_stride,
+                            long long o_tok_stride, bool causal, float scale, int* status, cudaStream_t stream);
+void flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                    void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch, int seq, int heads,
+                    int kv_heads, int head_dim, bool causal, float scale, int* status, cudaStream_t stream);
+void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                            const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch,
+                            int seq, int heads, int kv_heads, int head_dim, long long q_tok_stride,
+                            long long kv_tok_stride, long long dq_tok_stride, long long dkv_tok_stride, bool causal,
+                            float scale, int* status, cudaStream_t stream);
+
+long long launch_count();
+
+}  // namespace mb

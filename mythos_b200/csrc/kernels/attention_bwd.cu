@@ -1,0 +1,430 @@
+// Flash attention backward on tcgen05 tensor cores (head_dim 128).
+//
+// One CTA owns a 128-row K/V tile of one (batch, kv head) and walks the 64-row query tiles that
+// can see it (all query heads of the GQA group). Everything is computed transposed so that one
+// thread owns one kv row:
+//     S^T  = K Q^T            dP^T = V dO^T                       (TMEM, 64 columns each)
+//     P^T  = exp2(S^T*c - lse)        dS^T = P^T o (dP^T - delta) * scale   (registers -> smem)
+//     dV  += P^T dO           dK  += dS^T Q                        (TMEM, 128 columns each)
+//     dQ^T = K^T dS^T                                              (TMEM, 64 columns) -> fp32 atomics
+// The same shared tiles serve as K-major operands in one product and MN-major in another, so
+// nothing is transposed in memory. dQ is accumulated in an fp32 scratch buffer and converted
+// to bf16 by a second kernel. Replaces the reference's four O(S^2 D) scalar loops
+// (src/autograd.cpp:463-584).
+#include "api.h"
+#include "common.cuh"
+#include "host_util.h"
+#include "tc.cuh"
+
+namespace mb {
+
+CUtensorMap make_bshd_map(const void* base, int batch, int seq, int nheads, int head_dim, long long tok_stride,
+                          int box_rows);
+
+namespace {
+
+constexpr int BW_THREADS = 192;
+constexpr int BW_KV = 128;  // kv rows per CTA
+constexpr int BW_Q = 64;    // query rows per step
+constexpr int BW_D = 128;
+
+struct BwCfg {
+  static constexpr int KV_BYTES = BW_KV * BW_D * 2;      // 32 KB, two 64-wide chunks of [128 x 128 B]
+  static constexpr int QT_BYTES = BW_Q * BW_D * 2;       // 16 KB, two chunks of [64 x 128 B]
+  static constexpr int STAGE_BYTES = 2 * QT_BYTES;       // Q + dO
+  static constexpr int PT_BYTES = BW_KV * BW_Q * 2;      // 16 KB
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = KV_BYTES;
+  static constexpr int OFF_ST = 2 * KV_BYTES;
+  static constexpr int OFF_PT = OFF_ST + 2 * STAGE_BYTES;
+  static constexpr int OFF_DST = OFF_PT + PT_BYTES;
+  static constexpr int OFF_STATS = OFF_DST + PT_BYTES;   // [4 warps][2 parity][lse 64 | delta 64] floats
+  static constexpr int OFF_BAR = OFF_STATS + 4 * 2 * 128 * 4;
+  static constexpr int NUM_BARS = 10;
+  static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256, COL_DQT = 384;
+};
+
+__global__ void __launch_bounds__(BW_THREADS, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+              const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dq_accum,
+              __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, long long dkv_tok_stride, int seq,
+              int heads, int kv_heads, int causal, float scale, float scale_log2, int* status) {
+  using Cfg = BwCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* kv_full = bars;         // K and V landed
+  uint64_t* q_full = bars + 1;      // [2] Q and dO of a step landed
+  uint64_t* q_empty = bars + 3;     // [2] the MMAs reading that stage completed
+  uint64_t* s_full = bars + 5;      // S^T and dP^T of a step computed
+  uint64_t* sp_free = bars + 6;     // compute threads hold S^T/dP^T in registers
+  uint64_t* pds_full = bars + 7;    // P^T and dS^T written to shared memory
+  uint64_t* mma_done = bars + 8;    // dV, dK, dQ^T products of a step completed
+  uint64_t* dq_free = bars + 9;     // compute threads drained dQ^T
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  float* stats = reinterpret_cast<float*>(smem + Cfg::OFF_STATS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvt = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int group = heads / kv_heads;
+  const int kv0 = kvt * BW_KV;
+  const int n_qt = (seq + BW_Q - 1) / BW_Q;
+  const int i_start = causal ? kv0 / BW_Q : 0;
+  const int per_head = n_qt - i_start;
+  const int N = group * per_head;  // steps of this CTA
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(sp_free, 128);
+    mbar_init(pds_full, 128);
+    mbar_init(mma_done, 1);
+    mbar_init(dq_free, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ loader
+    if (lane == 0 && N > 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * Cfg::KV_BYTES);
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(smem + Cfg::OFF_K + c * (BW_KV * 128), &tm_k, kv_full, c * 64, hkv, kv0, b);
+        tma_load_4d(smem + Cfg::OFF_V + c * (BW_KV * 128), &tm_v, kv_full, c * 64, hkv, kv0, b);
+      }
+      for (int n = 0; n < N; ++n) {
+        const int st = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, status, 21)) break;
+        const int h = hkv * group + n / per_head;
+        const int q0 = (i_start + n % per_head) * BW_Q;
+        mbar_arrive_expect_tx(&q_full[st], Cfg::STAGE_BYTES);
+        uint8_t* sq = smem + Cfg::OFF_ST + st * Cfg::STAGE_BYTES;
+        uint8_t* sdo = sq + Cfg::QT_BYTES;
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(sq + c * (BW_Q * 128), &tm_q, &q_full[st], c * 64, h, q0, b);
+          tma_load_4d(sdo + c * (BW_Q * 128), &tm_do, &q_full[st], c * 64, h, q0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && N > 0) {
+      constexpr uint32_t IDESC_ST = umma_idesc_bf16(BW_KV, BW_Q, false, false);   // S^T, dP^T
+      constexpr uint32_t IDESC_ACC = umma_idesc_bf16(BW_KV, BW_D, false, true);   // dV, dK
+      constexpr uint32_t IDESC_DQT = umma_idesc_bf16(BW_D, BW_Q, true, true);     // dQ^T
+      const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K);
+      const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V);
+      const uint32_t st_addr = smem_u32(smem + Cfg::OFF_ST);
+      const uint32_t pt_addr = smem_u32(smem + Cfg::OFF_PT);
+      const uint32_t dst_addr = smem_u32(smem + Cfg::OFF_DST);
+      auto issue_scores = [&](int n) {
+        const uint32_t qa = st_addr + (n & 1) * Cfg::STAGE_BYTES;
+        const uint32_t doa = qa + Cfg::QT_BYTES;
+#pragma unroll
+        for (int k = 0; k < BW_D / 16; ++k) {
+          const int c = k >> 2, kk = k & 3;
+          umma_f16(tmem_base + Cfg::COL_ST, umma_desc_sw128(k_addr + c * (BW_KV * 128) + kk * 32, 0, 1024),
+                   umma_desc_sw128(qa + c * (BW_Q * 128) + kk * 32, 0, 1024), IDESC_ST, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < BW_D / 16; ++k) {
+          const int c = k >> 2, kk = k & 3;
+          umma_f16(tmem_base + Cfg::COL_DPT, umma_desc_sw128(v_addr + c * (BW_KV * 128) + kk * 32, 0, 1024),
+                   umma_desc_sw128(doa + c * (BW_Q * 128) + kk * 32, 0, 1024), IDESC_ST, k > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, status, 22);
+      if (ok) ok = mbar_wait(&q_full[0], 0, abort_flag, status, 23);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int n = 0; n < N && ok; ++n) {
+        if (n + 1 < N) {
+          const int st = (n + 1) & 1;
+          if (!mbar_wait(&q_full[st], ((n + 1) >> 1) & 1, abort_flag, status, 24)) { ok = false; break; }
+          if (!mbar_wait(sp_free, n & 1, abort_flag, status, 25)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(n + 1);
+        }
+        if (!mbar_wait(pds_full, n & 1, abort_flag, status, 26)) { ok = false; break; }
+        if (n > 0 && !mbar_wait(dq_free, (n - 1) & 1, abort_flag, status, 27)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t qa = st_addr + (n & 1) * Cfg::STAGE_BYTES;
+        const uint32_t doa = qa + Cfg::QT_BYTES;
+#pragma unroll
+        for (int k = 0; k < BW_Q / 16; ++k)  // dV += P^T dO
+          umma_f16(tmem_base + Cfg::COL_DV, umma_desc_sw128(pt_addr + k * 32, 0, 1024),
+                   umma_desc_sw128(doa + k * 2048, BW_Q * 128, 1024), IDESC_ACC, (n > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < BW_Q / 16; ++k)  // dK += dS^T Q
+          umma_f16(tmem_base + Cfg::COL_DK, umma_desc_sw128(dst_addr + k * 32, 0, 1024),
+                   umma_desc_sw128(qa + k * 2048, BW_Q * 128, 1024), IDESC_ACC, (n > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < BW_KV / 16; ++k)  // dQ^T = K^T dS^T
+          umma_f16(tmem_base + Cfg::COL_DQT, umma_desc_sw128(k_addr + k * 2048, BW_KV * 128, 1024),
+                   umma_desc_sw128(dst_addr + k * 2048, BW_KV * 128, 1024), IDESC_DQT, k > 0 ? 1u : 0u);
+        umma_commit(mma_done);
+        umma_commit(&q_empty[n & 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warpgroup
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;   // kv row of this thread; also the d row of dQ^T
+    const int kv_row = kv0 + r;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    bool ok = true;
+
+    auto drain_dq = [&](int n) {
+      // dQ^T of step n is in TMEM: lane = d, column = q. Add it to the fp32 dQ buffer.
+      const int h = hkv * group + n / per_head;
+      const int q0 = (i_start + n % per_head) * BW_Q;
+      uint32_t a[2][32];
+      tmem_ld32(tmem_base + Cfg::COL_DQT + lane_sel, a[0]);
+      tmem_ld32(tmem_base + Cfg::COL_DQT + 32 + lane_sel, a[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dq_free);
+      float* base = dq_accum + (((long long)b * seq + q0) * heads + h) * BW_D + r;
+      const int nq = min(BW_Q, seq - q0);
+#pragma unroll
+      for (int q = 0; q < BW_Q; ++q)
+        if (q < nq) atomicAdd(base + (long long)q * heads * BW_D, __uint_as_float(a[q >> 5][q & 31]));
+    };
+
+    for (int n = 0; n < N && ok; ++n) {
+      const int h = hkv * group + n / per_head;
+      const int q0 = (i_start + n % per_head) * BW_Q;
+      // Each warp stages lse / delta of this query tile in its own shared-memory slot
+      // (double-buffered by step parity), so no CTA-wide barrier is needed here.
+      float* st_lse = stats + (quarter * 2 + (n & 1)) * 128;
+      float* st_dl = st_lse + 64;
+      {
+        const long long off = ((long long)b * heads + h) * seq;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int qi = half * 32 + lane;
+          const int q = q0 + qi;
+          st_lse[qi] = (q < seq) ? lse[off + q] * LOG2E : INFINITY;
+          st_dl[qi] = (q < seq) ? delta[off + q] : 0.f;
+        }
+      }
+      __syncwarp();
+
+      ok = mbar_wait(s_full, n & 1, abort_flag, status, 28);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[2][32], dr[2][32];
+      tmem_ld32(tmem_base + Cfg::COL_ST + lane_sel, sr[0]);
+      tmem_ld32(tmem_base + Cfg::COL_ST + 32 + lane_sel, sr[1]);
+      tmem_ld32(tmem_base + Cfg::COL_DPT + lane_sel, dr[0]);
+      tmem_ld32(tmem_base + Cfg::COL_DPT + 32 + lane_sel, dr[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(sp_free);
+      float* s = reinterpret_cast<float*>(&sr[0][0]);
+      float* d = reinterpret_cast<float*>(&dr[0][0]);
+      const bool diag = causal && (q0 < kv0 + BW_KV);
+#pragma unroll
+      for (int i = 0; i < BW_Q; ++i) {
+        float p = exp2f(s[i] * scale_log2 - st_lse[i]);
+        if (diag && (kv_row > q0 + i)) p = 0.f;
+        s[i] = p;
+        d[i] = p * (d[i] - st_dl[i]) * scale;
+      }
+      if (n > 0) {
+        ok = mbar_wait(mma_done, (n - 1) & 1, abort_flag, status, 29);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        drain_dq(n - 1);
+      }
+      uint8_t* pt = smem + Cfg::OFF_PT;
+      uint8_t* dst = smem + Cfg::OFF_DST;
+#pragma unroll
+      for (int c = 0; c < BW_Q / 8; ++c) {
+        uint4 v, w;
+        v.x = pack_bf16x2(s[8 * c + 0], s[8 * c + 1]);
+        v.y = pack_bf16x2(s[8 * c + 2], s[8 * c + 3]);
+        v.z = pack_bf16x2(s[8 * c + 4], s[8 * c + 5]);
+        v.w = pack_bf16x2(s[8 * c + 6], s[8 * c + 7]);
+        w.x = pack_bf16x2(d[8 * c + 0], d[8 * c + 1]);
+        w.y = pack_bf16x2(d[8 * c + 2], d[8 * c + 3]);
+        w.z = pack_bf16x2(d[8 * c + 4], d[8 * c + 5]);
+        w.w = pack_bf16x2(d[8 * c + 6], d[8 * c + 7]);
+        *reinterpret_cast<uint4*>(pt + sw128_offset(r, c)) = v;
+        *reinterpret_cast<uint4*>(dst + sw128_offset(r, c)) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+    }
+    if (ok && N > 0) {
+      ok = mbar_wait(mma_done, (N - 1) & 1, abort_flag, status, 30);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        drain_dq(N - 1);
+        // dV and dK rows of this thread
+        const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          __nv_bfloat16* out = (which == 0 ? dv : dk) + row_off;
+          const uint32_t col = which == 0 ? Cfg::COL_DV : Cfg::COL_DK;
+#pragma unroll 1
+          for (int c = 0; c < BW_D / 32; ++c) {
+            uint32_t a[32];
+            tmem_ld32(tmem_base + col + c * 32 + lane_sel, a);
+            tmem_ld_wait();
+            if (kv_row < seq) {
+              uint4* p4 = reinterpret_cast<uint4*>(out + c * 32);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(a[8 * i + 0]), __uint_as_float(a[8 * i + 1]));
+                v.y = pack_bf16x2(__uint_as_float(a[8 * i + 2]), __uint_as_float(a[8 * i + 3]));
+                v.z = pack_bf16x2(__uint_as_float(a[8 * i + 4]), __uint_as_float(a[8 * i + 5]));
+                v.w = pack_bf16x2(__uint_as_float(a[8 * i + 6]), __uint_as_float(a[8 * i + 7]));
+                p4[i] = v;
+              }
+            }
+          }
+        }
+      }
+    } else if (N == 0 && kv_row < seq) {
+      // no query can see this tile (cannot happen with causal self-attention, kept for safety)
+      const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
+      for (int i = 0; i < BW_D; ++i) {
+        dv[row_off + i] = __float2bfloat16(0.f);
+        dk[row_off + i] = __float2bfloat16(0.f);
+      }
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 10000000LL) {}
+    __syncthreads();
+  }
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h) row.
+__global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                    float* __restrict__ delta, long long rows, int seq, int heads, int head_dim) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float s = 0.f;
+  for (int c = lane * 8; c < head_dim; c += 256) {
+    float a[8], g[8];
+    unpack8(ldg8(o, row * head_dim + c), a);
+    unpack8(ldg8(dout, row * head_dim + c), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += a[i] * g[i];
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long bs = row / heads;  // b*seq + s
+    const int h = (int)(row % heads);
+    const long long bb = bs / seq, ss = bs % seq;
+    delta[(bb * heads + h) * seq + ss] = s;
+  }
+}
+
+// dst[r, 0:cols] (row stride dst_stride) = bf16(src[r, 0:cols]); cols is a multiple of 4.
+__global__ void cast_rows_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows,
+                                 int cols, long long dst_stride) {
+  const int per_row = cols >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per_row;
+    const int c = (int)(i % per_row) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(src + r * cols + c);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst + r * dst_stride + c) = o;
+  }
+}
+
+}  // namespace
+
+void flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                    void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch, int seq, int heads,
+                    int kv_heads, int head_dim, bool causal, float scale, int* status, cudaStream_t stream) {
+  flash_attn_bwd_strided(q, k, v, o, dout, lse, dq, dk, dv, dq_accum, delta, batch, seq, heads, kv_heads, head_dim,
+                         (long long)heads * head_dim, (long long)kv_heads * head_dim, (long long)heads * head_dim,
+                         (long long)kv_heads * head_dim, causal, scale, status, stream);
+}
+
+void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                            const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch,
+                            int seq, int heads, int kv_heads, int head_dim, long long q_tok_stride,
+                            long long kv_tok_stride, long long dq_tok_stride, long long dkv_tok_stride, bool causal,
+                            float scale, int* status, cudaStream_t stream) {
+  MB_REQUIRE(head_dim == 128, "flash_attn_bwd: head_dim must be 128");
+  MB_REQUIRE(heads % kv_heads == 0, "flash_attn_bwd: heads must be a multiple of kv_heads");
+  if (batch == 0 || seq == 0) return;
+  const long long rows = (long long)batch * seq * heads;
+  fa_bwd_delta_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                             delta, rows, seq, heads, head_dim);
+  count_launch();
+  check_launch();
+  MB_CUDA_CHECK(cudaMemsetAsync(dq_accum, 0, rows * head_dim * sizeof(float), stream));
+  const CUtensorMap tq = make_bshd_map(q, batch, seq, heads, head_dim, q_tok_stride, BW_Q);
+  const CUtensorMap tdo = make_bshd_map(dout, batch, seq, heads, head_dim, (long long)heads * head_dim, BW_Q);
+  const CUtensorMap tk = make_bshd_map(k, batch, seq, kv_heads, head_dim, kv_tok_stride, BW_KV);
+  const CUtensorMap tv = make_bshd_map(v, batch, seq, kv_heads, head_dim, kv_tok_stride, BW_KV);
+  static bool configured = false;
+  if (!configured) {
+    MB_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwCfg::SMEM_BYTES));
+    configured = true;
+  }
+  const dim3 grid((seq + BW_KV - 1) / BW_KV, kv_heads, batch);
+  fa_bwd_kernel<<<grid, BW_THREADS, BwCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, lse, delta, dq_accum,
+                                                                 (__nv_bfloat16*)dk, (__nv_bfloat16*)dv,
+                                                                 dkv_tok_stride, seq, heads, kv_heads, causal ? 1 : 0, scale,
+                                                                 scale * 1.4426950408889634f, status);
+  count_launch();
+  check_launch();
+  {
+    const long long tok = (long long)batch * seq;
+    const int cols = heads * head_dim;
+    long long g = (tok * (cols / 4) + 255) / 256;
+    const long long cap = (long long)sm_count() * 16;
+    if (g > cap) g = cap;
+    cast_rows_kernel<<<(int)g, 256, 0, stream>>>(dq_accum, (__nv_bfloat16*)dq, tok, cols, dq_tok_stride);
+    count_launch();
+    check_launch();
+  }
+}
+
+}  // namespace mb

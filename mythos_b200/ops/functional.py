@@ -1,0 +1,427 @@
+"""Differentiable operators of the framework.
+
+Every function here has two execution paths with the same semantics:
+
+* CUDA tensors run the hand-written sm_100a kernels (``mythos_b200._C``) wrapped in
+  ``torch.autograd.Function`` objects. Activations are bf16; weight gradients are accumulated in
+  fp32 directly into a caller-provided ``grad_target`` buffer (the flat gradient buffer that the
+  sharded optimizer and the fused reduce-scatter work on), so no per-parameter ``.grad`` tensors
+  exist on this path.
+* CPU tensors run the PyTorch reference formulas of :mod:`mythos_b200.ops.reference` under
+  ordinary autograd. That path is the oracle of the kernel tests.
+
+There is no fallback from the first path to the second: a CUDA tensor without the compiled
+extension raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import native, reference as ref
+
+EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_F32_ATOMIC = 0, 1, 2, 3
+
+
+def _C():
+    return native.require()
+
+
+# --------------------------------------------------------------------------------------- GEMM
+def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, epi: int = EPI_BF16, alpha: float = 1.0):
+    """``out[M,N] (+)= alpha * A @ B^T`` on tcgen05. ``a_mn``/``b_mn``: the operand is stored
+    transposed (``[K,M]`` / ``[K,N]``). ``epi`` selects bf16 store, fp32 store, fp32 read-add-store
+    or fp32 atomic accumulate (split-K)."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32)
+    _C().gemm(a, b, out, a_mn, b_mn, epi, alpha, native.status_word(a.device))
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T with W [N,K] bf16. Backward: dx = dy W (MN-major B), dW = dy^T x (both MN-major)
+    accumulated in fp32 into ``grad_target`` when given, else returned."""
+
+    @staticmethod
+    def forward(ctx, x, w, grad_target):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = gemm(x2, w)
+        ctx.save_for_backward(x2, w)
+        ctx.grad_target = grad_target
+        ctx.x_shape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
+        dw = None
+        if ctx.grad_target is not None:
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_target, epi=EPI_F32_ACC)
+        elif ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, epi=EPI_F32).to(w.dtype)
+        return dx, dw, None
+
+
+def linear(x, w, grad_target=None):
+    """``x @ w.T``. CUDA: tcgen05 GEMMs (bf16). CPU: torch matmul in the weight's dtype."""
+    if x.is_cuda:
+        return _LinearFn.apply(x, w, grad_target)
+    return torch.nn.functional.linear(x, w.to(x.dtype))
+
+
+# --------------------------------------------------------------------------------------- RMSNorm
+def _n_partial(rows: int, device) -> int:
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    return max(1, min(rows, sms * 2))
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, gamma, eps, grad_target):
+        C = _C()
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        rows = xc.numel() // xc.shape[-1]
+        rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
+        if residual is not None:
+            h = torch.empty_like(xc)
+            C.rmsnorm_fwd(xc, residual.contiguous(), gamma, y, h, rstd, eps)
+            h_out = h
+        else:
+            h = xc
+            C.rmsnorm_fwd(xc, None, gamma, y, None, rstd, eps)
+            h_out = torch.empty(0, device=x.device, dtype=x.dtype)  # placeholder: h is x itself
+            ctx.mark_non_differentiable(h_out)
+        ctx.save_for_backward(h, gamma, rstd)
+        ctx.grad_target = grad_target
+        ctx.has_residual = residual is not None
+        return y, h_out
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        C = _C()
+        h, gamma, rstd = ctx.saved_tensors
+        dim = h.shape[-1]
+        rows = h.numel() // dim
+        dx = torch.empty_like(h)
+        npart = _n_partial(rows, h.device)
+        partial = torch.empty(npart, dim, device=h.device, dtype=torch.float32)
+        if ctx.grad_target is not None:
+            C.rmsnorm_bwd(dy.contiguous(), h, gamma, rstd, dx, partial, ctx.grad_target, True)
+            dgamma = None
+        else:
+            dg = torch.empty(dim, device=h.device, dtype=torch.float32)
+            C.rmsnorm_bwd(dy.contiguous(), h, gamma, rstd, dx, partial, dg, False)
+            dgamma = dg.to(gamma.dtype)
+        if ctx.has_residual and dh is not None:
+            C.add(dx, dh.contiguous(), dx)
+        return dx, (dx if ctx.has_residual else None), dgamma, None, None
+
+
+def rmsnorm(x, gamma, eps: float = 1e-5, residual=None, grad_target=None):
+    """Returns ``(y, h)``: ``h = x + residual`` (``x`` itself without residual) and
+    ``y = h * rsqrt(mean(h^2)+eps) * gamma``."""
+    if x.is_cuda:
+        y, h = _RMSNormFn.apply(x, residual, gamma, eps, grad_target)
+        return y, (h if residual is not None else x)
+    h = x if residual is None else x + residual
+    rstd = torch.rsqrt(h.float().pow(2).mean(-1, keepdim=True) + eps)
+    return (h.float() * rstd * gamma.float()).to(x.dtype), h
+
+
+def layernorm(x, gamma, beta=None, eps: float = 1e-5):
+    if x.is_cuda and not torch.is_grad_enabled():
+        y = torch.empty_like(x.contiguous())
+        _C().layernorm_fwd(x.contiguous(), gamma, beta, y, eps)
+        return y
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), gamma.float(),
+                                          None if beta is None else beta.float(), eps).to(x.dtype)
+
+
+# --------------------------------------------------------------------------------------- attention
+_SUPPORTED_BWD_HEAD_DIMS = (128,)
+
+
+class _AttentionFn(torch.autograd.Function):
+    """RoPE (in place on the q and k slices of the fused projection) + causal flash attention.
+
+    qkv: [B, S, (H + 2*Hkv) * D] bf16, laid out q | k | v along the last dimension."""
+
+    @staticmethod
+    def forward(ctx, qkv, pos, H, Hkv, D, theta, causal, scale):
+        C = _C()
+        B, S, W = qkv.shape
+        assert W == (H + 2 * Hkv) * D and qkv.is_contiguous()
+        flat = qkv.view(B * S, W)
+        q = flat[:, : H * D].unflatten(-1, (H, D))
+        k = flat[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+        if theta > 0:
+            C.rope(q, pos, theta, False)
+            C.rope(k, pos, theta, False)
+        q4 = qkv[..., : H * D].unflatten(-1, (H, D))
+        k4 = qkv[..., H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+        v4 = qkv[..., (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+        o = torch.empty(B, S, H, D, device=qkv.device, dtype=qkv.dtype)
+        lse = torch.empty(B, H, S, device=qkv.device, dtype=torch.float32)
+        C.flash_attn_fwd(q4, k4, v4, o, lse, causal, scale, native.status_word(qkv.device))
+        ctx.save_for_backward(qkv, pos, o, lse)
+        ctx.cfg = (H, Hkv, D, theta, causal, scale)
+        return o.view(B, S, H * D)
+
+    @staticmethod
+    def backward(ctx, do):
+        C = _C()
+        qkv, pos, o, lse = ctx.saved_tensors
+        H, Hkv, D, theta, causal, scale = ctx.cfg
+        if D not in _SUPPORTED_BWD_HEAD_DIMS:
+            raise NotImplementedError(f"flash attention backward supports head_dim {_SUPPORTED_BWD_HEAD_DIMS}, got {D}")
+        B, S, W = qkv.shape
+        q4 = qkv[..., : H * D].unflatten(-1, (H, D))
+        k4 = qkv[..., H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+        v4 = qkv[..., (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+        dqkv = torch.empty_like(qkv)
+        dq4 = dqkv[..., : H * D].unflatten(-1, (H, D))
+        dk4 = dqkv[..., H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+        dv4 = dqkv[..., (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+        dq_accum = torch.empty(B * S * H * D, device=qkv.device, dtype=torch.float32)
+        delta = torch.empty(B * H * S, device=qkv.device, dtype=torch.float32)
+        do4 = do.reshape(B, S, H, D).contiguous()
+        C.flash_attn_bwd(q4, k4, v4, o, do4, lse, dq4, dk4, dv4, dq_accum, delta, causal, scale,
+                         native.status_word(qkv.device))
+        if theta > 0:
+            flat = dqkv.view(B * S, W)
+            C.rope(flat[:, : H * D].unflatten(-1, (H, D)), pos, theta, True)
+            C.rope(flat[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D)), pos, theta, True)
+        return dqkv, None, None, None, None, None, None, None
+
+
+def attention_qkv(qkv, pos, n_heads: int, n_kv_heads: int, head_dim: int, theta: float = 10000.0,
+                  causal: bool = True, scale: float | None = None):
+    """Self-attention over a fused projection ``qkv`` = [B, S, (H+2Hkv)*D] (q | k | v). RoPE with
+    half-split pairs is applied to q and k at positions ``pos`` ([B*S] int32); ``theta <= 0``
+    disables it. Returns [B, S, H*D]. On CUDA the projection buffer is rotated in place."""
+    scale = (1.0 / math.sqrt(head_dim)) if scale is None else scale
+    if qkv.is_cuda:
+        return _AttentionFn.apply(qkv, pos, n_heads, n_kv_heads, head_dim, theta, causal, scale)
+    B, S, _ = qkv.shape
+    H, Hkv, D = n_heads, n_kv_heads, head_dim
+    q = qkv[..., : H * D].reshape(B * S, H, D)
+    k = qkv[..., H * D: (H + Hkv) * D].reshape(B * S, Hkv, D)
+    v = qkv[..., (H + Hkv) * D:].reshape(B, S, Hkv, D)
+    if theta > 0:
+        q = ref.rope(q, pos, theta)
+        k = ref.rope(k, pos, theta)
+    o, _ = ref.attention(q.reshape(B, S, H, D), k.reshape(B, S, Hkv, D), v, causal, scale)
+    return o.reshape(B, S, H * D)
+
+
+def flash_attention(q, k, v, causal: bool = True, scale: float | None = None):
+    """Forward-only attention on [B,S,H,D] tensors (no RoPE). Returns (o, lse)."""
+    D = q.shape[-1]
+    scale = (1.0 / math.sqrt(D)) if scale is None else scale
+    if q.is_cuda:
+        B, S, H, _ = q.shape
+        o = torch.empty(B, S, H, D, device=q.device, dtype=q.dtype)
+        lse = torch.empty(B, H, S, device=q.device, dtype=torch.float32)
+        _C().flash_attn_fwd(q, k, v, o, lse, causal, scale, native.status_word(q.device))
+        return o, lse
+    return ref.attention(q, k, v, causal, scale)
+
+
+# --------------------------------------------------------------------------------------- gates
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        gu = gate_up.contiguous()
+        out = torch.empty(*gu.shape[:-1], gu.shape[-1] // 2, device=gu.device, dtype=gu.dtype)
+        _C().swiglu_fused_fwd(gu, out)
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        dgu = torch.empty_like(gu)
+        _C().swiglu_fused_bwd(gu, dout.contiguous(), dgu)
+        return dgu
+
+
+def swiglu(gate_up):
+    """``silu(gate) * up`` for a fused [.., 2*ffn] projection (gate first)."""
+    if gate_up.is_cuda:
+        return _SwiGLUFn.apply(gate_up)
+    f = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :f], gate_up[..., f:]
+    return g * torch.sigmoid(g) * u
+
+
+class _ReLU2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        _C().relu2_fwd(xc, out)
+        ctx.save_for_backward(xc)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (x,) = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        _C().relu2_bwd(x, dout.contiguous(), dx)
+        return dx
+
+
+def relu2(x):
+    """Squared ReLU (BitNet-style FFN activation)."""
+    if x.is_cuda:
+        return _ReLU2Fn.apply(x)
+    return torch.relu(x).pow(2)
+
+
+_ACT_IDS = {"relu": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "sigmoid": 4, "tanh": 5}
+
+
+def activation(x, kind: str):
+    """Inference-time pointwise activation (no autograd on the CUDA path)."""
+    if x.is_cuda and not torch.is_grad_enabled():
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        _C().act_fwd(xc, out, _ACT_IDS[kind])
+        return out
+    xf = x
+    if kind == "relu":
+        return torch.relu(xf)
+    if kind == "gelu":
+        return ref.gelu_erf(xf)
+    if kind == "gelu_tanh":
+        return ref.gelu_tanh(xf)
+    if kind == "silu":
+        return xf * torch.sigmoid(xf)
+    if kind == "sigmoid":
+        return torch.sigmoid(xf)
+    return torch.tanh(xf)
+
+
+# --------------------------------------------------------------------------------------- embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table, grad_target):
+        out = torch.empty(*ids.shape, table.shape[1], device=table.device, dtype=table.dtype)
+        _C().embedding_fwd(ids.contiguous(), table, out)
+        ctx.save_for_backward(ids)
+        ctx.grad_target = grad_target
+        ctx.tshape = table.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        if ctx.grad_target is not None:
+            _C().embedding_bwd(ids.contiguous(), dout.contiguous(), ctx.grad_target)
+            return None, None, None
+        dt = torch.zeros(ctx.tshape, device=dout.device, dtype=torch.float32)
+        _C().embedding_bwd(ids.contiguous(), dout.contiguous(), dt)
+        return None, dt.to(dout.dtype), None
+
+
+def embedding(ids, table, grad_target=None):
+    """Row gather; ids int32. Backward scatter-adds in fp32 (into ``grad_target`` when given)."""
+    if table.is_cuda:
+        return _EmbeddingFn.apply(ids, table, grad_target)
+    return torch.nn.functional.embedding(ids.long().clamp(0, table.shape[0] - 1), table)
+
+
+# --------------------------------------------------------------------------------------- loss
+class _CrossEntropyFn(torch.autograd.Function):
+    """Sum of per-row losses; the gradient (softmax - onehot) * grad_scale overwrites ``logits``
+    during the forward pass, so backward is free. The upstream gradient must be 1."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, grad_scale):
+        losses = torch.empty(logits.shape[0], device=logits.device, dtype=torch.float32)
+        _C().cross_entropy_fwd_bwd(logits, targets, losses, grad_scale)
+        ctx.save_for_backward(logits)
+        return losses.sum() * grad_scale
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return dlogits, None, None
+
+
+def cross_entropy(logits, targets, grad_scale: float | None = None):
+    """Scaled sum of next-token losses: ``grad_scale * sum_rows(logsumexp - logit[target])``
+    (``grad_scale`` defaults to 1/rows, i.e. the mean). logits: [rows, V]; targets int32 [rows].
+    On CUDA the logits buffer is consumed (overwritten with its gradient)."""
+    rows = logits.shape[0]
+    gs = (1.0 / rows) if grad_scale is None else grad_scale
+    if logits.is_cuda:
+        if torch.is_grad_enabled() and logits.requires_grad:
+            return _CrossEntropyFn.apply(logits, targets, gs)
+        losses = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        _C().cross_entropy_fwd(logits, targets, losses)
+        return losses.sum() * gs
+    return ref.cross_entropy(logits, targets).sum() * gs
+
+
+# --------------------------------------------------------------------------------------- quantisation / optimizer
+def oil_fake_quant(w, codebooks, cb_map, bs: int, want_idx: bool = False, out=None):
+    """Nearest-centroid fake quantisation of a flat fp32 tensor through sorted codebooks.
+    Returns (w_q bf16 on CUDA / fp32 on CPU, indices or None)."""
+    if w.is_cuda:
+        flat = w.reshape(-1)
+        wq = out if out is not None else torch.empty(flat.numel(), device=w.device, dtype=torch.bfloat16)
+        idx = torch.empty(flat.numel(), device=w.device, dtype=torch.uint8) if want_idx else None
+        _C().oil_fake_quant(flat, codebooks.contiguous(), cb_map, bs, wq, idx)
+        return wq.view(w.shape) if out is None else wq, idx
+    idx, deq = ref.nearest_centroid(w.reshape(-1), codebooks, cb_map, bs)
+    return deq.view(w.shape), (idx if want_idx else None)
+
+
+def i2s_fake_quant(w, bs: int, want_codes: bool = False, out=None):
+    if w.is_cuda:
+        flat = w.reshape(-1)
+        nb = (flat.numel() + bs - 1) // bs
+        wq = out if out is not None else torch.empty(flat.numel(), device=w.device, dtype=torch.bfloat16)
+        codes = torch.empty(flat.numel(), device=w.device, dtype=torch.uint8) if want_codes else None
+        scales = torch.empty(nb, device=w.device, dtype=torch.float32)
+        _C().i2s_fake_quant(flat, bs, wq, codes, scales)
+        return (wq.view(w.shape) if out is None else wq), codes, scales
+    codes, scales, deq = ref.i2s_quant(w.reshape(-1), bs)
+    return deq.view(w.shape), (codes if want_codes else None), scales
+
+
+def adamw_step(p, m, v, g, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=1, grad_scale=1.0,
+               clip_coef=None, p_bf16=None):
+    """One fused AdamW step on flat fp32 tensors (in place). ``clip_coef``: optional 1-element
+    device tensor multiplied into the gradient (global-norm clipping without a host sync)."""
+    if p.is_cuda:
+        _C().adamw_step(p, m, v, g, p_bf16, lr, beta1, beta2, eps, weight_decay, step, grad_scale, clip_coef)
+        return
+    gs = grad_scale * (float(clip_coef) if clip_coef is not None else 1.0)
+    ref.adamw_step(p, m, v, g, lr, beta1, beta2, eps, weight_decay, step, gs)
+    if p_bf16 is not None:
+        p_bf16.copy_(p)
+
+
+def sumsq(x, out=None):
+    """Sum of squares of a flat fp32 tensor, accumulated into ``out`` (1-element fp32)."""
+    if out is None:
+        out = torch.zeros(1, device=x.device, dtype=torch.float32)
+    if x.is_cuda:
+        _C().sumsq(x.reshape(-1), out)
+    else:
+        out += x.float().pow(2).sum()
+    return out

@@ -1,0 +1,214 @@
+"""Memory-bound kernels and flash attention against fp32 PyTorch references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    lim = atol + rtol * b.abs().max().item()
+    assert err <= lim, f"max err {err} > {lim}"
+
+
+@pytest.mark.parametrize("rows,dim", [(7, 256), (1024, 2048), (33, 4096), (5, 14336)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm_fwd_bwd(rows, dim, with_res):
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(rows + dim)
+    x = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
+    r = torch.randn(rows, dim, device="cuda").to(torch.bfloat16) if with_res else None
+    g = (1 + 0.1 * torch.randn(dim, device="cuda")).to(torch.bfloat16)
+    xg = x.clone().requires_grad_()
+    gg = g.clone().requires_grad_()
+    y, h = F.rmsnorm(xg, gg, 1e-5, r)
+    yr, hr = ref.rmsnorm(x, g, 1e-5, r)
+    _close(y, yr)
+    _close(h, hr)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    hf = hr.float().requires_grad_()
+    gf = g.float().requires_grad_()
+    rstd = torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5)
+    (hf * rstd * gf).backward(dy.float())
+    _close(xg.grad, hf.grad, atol=3e-2)
+    _close(gg.grad, gf.grad, rtol=3e-2, atol=0.15)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_rope_matches_formula(D):
+    from mythos_b200.ops import native, reference as ref
+
+    torch.manual_seed(D)
+    T, H = 50, 3
+    buf = torch.randn(T, H * D + 32, device="cuda").to(torch.bfloat16)
+    x = buf[:, : H * D].unflatten(-1, (H, D))
+    pos = torch.randint(0, 4096, (T,), device="cuda", dtype=torch.int32)
+    want = ref.rope(x.clone(), pos, 10000.0)
+    orig = x.clone()
+    native.require().rope(x, pos, 10000.0, False)
+    _close(x, want, atol=2e-2)
+    native.require().rope(x, pos, 10000.0, True)
+    _close(x, orig, atol=3e-2)
+
+
+def test_swiglu_relu2_and_activations():
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(3)
+    gu = torch.randn(37, 2 * 5504, device="cuda").to(torch.bfloat16).requires_grad_()
+    out = F.swiglu(gu)
+    _close(out, ref.swiglu(gu.detach()))
+    d = torch.randn_like(out)
+    out.backward(d)
+    gr = gu.detach().float().requires_grad_()
+    f = gr.shape[-1] // 2
+    (gr[:, :f] * torch.sigmoid(gr[:, :f]) * gr[:, f:]).backward(d.float())
+    _close(gu.grad, gr.grad, atol=4e-2)
+    x = torch.randn(64, 1024, device="cuda").to(torch.bfloat16).requires_grad_()
+    y = F.relu2(x)
+    _close(y, ref.relu2(x.detach()))
+    y.backward(torch.ones_like(y))
+    _close(x.grad, 2 * torch.relu(x.detach().float()))
+    with torch.no_grad():
+        for kind, fn in [("gelu", ref.gelu_erf), ("gelu_tanh", ref.gelu_tanh), ("sigmoid", torch.sigmoid),
+                         ("tanh", torch.tanh), ("relu", torch.relu)]:
+            _close(F.activation(x.detach(), kind), fn(x.detach().float()))
+        _close(F.layernorm(x.detach(), torch.ones(1024, device="cuda", dtype=torch.bfloat16)),
+               ref.layernorm(x.detach(), torch.ones(1024, device="cuda")))
+
+
+def test_embedding_fwd_bwd():
+    from mythos_b200.ops import functional as F
+
+    torch.manual_seed(4)
+    V, D = 1000, 256
+    table = torch.randn(V, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    ids = torch.randint(0, V, (3, 77), device="cuda", dtype=torch.int32)
+    gt = torch.zeros(V, D, device="cuda")
+    out = F.embedding(ids, table, gt)
+    assert torch.equal(out, table.detach()[ids.long()])
+    d = torch.randn_like(out)
+    out.backward(d)
+    want = torch.zeros(V, D, device="cuda").index_add_(0, ids.reshape(-1).long(), d.reshape(-1, D).float())
+    _close(gt, want, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("rows,V", [(64, 32000), (9, 1003), (16, 128256)])
+def test_cross_entropy_fused(rows, V):
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(V)
+    logits = (torch.randn(rows, V, device="cuda") * 3).to(torch.bfloat16)
+    pad = (8 - V % 8) % 8
+    buf = torch.zeros(rows, V + pad, device="cuda", dtype=torch.bfloat16)
+    buf[:, :V] = logits
+    lg = buf[:, :V].requires_grad_()
+    tg = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+    want = ref.cross_entropy(logits, tg).sum() / rows
+    wgrad = ref.cross_entropy_grad(logits, tg, 1.0 / rows)
+    loss = F.cross_entropy(lg, tg)
+    loss.backward()
+    assert abs(loss.item() - want.item()) < 2e-3 * max(1.0, abs(want.item()))
+    _close(lg.grad, wgrad, atol=2e-3 / rows + 1e-4)
+
+
+def test_adamw_and_sumsq():
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(5)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    m = torch.randn(n, device="cuda") * 0.01
+    v = torch.rand(n, device="cuda") * 0.01
+    g = torch.randn(n, device="cuda")
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    ref.adamw_step(pr, mr, vr, g, 3e-4, 0.9, 0.999, 1e-8, 0.01, 7, 0.5)
+    clip = torch.tensor([0.5], device="cuda")
+    pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    F.adamw_step(p, m, v, g, lr=3e-4, step=7, clip_coef=clip, p_bf16=pb)
+    assert torch.allclose(p, pr, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(m, mr, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(v, vr, rtol=1e-5, atol=1e-7)
+    assert torch.equal(pb, p.to(torch.bfloat16))
+    ss = F.sumsq(g)
+    assert abs(ss.item() - g.double().pow(2).sum().item()) < 1e-3 * n
+
+
+@pytest.mark.parametrize("fmt,bs,group", [("oil8", 64, 1), ("oil8", 256, 16), ("oil4", 256, 4)])
+def test_fake_quant_matches_bruteforce(fmt, bs, group):
+    from mythos_b200.oil import codebook as cbk
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(bs + group)
+    n = bs * 37 + 11
+    w = torch.randn(n, device="cuda") * 0.02
+    size = 256 if fmt == "oil8" else 16
+    nb = (n + bs - 1) // bs
+    ncb = (nb + group - 1) // group
+    cb = cbk.quantile_codebook(size, 0.02, fp16=(fmt == "oil4")).cuda()[None].repeat(ncb, 1)
+    cb = (cb * (1 + 0.1 * torch.rand(ncb, 1, device="cuda"))).contiguous()
+    cmap = (torch.arange(nb, device="cuda") // group).to(torch.int32) if group > 1 else None
+    wq, idx = F.oil_fake_quant(w, cb, cmap, bs, want_idx=True)
+    ridx, rdeq = ref.nearest_centroid(w, cb, cmap, bs)
+    assert torch.equal(idx, ridx)
+    assert torch.equal(wq, rdeq.to(torch.bfloat16))
+
+
+def test_i2s_fake_quant():
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(6)
+    w = torch.randn(256 * 9 + 5, device="cuda") * 0.02
+    wq, codes, scales = F.i2s_fake_quant(w, 256, want_codes=True)
+    rc, rs, rd = ref.i2s_quant(w, 256)
+    assert torch.allclose(scales, rs, rtol=1e-5)
+    assert (codes != rc).float().mean().item() < 1e-3  # round-half ties may differ by one ulp of w/scale
+    _close(wq, rd, atol=1e-3)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,D,causal", [
+    (1, 256, 2, 2, 128, True), (2, 512, 4, 2, 128, True), (1, 300, 2, 1, 128, True), (1, 384, 2, 2, 128, False),
+    (2, 256, 4, 4, 64, True), (1, 2048, 2, 2, 128, True)])
+def test_flash_attention_forward(B, S, H, Hkv, D, causal):
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(S + H)
+    q = torch.randn(B, S, H, D, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
+    o, lse = F.flash_attention(q, k, v, causal)
+    orf, lser = ref.attention(q, k, v, causal)
+    _close(o, orf, atol=2e-2)
+    assert torch.allclose(lse, lser, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 256, 2, 2), (2, 384, 4, 2), (1, 200, 2, 1), (1, 1024, 2, 2)])
+def test_attention_qkv_forward_backward(B, S, H, Hkv):
+    """RoPE + flash attention over a fused projection, gradients against autograd of the naive form."""
+    from mythos_b200.ops import functional as F, reference as ref
+
+    torch.manual_seed(S)
+    D = 128
+    W = (H + 2 * Hkv) * D
+    qkv = (torch.randn(B, S, W, device="cuda") * 0.5).to(torch.bfloat16)
+    pos = torch.arange(S, device="cuda", dtype=torch.int32).repeat(B)
+    x = qkv.clone().requires_grad_()
+    o = F.attention_qkv(x, pos, H, Hkv, D, 10000.0, True)
+    do = torch.randn_like(o)
+    o.backward(do)
+
+    xr = qkv.float().requires_grad_()
+    qf = xr[..., : H * D].reshape(B * S, H, D)
+    kf = xr[..., H * D:(H + Hkv) * D].reshape(B * S, Hkv, D)
+    vf = xr[..., (H + Hkv) * D:].reshape(B, S, Hkv, D)
+    qf, kf = ref.rope(qf, pos, 10000.0), ref.rope(kf, pos, 10000.0)
+    orf, _ = ref.attention(qf.reshape(B, S, H, D), kf.reshape(B, S, Hkv, D), vf, True)
+    orf = orf.reshape(B, S, H * D)
+    orf.backward(do.float())
+    _close(o, orf, atol=2e-2)
+    _close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
