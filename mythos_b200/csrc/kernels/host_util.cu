@@ -53,6 +53,13 @@ CUtensorMap make_tensor_map(const void* base, TmaDType dt, int rank, const uint6
   }
   MB_REQUIRE((box[0] * esz) % 16 == 0, "TMA box inner extent must be a multiple of 16 bytes");
   if (swizzle128) MB_REQUIRE(box[0] * esz == 128, "128-byte swizzle needs a 128-byte inner box");
+  // The encoder is a driver entry point and needs this thread's context to be current; a thread
+  // that has made no runtime call yet (an autograd worker) has none until the runtime binds one.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    MB_CUDA_CHECK(cudaFree(nullptr));
+    ctx_bound = true;
+  }
   CUtensorMap m;
   CUresult r = encode_fn()(&m, cdt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, gbox, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE,

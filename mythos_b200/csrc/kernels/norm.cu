@@ -13,7 +13,7 @@ namespace {
 constexpr int MAXC = 4;  // most 8-element chunks cached per thread (template NC <= MAXC)
 
 template <int NC>
-__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+__global__ void __launch_bounds__(1024) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                                    const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ y,
                                    __nv_bfloat16* __restrict__ resid_out, float* __restrict__ rstd_out, int dim,
                                    float eps) {
@@ -60,7 +60,7 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
 
 // Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dgamma partial in registers.
 template <int NC>
-__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ rstd,
                                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma_partial, int rows,
                                    int dim) {
@@ -127,7 +127,7 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
 }
 
 template <int NC>
-__global__ void layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+__global__ void __launch_bounds__(1024) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                                      const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y, int dim,
                                      float eps) {
   __shared__ float scratch[32];
@@ -172,12 +172,13 @@ __global__ void layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const 
   }
 }
 
-int norm_threads(int dim) {
+int norm_threads(int dim, int max_threads = 1024) {
   MB_REQUIRE(dim % 8 == 0, "norm: dim must be a multiple of 8");
   const int chunks = dim / 8;
-  MB_REQUIRE(chunks <= MAXC * 1024, "norm: dim too large (max 32768)");
+  MB_REQUIRE(chunks <= MAXC * max_threads, "norm: row too long for this kernel");
   int t = chunks <= 512 ? chunks : (chunks <= 2048 ? 512 : 1024);  // one chunk per thread for short rows
   t = ((t + 31) / 32) * 32;
+  if (t > max_threads) t = max_threads;
   return t < 32 ? 32 : t;
 }
 
@@ -207,7 +208,7 @@ void rmsnorm_fwd(const void* x, const void* residual, const void* gamma, void* y
 void rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, void* dx, float* dgamma_partial,
                  int rows, int dim, int n_partial, cudaStream_t stream) {
   if (rows == 0) return;
-  const int th = norm_threads(dim);
+  const int th = norm_threads(dim, 512);  // the backward keeps four row-sized arrays in registers
   MB_NORM_DISPATCH(norm_nc(dim, th), rmsnorm_bwd_kernel,
                    <<<n_partial, th, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                   (const __nv_bfloat16*)gamma, rstd, (__nv_bfloat16*)dx,

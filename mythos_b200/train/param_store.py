@@ -70,7 +70,9 @@ class ParamStore:
             s.param.data = view
             if self.bound:
                 s.param.main_grad = self.grad[s.offset:s.offset + s.numel].view(s.param.shape)
-                s.param.compute = self.compute[s.offset:s.offset + s.numel].view(s.param.shape)
+                # The compute image is a leaf that "requires grad" so autograd records the graph of
+                # the custom functions; their backward adds into main_grad and returns no gradient.
+                s.param.compute = self.compute[s.offset:s.offset + s.numel].view(s.param.shape).requires_grad_()
         model.to(device)  # buffers (codebooks, maps); parameters already live in the flat buffer
         for s in self.slots:  # .to() may have rebound param.data; restore the views
             s.param.data = self.master[s.offset:s.offset + s.numel].view(s.param.shape)
