@@ -323,6 +323,72 @@ void flash_attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Ten
                              status_ptr(status), cur_stream());
 }
 
+mb::PeerPtrs to_peers(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() <= (size_t)mb::MAX_PEERS, "too many peers");
+  mb::PeerPtrs pp{};
+  for (size_t i = 0; i < ptrs.size(); ++i) pp.p[i] = reinterpret_cast<void*>(static_cast<uintptr_t>(ptrs[i]));
+  return pp;
+}
+
+// flag_ptrs / slot_ptrs: per-rank addresses (as mapped in this process) of the int32 flag array and
+// the fp32 slot array. send_val: optional 1-element fp32 tensor delivered to every rank.
+void symm_barrier(const std::vector<int64_t>& flag_ptrs, const std::vector<int64_t>& slot_ptrs,
+                  const OptTensor& send_val, int64_t rank, int64_t epoch, int64_t limit_cycles,
+                  const OptTensor& status) {
+  mb::symm_barrier(to_peers(flag_ptrs), to_peers(slot_ptrs),
+                   send_val.has_value() ? send_val->data_ptr<float>() : nullptr, (int)rank, (int)flag_ptrs.size(),
+                   (int)epoch, limit_cycles, status_ptr(status), cur_stream());
+}
+
+void zero_reduce_scatter(const std::vector<int64_t>& grad_ptrs, Tensor& out, int64_t shard_off, Tensor& sumsq) {
+  chk_c(out, F32, "out");
+  chk_c(sumsq, F32, "sumsq");
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::zero_reduce_scatter(to_peers(grad_ptrs), out.data_ptr<float>(), shard_off, out.numel(), (int)grad_ptrs.size(),
+                          sumsq.data_ptr<float>(), cur_stream());
+}
+
+void zero_adamw_ste_allgather(Tensor& p, Tensor& m, Tensor& v, const Tensor& g,
+                              const std::vector<int64_t>& compute_ptrs, int64_t shard_off, const OptTensor& seg_fmt,
+                              const OptTensor& seg_cb, const OptTensor& codebooks8, const OptTensor& codebooks4,
+                              const Tensor& norm_partials, OptTensor grad_norm_out, double max_norm, double lr,
+                              double beta1, double beta2, double eps, double weight_decay, int64_t step,
+                              double grad_scale, int64_t rank) {
+  chk_c(p, F32, "p");
+  chk_c(m, F32, "m");
+  chk_c(v, F32, "v");
+  chk_c(g, F32, "g");
+  chk_c(norm_partials, F32, "norm_partials");
+  mb::ZeroFusedArgs a{};
+  a.p = p.data_ptr<float>();
+  a.m = m.data_ptr<float>();
+  a.v = v.data_ptr<float>();
+  a.g = g.data_ptr<float>();
+  a.compute = to_peers(compute_ptrs);
+  a.shard_off = shard_off;
+  a.n = p.numel();
+  a.seg_fmt = seg_fmt.has_value() ? seg_fmt->data_ptr<uint8_t>() : nullptr;
+  a.seg_cb = seg_cb.has_value() ? seg_cb->data_ptr<int>() : nullptr;
+  a.codebooks8 = codebooks8.has_value() ? codebooks8->data_ptr<float>() : nullptr;
+  a.codebooks4 = codebooks4.has_value() ? codebooks4->data_ptr<float>() : nullptr;
+  a.norm_partials = norm_partials.data_ptr<float>();
+  a.grad_norm_out = grad_norm_out.has_value() ? grad_norm_out->data_ptr<float>() : nullptr;
+  a.max_norm = (float)max_norm;
+  a.opt.lr = (float)lr;
+  a.opt.beta1 = (float)beta1;
+  a.opt.beta2 = (float)beta2;
+  a.opt.eps = (float)eps;
+  a.opt.weight_decay = (float)weight_decay;
+  a.opt.bc1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.opt.bc2 = (float)(1.0 - std::pow(beta2, (double)step));
+  a.opt.grad_scale = (float)grad_scale;
+  a.rank = (int)rank;
+  a.world = (int)compute_ptrs.size();
+  TORCH_CHECK((int64_t)norm_partials.numel() >= a.world, "norm_partials needs one slot per rank");
+  c10::cuda::CUDAGuard guard(p.device());
+  mb::zero_adamw_ste_allgather(a, cur_stream());
+}
+
 int64_t launch_count() { return mb::launch_count(); }
 
 }  // namespace
@@ -356,5 +422,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("oil_codebook_stats", &oil_codebook_stats);
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("flash_attn_bwd", &flash_attn_bwd);
+  m.def("symm_barrier", &symm_barrier);
+  m.def("zero_reduce_scatter", &zero_reduce_scatter);
+  m.def("zero_adamw_ste_allgather", &zero_adamw_ste_allgather);
   m.def("launch_count", &launch_count);
 }

@@ -97,6 +97,35 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
                             long long kv_tok_stride, long long dq_tok_stride, long long dkv_tok_stride, bool causal,
                             float scale, int* status, cudaStream_t stream);
 
+// ---- peer-memory collectives fused with compute (comm.cu)
+constexpr int MAX_PEERS = 16;
+struct PeerPtrs {
+  void* p[MAX_PEERS];  // the same symmetric buffer as mapped on this rank, one pointer per rank
+};
+enum : int { ZERO_FMT_CAST = 0, ZERO_FMT_OIL8 = 1, ZERO_FMT_OIL4 = 2, ZERO_FMT_I2S = 3 };
+struct ZeroFusedArgs {
+  float *p, *m, *v;            // local fp32 shard of master weights and Adam moments, n elements
+  const float* g;              // local reduced gradient shard
+  PeerPtrs compute;            // every rank's full bf16 compute buffer
+  long long shard_off, n;      // element offset of the shard in the flat buffer; shard length
+  const uint8_t* seg_fmt;      // per 256-element segment of the flat buffer: ZERO_FMT_*
+  const int* seg_cb;           // per segment: codebook row in codebooks8 / codebooks4
+  const float* codebooks8;     // [n, 256] ascending fp32
+  const float* codebooks4;     // [n, 16] ascending fp32
+  const float* norm_partials;  // world floats: each rank's sum of squares of its reduced shard
+  float* grad_norm_out;        // optional: the global gradient norm
+  float max_norm;              // clip threshold (0 = off)
+  AdamWArgs opt;
+  int rank, world;
+};
+// Flag barrier across ranks; with send_val != null also delivers *send_val into slot [rank] of every
+// rank's `slots` array. The wait gives up after limit_cycles and records it in `status`.
+void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* send_val, int rank, int world, int epoch,
+                  long long limit_cycles, int* status, cudaStream_t stream);
+void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,
+                         cudaStream_t stream);
+void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream);
+
 long long launch_count();
 
 }  // namespace mb

@@ -1,0 +1,205 @@
+// Data-parallel collectives fused with compute, over NVLink peer memory.
+//
+// Every rank maps the other ranks' buffers (symmetric memory) and the kernels issue plain
+// peer loads and stores; nothing here goes through a library collective.
+//
+//   symm_barrier        flag barrier between ranks (st.release.sys / ld.acquire.sys on peer
+//                       memory), optionally carrying one float per rank (the partial gradient
+//                       norm). The wait is bounded and reports a timeout in the status word.
+//   zero_reduce_scatter rank r sums slice r of every rank's fp32 gradient buffer in fixed rank
+//                       order (deterministic), keeps the result locally and accumulates its
+//                       sum of squares: reduce-scatter + global-norm partial in one pass.
+//   zero_adamw_ste_allgather
+//                       on the local shard: clip coefficient from the gathered norm partials,
+//                       AdamW on the fp32 master, STE fake-quantisation of the updated weights
+//                       (OIL8 / OIL4 nearest centroid in a sorted codebook, I2_S absmean ternary,
+//                       or plain cast) and the bf16 result stored straight into every rank's
+//                       compute buffer: optimizer + quantiser + all-gather in one pass.
+//
+// The reference's counterpart is DDPWrapper::sync_gradients (src/distributed.cpp:102-138): one
+// blocking all-reduce per parameter through a mutex-protected host buffer, followed by a
+// separate optimizer loop.
+#include "api.h"
+#include "common.cuh"
+#include "host_util.h"
+
+namespace mb {
+namespace {
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// One thread per peer. flags[r] on every rank is an int array of `world` slots; slot s of rank r
+// holds the last epoch that rank s announced to rank r.
+__global__ void symm_barrier_kernel(PeerPtrs flags, PeerPtrs slots, const float* send_val, int rank, int world,
+                                    int epoch, long long limit_cycles, int* status) {
+  const int p = threadIdx.x;
+  if (p >= world) return;
+  __threadfence_system();
+  if (send_val) reinterpret_cast<float*>(slots.p[p])[rank] = *send_val;
+  st_release_sys(reinterpret_cast<int*>(flags.p[p]) + rank, epoch);
+  const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + p;
+  const long long t0 = clock64();
+  while (ld_acquire_sys(mine) < epoch) {
+    if (clock64() - t0 > limit_cycles) {
+      if (status) atomicCAS(status, 0, 1 | (40 << 16));
+      break;
+    }
+  }
+}
+
+__global__ void zero_reduce_scatter_kernel(PeerPtrs grads, float* __restrict__ out, long long shard_off, long long n,
+                                           int world, float* __restrict__ sumsq) {
+  __shared__ float scratch[32];
+  float ss = 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int r = 0; r < world; ++r) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + shard_off) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq) atomicAdd(sumsq, ss);
+}
+
+template <int CB>
+__device__ __forceinline__ int nearest_sorted_dev(const float* cb, float w) {
+  int lo = 0;
+#pragma unroll
+  for (int step = CB >> 1; step > 0; step >>= 1)
+    if (cb[lo + step - 1] < w) lo += step;
+  if (lo < CB && cb[lo] < w) ++lo;
+  int j;
+  if (lo == 0) j = 0;
+  else if (lo >= CB) j = CB - 1;
+  else j = (w - cb[lo - 1] <= cb[lo] - w) ? lo - 1 : lo;
+  while (j > 0 && cb[j - 1] == cb[j]) --j;
+  return j;
+}
+
+// One warp per 256-element segment of the local shard.
+__global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a) {
+  extern __shared__ float cb_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  float* cb = cb_smem + warp * 256;
+  float total = 0.f;
+  for (int r = 0; r < a.world; ++r) total += a.norm_partials[r];
+  const float norm = sqrtf(total);
+  const float clip = (a.max_norm > 0.f && norm > a.max_norm) ? a.max_norm / (norm + 1e-8f) : 1.f;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && a.grad_norm_out) *a.grad_norm_out = norm;
+  const float gs = a.opt.grad_scale * clip;
+  const long long nseg = a.n >> 8;
+  int cached = -1;
+  for (long long seg = (long long)blockIdx.x * wpb + warp; seg < nseg; seg += (long long)gridDim.x * wpb) {
+    const long long base = seg * 256 + lane * 8;
+    float p[8], m[8], v[8], g[8];
+    *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(a.p + base);
+    *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(a.p + base + 4);
+    *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(a.m + base);
+    *reinterpret_cast<float4*>(m + 4) = *reinterpret_cast<const float4*>(a.m + base + 4);
+    *reinterpret_cast<float4*>(v) = *reinterpret_cast<const float4*>(a.v + base);
+    *reinterpret_cast<float4*>(v + 4) = *reinterpret_cast<const float4*>(a.v + base + 4);
+    *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(a.g + base);
+    *reinterpret_cast<float4*>(g + 4) = *reinterpret_cast<const float4*>(a.g + base + 4);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = g[k] * gs;
+      p[k] -= a.opt.lr * a.opt.weight_decay * p[k];
+      m[k] = a.opt.beta1 * m[k] + (1.f - a.opt.beta1) * gk;
+      v[k] = a.opt.beta2 * v[k] + (1.f - a.opt.beta2) * gk * gk;
+      p[k] -= a.opt.lr * (m[k] / a.opt.bc1) / (sqrtf(v[k] / a.opt.bc2) + a.opt.eps);
+    }
+    *reinterpret_cast<float4*>(a.p + base) = *reinterpret_cast<float4*>(p);
+    *reinterpret_cast<float4*>(a.p + base + 4) = *reinterpret_cast<float4*>(p + 4);
+    *reinterpret_cast<float4*>(a.m + base) = *reinterpret_cast<float4*>(m);
+    *reinterpret_cast<float4*>(a.m + base + 4) = *reinterpret_cast<float4*>(m + 4);
+    *reinterpret_cast<float4*>(a.v + base) = *reinterpret_cast<float4*>(v);
+    *reinterpret_cast<float4*>(a.v + base + 4) = *reinterpret_cast<float4*>(v + 4);
+
+    const long long gseg = (a.shard_off >> 8) + seg;  // segment index in the full flat buffer
+    const int fmt = a.seg_fmt ? a.seg_fmt[gseg] : ZERO_FMT_CAST;
+    float q[8];
+    if (fmt == ZERO_FMT_OIL8 || fmt == ZERO_FMT_OIL4) {
+      const int cbi = a.seg_cb[gseg];
+      const int key = cbi * 2 + (fmt == ZERO_FMT_OIL4 ? 1 : 0);
+      if (key != cached) {
+        __syncwarp();
+        if (fmt == ZERO_FMT_OIL8) {
+          for (int i = lane; i < 256; i += 32) cb[i] = a.codebooks8[(long long)cbi * 256 + i];
+        } else if (lane < 16) {
+          cb[lane] = a.codebooks4[(long long)cbi * 16 + lane];
+        }
+        cached = key;
+        __syncwarp();
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        q[k] = (fmt == ZERO_FMT_OIL8) ? cb[nearest_sorted_dev<256>(cb, p[k])] : cb[nearest_sorted_dev<16>(cb, p[k])];
+    } else if (fmt == ZERO_FMT_I2S) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += fabsf(p[k]);
+      s = warp_sum(s);
+      const float scale = s * (1.f / 256.f);
+      const float inv = scale > 0.f ? 1.f / scale : 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = fminf(1.f, fmaxf(-1.f, rintf(p[k] * inv))) * scale;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = p[k];
+    }
+    const bf16x8 packed = pack8(q);
+    const long long gelem = a.shard_off + base;
+    for (int r = 0; r < a.world; ++r) {
+      const int dst = (a.rank + r) % a.world;  // start with the local copy, then fan out
+      stg8(a.compute.p[dst], gelem, packed);
+    }
+  }
+}
+
+}  // namespace
+
+void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* send_val, int rank, int world, int epoch,
+                  long long limit_cycles, int* status, cudaStream_t stream) {
+  MB_REQUIRE(world >= 1 && world <= MAX_PEERS, "symm_barrier: world size out of range");
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(flags, slots, send_val, rank, world, epoch, limit_cycles, status);
+  count_launch();
+  check_launch();
+}
+
+void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,
+                         cudaStream_t stream) {
+  MB_REQUIRE(n % 4 == 0 && shard_off % 4 == 0, "zero_reduce_scatter: shard must be a multiple of 4 elements");
+  if (n == 0) return;
+  long long grid = (n / 4 + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (grid > cap) grid = cap;
+  zero_reduce_scatter_kernel<<<(int)grid, 256, 0, stream>>>(grads, out, shard_off, n, world, sumsq);
+  count_launch();
+  check_launch();
+}
+
+void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream) {
+  MB_REQUIRE(a.n % 256 == 0 && a.shard_off % 256 == 0, "zero_adamw_ste_allgather: shard must be 256-aligned");
+  if (a.n == 0) return;
+  const int threads = 256, wpb = threads / 32;
+  long long grid = ((a.n >> 8) + wpb - 1) / wpb;
+  const long long cap = (long long)sm_count() * 8;
+  if (grid > cap) grid = cap;
+  zero_adamw_ste_allgather_kernel<<<(int)grid, threads, wpb * 256 * sizeof(float), stream>>>(a);
+  count_launch();
+  check_launch();
+}
+
+}  // namespace mb

@@ -1,0 +1,184 @@
+"""Kernel micro-benchmarks (the role of the reference's ``oil_bench --kernel`` and
+``bench/bench_kernels.cpp``): times one kernel with CUDA events after warm-up, flushing L2 between
+iterations, and reports achieved TFLOP/s or GB/s next to the measured device peaks.
+
+    python -m mythos_b200.tools.kernel_bench --kernel gemm --m 16384 --n 2048 --k 2048
+    python -m mythos_b200.tools.kernel_bench --kernel attn_fwd --batch 8 --seq 2048 --heads 16
+    python -m mythos_b200.tools.kernel_bench --kernel all
+
+This is also the program profiled for the summaries under ``profiles/``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p.get("bf16_tflops", 1590.0), p.get("hbm_gbs", 6650.0), "measured"
+    except OSError:
+        return 1590.0, 6650.0, "fallback"
+
+
+class Timer:
+    def __init__(self, iters: int, warmup: int, flush: bool = True):
+        self.iters, self.warmup, self.flush = iters, warmup, flush
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+
+    def __call__(self, fn) -> float:
+        """Median milliseconds per call."""
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(self.iters):
+            if self.buf is not None:
+                self.buf.zero_()  # 256 MB write evicts the 126 MB L2
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        times.sort()
+        return times[len(times) // 2]
+
+
+def bench_gemm(t: Timer, M, N, K, layout="kk", epi=0):
+    from mythos_b200.ops import functional as F
+
+    a_mn, b_mn = {"kk": (False, False), "kmn": (False, True), "mnmn": (True, True)}[layout]
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16 if epi == 0 else torch.float32)
+    ms = t(lambda: F.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, epi=epi))
+    return ms, 2.0 * M * N * K / ms / 1e9, "TFLOP/s"
+
+
+def bench_attn(t: Timer, B, S, H, Hkv, D, backward=False):
+    from mythos_b200.ops import functional as F
+
+    W = (H + 2 * Hkv) * D
+    qkv = (torch.randn(B, S, W, device="cuda") * 0.5).to(torch.bfloat16)
+    pos = torch.arange(S, device="cuda", dtype=torch.int32).repeat(B)
+    flops_fwd = 4.0 * B * H * S * S * D * 0.5
+    if not backward:
+        q = qkv[..., : H * D].unflatten(-1, (H, D))
+        k = qkv[..., H * D:(H + Hkv) * D].unflatten(-1, (Hkv, D))
+        v = qkv[..., (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+        ms = t(lambda: F.flash_attention(q, k, v, True))
+        return ms, flops_fwd / ms / 1e9, "TFLOP/s"
+    x = qkv.clone().requires_grad_()
+    o = F.attention_qkv(x, pos, H, Hkv, D, 0.0, True)
+    do = torch.randn_like(o)
+    ms = t(lambda: torch.autograd.grad(o, x, do, retain_graph=True))
+    return ms, 2.5 * flops_fwd / ms / 1e9, "TFLOP/s"
+
+
+def bench_memory_bound(t: Timer, name: str, rows: int, dim: int):
+    from mythos_b200.ops import native, reference  # noqa: F401
+
+    C = native.require()
+    x = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
+    g = torch.ones(dim, device="cuda", dtype=torch.bfloat16)
+    y = torch.empty_like(x)
+    if name == "rmsnorm":
+        rstd = torch.empty(rows, device="cuda")
+        ms = t(lambda: C.rmsnorm_fwd(x, None, g, y, None, rstd, 1e-5))
+        nbytes = 2 * x.numel() * 2
+    elif name == "swiglu":
+        out = torch.empty(rows, dim // 2, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: C.swiglu_fused_fwd(x, out))
+        nbytes = x.numel() * 2 + out.numel() * 2
+    elif name == "ce":
+        tg = torch.randint(0, dim, (rows,), device="cuda", dtype=torch.int32)
+        losses = torch.empty(rows, device="cuda")
+        ms = t(lambda: C.cross_entropy_fwd_bwd(x, tg, losses, 1.0 / rows))
+        nbytes = 3 * x.numel() * 2
+    elif name == "adamw":
+        n = rows * dim
+        p, m, v, gr = (torch.randn(n, device="cuda") for _ in range(4))
+        ms = t(lambda: C.adamw_step(p, m, v, gr, None, 3e-4, 0.9, 0.999, 1e-8, 0.01, 5, 1.0, None))
+        nbytes = n * 4 * 7
+    elif name == "fake_quant":
+        from mythos_b200.oil.codebook import quantile_codebook
+
+        n = rows * dim
+        w = torch.randn(n, device="cuda") * 0.02
+        nb = n // 256
+        cb = quantile_codebook(256).cuda()[None].repeat((nb + 127) // 128, 1).contiguous()
+        cmap = (torch.arange(nb, device="cuda") // 128).to(torch.int32)
+        out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: C.oil_fake_quant(w, cb, cmap, 256, out, None))
+        nbytes = n * 6
+    else:
+        raise ValueError(name)
+    return ms, nbytes / ms / 1e6, "GB/s"
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--kernel", default="all")
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=2048)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--layout", default="kk", choices=["kk", "kmn", "mnmn"])
+    ap.add_argument("--epi", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=0)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--dim", type=int, default=2048)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+    tf_peak, bw_peak, src = _peaks()
+    t = Timer(args.iters, args.warmup, not args.no_flush)
+    hkv = args.kv_heads or args.heads
+    rows = []
+
+    def report(name, res):
+        ms, val, unit = res
+        frac = val / (tf_peak if unit == "TFLOP/s" else bw_peak)
+        rows.append({"kernel": name, "ms": round(ms, 4), "value": round(val, 1), "unit": unit,
+                     f"fraction_of_{src}_peak": round(frac, 3)})
+        print(json.dumps(rows[-1]), flush=True)
+
+    k = args.kernel
+    if k in ("gemm", "all"):
+        if k == "gemm":
+            report(f"gemm_{args.layout}_{args.m}x{args.n}x{args.k}_epi{args.epi}",
+                   bench_gemm(t, args.m, args.n, args.k, args.layout, args.epi))
+        else:
+            for (M, N, K, lay, epi) in [(16384, 6144, 2048, "kk", 0), (16384, 2048, 2048, "kk", 0),
+                                        (16384, 11008, 2048, "kk", 0), (16384, 2048, 5504, "kk", 0),
+                                        (16384, 32000, 2048, "kk", 0), (16384, 2048, 6144, "kmn", 0),
+                                        (16384, 5504, 2048, "kmn", 0), (6144, 2048, 16384, "mnmn", 2),
+                                        (11008, 2048, 16384, "mnmn", 2), (2048, 5504, 16384, "mnmn", 2),
+                                        (32000, 2048, 16384, "mnmn", 2), (8192, 8192, 8192, "kk", 0)]:
+                report(f"gemm_{lay}_{M}x{N}x{K}_epi{epi}", bench_gemm(t, M, N, K, lay, epi))
+    if k in ("attn_fwd", "all"):
+        report(f"attn_fwd_b{args.batch}_s{args.seq}_h{args.heads}_d{args.head_dim}",
+               bench_attn(t, args.batch, args.seq, args.heads, hkv, args.head_dim, False))
+    if k in ("attn_bwd", "all"):
+        report(f"attn_bwd_b{args.batch}_s{args.seq}_h{args.heads}_d128",
+               bench_attn(t, args.batch, args.seq, args.heads, hkv, 128, True))
+    for name, r, d in [("rmsnorm", args.rows, args.dim), ("swiglu", args.rows, 11008), ("ce", 4096, 32000),
+                       ("adamw", 16384, 4096), ("fake_quant", 16384, 4096)]:
+        if k in (name, "all"):
+            report(f"{name}_{r}x{d}", bench_memory_bound(t, name, r, d))
+
+
+if __name__ == "__main__":
+    main()

@@ -35,23 +35,29 @@ class Slot:
 
 
 class ParamStore:
-    def __init__(self, model: nn.Module, device=None, world_size: int = 1, grad_buffer: torch.Tensor | None = None,
-                 compute_buffer: torch.Tensor | None = None):
+    @staticmethod
+    def plan(model: nn.Module, world_size: int = 1):
+        """Flat layout of the trainable parameters: (slots, total elements). ``total`` is padded so
+        that every rank's shard is a whole number of 256-element segments."""
         params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
         if not params:
             raise ValueError("model has no trainable parameters")
-        device = torch.device(device) if device is not None else params[0][1].device
         owners = {}
         for m in model.modules():
             if isinstance(m, OILLinear):
                 owners[id(m.weight)] = m
-        self.slots: list[Slot] = []
+        slots: list[Slot] = []
         off = 0
         for n, p in params:
-            self.slots.append(Slot(n, p, off, p.numel(), owners.get(id(p))))
+            slots.append(Slot(n, p, off, p.numel(), owners.get(id(p))))
             off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
         unit = ALIGN * world_size
-        self.total = (off + unit - 1) // unit * unit
+        return slots, (off + unit - 1) // unit * unit
+
+    def __init__(self, model: nn.Module, device=None, world_size: int = 1, grad_buffer: torch.Tensor | None = None,
+                 compute_buffer: torch.Tensor | None = None):
+        self.slots, self.total = self.plan(model, world_size)
+        device = torch.device(device) if device is not None else self.slots[0].param.device
         self.world_size = world_size
         self.shard = self.total // world_size
         self.device = device

@@ -175,6 +175,9 @@ class Trainer:
         (reference: every 100 steps, decay 0.999, src/trainer.cpp:507-512)."""
         from ..oil.codebook import EMAState
 
+        if self.dp is not None:
+            self.dp.gather_master()  # statistics are taken over the full, current master weights
+            self._force_refresh = True
         for mod in self.model.modules():
             if not isinstance(mod, OILLinear) or mod.codebooks is None:
                 continue
@@ -191,9 +194,7 @@ class Trainer:
                 slot = cbi.repeat_interleave(mod.block_size)[: w.numel()] * mod.codebooks.shape[-1] + idx.long()
                 counts.view(-1).index_add_(0, slot, torch.ones_like(w))
                 sums.view(-1).index_add_(0, slot, w.float())
-            if self.dp is not None:
-                self.dp.all_reduce_(counts)
-                self.dp.all_reduce_(sums)
+            # data parallel: every rank sees the same gathered weights, so the statistics agree
             ema = self._ema.get(id(mod))
             if ema is None:
                 ema = self._ema[id(mod)] = EMAState(mod.codebooks, self.cfg.codebook_ema_decay)

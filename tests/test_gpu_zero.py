@@ -1,0 +1,100 @@
+"""Peer-memory data-parallel kernels, checked on one GPU by emulating the ranks: every "rank"
+gets its own buffers on the same device and the kernels (which never wait on one another) are
+launched rank by rank. The flag barrier is exercised with a single rank and with a flag that
+nothing sets (the bounded wait must expire and report, not hang)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reduce_scatter_adamw_ste_allgather_emulated_ranks():
+    from mythos_b200.oil.codebook import quantile_codebook
+    from mythos_b200.ops import native, reference as ref
+
+    C = native.require()
+    torch.manual_seed(0)
+    world, seg = 2, 256
+    n_seg = 64
+    total = n_seg * seg
+    shard = total // world
+    master = torch.randn(total, device="cuda") * 0.02
+    grads = [torch.randn(total, device="cuda") * 0.01 for _ in range(world)]
+    compute = [torch.zeros(total, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    # segments: first quarter cast, then OIL8 (two codebooks), OIL4, I2_S
+    seg_fmt = torch.zeros(n_seg, dtype=torch.uint8)
+    seg_cb = torch.zeros(n_seg, dtype=torch.int32)
+    seg_fmt[16:32] = 1
+    seg_cb[24:32] = 1
+    seg_fmt[32:48] = 2
+    seg_fmt[48:] = 3
+    cb8 = torch.stack([quantile_codebook(256, 0.02), quantile_codebook(256, 0.03)]).cuda()
+    cb4 = quantile_codebook(16, 0.02, fp16=True)[None].cuda()
+    seg_fmt, seg_cb = seg_fmt.cuda(), seg_cb.cuda()
+    ms = [torch.zeros(shard, device="cuda") for _ in range(world)]
+    vs = [torch.zeros(shard, device="cuda") for _ in range(world)]
+    masters = [master.clone() for _ in range(world)]
+    gsh = [torch.empty(shard, device="cuda") for _ in range(world)]
+    parts = torch.zeros(world, device="cuda")
+    for r in range(world):
+        p = torch.zeros(1, device="cuda")
+        C.zero_reduce_scatter([g.data_ptr() for g in grads], gsh[r], r * shard, p)
+        parts[r] = p[0]
+    gsum = grads[0] + grads[1]
+    for r in range(world):
+        assert torch.allclose(gsh[r], gsum[r * shard:(r + 1) * shard], atol=1e-7)
+    assert abs(parts.sum().item() - gsum.double().pow(2).sum().item()) < 1e-4
+    gn = torch.zeros(1, device="cuda")
+    max_norm = 0.5 * gsum.norm().item()  # force clipping
+    for r in range(world):
+        C.zero_adamw_ste_allgather(masters[r][r * shard:(r + 1) * shard], ms[r], vs[r], gsh[r],
+                                   [c.data_ptr() for c in compute], r * shard, seg_fmt, seg_cb, cb8, cb4, parts, gn,
+                                   max_norm, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, r)
+    torch.cuda.synchronize()
+    assert abs(gn.item() - gsum.norm().item()) < 1e-3 * gsum.norm().item()
+    # reference: AdamW on the clipped summed gradient, then per-segment quantisation
+    pr, mr, vr = master.clone(), torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
+    clip = max_norm / (gsum.norm().item() + 1e-8)
+    ref.adamw_step(pr, mr, vr, gsum, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, clip)
+    new_master = torch.cat([masters[r][r * shard:(r + 1) * shard] for r in range(world)])
+    assert torch.allclose(new_master, pr, rtol=1e-5, atol=1e-7)
+    want = torch.empty(total, device="cuda")
+    want[:16 * seg] = pr[:16 * seg]
+    _, d = ref.nearest_centroid(pr[16 * seg:24 * seg], cb8[0:1], torch.zeros(8, dtype=torch.int32, device="cuda"), seg)
+    want[16 * seg:24 * seg] = d
+    _, d = ref.nearest_centroid(pr[24 * seg:32 * seg], cb8[1:2], torch.zeros(8, dtype=torch.int32, device="cuda"), seg)
+    want[24 * seg:32 * seg] = d
+    _, d = ref.nearest_centroid(pr[32 * seg:48 * seg], cb4, torch.zeros(16, dtype=torch.int32, device="cuda"), seg)
+    want[32 * seg:48 * seg] = d
+    _, _, d = ref.i2s_quant(pr[48 * seg:], seg)
+    want[48 * seg:] = d
+    for r in range(world):
+        got = compute[r].float()
+        mism = (got != want.to(torch.bfloat16).float()).float().mean().item()
+        assert mism < 2e-3, f"rank {r}: {mism} of the compute image differs"  # ulp-level AdamW differences may flip a centroid
+        assert torch.equal(compute[0], compute[r])
+
+
+def test_flag_barrier_single_rank_and_timeout():
+    from mythos_b200.ops import native
+    from mythos_b200.parallel import symm
+
+    C = native.require()
+    bar = symm.FlagBarrier("cuda")
+    val = torch.tensor([3.5], device="cuda")
+    bar.sync(val)
+    bar.sync()
+    torch.cuda.synchronize()
+    native.check_status("cuda")
+    assert bar.slots[0].item() == 3.5
+    # two "ranks" whose second flag array nobody signals: rank 0 must give up after the limit
+    fa = torch.zeros(64, dtype=torch.int32, device="cuda")
+    fb = torch.zeros(64, dtype=torch.int32, device="cuda")
+    sl = torch.zeros(64, device="cuda")
+    C.symm_barrier([fa.data_ptr(), fb.data_ptr()], [sl.data_ptr(), sl.data_ptr()], None, 0, 1, 2_000_000,
+                   native.status_word("cuda"))
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="status 1"):
+        native.check_status("cuda")
+    native.check_status("cuda")  # cleared
+    assert fb[0].item() == 1  # the signal to the peer was still delivered
