@@ -334,10 +334,11 @@ mb::PeerPtrs to_peers(const std::vector<int64_t>& ptrs) {
 // the fp32 slot array. send_val: optional 1-element fp32 tensor delivered to every rank.
 void symm_barrier(const std::vector<int64_t>& flag_ptrs, const std::vector<int64_t>& slot_ptrs,
                   const OptTensor& send_val, int64_t rank, int64_t epoch, int64_t limit_cycles,
-                  const OptTensor& status) {
+                  const OptTensor& status, const OptTensor& epoch_dev) {
   mb::symm_barrier(to_peers(flag_ptrs), to_peers(slot_ptrs),
                    send_val.has_value() ? send_val->data_ptr<float>() : nullptr, (int)rank, (int)flag_ptrs.size(),
-                   (int)epoch, limit_cycles, status_ptr(status), cur_stream());
+                   (int)epoch, epoch_dev.has_value() ? epoch_dev->data_ptr<int>() : nullptr, limit_cycles,
+                   status_ptr(status), cur_stream());
 }
 
 void zero_reduce_scatter(const std::vector<int64_t>& grad_ptrs, Tensor& out, int64_t shard_off, Tensor& sumsq) {
@@ -389,6 +390,160 @@ void zero_adamw_ste_allgather(Tensor& p, Tensor& m, Tensor& v, const Tensor& g,
   mb::zero_adamw_ste_allgather(a, cur_stream());
 }
 
+mb::DequantWeights to_weights(const Tensor& packed, const OptTensor& codebooks, const OptTensor& cb_map,
+                              const OptTensor& scales, int64_t fmt, int64_t N, int64_t K, int64_t block_size) {
+  chk_c(packed, U8, "packed");
+  mb::DequantWeights w{};
+  w.packed = packed.data_ptr<uint8_t>();
+  if (codebooks.has_value()) {
+    chk_c(*codebooks, BF16, "codebooks");
+    w.codebooks = codebooks->data_ptr();
+  }
+  if (cb_map.has_value()) {
+    chk_c(*cb_map, I32, "cb_map");
+    w.cb_map = cb_map->data_ptr<int>();
+  }
+  if (scales.has_value()) {
+    chk_c(*scales, F32, "scales");
+    w.scales = scales->data_ptr<float>();
+  }
+  w.fmt = (int)fmt;
+  w.N = (int)N;
+  w.K = (int)K;
+  w.block_size = (int)block_size;
+  const int64_t need = fmt == mb::QFMT_OIL8 ? N * K : (fmt == mb::QFMT_OIL4 ? N * K / 2 : N * K / 4);
+  TORCH_CHECK(packed.numel() >= need, "packed weight buffer too small: ", packed.numel(), " < ", need);
+  TORCH_CHECK(fmt == mb::QFMT_I2S ? scales.has_value() : codebooks.has_value(), "missing codebooks / scales");
+  return w;
+}
+
+// y = x @ dequant(W)^T. out: bf16 [M,N] (direct) or fp32 [M,N] accumulator; peer_ptrs: fp32
+// accumulators of all ranks (fused all-reduce), in which case `out` is ignored.
+void dequant_gemm(const Tensor& x, const Tensor& packed, const OptTensor& codebooks, const OptTensor& cb_map,
+                  const OptTensor& scales, int64_t fmt, int64_t N, int64_t K, int64_t block_size, OptTensor out,
+                  const std::vector<int64_t>& peer_ptrs, int64_t k_splits, const OptTensor& status) {
+  chk(x, BF16, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) == K, "dequant_gemm: x must be [M, K]");
+  const auto w = to_weights(packed, codebooks, cb_map, scales, fmt, N, K, block_size);
+  void* o16 = nullptr;
+  float* o32 = nullptr;
+  int64_t ld = N;
+  if (peer_ptrs.empty()) {
+    TORCH_CHECK(out.has_value(), "dequant_gemm: need an output tensor");
+    TORCH_CHECK(out->dim() == 2 && out->size(0) == x.size(0) && out->size(1) == N && out->stride(1) == 1,
+                "dequant_gemm: output must be [M, N]");
+    ld = out->stride(0);
+    if (out->scalar_type() == BF16) o16 = out->data_ptr();
+    else {
+      chk(*out, F32, "out");
+      o32 = out->data_ptr<float>();
+    }
+  }
+  const mb::PeerPtrs pp = to_peers(peer_ptrs);
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::dequant_gemm(x.data_ptr(), x.stride(0), (int)x.size(0), w, o16, o32, peer_ptrs.empty() ? nullptr : &pp,
+                   (int)peer_ptrs.size(), ld, (int)k_splits, status_ptr(status), cur_stream());
+}
+
+void finalize_acc(Tensor& acc, const OptTensor& residual, Tensor& out) {
+  chk_c(acc, F32, "acc");
+  chk_c(out, BF16, "out");
+  c10::cuda::CUDAGuard guard(acc.device());
+  mb::finalize_acc(acc.data_ptr<float>(), cptr(residual), out.data_ptr(), out.numel(), cur_stream());
+}
+
+void dequant_to_bf16(const Tensor& packed, const OptTensor& codebooks, const OptTensor& cb_map, const OptTensor& scales,
+                     int64_t fmt, int64_t N, int64_t K, int64_t block_size, Tensor& out) {
+  chk_c(out, BF16, "out");
+  TORCH_CHECK(out.numel() >= N * K, "dequant_to_bf16: output too small");
+  const auto w = to_weights(packed, codebooks, cb_map, scales, fmt, N, K, block_size);
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::dequant_to_bf16(w, out.data_ptr(), cur_stream());
+}
+
+void i2s_gemv(const Tensor& x, const Tensor& packed, const Tensor& scales, int64_t N, int64_t K, int64_t block_size,
+              Tensor& y) {
+  chk_c(x, BF16, "x");
+  chk_c(y, BF16, "y");
+  const auto w = to_weights(packed, c10::nullopt, c10::nullopt, scales, mb::QFMT_I2S, N, K, block_size);
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::i2s_gemv(x.data_ptr(), w, y.data_ptr(), cur_stream());
+}
+
+// k, v: [tokens, kv_heads, head_dim] views (token stride arbitrary); caches [pages, page, kv_heads, head_dim].
+void kv_append(const Tensor& k, const Tensor& v, Tensor& k_cache, Tensor& v_cache, const Tensor& block_table,
+               const Tensor& positions, const Tensor& seq_ids) {
+  chk(k, BF16, "k");
+  chk(v, BF16, "v");
+  chk_c(k_cache, BF16, "k_cache");
+  chk_c(v_cache, BF16, "v_cache");
+  chk_c(block_table, I32, "block_table");
+  chk_c(positions, I32, "positions");
+  chk_c(seq_ids, I32, "seq_ids");
+  TORCH_CHECK(k.dim() == 3 && k.stride(2) == 1 && k.stride(1) == k.size(2) && k.stride(0) == v.stride(0),
+              "kv_append: k/v must be [tokens, kv_heads, head_dim] with a shared token stride");
+  c10::cuda::CUDAGuard guard(k.device());
+  mb::kv_append(k.data_ptr(), v.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int>(),
+                positions.data_ptr<int>(), seq_ids.data_ptr<int>(), (int)k.size(0), (int)k.size(1), (int)k.size(2),
+                (int)k_cache.size(1), (int)block_table.size(1), k.stride(0), cur_stream());
+}
+
+void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
+                       const Tensor& context_lens, Tensor& out, Tensor& scratch, Tensor& counters, int64_t splits,
+                       double scale) {
+  chk_c(q, BF16, "q");
+  chk_c(k_cache, BF16, "k_cache");
+  chk_c(v_cache, BF16, "v_cache");
+  chk_c(block_table, I32, "block_table");
+  chk_c(context_lens, I32, "context_lens");
+  chk_c(out, BF16, "out");
+  chk_c(scratch, F32, "scratch");
+  chk_c(counters, I32, "counters");
+  const int64_t B = q.size(0), H = q.size(1), D = q.size(2), Hkv = k_cache.size(2);
+  TORCH_CHECK(scratch.numel() >= B * H * splits * (D + 2), "paged_attn_decode: scratch too small");
+  TORCH_CHECK(counters.numel() >= B * Hkv, "paged_attn_decode: counters too small");
+  c10::cuda::CUDAGuard guard(q.device());
+  mb::paged_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int>(),
+                        context_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(),
+                        counters.data_ptr<int>(), (int)B, (int)H, (int)Hkv, (int)D, (int)k_cache.size(1),
+                        (int)block_table.size(1), (int)splits, (float)scale, cur_stream());
+}
+
+void sample_tokens(const Tensor& logits, const OptTensor& history, const OptTensor& allow_mask, double temperature,
+                   int64_t top_k, double top_p, double repetition_penalty, int64_t seed, Tensor& out_tokens,
+                   OptTensor out_logprob) {
+  chk(logits, BF16, "logits");
+  chk_c(out_tokens, I32, "out_tokens");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "sample_tokens: logits must be [rows, vocab]");
+  const int* hist = nullptr;
+  int hist_len = 0;
+  if (history.has_value()) {
+    chk_c(*history, I32, "history");
+    hist = history->data_ptr<int>();
+    hist_len = (int)history->size(1);
+  }
+  mb::SamplerArgs a{(float)temperature, (float)top_p, (float)repetition_penalty, (int)top_k,
+                    (unsigned long long)seed};
+  c10::cuda::CUDAGuard guard(logits.device());
+  mb::sample_tokens(logits.data_ptr(), logits.stride(0), (int)logits.size(0), (int)logits.size(1), hist, hist_len,
+                    allow_mask.has_value() ? allow_mask->data_ptr<unsigned char>() : nullptr, a,
+                    out_tokens.data_ptr<int>(), out_logprob.has_value() ? out_logprob->data_ptr<float>() : nullptr,
+                    nullptr, cur_stream());
+}
+
+void peer_add_f32(const Tensor& part, const std::vector<int64_t>& ptrs) {
+  chk_c(part, F32, "part");
+  c10::cuda::CUDAGuard guard(part.device());
+  mb::peer_add_f32(part.data_ptr<float>(), to_peers(ptrs), (int)ptrs.size(), part.numel(), cur_stream());
+}
+void peer_gather_cols(const Tensor& src, const std::vector<int64_t>& ptrs, int64_t rank, int64_t world) {
+  chk_c(src, BF16, "src");
+  TORCH_CHECK(src.dim() == 2 && (int64_t)ptrs.size() == world, "peer_gather_cols: src must be [rows, cols]");
+  c10::cuda::CUDAGuard guard(src.device());
+  mb::peer_gather_cols(src.data_ptr(), to_peers(ptrs), (int)world, (int)rank, src.size(0), (int)src.size(1),
+                       cur_stream());
+}
+
 int64_t launch_count() { return mb::launch_count(); }
 
 }  // namespace
@@ -422,8 +577,19 @@ PYBIND11_MODULE(_C, m) {
   m.def("oil_codebook_stats", &oil_codebook_stats);
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("flash_attn_bwd", &flash_attn_bwd);
+  m.def("dequant_gemm", &dequant_gemm);
+  m.def("finalize_acc", &finalize_acc);
+  m.def("dequant_to_bf16", &dequant_to_bf16);
+  m.def("i2s_gemv", &i2s_gemv);
+  m.def("kv_append", &kv_append);
+  m.def("paged_attn_decode", &paged_attn_decode);
+  m.def("sample_tokens", &sample_tokens);
+  m.def("peer_add_f32", &peer_add_f32);
+  m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);
   m.def("zero_reduce_scatter", &zero_reduce_scatter);
   m.def("zero_adamw_ste_allgather", &zero_adamw_ste_allgather);
+  m.def("set_gemm_mode", [](int64_t mode) { mb::set_gemm_mode((int)mode); });
+  m.def("get_gemm_mode", []() { return (int64_t)mb::get_gemm_mode(); });
   m.def("launch_count", &launch_count);
 }

@@ -17,6 +17,14 @@ enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_F32_ATOMIC = 3 };
 void gemm_bf16(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
                long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream);
 
+// Paired-SM variant (cta_group::2, 256x256 tile per 2-CTA cluster); same contract.
+void gemm_bf16_2cta(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
+                    long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream);
+double gemm_2cta_waves(int M, int N, int sms);
+// 0 = choose per problem, 1 = always the single-CTA kernel, 2 = the paired kernel whenever it applies.
+void set_gemm_mode(int mode);
+int get_gemm_mode();
+
 // ---- normalisation (norm.cu)
 void rmsnorm_fwd(const void* x, const void* residual, const void* gamma, void* y, void* resid_out, float* rstd,
                  int rows, int dim, float eps, cudaStream_t stream);
@@ -120,11 +128,60 @@ struct ZeroFusedArgs {
 };
 // Flag barrier across ranks; with send_val != null also delivers *send_val into slot [rank] of every
 // rank's `slots` array. The wait gives up after limit_cycles and records it in `status`.
+// With epoch_ptr != null the epoch is read from (and advanced in) device memory instead of `epoch`.
 void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* send_val, int rank, int world, int epoch,
-                  long long limit_cycles, int* status, cudaStream_t stream);
+                  int* epoch_ptr, long long limit_cycles, int* status, cudaStream_t stream);
 void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,
                          cudaStream_t stream);
 void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream);
+// dst_r[i] += part[i] on every rank r (fp32 peer reductions).
+void peer_add_f32(const float* part, const PeerPtrs& dst, int n_peers, long long n, cudaStream_t stream);
+// Column all-gather by peer stores: dst_r[b, rank*cols + j] = src[b, j] on every rank r.
+void peer_gather_cols(const void* src, const PeerPtrs& dst, int n_peers, int rank, long long rows, int cols,
+                      cudaStream_t stream);
+
+// ---- inference: codebook-dequant GEMM (dequant_gemm.cu)
+enum : int { QFMT_OIL8 = 3, QFMT_OIL4 = 2, QFMT_I2S = 1 };  // numeric values of the container's Format enum
+struct DequantWeights {
+  const uint8_t* packed;     // OIL8: N*K bytes; OIL4: N*K/2 (even index in the low nibble); I2_S: N*K/4 (LSB first)
+  const void* codebooks;     // bf16 [n_cb, 256] (OIL8) or [n_cb, 16] (OIL4); unused for I2_S
+  const int* cb_map;         // per block: codebook row (null = block index)
+  const float* scales;       // I2_S: per-block scale
+  int fmt, N, K, block_size; // blocks run along K inside a row; K % block_size == 0
+};
+// y = x * dequant(W)^T. Exactly one output: out_bf16 (no split-K), or fp32 accumulation into
+// out_f32 / into every buffer of `peers` (fused all-reduce; buffers must hold zeros or a residual).
+// k_splits <= 0 picks enough splits to fill the GPU.
+void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, void* out_bf16, float* out_f32,
+                  const PeerPtrs* peers, int n_peers, long long ld_out, int k_splits, int* status, cudaStream_t stream);
+// out = bf16(acc (+ residual)); acc is reset to zero for its next accumulation.
+void finalize_acc(float* acc, const void* residual, void* out, long long n, cudaStream_t stream);
+// Whole-matrix dequantisation into a bf16 scratch buffer (prefill path).
+void dequant_to_bf16(const DequantWeights& w, void* out, cudaStream_t stream);
+
+// ---- inference: paged KV cache, decode attention, sampler (paged_attn.cu, sampler.cu)
+// Cache layout: k_cache / v_cache [num_pages, page_size, kv_heads, head_dim] bf16;
+// block_table [batch, max_pages] int32 (page index of each logical page of a sequence).
+void kv_append(const void* k, const void* v, void* k_cache, void* v_cache, const int* block_table,
+               const int* positions, const int* seq_ids, int tokens, int kv_heads, int head_dim, int page_size,
+               int max_pages, long long kv_tok_stride, cudaStream_t stream);
+// One query token per sequence: q [batch, heads, head_dim]; context_lens [batch]. Split-KV flash
+// decoding: partials in `scratch` (>= batch*heads*splits*(head_dim+2) floats), combined in-kernel.
+void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                       const int* context_lens, void* out, float* scratch, int* counters, int batch, int heads,
+                       int kv_heads, int head_dim, int page_size, int max_pages, int splits, float scale,
+                       cudaStream_t stream);
+// Greedy / temperature / top-k / top-p / repetition-penalty sampling of one token per row.
+struct SamplerArgs {
+  float temperature, top_p, repetition_penalty;
+  int top_k;
+  unsigned long long seed;
+};
+void sample_tokens(const void* logits, long long ld, int rows, int vocab, const int* history, int history_len,
+                   const unsigned char* allow_mask, SamplerArgs a, int* out_tokens, float* out_logprob, float* scratch,
+                   cudaStream_t stream);
+// y[n] = sum_k dequant(W)[n,k] * x[k] for one token (CUDA-core GEMV over packed I2_S trits).
+void i2s_gemv(const void* x, const DequantWeights& w, void* y, cudaStream_t stream);
 
 long long launch_count();
 

@@ -38,8 +38,13 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 // One thread per peer. flags[r] on every rank is an int array of `world` slots; slot s of rank r
 // holds the last epoch that rank s announced to rank r.
 __global__ void symm_barrier_kernel(PeerPtrs flags, PeerPtrs slots, const float* send_val, int rank, int world,
-                                    int epoch, long long limit_cycles, int* status) {
+                                    int epoch, int* epoch_ptr, long long limit_cycles, int* status) {
   const int p = threadIdx.x;
+  // With epoch_ptr the epoch lives on the device and advances by one per launch, so the same
+  // launch can be replayed from a CUDA graph.
+  if (epoch_ptr) epoch = *epoch_ptr + 1;
+  __syncwarp();
+  if (p == 0 && epoch_ptr) *epoch_ptr = epoch;
   if (p >= world) return;
   __threadfence_system();
   if (send_val) reinterpret_cast<float*>(slots.p[p])[rank] = *send_val;
@@ -171,9 +176,9 @@ __global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a) {
 }  // namespace
 
 void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* send_val, int rank, int world, int epoch,
-                  long long limit_cycles, int* status, cudaStream_t stream) {
+                  int* epoch_ptr, long long limit_cycles, int* status, cudaStream_t stream) {
   MB_REQUIRE(world >= 1 && world <= MAX_PEERS, "symm_barrier: world size out of range");
-  symm_barrier_kernel<<<1, 32, 0, stream>>>(flags, slots, send_val, rank, world, epoch, limit_cycles, status);
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(flags, slots, send_val, rank, world, epoch, epoch_ptr, limit_cycles, status);
   count_launch();
   check_launch();
 }
@@ -198,6 +203,54 @@ void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream) {
   const long long cap = (long long)sm_count() * 8;
   if (grid > cap) grid = cap;
   zero_adamw_ste_allgather_kernel<<<(int)grid, threads, wpb * 256 * sizeof(float), stream>>>(a);
+  count_launch();
+  check_launch();
+}
+
+namespace {
+
+__global__ void peer_add_kernel(const float* __restrict__ part, PeerPtrs dst, int n_peers, long long n4) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(part)[i];
+    for (int p = 0; p < n_peers; ++p) atomicAdd(reinterpret_cast<float4*>(dst.p[p]) + i, v);
+  }
+}
+
+// dst_r[b, rank*cols + j] = src[b, j] for every rank r (cols is a multiple of 8).
+__global__ void peer_gather_cols_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, int n_peers, int rank,
+                                        long long rows, int cols) {
+  const int per_row = cols >> 3;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per_row;
+    const int c = (int)(i % per_row) * 8;
+    const bf16x8 v = ldg8(src, r * cols + c);
+    const long long off = r * ((long long)cols * n_peers) + (long long)rank * cols + c;
+    for (int p = 0; p < n_peers; ++p) stg8(dst.p[(rank + p) % n_peers], off, v);
+  }
+}
+
+}  // namespace
+
+void peer_add_f32(const float* part, const PeerPtrs& dst, int n_peers, long long n, cudaStream_t stream) {
+  MB_REQUIRE(n % 4 == 0, "peer_add_f32: element count must be a multiple of 4");
+  if (n == 0) return;
+  long long g = (n / 4 + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  peer_add_kernel<<<(int)g, 256, 0, stream>>>(part, dst, n_peers, n / 4);
+  count_launch();
+  check_launch();
+}
+
+void peer_gather_cols(const void* src, const PeerPtrs& dst, int n_peers, int rank, long long rows, int cols,
+                      cudaStream_t stream) {
+  MB_REQUIRE(cols % 8 == 0, "peer_gather_cols: column count must be a multiple of 8");
+  if (rows == 0) return;
+  long long g = (rows * (cols / 8) + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  peer_gather_cols_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)src, dst, n_peers, rank, rows, cols);
   count_launch();
   check_launch();
 }

@@ -272,7 +272,12 @@ void launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, in
 // Relative cost of running `tiles` equal tiles of width bn on `sms` SMs.
 inline double wave_cost(long long tiles, int bn, int sms) { return (double)((tiles + sms - 1) / sms) * bn; }
 
+int g_gemm_mode = 0;
+
 }  // namespace
+
+void set_gemm_mode(int mode) { g_gemm_mode = mode; }
+int get_gemm_mode() { return g_gemm_mode; }
 
 void gemm_bf16(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
                long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream) {
@@ -290,6 +295,21 @@ void gemm_bf16(const void* A, long long lda, bool a_mn, const void* B, long long
   const bool use256 = N > 128 && wave_cost(t256, 256, sms) <= wave_cost(t128, 128, sms) / 0.72;
   const int BN = use256 ? 256 : 128;
   const long long tiles = use256 ? t256 : t128;
+  // Paired-SM kernel: one 256x256 tile per SM pair costs the time of one 128x256 tile per SM and
+  // streams a third fewer bytes per FLOP, which measured faster whenever its wave count is close.
+  if (g_gemm_mode != 1 && M >= 256 && N >= 256) {
+    const double c2 = gemm_2cta_waves(M, N, sms) * 256.0;
+    const double c1 = use256 ? wave_cost(t256, 256, sms) : wave_cost(t128, 128, sms) / 0.72;
+    // Measured on B200: with K-major operands the paired kernel wins whenever its wave count is
+    // close (1.19 -> 1.38 PFLOP/s at 16384x6144x2048); with an MN-major B and a K-major A it
+    // lost 5 % on every shape tried; with both MN-major it wins only from about four full waves.
+    const long long tiles2 = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    const bool layout_ok = !b_mn || (a_mn && tiles2 >= 4LL * (sms / 2));
+    if (g_gemm_mode == 2 || (layout_ok && c2 <= c1 * 1.15)) {
+      gemm_bf16_2cta(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, epi, alpha, status, stream);
+      return;
+    }
+  }
   const int kblocks = (K + BK - 1) / BK;
   int k_splits = 1;
   if (epi == EPI_F32_ATOMIC) {

@@ -1,0 +1,375 @@
+"""Inference engine: paged KV cache, prefill + decode, tensor parallelism, CUDA-graph decode.
+
+Role of the reference's ``Generator`` (src/generator.cpp:14-145), ``engine::InferenceEngine``
+(engines/inference/inference.cpp) and ``ContinuousBatching`` (src/inference_opt.cpp:281-373), for
+batches of sequences instead of one, with weights kept in their OIL storage format.
+
+Per layer: RMSNorm (+ residual add) -> fused QKV projection (codebook-dequant GEMM) -> RoPE in
+place -> K/V scattered into pages -> attention (tcgen05 flash attention over the prompt for
+prefill, split-KV paged attention for decode) -> output projection -> RMSNorm -> gate/up
+projection -> SwiGLU / ReLU^2 gate -> down projection.
+
+Tensor parallelism (``tp``): attention heads and FFN columns are sharded; the two row-parallel
+projections of a layer add their fp32 partial tiles straight into every rank's accumulation
+buffer from the GEMM epilogue (peer ``red.add`` over NVLink), a flag barrier follows, and a small
+kernel turns the accumulator into the bf16 activation and clears it. No library collective runs
+inside a decode step. The lm_head is vocabulary-parallel; logits are gathered with peer stores.
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from ..models.config import TransformerConfig
+from ..ops import functional as F
+from ..ops import native
+from .kv_paged import PagedKVCache
+from .quant_weights import QuantLinear
+from .sampler import SamplerConfig, sample
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    new_tokens: int = 0
+    ttft_s: float = 0.0            # prefill + first sample
+    decode_s: float = 0.0
+    tokens_per_s: float = 0.0      # generated tokens per second over the whole batch (decode phase)
+    kv_bytes: int = 0
+    kv_utilization: float = 0.0
+
+
+@dataclass
+class GenerationResult:
+    tokens: list = field(default_factory=list)   # per sequence: generated token ids
+    stats: GenerationStats = field(default_factory=GenerationStats)
+
+
+class TPContext:
+    """Tensor-parallel state of one rank: symmetric fp32 accumulators (double-buffered), a
+    symmetric logits buffer and a flag barrier whose epoch lives on the device."""
+
+    def __init__(self, group, device, max_tokens: int, hidden: int, vocab_shard: int, max_batch: int):
+        import torch.distributed as dist
+
+        from ..parallel import symm
+
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.acc = [symm.make_buffer(max_tokens * hidden, torch.float32, device, group).zero_() for _ in range(2)]
+        self.logits = symm.make_buffer(max_batch * vocab_shard * self.world, torch.bfloat16, device, group)
+        self.barrier = symm.FlagBarrier(device, group, device_epoch=True)
+        self.which = 0
+
+
+class _Layer:
+    __slots__ = ("attn_norm", "ffn_norm", "qkv", "o", "up", "down")
+
+
+class InferenceEngine:
+    def __init__(self, cfg: TransformerConfig, device="cuda", max_batch: int = 64, max_seq_len: int | None = None,
+                 page_size: int = 16, tp: TPContext | None = None, kv_pages: int | None = None):
+        self.cfg, self.device, self.tp = cfg, torch.device(device), tp
+        self.max_batch = max_batch
+        self.max_seq_len = max_seq_len or cfg.max_seq_len
+        self.page_size = page_size
+        self.world = tp.world if tp is not None else 1
+        self.rank = tp.rank if tp is not None else 0
+        if cfg.num_heads % self.world or cfg.kv_heads % self.world:
+            raise ValueError(f"heads ({cfg.num_heads}/{cfg.kv_heads}) must divide by the tensor-parallel size {self.world}")
+        self.h_local = cfg.num_heads // self.world
+        self.hkv_local = cfg.kv_heads // self.world
+        pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
+        self.cache = PagedKVCache(cfg.num_layers, self.hkv_local, cfg.head_dim, kv_pages or max_batch * pages_per_seq,
+                                  page_size, max_batch, pages_per_seq, self.device)
+        self.layers: list[_Layer] = []
+        self.embed = None        # bf16 [V, d]
+        self.final_norm = None
+        self.head: QuantLinear | None = None
+        self._graph = None
+        self._static = {}
+        sm = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1
+        self._sms = sm
+        self._scratch = None
+        self._counters = None
+
+    # ------------------------------------------------------------------ weights
+    @classmethod
+    def from_model(cls, model, **kw) -> "InferenceEngine":
+        """Pack a (trained or random) ``DenseModel`` into inference weights. Under tensor
+        parallelism every rank packs its own shard of each matrix."""
+        cfg = model.cfg
+        eng = cls(cfg, **kw)
+        dev = eng.device
+        W, r = eng.world, eng.rank
+        D, H, Hkv = cfg.head_dim, cfg.num_heads, cfg.kv_heads
+        eng.embed = model.tok_embeddings.weight.detach().to(dev, torch.bfloat16).contiguous()
+        eng.final_norm = model.norm.weight.detach().to(dev, torch.bfloat16).contiguous()
+        for blk in model.layers:
+            L = _Layer()
+            L.attn_norm = blk.attention_norm.weight.detach().to(dev, torch.bfloat16).contiguous()
+            L.ffn_norm = blk.ffn_norm.weight.detach().to(dev, torch.bfloat16).contiguous()
+            att, ffn = blk.attention, blk.ffn
+            if W == 1:
+                L.qkv = QuantLinear.from_oil_linear(att.qkv_proj)
+                L.o = QuantLinear.from_oil_linear(att.o_proj)
+                L.up = QuantLinear.from_oil_linear(ffn.up_proj)
+                L.down = QuantLinear.from_oil_linear(ffn.down_proj)
+            else:
+                L.qkv = _shard_rows_multi(att.qkv_proj, [(0, H * D), (H * D, Hkv * D), ((H + Hkv) * D, Hkv * D)], r, W)
+                L.o = _shard_cols(att.o_proj, r, W)
+                f = ffn.up_proj.out_features // (2 if ffn.gated else 1)
+                parts = [(0, f), (f, f)] if ffn.gated else [(0, f)]
+                L.up = _shard_rows_multi(ffn.up_proj, parts, r, W)
+                L.down = _shard_cols(ffn.down_proj, r, W)
+            eng.layers.append(L)
+        head_mod = model.lm_head
+        if head_mod is None:
+            w = model.tok_embeddings.weight.detach().float()
+            V = w.shape[0]
+            rows = slice(r * V // W, (r + 1) * V // W)
+            eng.head = QuantLinear.from_float(w[rows].to(dev), "bf16")
+        elif W == 1:
+            eng.head = QuantLinear.from_oil_linear(head_mod)
+        else:
+            eng.head = _shard_rows_multi(head_mod, [(0, head_mod.out_features)], r, W)
+        return eng
+
+    def weight_bytes(self) -> int:
+        n = self.head.nbytes() + self.embed.numel() * 2
+        for L in self.layers:
+            n += L.qkv.nbytes() + L.o.nbytes() + L.up.nbytes() + L.down.nbytes()
+        return n
+
+    # ------------------------------------------------------------------ building blocks
+    def _row_parallel(self, lin: QuantLinear, x: torch.Tensor) -> torch.Tensor:
+        """x [T, K_local] @ W_shard^T, summed over ranks -> bf16 [T, d]."""
+        if self.tp is None:
+            return lin.matmul(x)
+        tp = self.tp
+        T = x.shape[0]
+        buf = tp.acc[tp.which]
+        tp.which ^= 1
+        if lin.dense is not None or T > 256:
+            # prefill-sized: local dense GEMM into fp32, then peer adds of the whole tile
+            part = F.gemm(x, lin.dequantize(), epi=F.EPI_F32)
+            _peer_add(part, buf.ptrs)
+        else:
+            lin.matmul(x, peer_ptrs=buf.ptrs)
+        tp.barrier.sync()
+        out = torch.empty(T, lin.N, device=x.device, dtype=torch.bfloat16)
+        native.require().finalize_acc(buf.tensor[: T * lin.N], None, out)
+        return out
+
+    def _forward(self, ids, pos, seq_ids, ctx_lens, prefill_shape=None):
+        """ids/pos/seq_ids: int32 [T]; ctx_lens int32 [B] (decode). Returns final hidden [T, d]."""
+        cfg, C = self.cfg, native.require()
+        D, H, Hkv = cfg.head_dim, self.h_local, self.hkv_local
+        scale = 1.0 / math.sqrt(D)
+        table = self.cache.block_table
+        x = torch.empty(ids.numel(), cfg.hidden_size, device=self.device, dtype=torch.bfloat16)
+        C.embedding_fwd(ids, self.embed, x)
+        branch, stream = x, None
+        for li, L in enumerate(self.layers):
+            n, stream = F.rmsnorm(branch, L.attn_norm, cfg.norm_eps, stream)
+            qkv = L.qkv.matmul(n)
+            T = qkv.shape[0]
+            q = qkv[:, : H * D].unflatten(-1, (H, D))
+            k = qkv[:, H * D:(H + Hkv) * D].unflatten(-1, (Hkv, D))
+            v = qkv[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+            if cfg.rope_theta > 0:
+                C.rope(q, pos, cfg.rope_theta, False)
+                C.rope(k, pos, cfg.rope_theta, False)
+            C.kv_append(k, v, self.cache.k[li], self.cache.v[li], table, pos, seq_ids)
+            if prefill_shape is not None:
+                B, S = prefill_shape
+                o = torch.empty(B, S, H, D, device=self.device, dtype=torch.bfloat16)
+                lse = torch.empty(B, H, S, device=self.device, dtype=torch.float32)
+                q4 = qkv.view(B, S, -1)[..., : H * D].unflatten(-1, (H, D))
+                k4 = qkv.view(B, S, -1)[..., H * D:(H + Hkv) * D].unflatten(-1, (Hkv, D))
+                v4 = qkv.view(B, S, -1)[..., (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+                C.flash_attn_fwd(q4, k4, v4, o, lse, True, scale, native.status_word(self.device))
+                o = o.view(T, H * D)
+            else:
+                o = torch.empty(T, H, D, device=self.device, dtype=torch.bfloat16)
+                C.paged_attn_decode(q.contiguous(), self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
+                                    self._scratch, self._counters, self._splits, scale)
+                o = o.view(T, H * D)
+            a = self._row_parallel(L.o, o)
+            n, stream = F.rmsnorm(a, L.ffn_norm, cfg.norm_eps, stream)
+            u = L.up.matmul(n)
+            if cfg.gated_ffn:
+                if cfg.activation == "relu2":
+                    f = u.shape[-1] // 2
+                    h = F.relu2(u[:, :f].contiguous()) * u[:, f:]
+                else:
+                    h = F.swiglu(u)
+            else:
+                h = F.relu2(u) if cfg.activation == "relu2" else F.activation(u, cfg.activation)
+            branch = self._row_parallel(L.down, h)
+        hfin, _ = F.rmsnorm(branch, self.final_norm, cfg.norm_eps, stream)
+        return hfin
+
+    def _logits(self, h: torch.Tensor) -> torch.Tensor:
+        lg = self.head.matmul(h)
+        if self.tp is None:
+            return lg
+        return _gather_columns(lg, self.tp)
+
+    def _prepare_decode_scratch(self, batch: int, max_ctx: int):
+        splits = max(1, min(32, (2 * self._sms) // max(1, batch * self.hkv_local), (max_ctx + 255) // 256))
+        self._splits = splits
+        need = batch * self.h_local * splits * (self.cfg.head_dim + 2)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, device=self.device, dtype=torch.float32)
+            self._counters = torch.zeros(batch * self.hkv_local + 64, device=self.device, dtype=torch.int32)
+
+    # ------------------------------------------------------------------ generation
+    @torch.no_grad()
+    def generate(self, prompts, max_new_tokens: int = 32, sampler: SamplerConfig | None = None, stream_callback=None,
+                 eos_id: int | None = None, use_graph: bool = True) -> GenerationResult:
+        """prompts: list of equal-length token lists (or an int tensor [B, S])."""
+        sampler = sampler or SamplerConfig(temperature=0.0)
+        ids = torch.as_tensor(prompts, dtype=torch.int32)
+        B, S = ids.shape
+        if B > self.max_batch or S + max_new_tokens > self.max_seq_len:
+            raise ValueError("batch or sequence length exceeds the engine's limits")
+        cache = self.cache
+        seqs = [cache.new_sequence() for _ in range(B)]
+        for s in seqs:
+            cache.reserve(s, S + max_new_tokens)
+        cache.sync_tables()
+        dev = self.device
+        seq_t = torch.tensor(seqs, dtype=torch.int32, device=dev)
+        stats = GenerationStats(prompt_tokens=B * S)
+        self._prepare_decode_scratch(B, S + max_new_tokens)
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        # ---- prefill
+        ids_d = ids.to(dev).reshape(-1)
+        pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
+        h = self._forward(ids_d, pos, seq_t.repeat_interleave(S), None, prefill_shape=(B, S))
+        last = h.view(B, S, -1)[:, -1, :].contiguous()
+        tok = sample(self._logits(last), sampler, step=0)
+        for s in seqs:
+            cache.advance(s, S)
+        torch.cuda.synchronize(dev)
+        stats.ttft_s = time.perf_counter() - t0
+        out = [tok.clone()]
+        if stream_callback is not None:
+            stream_callback(0, tok)
+        # ---- decode
+        cur = tok.clone()
+        posd = torch.full((B,), S, device=dev, dtype=torch.int32)
+        ctx = torch.full((B,), S + 1, device=dev, dtype=torch.int32)
+        graph = None
+        graph_ok = use_graph and sampler.greedy and stream_callback is None and eos_id is None
+
+        def step_fn():
+            hh = self._forward(cur, posd, seq_t, ctx, None)
+            nt = sample(self._logits(hh), sampler, step=1)
+            cur.copy_(nt)
+            posd.add_(1)
+            ctx.add_(1)
+
+        t1 = time.perf_counter()
+        steps = max_new_tokens - 1
+        done = 0
+        if graph_ok and steps > 2:
+            step_fn()  # warm-up outside capture (allocations, lazy initialisation)
+            out.append(cur.clone())
+            done = 1
+            torch.cuda.synchronize(dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_fn()
+            out.append(cur.clone())
+            done = 2
+            for _ in range(done, steps):
+                graph.replay()
+                out.append(cur.clone())
+        else:
+            for i in range(steps):
+                hh = self._forward(cur, posd, seq_t, ctx, None)
+                nt = sample(self._logits(hh), sampler, step=i + 1)
+                cur.copy_(nt)
+                posd.add_(1)
+                ctx.add_(1)
+                out.append(nt.clone())
+                if stream_callback is not None:
+                    stream_callback(i + 1, nt)
+                if eos_id is not None and bool((nt == eos_id).all()):
+                    break
+        torch.cuda.synchronize(dev)
+        native.check_status(dev)
+        stats.decode_s = time.perf_counter() - t1
+        toks = torch.stack(out, dim=1).cpu()
+        stats.new_tokens = toks.numel()
+        stats.tokens_per_s = (toks.numel() - B) / max(stats.decode_s, 1e-9)
+        stats.kv_bytes = cache.size_bytes()
+        stats.kv_utilization = cache.utilization()
+        for s in seqs:
+            cache.free_sequence(s)
+        return GenerationResult(tokens=[t.tolist() for t in toks], stats=stats)
+
+
+# ---------------------------------------------------------------------------------------- TP helpers
+def _shard_rows_multi(mod, parts, rank: int, world: int) -> QuantLinear:
+    """Column-parallel shard of a fused projection: from each (start, size) part of the output rows
+    take this rank's 1/world slice, concatenate, and pack with the module's codebooks."""
+    w = mod.weight.detach().float()
+    K = w.shape[1]
+    pieces, maps = [], []
+    for start, size in parts:
+        per = size // world
+        lo = start + rank * per
+        pieces.append(w[lo:lo + per])
+        if mod.codebooks is not None:
+            b0, b1 = lo * K // mod.block_size, (lo + per) * K // mod.block_size
+            maps.append(torch.arange(b0, b1, device=w.device, dtype=torch.int32) if mod.cb_map is None
+                        else mod.cb_map[b0:b1])
+    ws = torch.cat(pieces, dim=0).contiguous()
+    if mod.fmt not in ("oil8", "oil4", "i2s"):
+        return QuantLinear.from_float(ws, "bf16")
+    if mod.codebooks is None:
+        return QuantLinear.from_float(ws, mod.fmt, mod.block_size)
+    return QuantLinear.from_float(ws, mod.fmt, mod.block_size, 1, mod.codebooks.float(), torch.cat(maps).contiguous())
+
+
+def _shard_cols(mod, rank: int, world: int) -> QuantLinear:
+    """Row-parallel shard (input features split). Quantisation blocks run along the input
+    dimension, so the shard is re-blocked: block b of the shard keeps the codebook of the original
+    block it came from as long as shard boundaries fall on block boundaries; otherwise the shard
+    gets fresh quantile codebooks."""
+    w = mod.weight.detach().float()
+    N, K = w.shape
+    per = K // world
+    ws = w[:, rank * per:(rank + 1) * per].contiguous()
+    if mod.fmt not in ("oil8", "oil4", "i2s"):
+        return QuantLinear.from_float(ws, "bf16")
+    bs = mod.block_size
+    if mod.codebooks is None or per % bs != 0:
+        return QuantLinear.from_float(ws, mod.fmt, bs if per % bs == 0 else 64, mod.codebook_group)
+    blocks_per_row, shard_blocks = K // bs, per // bs
+    rows = torch.arange(N, device=w.device)[:, None]
+    cols = torch.arange(shard_blocks, device=w.device)[None, :] + rank * shard_blocks
+    orig = (rows * blocks_per_row + cols).reshape(-1)
+    cmap = orig.to(torch.int32) if mod.cb_map is None else mod.cb_map[orig]
+    return QuantLinear.from_float(ws, mod.fmt, bs, 1, mod.codebooks.float(), cmap.contiguous())
+
+
+def _peer_add(part: torch.Tensor, ptrs) -> None:
+    """Add an fp32 tile into every rank's accumulator (prefill-sized row-parallel outputs)."""
+    native.require().peer_add_f32(part.contiguous(), list(ptrs))
+
+
+def _gather_columns(lg: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    """Vocabulary-parallel logits [B, V/W] of every rank -> [B, V] on every rank (peer stores)."""
+    B, Vs = lg.shape
+    native.require().peer_gather_cols(lg.contiguous(), list(tp.logits.ptrs), tp.rank, tp.world)
+    tp.barrier.sync()
+    return tp.logits.tensor[: B * Vs * tp.world].view(B, Vs * tp.world)

@@ -62,8 +62,11 @@ class FlagBarrier:
     stream. ``sync(send)`` optionally delivers one float from every rank to every rank
     (``self.slots`` then holds the world's values in rank order)."""
 
-    def __init__(self, device, group=None, limit_cycles: int = DEFAULT_BARRIER_LIMIT_CYCLES):
+    def __init__(self, device, group=None, limit_cycles: int = DEFAULT_BARRIER_LIMIT_CYCLES,
+                 device_epoch: bool = False):
         self.device = torch.device(device)
+        # device-resident epoch: the barrier launch becomes replayable from a CUDA graph
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device) if device_epoch else None
         self.limit = limit_cycles
         self.epoch = 0
         self._flags = make_buffer(64, torch.int32, self.device, group).zero_()
@@ -77,4 +80,4 @@ class FlagBarrier:
     def sync(self, send: torch.Tensor | None = None) -> None:
         self.epoch += 1
         native.require().symm_barrier(self._flags.ptrs, self._slots.ptrs, send, self.rank, self.epoch, self.limit,
-                                      native.status_word(self.device))
+                                      native.status_word(self.device), self.epoch_dev)

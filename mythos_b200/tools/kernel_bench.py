@@ -142,7 +142,11 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 single-CTA kernel, 2 paired-SM kernel")
     args = ap.parse_args()
+    from mythos_b200.ops import native
+
+    native.require().set_gemm_mode(args.gemm_mode)
     tf_peak, bw_peak, src = _peaks()
     t = Timer(args.iters, args.warmup, not args.no_flush)
     hkv = args.kv_heads or args.heads

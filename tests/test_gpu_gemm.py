@@ -82,3 +82,27 @@ def test_linear_autograd_matches_reference():
     _check(y, yr.detach(), 256)
     _check(x.grad, xr.grad, 384)
     _check(gt, wr.grad, 4 * 96)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (1000, 1000, 200), (4096, 5504, 2048)])
+@pytest.mark.parametrize("layout", ["kk", "kmn", "mnmn"])
+def test_gemm_paired_sm_kernel(M, N, K, layout):
+    """The cta_group::2 kernel forced on (mode 2), including ragged edges of the 256x256 tile."""
+    from mythos_b200.ops import functional as F, native
+
+    C = native.require()
+    torch.manual_seed(M * 3 + N + K)
+    a_mn, b_mn = {"kk": (False, False), "kmn": (False, True), "mnmn": (True, True)}[layout]
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
+    C.set_gemm_mode(2)
+    try:
+        out = F.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        acc = torch.ones(M, N, device="cuda")
+        F.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, epi=F.EPI_F32_ACC)
+        torch.cuda.synchronize()
+    finally:
+        C.set_gemm_mode(0)
+    ref = _ref(a, b, a_mn, b_mn)
+    _check(out, ref, K)
+    _check(acc, ref + 1.0, K)

@@ -92,7 +92,7 @@ def test_flag_barrier_single_rank_and_timeout():
     fb = torch.zeros(64, dtype=torch.int32, device="cuda")
     sl = torch.zeros(64, device="cuda")
     C.symm_barrier([fa.data_ptr(), fb.data_ptr()], [sl.data_ptr(), sl.data_ptr()], None, 0, 1, 2_000_000,
-                   native.status_word("cuda"))
+                   native.status_word("cuda"), None)
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="status 1"):
         native.check_status("cuda")
