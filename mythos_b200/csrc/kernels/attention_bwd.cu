@@ -39,7 +39,8 @@ struct BwCfg {
   static constexpr int OFF_PT = OFF_ST + 2 * STAGE_BYTES;
   static constexpr int OFF_DST = OFF_PT + PT_BYTES;
   static constexpr int OFF_STATS = OFF_DST + PT_BYTES;   // [4 warps][2 parity][lse 64 | delta 64] floats
-  static constexpr int OFF_BAR = OFF_STATS + 4 * 2 * 128 * 4;
+  static constexpr int OFF_DQ = OFF_STATS + 4 * 2 * 128 * 4;  // [4 warps][64 q][32 d] fp32 staging for the dQ reduce
+  static constexpr int OFF_BAR = OFF_DQ + BW_Q * BW_D * 4;
   static constexpr int NUM_BARS = 10;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 512;
@@ -49,7 +50,8 @@ struct BwCfg {
 __global__ void __launch_bounds__(BW_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-              const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dq_accum,
+              const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse,
+              const float* __restrict__ delta,
               __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, long long dkv_tok_stride, int seq,
               int heads, int kv_heads, int causal, float scale, float scale_log2, int* status) {
   using Cfg = BwCfg;
@@ -199,8 +201,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
 
+    float* dq_stage = reinterpret_cast<float*>(smem + Cfg::OFF_DQ) + quarter * (BW_Q * 32);
     auto drain_dq = [&](int n) {
-      // dQ^T of step n is in TMEM: lane = d, column = q. Add it to the fp32 dQ buffer.
+      // dQ^T of step n is in TMEM: lane = d, column = q. Each warp transposes its 32 d-columns into
+      // a [64 q][32 d] fp32 tile in shared memory and adds it to the fp32 dQ buffer with one bulk
+      // tensor reduction (no per-element atomics).
       const int h = hkv * group + n / per_head;
       const int q0 = (i_start + n % per_head) * BW_Q;
       uint32_t a[2][32];
@@ -209,11 +214,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_free);
-      float* base = dq_accum + (((long long)b * seq + q0) * heads + h) * BW_D + r;
-      const int nq = min(BW_Q, seq - q0);
+      if (lane == 0) tma_store_wait_read0();  // the previous reduction has finished reading the staging tile
+      __syncwarp();
 #pragma unroll
-      for (int q = 0; q < BW_Q; ++q)
-        if (q < nq) atomicAdd(base + (long long)q * heads * BW_D, __uint_as_float(a[q >> 5][q & 31]));
+      for (int q = 0; q < BW_Q; ++q) dq_stage[q * 32 + lane] = __uint_as_float(a[q >> 5][q & 31]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_reduce_add_4d(&tm_dq, dq_stage, quarter * 32, h, q0, b);
+        tma_store_commit();
+      }
     };
 
     for (int n = 0; n < N && ok; ++n) {
@@ -252,7 +262,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const bool diag = causal && (q0 < kv0 + BW_KV);
 #pragma unroll
       for (int i = 0; i < BW_Q; ++i) {
-        float p = exp2f(s[i] * scale_log2 - st_lse[i]);
+        const float e = fmaf(s[i], scale_log2, -st_lse[i]);
+        float p = ((i & 3) == 3) ? poly_exp2(e) : fast_exp2(e);
         if (diag && (kv_row > q0 + i)) p = 0.f;
         s[i] = p;
         d[i] = p * (d[i] - st_dl[i]) * scale;
@@ -290,6 +301,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) {
         tc_fence_after();
         drain_dq(N - 1);
+        if (lane == 0) tma_store_wait0();  // all dQ reductions of this warp have landed
         // dV and dK rows of this thread
         const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
 #pragma unroll 1
@@ -403,13 +415,21 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
   const CUtensorMap tdo = make_bshd_map(dout, batch, seq, heads, head_dim, (long long)heads * head_dim, BW_Q);
   const CUtensorMap tk = make_bshd_map(k, batch, seq, kv_heads, head_dim, kv_tok_stride, BW_KV);
   const CUtensorMap tv = make_bshd_map(v, batch, seq, kv_heads, head_dim, kv_tok_stride, BW_KV);
+  CUtensorMap tdq;
+  {
+    uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)heads, (uint64_t)seq, (uint64_t)batch};
+    uint64_t strides[3] = {(uint64_t)head_dim * 4, (uint64_t)heads * head_dim * 4,
+                           (uint64_t)seq * heads * head_dim * 4};
+    uint32_t box[4] = {32, 1, BW_Q, 1};
+    tdq = make_tensor_map(dq_accum, TmaDType::F32, 4, dims, strides, box, false);
+  }
   static bool configured = false;
   if (!configured) {
     MB_CUDA_CHECK(cudaFuncSetAttribute(fa_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwCfg::SMEM_BYTES));
     configured = true;
   }
   const dim3 grid((seq + BW_KV - 1) / BW_KV, kv_heads, batch);
-  fa_bwd_kernel<<<grid, BW_THREADS, BwCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, lse, delta, dq_accum,
+  fa_bwd_kernel<<<grid, BW_THREADS, BwCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, lse, delta,
                                                                  (__nv_bfloat16*)dk, (__nv_bfloat16*)dv,
                                                                  dkv_tok_stride, seq, heads, kv_heads, causal ? 1 : 0, scale,
                                                                  scale * 1.4426950408889634f, status);

@@ -207,9 +207,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int i = 0; i < FA_BN; ++i)
           if (kv0 + i > limit) s[i] = -INFINITY;
       }
-      float mx = s[0];
+      float mx4[4] = {s[0], s[1], s[2], s[3]};  // four independent chains instead of one of length 64
 #pragma unroll
-      for (int i = 1; i < FA_BN; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 4; i < FA_BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = mx * scale_log2;
       float alpha = 1.f;
       bool need = false;
@@ -217,16 +218,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         m_ref = (m_new == -INFINITY) ? 0.f : m_new;
       } else if (m_new - m_ref > 8.f) {
         need = true;
-        alpha = exp2f(m_ref - m_new);
+        alpha = fast_exp2(m_ref - m_new);
         m_ref = m_new;
       }
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < FA_BN; ++i) {
-        s[i] = exp2f(s[i] * scale_log2 - m_ref);
-        rs += s[i];
+        // three of four exponentials on the special-function unit, one on the FMA pipe
+        const float e = fmaf(s[i], scale_log2, -m_ref);
+        s[i] = ((i & 3) == 3) ? poly_exp2(e) : fast_exp2(e);
+        rs4[i & 3] += s[i];
       }
-      l = l * alpha + rs;
+      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
       if (j > 0) {
         ok = mbar_wait(&o_done[t], (j - 1) & 1, abort_flag, status, 17);
         ok = __all_sync(0xffffffffu, ok);

@@ -211,6 +211,33 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t r, uint32_t c) {
   return r * 128u + ((c ^ (r & 7u)) << 4);
 }
 
+// 2^x on the special-function unit (one MUFU op, flush-to-zero).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x on the FMA pipe: round-to-nearest split x = i + f, f in [-0.5, 0.5], cubic for 2^f, exponent
+// patched in with integer adds. Relative error < 7e-4 (enough for probabilities stored as bf16);
+// used for part of each softmax row so that the special-function unit is not the bottleneck.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.f);
+  const float magic = 12582912.f;  // 1.5 * 2^23
+  const float xr = x + magic;
+  const float f = x - (xr - magic);
+  float p = fmaf(f, 0.0555041f, 0.2402265f);
+  p = fmaf(p, f, 0.6931472f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
+// cp.reduce.async.bulk.tensor: add a shared-memory tile into global memory (type from the tensor map).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* src, int x, int y, int z, int w) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(m), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

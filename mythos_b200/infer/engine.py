@@ -286,9 +286,7 @@ class InferenceEngine:
             torch.cuda.synchronize(dev)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                step_fn()
-            out.append(cur.clone())
-            done = 2
+                step_fn()  # recorded only: nothing runs and no state advances during capture
             for _ in range(done, steps):
                 graph.replay()
                 out.append(cur.clone())
