@@ -156,7 +156,16 @@ __global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) s += fabsf(p[k]);
       s = warp_sum(s);
-      const float scale = s * (1.f / 256.f);
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(p[k]));
+      amax = warp_max(amax);
+      int exact = 1;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (p[k] != 0.f && fabsf(p[k]) != amax) exact = 0;
+      exact = __all_sync(0xffffffffu, exact);
+      const float scale = exact ? amax : s * (1.f / 256.f);  // already-ternary blocks keep their scale
       const float inv = scale > 0.f ? 1.f / scale : 0.f;
 #pragma unroll
       for (int k = 0; k < 8; ++k) q[k] = fminf(1.f, fmaxf(-1.f, rintf(p[k] * inv))) * scale;

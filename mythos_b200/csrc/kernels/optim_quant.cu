@@ -131,10 +131,22 @@ __global__ void i2s_fake_quant_kernel(const float* __restrict__ w, int bs, long 
   for (long long b = (long long)blockIdx.x * wpb + warp; b < nblocks; b += (long long)gridDim.x * wpb) {
     const long long start = b * bs;
     const long long end = (start + bs < n) ? start + bs : n;
-    float s = 0.f;
-    for (long long i = start + lane; i < end; i += 32) s += fabsf(w[i]);
+    float s = 0.f, amax = 0.f;
+    for (long long i = start + lane; i < end; i += 32) {
+      const float a = fabsf(w[i]);
+      s += a;
+      amax = fmaxf(amax, a);
+    }
     s = warp_sum(s);
-    const float scale = s / (float)(end - start);
+    amax = warp_max(amax);
+    // A block that already is {-a, 0, +a} keeps a as its scale: quantising is idempotent.
+    int exact = 1;
+    for (long long i = start + lane; i < end; i += 32) {
+      const float a = fabsf(w[i]);
+      if (a != 0.f && a != amax) exact = 0;
+    }
+    exact = __all_sync(0xffffffffu, exact);
+    const float scale = exact ? amax : s / (float)(end - start);
     const float inv = scale > 0.f ? 1.f / scale : 0.f;
     if (lane == 0 && scales) scales[b] = scale;
     for (long long i = start + lane; i < end; i += 32) {

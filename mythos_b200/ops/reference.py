@@ -160,7 +160,11 @@ def i2s_quant(w, bs: int):
     cnt = torch.full((nb,), bs, dtype=torch.float32, device=w.device)
     if pad:
         cnt[-1] = bs - pad
-    scale = wf.abs().sum(-1) / cnt
+    a = wf.abs()
+    amax = a.amax(-1)
+    # a block that already is {-s, 0, +s} keeps s, so quantising twice equals quantising once
+    exact = ((a == 0) | (a == amax[:, None])).all(-1)
+    scale = torch.where(exact, amax, a.sum(-1) / cnt)
     inv = torch.where(scale > 0, 1.0 / scale, torch.zeros_like(scale))
     t = torch.round(wf * inv[:, None]).clamp(-1, 1)
     deq = t * scale[:, None]
