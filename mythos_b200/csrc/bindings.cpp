@@ -544,6 +544,40 @@ void peer_gather_cols(const Tensor& src, const std::vector<int64_t>& ptrs, int64
                        cur_stream());
 }
 
+void moe_topk(const Tensor& probs, int64_t k, Tensor& topk_idx, Tensor& slot, Tensor& counts) {
+  chk_c(probs, F32, "probs");
+  chk_c(topk_idx, I32, "topk_idx");
+  chk_c(slot, I32, "slot");
+  chk_c(counts, I32, "counts");
+  c10::cuda::CUDAGuard guard(probs.device());
+  mb::moe_topk(probs.data_ptr<float>(), (int)probs.size(0), (int)probs.size(1), (int)k, topk_idx.data_ptr<int>(),
+               slot.data_ptr<int>(), counts.data_ptr<int>(), cur_stream());
+}
+void moe_dispatch(const Tensor& x, const Tensor& topk_idx, const Tensor& slot, const Tensor& send_off,
+                  const OptTensor& row_scale, const std::vector<int64_t>& recv_ptrs, int64_t experts_per_rank,
+                  int64_t rank, int64_t cap) {
+  chk_c(x, BF16, "x");
+  chk_c(topk_idx, I32, "topk_idx");
+  chk_c(slot, I32, "slot");
+  chk_c(send_off, I32, "send_off");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::moe_dispatch(x.data_ptr(), topk_idx.data_ptr<int>(), slot.data_ptr<int>(), send_off.data_ptr<int>(),
+                   row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr, to_peers(recv_ptrs), (int)x.size(0),
+                   (int)topk_idx.size(1), (int)x.size(1), (int)experts_per_rank, (int)rank, cap, cur_stream());
+}
+void moe_combine(const std::vector<int64_t>& ybuf_ptrs, const Tensor& topk_idx, const Tensor& slot,
+                 const Tensor& send_off, const OptTensor& w, const OptTensor& dout, OptTensor out, OptTensor dw,
+                 int64_t dim, int64_t experts_per_rank, int64_t rank, int64_t cap) {
+  chk_c(topk_idx, I32, "topk_idx");
+  chk_c(slot, I32, "slot");
+  chk_c(send_off, I32, "send_off");
+  c10::cuda::CUDAGuard guard(topk_idx.device());
+  mb::moe_combine(to_peers(ybuf_ptrs), topk_idx.data_ptr<int>(), slot.data_ptr<int>(), send_off.data_ptr<int>(),
+                  w.has_value() ? w->data_ptr<float>() : nullptr, cptr(dout), mptr(out),
+                  dw.has_value() ? dw->data_ptr<float>() : nullptr, (int)topk_idx.size(0), (int)topk_idx.size(1),
+                  (int)dim, (int)experts_per_rank, (int)rank, cap, cur_stream());
+}
+
 int64_t launch_count() { return mb::launch_count(); }
 
 }  // namespace
@@ -584,6 +618,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("kv_append", &kv_append);
   m.def("paged_attn_decode", &paged_attn_decode);
   m.def("sample_tokens", &sample_tokens);
+  m.def("moe_topk", &moe_topk);
+  m.def("moe_dispatch", &moe_dispatch);
+  m.def("moe_combine", &moe_combine);
   m.def("peer_add_f32", &peer_add_f32);
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);

@@ -183,6 +183,17 @@ void sample_tokens(const void* logits, long long ld, int rows, int vocab, const 
 // y[n] = sum_k dequant(W)[n,k] * x[k] for one token (CUDA-core GEMV over packed I2_S trits).
 void i2s_gemv(const void* x, const DequantWeights& w, void* y, cudaStream_t stream);
 
+// ---- mixture of experts: routing, dispatch / combine exchange (moe.cu)
+void moe_topk(const float* probs, int T, int E, int k, int* topk_idx, int* slot, int* counts, cudaStream_t stream);
+// Row (t, j) goes to recv[owner(e)] at row rank*cap + send_off[e] + slot[t, j] (optionally scaled).
+void moe_dispatch(const void* x, const int* topk_idx, const int* slot, const int* send_off, const float* row_scale,
+                  const PeerPtrs& recv, int T, int k, int dim, int experts_per_rank, int rank, long long cap,
+                  cudaStream_t stream);
+// out[t] = sum_j w[t,j] * ybuf[owner][row(t,j)] (w null = 1); with dw also dw[t,j] = <dout[t], y row>.
+void moe_combine(const PeerPtrs& ybuf, const int* topk_idx, const int* slot, const int* send_off, const float* w,
+                 const void* dout, void* out, float* dw, int T, int k, int dim, int experts_per_rank, int rank,
+                 long long cap, cudaStream_t stream);
+
 long long launch_count();
 
 }  // namespace mb

@@ -93,6 +93,14 @@ class OILLinear(nn.Module):
             return c
         if torch.is_grad_enabled() and self.weight.requires_grad:
             return _STEQuantFn.apply(self.weight, self)
+        if not self.weight.requires_grad:
+            # frozen base (LoRA fine-tuning, evaluation): quantise once and keep the image
+            key = (self.weight.data_ptr(), self.weight._version, self.weight.device)
+            cached = getattr(self, "_frozen_image", None)
+            if cached is None or cached[0] != key:
+                cached = (key, self.quantize_now(self.weight.detach()))
+                self._frozen_image = cached
+            return cached[1]
         return self.quantize_now(self.weight.detach())
 
     def forward(self, x):

@@ -1,0 +1,221 @@
+"""CPU tests of the model layer: config blob, reference operators, dense / MoE / LoRA behaviour,
+trainer mechanics, schedules, codebooks."""
+import math
+import struct
+
+import pytest
+import torch
+
+from mythos_b200.models import DenseModel, TransformerConfig
+from mythos_b200.models.config import NAMED_CONFIGS
+
+
+def _tiny(**kw):
+    base = dict(vocab_size=64, hidden_size=32, num_layers=2, num_heads=2, head_dim=16, ffn_hidden_size=64,
+                max_seq_len=32, oil_block_size=32)
+    base.update(kw)
+    return TransformerConfig(**base)
+
+
+def test_config_blob_matches_reference_struct_layout():
+    cfg = TransformerConfig(vocab_size=32000, hidden_size=768, num_layers=12, num_heads=12, head_dim=64,
+                            ffn_hidden_size=3072, norm_eps=1e-5, rope_theta=10000.0, max_seq_len=2048,
+                            activation="silu", num_kv_heads=4, use_parallel_residual=True)
+    blob = cfg.to_bytes(extended=False)
+    assert len(blob) == 88
+    assert struct.unpack_from("<q", blob, 0)[0] == 32000 and struct.unpack_from("<q", blob, 8)[0] == 768
+    assert struct.unpack_from("<q", blob, 40)[0] == 3072
+    assert abs(struct.unpack_from("<f", blob, 48)[0] - 1e-5) < 1e-12 and struct.unpack_from("<f", blob, 52)[0] == 10000.0
+    assert struct.unpack_from("<q", blob, 56)[0] == 2048 and struct.unpack_from("<i", blob, 64)[0] == 2
+    assert struct.unpack_from("<q", blob, 72)[0] == 4 and blob[80] == 1
+    assert blob[68:72] == b"\0\0\0\0" and blob[81:88] == b"\0" * 7
+    back = TransformerConfig.from_bytes(blob)
+    assert back.weight_format == "fp32" and back.num_kv_heads == 4 and back.hidden_size == 768
+    ext = TransformerConfig.from_bytes(cfg.to_bytes())
+    assert ext.weight_format == cfg.weight_format and ext.oil_block_size == cfg.oil_block_size
+    for name, fn in NAMED_CONFIGS.items():
+        c = fn()
+        assert c.hidden_size % 8 == 0 and c.param_count() > 0, name
+    assert 1.2e9 < NAMED_CONFIGS["llama-1.3b"]().param_count() < 1.5e9
+
+
+def test_reference_attention_is_causal_and_gqa_grouped():
+    from mythos_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    q = torch.randn(1, 6, 4, 8)
+    k = torch.randn(1, 6, 2, 8)
+    v = torch.randn(1, 6, 2, 8)
+    o, lse = ref.attention(q, k, v, True)
+    k2, v2 = k.clone(), v.clone()
+    k2[:, 4:] += 5
+    v2[:, 4:] -= 3
+    o2, _ = ref.attention(q, k2, v2, True)
+    assert torch.allclose(o[:, :4], o2[:, :4])          # the future does not leak
+    o3, _ = ref.attention(q[:, :, :2], k[:, :, :1], v[:, :, :1], True)
+    assert torch.allclose(o[:, :, :2], o3, atol=1e-6)   # heads 0,1 read kv head 0
+    assert lse.shape == (1, 4, 6)
+
+
+def test_rope_is_a_rotation_and_inverts():
+    from mythos_b200.ops import reference as ref
+
+    x = torch.randn(5, 3, 16)
+    pos = torch.tensor([0, 1, 7, 100, 2047], dtype=torch.int32)
+    y = ref.rope(x, pos, 10000.0)
+    assert torch.allclose(y[0], x[0])
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+    assert torch.allclose(ref.rope(y, pos, 10000.0, inverse=True), x, atol=1e-5)
+    j, d, p = 3, 16, 7.0
+    ang = p * 10000.0 ** (-2.0 * j / d)
+    want = x[2, 0, j] * math.cos(ang) - x[2, 0, j + 8] * math.sin(ang)
+    assert abs(float(y[2, 0, j]) - float(want)) < 1e-5
+
+
+def test_dense_model_trains_on_cpu_and_ste_quantises():
+    from mythos_b200.train.data import ZipfStream
+    from mythos_b200.train.trainer import TrainConfig, Trainer
+
+    torch.manual_seed(0)
+    m = DenseModel(_tiny())
+    tr = Trainer(m, TrainConfig(batch_size=8, micro_batch_size=4, seq_length=16, lr=5e-3, warmup_steps=2,
+                                max_steps=50, codebook_ema_interval=5), device="cpu")
+    ds = ZipfStream(64, 8, 16, seed=1)
+    losses = [float(tr.train_step(*ds.next_batch())) for _ in range(20)]
+    assert losses[-1] < losses[0] - 0.2
+    lin = m.layers[0].attention.qkv_proj
+    wq = lin.compute_weight().detach()
+    assert len(torch.unique(wq.reshape(-1, lin.block_size)[0])) <= 256
+    assert not torch.equal(wq, lin.weight.detach())
+    cb = lin.codebooks
+    assert bool((cb[:, 1:] >= cb[:, :-1]).all())  # codebooks stay sorted after EMA updates
+
+
+def test_grad_accumulation_equals_one_big_batch():
+    from mythos_b200.train.trainer import TrainConfig, Trainer
+
+    torch.manual_seed(1)
+    a, b = DenseModel(_tiny(weight_format="fp32")), DenseModel(_tiny(weight_format="fp32"))
+    b.load_state_dict(a.state_dict())
+    ta = Trainer(a, TrainConfig(batch_size=4, micro_batch_size=4, lr=1e-3, warmup_steps=0), device="cpu")
+    tb = Trainer(b, TrainConfig(batch_size=4, micro_batch_size=1, lr=1e-3, warmup_steps=0), device="cpu")
+    ids = torch.randint(0, 64, (4, 16), dtype=torch.int32)
+    tg = torch.randint(0, 64, (4, 16), dtype=torch.int32)
+    la, lb = ta.train_step(ids, tg), tb.train_step(ids, tg)
+    assert abs(float(la) - float(lb)) < 1e-5
+    assert torch.allclose(ta.store.master, tb.store.master, atol=1e-6)
+
+
+def test_moe_reference_matches_per_token_loop_and_aux_loss():
+    from mythos_b200.models.moe import MoEFFN, MoEModel
+    from mythos_b200.ops import reference as ref
+
+    torch.manual_seed(2)
+    cfg = _tiny(num_experts=4, moe_top_k=2, moe_ffn_hidden_size=48, weight_format="fp32", moe_aux_coef=0.01)
+    moe = MoEFFN(cfg)
+    x = torch.randn(10, 32)
+    out = moe(x)
+    probs = torch.softmax(moe.router(x).float(), -1)
+    w, idx = torch.topk(probs, 2, dim=-1)
+    want = torch.zeros_like(x)
+    for t in range(10):
+        for j in range(2):
+            want[t] += w[t, j] * moe._expert(int(idx[t, j]), x[t:t + 1])[0]   # weights are not renormalised
+    assert torch.allclose(out, want, atol=1e-5)
+    f = torch.bincount(idx.reshape(-1), minlength=4).float() / 10
+    P = torch.stack([(probs[:, e] * (idx == e).any(1)).sum() / 10 for e in range(4)])
+    assert abs(float(moe.last_aux) - 0.01 * 4 * float((f * P).sum())) < 1e-6
+    assert abs(float(ref.z_loss(torch.zeros(3, 4), 0.5)) - 0.5 * math.log(4) ** 2) < 1e-6
+    model = MoEModel(cfg)
+    ids = torch.randint(0, 64, (2, 8), dtype=torch.int32)
+    loss = model(ids, ids)
+    loss.backward()
+    assert model.layers[0].ffn.router.weight.grad is not None
+    assert any(e.weight.grad is not None for e in model.layers[0].ffn.experts_up)
+    # capacity factor drops overflow tokens; shared experts always run
+    capped = MoEFFN(_tiny(num_experts=4, moe_top_k=1, weight_format="fp32", moe_shared_experts=1),
+                    capacity_factor=0.5, drop_policy="drop")
+    capped(torch.randn(16, 32))
+    assert capped.last_stats["tokens_dropped"] > 0
+    for routing in ("hash", "expert_choice", "dense"):
+        assert MoEFFN(cfg, routing=routing)(x).shape == x.shape
+
+
+def test_lora_adapters_train_while_base_stays_frozen():
+    from mythos_b200.models.lora import LoRALinear, apply_lora, merge_all, nf4_codebook
+
+    torch.manual_seed(3)
+    m = DenseModel(_tiny(weight_format="oil4"))
+    ids = torch.randint(0, 64, (2, 12), dtype=torch.int32)
+    with torch.no_grad():
+        before = m(ids)
+    wrapped = apply_lora(m, rank=4, alpha=8.0, targets=("q", "v"))
+    assert len(wrapped) == 2 and all(isinstance(w, LoRALinear) for w in wrapped)
+    with torch.no_grad():
+        assert torch.allclose(m(ids), before, atol=1e-6)   # B = 0: adapters start as identity
+    trainable = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    base_w = m.layers[0].attention.qkv_proj.base.weight.clone()
+    opt = torch.optim.SGD([p for p in m.parameters() if p.requires_grad], lr=0.5)
+    for _ in range(3):
+        loss = m(ids, ids)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert torch.equal(m.layers[0].attention.qkv_proj.base.weight, base_w)
+    assert float(m.layers[0].attention.qkv_proj.lora_B[0].abs().sum()) > 0
+    lin = LoRALinear(DenseModel(_tiny(weight_format="fp32")).layers[0].attention.o_proj, rank=2)
+    with torch.no_grad():
+        lin.lora_B[0].normal_()
+    x = torch.randn(3, 32)
+    y = lin(x)
+    lin.merge()
+    assert torch.allclose(lin(x), y, atol=1e-5)
+    lin.unmerge()
+    assert torch.allclose(lin(x), y, atol=1e-5)
+    assert nf4_codebook().numel() == 16 and float(nf4_codebook(2.0).max()) == 2.0
+    merge_all(m)
+
+
+def test_schedules_match_reference_formulas():
+    from mythos_b200.train import sched
+
+    assert sched.builtin_lr("warmup_cosine", 3e-4, 50, 100, 10000) == pytest.approx(1.5e-4)
+    assert sched.builtin_lr("warmup_cosine", 3e-4, 100, 100, 10000) == pytest.approx(3e-4)
+    mid = sched.builtin_lr("warmup_cosine", 3e-4, 5050, 100, 10000)
+    assert mid == pytest.approx(3e-4 * 0.5 * (1 + math.cos(math.pi * 0.5)), abs=1e-9)
+    assert sched.builtin_lr("warmup_cosine", 3e-4, 10000, 100, 10000) == pytest.approx(1e-8)
+    assert sched.builtin_lr("constant", 1.0, 7) == 1.0
+    assert sched.LinearDecay(1.0, 10).lr(5) == pytest.approx(0.5)
+    assert sched.StepDecay(1.0, 10, 0.1).lr(25) == pytest.approx(0.01)
+    assert sched.ExponentialDecay(1.0, 0.5).lr(3) == pytest.approx(0.125)
+    assert sched.Warmup(sched.Constant(2.0), 4).lr(1) == pytest.approx(1.0)
+    assert sched.Sequential([sched.Constant(1.0), sched.Constant(0.1)], [5]).lr(7) == pytest.approx(0.1)
+    assert sched.Lambda(2.0, lambda s: 1.0 / (1 + s)).lr(1) == pytest.approx(1.0)
+    oc = sched.OneCycle(1.0, 100)
+    assert oc.lr(30) == pytest.approx(1.0) and oc.lr(0) < 0.1
+    rp = sched.ReduceLROnPlateau(1.0, factor=0.5, patience=1)
+    for v in (1.0, 1.0, 1.0):
+        rp.observe(v)
+    assert rp.lr(0) == pytest.approx(0.5)
+
+
+def test_codebook_kmeans_ema_and_serialisation():
+    from mythos_b200.oil import codebook as cbk
+
+    torch.manual_seed(4)
+    data = torch.cat([torch.randn(500) * 0.01 - 1, torch.randn(500) * 0.01 + 1])
+    cb = cbk.kmeans_codebook(data, 16)
+    assert bool((cb[1:] >= cb[:-1]).all()) and cb.min() < -0.9 and cb.max() > 0.9
+    idx, cnt, sums = cbk.quantize(data, cb)
+    assert int(cnt.sum()) == 1000 and idx.dtype == torch.uint8
+    q = cbk.quantile_codebook(256, 0.02)
+    assert abs(float(q.mean())) < 1e-6 and bool((q[1:] > q[:-1]).all())
+    kind, back = cbk.deserialize(cbk.serialize_oil8(q))
+    assert kind == "oil8" and torch.equal(torch.from_numpy(back.copy()), q)
+    kind4, back4 = cbk.deserialize(cbk.serialize_oil4(cbk.quantile_codebook(16, fp16=True)))
+    assert kind4 == "oil4" and back4.shape == (16,)
+    books = q[None].clone()
+    ema = cbk.EMAState(books, decay=0.5)
+    ema.update(books, torch.ones(1, 256), books * 2)
+    assert torch.allclose(books, torch.sort(q * 2).values[None])
