@@ -156,7 +156,9 @@ class MoEFFN(nn.Module):
         self.gating_dropout = gating_dropout
         f = cfg.moe_ffn_hidden_size or cfg.ffn_hidden_size
         fmt = cfg.format_for("ffn")
-        self.router = OILLinear(cfg.hidden_size, cfg.num_experts, "fp32", cfg.oil_block_size)
+        # The router's output width is padded to a multiple of 8 (TMA rows are 16-byte multiples);
+        # only the first num_experts columns are used, the rest receive zero gradients.
+        self.router = OILLinear(cfg.hidden_size, (cfg.num_experts + 7) // 8 * 8, "fp32", cfg.oil_block_size)
         self.experts_up = nn.ModuleList([OILLinear(cfg.hidden_size, 2 * f, fmt, cfg.oil_block_size, cfg.codebook_group)
                                          for _ in range(cfg.num_experts)])
         self.experts_down = nn.ModuleList([OILLinear(f, cfg.hidden_size, fmt, cfg.oil_block_size, cfg.codebook_group)
@@ -179,7 +181,7 @@ class MoEFFN(nn.Module):
     def _route(self, x2):
         from ..ops import reference as ref
 
-        logits = self.router(x2).float()
+        logits = self.router(x2)[:, : self.num_experts].float()
         if self.training and self.gating_dropout > 0:
             logits = logits + torch.empty_like(logits).bernoulli_(self.gating_dropout) * -1e4
         probs = torch.softmax(logits, dim=-1)
@@ -207,7 +209,7 @@ class MoEFFN(nn.Module):
         x2 = x.reshape(-1, shape[-1])
         T, E, k = x2.shape[0], self.num_experts, self.top_k
         if self.routing in ("dense", "soft"):
-            probs = torch.softmax(self.router(x2).float(), dim=-1)
+            probs = torch.softmax(self.router(x2)[:, :E].float(), dim=-1)
             out = sum(probs[:, e:e + 1].to(x2.dtype) * self._expert(e, x2) for e in range(E))
             self.last_aux = torch.zeros((), device=x.device)
         else:

@@ -115,7 +115,7 @@ def test_moe_reference_matches_per_token_loop_and_aux_loss():
     moe = MoEFFN(cfg)
     x = torch.randn(10, 32)
     out = moe(x)
-    probs = torch.softmax(moe.router(x).float(), -1)
+    probs = torch.softmax(moe.router(x)[:, :4].float(), -1)
     w, idx = torch.topk(probs, 2, dim=-1)
     want = torch.zeros_like(x)
     for t in range(10):
