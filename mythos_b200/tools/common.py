@@ -1,0 +1,50 @@
+"""Shared helpers of the command-line tools: JSON config files with the documented sections
+(``model``, ``training``, ``format``, ``quantization``), dotted overrides, device choice."""
+from __future__ import annotations
+
+import json
+
+import torch
+
+from ..models.config import NAMED_CONFIGS, TransformerConfig
+
+
+def pick_device(arg: str | None) -> torch.device:
+    if arg in (None, "", "auto"):
+        return torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    if arg.isdigit():
+        return torch.device("cuda", int(arg))
+    return torch.device(arg)
+
+
+def load_json_config(path: str | None) -> dict:
+    if not path:
+        return {}
+    with open(path) as f:
+        return json.load(f)
+
+
+def model_config_from(args, cfg_json: dict, vocab_size: int | None = None) -> TransformerConfig:
+    preset = getattr(args, "preset", None)
+    if preset:
+        cfg = NAMED_CONFIGS[preset]()
+    else:
+        m = dict(cfg_json.get("model", {}))
+        cfg = TransformerConfig.from_dict(m) if m else TransformerConfig()
+    for attr, field in (("hidden_size", "hidden_size"), ("dim", "hidden_size"), ("num_layers", "num_layers"),
+                        ("n_layers", "num_layers"), ("num_heads", "num_heads"), ("ffn_hidden_size", "ffn_hidden_size"),
+                        ("seq_length", "max_seq_len"), ("weight_format", "weight_format"),
+                        ("block_size", "oil_block_size")):
+        v = getattr(args, attr, None)
+        if v:
+            setattr(cfg, field, v)
+    if getattr(args, "hidden_size", None) or getattr(args, "dim", None) or getattr(args, "num_heads", None):
+        cfg.head_dim = cfg.hidden_size // cfg.num_heads
+        if not getattr(args, "ffn_hidden_size", None):
+            cfg.ffn_hidden_size = 4 * cfg.hidden_size
+    if vocab_size:
+        cfg.vocab_size = vocab_size
+    fmt = cfg_json.get("format", {})
+    if fmt.get("weight_format"):
+        cfg.weight_format = fmt["weight_format"]
+    return cfg
