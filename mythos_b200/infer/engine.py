@@ -315,6 +315,57 @@ class InferenceEngine:
         return GenerationResult(tokens=[t.tolist() for t in toks], stats=stats)
 
 
+    # ------------------------------------------------------------------ step-wise API (serving)
+    @torch.no_grad()
+    def start_sequence(self, prompt_ids, reuse_prefix: bool = True):
+        """Prefill one request. Returns ``(seq, logits)`` with the logits of the last prompt token
+        ([1, V]). A cached prefix (full pages of an earlier identical prompt head) is re-used only
+        when it covers the whole prompt but the last token, otherwise the prompt is recomputed."""
+        ids = [int(t) for t in prompt_ids]
+        cache = self.cache
+        seq = cache.new_sequence()
+        cache.reserve(seq, len(ids))
+        cache.sync_tables()
+        S = len(ids)
+        dev = self.device
+        self._prepare_decode_scratch(self.max_batch, self.max_seq_len)
+        t = torch.tensor(ids, dtype=torch.int32, device=dev)
+        pos = torch.arange(S, device=dev, dtype=torch.int32)
+        sid = torch.full((S,), seq, device=dev, dtype=torch.int32)
+        h = self._forward(t, pos, sid, None, prefill_shape=(1, S))
+        cache.advance(seq, S)
+        if reuse_prefix:
+            cache.publish_prefix(seq, ids)
+        return seq, self._logits(h[-1:].contiguous())
+
+    @torch.no_grad()
+    def decode(self, seqs, tokens):
+        """One decode step for the given sequences (any mix of lengths): appends ``tokens`` (one per
+        sequence) and returns the next-token logits [n, V]."""
+        cache, dev = self.cache, self.device
+        for s in seqs:
+            cache.reserve(s, 1)
+        cache.sync_tables()
+        n = len(seqs)
+        ids = torch.as_tensor(tokens, dtype=torch.int32).to(dev).reshape(n)
+        pos = torch.tensor([cache.lens[s] for s in seqs], dtype=torch.int32, device=dev)
+        sid = torch.tensor(list(seqs), dtype=torch.int32, device=dev)
+        # the decode kernel indexes block-table rows by position in the batch: gather the rows
+        table_rows = cache.block_table.index_select(0, sid.long()).contiguous()
+        saved = cache.block_table
+        cache.block_table = table_rows
+        try:
+            h = self._forward(ids, pos, torch.arange(n, device=dev, dtype=torch.int32), pos + 1, None)
+        finally:
+            cache.block_table = saved
+        for s in seqs:
+            cache.advance(s, 1)
+        return self._logits(h)
+
+    def release(self, seq: int) -> None:
+        self.cache.free_sequence(seq)
+
+
 # ---------------------------------------------------------------------------------------- TP helpers
 def _shard_rows_multi(mod, parts, rank: int, world: int) -> QuantLinear:
     """Column-parallel shard of a fused projection: from each (start, size) part of the output rows
