@@ -398,6 +398,7 @@ mb::DequantWeights to_weights(const Tensor& packed, const OptTensor& codebooks, 
   if (codebooks.has_value()) {
     chk_c(*codebooks, BF16, "codebooks");
     w.codebooks = codebooks->data_ptr();
+    w.n_codebooks = (int)codebooks->size(0);
   }
   if (cb_map.has_value()) {
     chk_c(*cb_map, I32, "cb_map");

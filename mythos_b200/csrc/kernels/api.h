@@ -148,6 +148,7 @@ struct DequantWeights {
   const int* cb_map;         // per block: codebook row (null = block index)
   const float* scales;       // I2_S: per-block scale
   int fmt, N, K, block_size; // blocks run along K inside a row; K % block_size == 0
+  int n_codebooks;           // rows of `codebooks`
 };
 // y = x * dequant(W)^T. Exactly one output: out_bf16 (no split-K), or fp32 accumulation into
 // out_f32 / into every buffer of `peers` (fused all-reduce; buffers must hold zeros or a residual).

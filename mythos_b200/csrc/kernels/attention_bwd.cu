@@ -8,7 +8,9 @@
 //     dV  += P^T dO           dK  += dS^T Q                        (TMEM, 128 columns each)
 //     dQ^T = K^T dS^T                                              (TMEM, 64 columns) -> fp32 atomics
 // The same shared tiles serve as K-major operands in one product and MN-major in another, so
-// nothing is transposed in memory. dQ is accumulated in an fp32 scratch buffer and converted
+// nothing is transposed in memory. Two compute warpgroups split the 64 query columns of a step
+// (32 each), so every SM sub-partition has two warps to hide TMEM-load and exp latency behind one
+// another. dQ is accumulated in an fp32 scratch buffer with bulk tensor reductions and converted
 // to bf16 by a second kernel. Replaces the reference's four O(S^2 D) scalar loops
 // (src/autograd.cpp:463-584).
 #include "api.h"
@@ -23,7 +25,8 @@ CUtensorMap make_bshd_map(const void* base, int batch, int seq, int nheads, int 
 
 namespace {
 
-constexpr int BW_THREADS = 192;
+constexpr int BW_THREADS = 320;  // loader warp, MMA warp, two compute warpgroups
+constexpr int BW_QH = 32;        // query columns per compute warpgroup
 constexpr int BW_KV = 128;  // kv rows per CTA
 constexpr int BW_Q = 64;    // query rows per step
 constexpr int BW_D = 128;
@@ -38,8 +41,8 @@ struct BwCfg {
   static constexpr int OFF_ST = 2 * KV_BYTES;
   static constexpr int OFF_PT = OFF_ST + 2 * STAGE_BYTES;
   static constexpr int OFF_DST = OFF_PT + PT_BYTES;
-  static constexpr int OFF_STATS = OFF_DST + PT_BYTES;   // [4 warps][2 parity][lse 64 | delta 64] floats
-  static constexpr int OFF_DQ = OFF_STATS + 4 * 2 * 128 * 4;  // [4 warps][64 q][32 d] fp32 staging for the dQ reduce
+  static constexpr int OFF_STATS = OFF_DST + PT_BYTES;   // [8 warps][2 parity][lse 32 | delta 32] floats
+  static constexpr int OFF_DQ = OFF_STATS + 8 * 2 * 64 * 4;   // [8 warps][32 q][32 d] fp32 staging for the dQ reduce
   static constexpr int OFF_BAR = OFF_DQ + BW_Q * BW_D * 4;
   static constexpr int NUM_BARS = 10;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
@@ -86,10 +89,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(sp_free, 128);
-    mbar_init(pds_full, 128);
+    mbar_init(sp_free, 256);
+    mbar_init(pds_full, 256);
     mbar_init(mma_done, 1);
-    mbar_init(dq_free, 128);
+    mbar_init(dq_free, 256);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
@@ -193,35 +196,36 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------------ compute warpgroup
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------------ compute warpgroups
+    const int quarter = warp & 3;        // TMEM lane quarter this warp may read
+    const int wg = (warp - 2) >> 2;      // 0/1: query columns [32 wg, 32 wg + 32) of every step
+    const int cw = warp - 2;             // 0..7
     const int r = quarter * 32 + lane;   // kv row of this thread; also the d row of dQ^T
     const int kv_row = kv0 + r;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
 
-    float* dq_stage = reinterpret_cast<float*>(smem + Cfg::OFF_DQ) + quarter * (BW_Q * 32);
+    float* dq_stage = reinterpret_cast<float*>(smem + Cfg::OFF_DQ) + cw * (BW_QH * 32);
     auto drain_dq = [&](int n) {
-      // dQ^T of step n is in TMEM: lane = d, column = q. Each warp transposes its 32 d-columns into
-      // a [64 q][32 d] fp32 tile in shared memory and adds it to the fp32 dQ buffer with one bulk
-      // tensor reduction (no per-element atomics).
+      // dQ^T of step n is in TMEM: lane = d, column = q. Each warp transposes its 32 d-rows x 32
+      // q-columns into a [32 q][32 d] fp32 tile in shared memory and adds it to the fp32 dQ buffer
+      // with one bulk tensor reduction (no per-element atomics).
       const int h = hkv * group + n / per_head;
       const int q0 = (i_start + n % per_head) * BW_Q;
-      uint32_t a[2][32];
-      tmem_ld32(tmem_base + Cfg::COL_DQT + lane_sel, a[0]);
-      tmem_ld32(tmem_base + Cfg::COL_DQT + 32 + lane_sel, a[1]);
+      uint32_t a[32];
+      tmem_ld32(tmem_base + Cfg::COL_DQT + wg * BW_QH + lane_sel, a);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_free);
       if (lane == 0) tma_store_wait_read0();  // the previous reduction has finished reading the staging tile
       __syncwarp();
 #pragma unroll
-      for (int q = 0; q < BW_Q; ++q) dq_stage[q * 32 + lane] = __uint_as_float(a[q >> 5][q & 31]);
+      for (int q = 0; q < BW_QH; ++q) dq_stage[q * 32 + lane] = __uint_as_float(a[q]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        tma_reduce_add_4d(&tm_dq, dq_stage, quarter * 32, h, q0, b);
+      if (lane == 0 && q0 + wg * BW_QH < seq) {   // a box wholly past the sequence end is not issued
+        tma_reduce_add_4d(&tm_dq, dq_stage, quarter * 32, h, q0 + wg * BW_QH, b);
         tma_store_commit();
       }
     };
@@ -231,17 +235,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int q0 = (i_start + n % per_head) * BW_Q;
       // Each warp stages lse / delta of this query tile in its own shared-memory slot
       // (double-buffered by step parity), so no CTA-wide barrier is needed here.
-      float* st_lse = stats + (quarter * 2 + (n & 1)) * 128;
-      float* st_dl = st_lse + 64;
+      float* st_lse = stats + (cw * 2 + (n & 1)) * 64;
+      float* st_dl = st_lse + 32;
+      const int qc0 = q0 + wg * BW_QH;   // first query row of this warpgroup's columns
       {
         const long long off = ((long long)b * heads + h) * seq;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int qi = half * 32 + lane;
-          const int q = q0 + qi;
-          st_lse[qi] = (q < seq) ? lse[off + q] * LOG2E : INFINITY;
-          st_dl[qi] = (q < seq) ? delta[off + q] : 0.f;
-        }
+        const int q = qc0 + lane;
+        st_lse[lane] = (q < seq) ? lse[off + q] * LOG2E : INFINITY;
+        st_dl[lane] = (q < seq) ? delta[off + q] : 0.f;
       }
       __syncwarp();
 
@@ -249,22 +250,20 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[2][32], dr[2][32];
-      tmem_ld32(tmem_base + Cfg::COL_ST + lane_sel, sr[0]);
-      tmem_ld32(tmem_base + Cfg::COL_ST + 32 + lane_sel, sr[1]);
-      tmem_ld32(tmem_base + Cfg::COL_DPT + lane_sel, dr[0]);
-      tmem_ld32(tmem_base + Cfg::COL_DPT + 32 + lane_sel, dr[1]);
+      uint32_t sr[32], dr[32];
+      tmem_ld32(tmem_base + Cfg::COL_ST + wg * BW_QH + lane_sel, sr);
+      tmem_ld32(tmem_base + Cfg::COL_DPT + wg * BW_QH + lane_sel, dr);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(sp_free);
-      float* s = reinterpret_cast<float*>(&sr[0][0]);
-      float* d = reinterpret_cast<float*>(&dr[0][0]);
-      const bool diag = causal && (q0 < kv0 + BW_KV);
+      float* s = reinterpret_cast<float*>(&sr[0]);
+      float* d = reinterpret_cast<float*>(&dr[0]);
+      const bool diag = causal && (qc0 < kv0 + BW_KV);
 #pragma unroll
-      for (int i = 0; i < BW_Q; ++i) {
+      for (int i = 0; i < BW_QH; ++i) {
         const float e = fmaf(s[i], scale_log2, -st_lse[i]);
         float p = ((i & 3) == 3) ? poly_exp2(e) : fast_exp2(e);
-        if (diag && (kv_row > q0 + i)) p = 0.f;
+        if (diag && (kv_row > qc0 + i)) p = 0.f;
         s[i] = p;
         d[i] = p * (d[i] - st_dl[i]) * scale;
       }
@@ -278,7 +277,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       uint8_t* pt = smem + Cfg::OFF_PT;
       uint8_t* dst = smem + Cfg::OFF_DST;
 #pragma unroll
-      for (int c = 0; c < BW_Q / 8; ++c) {
+      for (int c = 0; c < BW_QH / 8; ++c) {
         uint4 v, w;
         v.x = pack_bf16x2(s[8 * c + 0], s[8 * c + 1]);
         v.y = pack_bf16x2(s[8 * c + 2], s[8 * c + 3]);
@@ -288,8 +287,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         w.y = pack_bf16x2(d[8 * c + 2], d[8 * c + 3]);
         w.z = pack_bf16x2(d[8 * c + 4], d[8 * c + 5]);
         w.w = pack_bf16x2(d[8 * c + 6], d[8 * c + 7]);
-        *reinterpret_cast<uint4*>(pt + sw128_offset(r, c)) = v;
-        *reinterpret_cast<uint4*>(dst + sw128_offset(r, c)) = w;
+        *reinterpret_cast<uint4*>(pt + sw128_offset(r, wg * (BW_QH / 8) + c)) = v;
+        *reinterpret_cast<uint4*>(dst + sw128_offset(r, wg * (BW_QH / 8) + c)) = w;
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -302,10 +301,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         drain_dq(N - 1);
         if (lane == 0) tma_store_wait0();  // all dQ reductions of this warp have landed
-        // dV and dK rows of this thread
+        // this thread's kv row of dV (warpgroup 0) or dK (warpgroup 1)
         const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
-#pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
+        {
+          const int which = wg;
           __nv_bfloat16* out = (which == 0 ? dv : dk) + row_off;
           const uint32_t col = which == 0 ? Cfg::COL_DV : Cfg::COL_DK;
 #pragma unroll 1
@@ -328,7 +327,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
         }
       }
-    } else if (N == 0 && kv_row < seq) {
+    } else if (N == 0 && kv_row < seq && wg == 0) {
       // no query can see this tile (cannot happen with causal self-attention, kept for safety)
       const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
       for (int i = 0; i < BW_D; ++i) {
@@ -420,7 +419,7 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
     uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)heads, (uint64_t)seq, (uint64_t)batch};
     uint64_t strides[3] = {(uint64_t)head_dim * 4, (uint64_t)heads * head_dim * 4,
                            (uint64_t)seq * heads * head_dim * 4};
-    uint32_t box[4] = {32, 1, BW_Q, 1};
+    uint32_t box[4] = {32, 1, BW_QH, 1};
     tdq = make_tensor_map(dq_accum, TmaDType::F32, 4, dims, strides, box, false);
   }
   static bool configured = false;

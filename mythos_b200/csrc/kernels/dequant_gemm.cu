@@ -35,21 +35,28 @@ struct DqSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES_MAX;
   static constexpr int BAR_OFFSET = DQ_STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 3 * DQ_STAGES + 1;
-  static constexpr int SMEM_BYTES = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int CB_SLOTS = 16;                                // codebooks cached per producer warp
+  static constexpr int CB_OFFSET = (BAR_OFFSET + NUM_BARS * 8 + 16 + 15) / 16 * 16; // [4 warps][CB_SLOTS][256] bf16
+  static constexpr int SMEM_BYTES = CB_OFFSET + 4 * CB_SLOTS * 256 * 2 + 1024;
+  static_assert(SMEM_BYTES <= 232448, "dequant GEMM shared memory exceeds the per-CTA limit");
 };
 
 __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16(v));
 }
 
-// Expand 64 weights of one row into 8 packed uint4 (8 bf16 each).
-template <int FMT>
-__device__ __forceinline__ void dequant_row64(const DequantWeights& w, long long row, int k0, uint4 (&out)[8]) {
+template <bool SMEM>
+__device__ __forceinline__ uint32_t cb_at(const unsigned short* cb, uint32_t i) {
+  return SMEM ? (uint32_t)cb[i] : (uint32_t)__ldg(cb + i);
+}
+
+// Expand 64 weights of one row into 8 packed uint4 (8 bf16 each). `cb` is the row's codebook for
+// this k-block: a shared-memory copy (SMEM) or the table in global memory.
+template <int FMT, bool SMEM>
+__device__ __forceinline__ void dequant_row64(const DequantWeights& w, long long row, int k0,
+                                              const unsigned short* cb, uint4 (&out)[8]) {
   const long long elem = row * w.K + k0;
   if (FMT == QFMT_OIL8) {
-    const long long blk = elem / w.block_size;
-    const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
-    const unsigned short* cb = reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * 256;
     const uint4* ip = reinterpret_cast<const uint4*>(w.packed + elem);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -59,16 +66,13 @@ __device__ __forceinline__ void dequant_row64(const DequantWeights& w, long long
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t x = words[j];
-        o[2 * j] = (uint32_t)__ldg(cb + (x & 0xFF)) | ((uint32_t)__ldg(cb + ((x >> 8) & 0xFF)) << 16);
-        o[2 * j + 1] = (uint32_t)__ldg(cb + ((x >> 16) & 0xFF)) | ((uint32_t)__ldg(cb + (x >> 24)) << 16);
+        o[2 * j] = cb_at<SMEM>(cb, x & 0xFF) | (cb_at<SMEM>(cb, (x >> 8) & 0xFF) << 16);
+        o[2 * j + 1] = cb_at<SMEM>(cb, (x >> 16) & 0xFF) | (cb_at<SMEM>(cb, x >> 24) << 16);
       }
       out[2 * c] = make_uint4(o[0], o[1], o[2], o[3]);
       out[2 * c + 1] = make_uint4(o[4], o[5], o[6], o[7]);
     }
   } else if (FMT == QFMT_OIL4) {
-    const long long blk = elem / w.block_size;
-    const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
-    const unsigned short* cb = reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * 16;
     const uint4* ip = reinterpret_cast<const uint4*>(w.packed + elem / 2);
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
@@ -80,7 +84,7 @@ __device__ __forceinline__ void dequant_row64(const DequantWeights& w, long long
         uint32_t o[4];
 #pragma unroll
         for (int p = 0; p < 4; ++p)
-          o[p] = (uint32_t)__ldg(cb + ((x >> (8 * p)) & 0xF)) | ((uint32_t)__ldg(cb + ((x >> (8 * p + 4)) & 0xF)) << 16);
+          o[p] = cb_at<SMEM>(cb, (x >> (8 * p)) & 0xF) | (cb_at<SMEM>(cb, (x >> (8 * p + 4)) & 0xF) << 16);
         out[4 * c + j] = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
@@ -182,13 +186,45 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, DequantWeights w,
     const long long row = (long long)n0 + r;
     const bool row_ok = row < w.N;
     bool ok = true;
+    constexpr int CBSZ = (FMT == QFMT_OIL4) ? 16 : 256;
+    unsigned short* warp_cb =
+        reinterpret_cast<unsigned short*>(smem + S::CB_OFFSET) + (warp & 3) * (S::CB_SLOTS * 256);
+    const unsigned short* cb_global = reinterpret_cast<const unsigned short*>(w.codebooks);
+    int cached_lo = 0, cached_hi = -1;   // codebooks [cached_lo, cached_hi] are in warp_cb
     for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
       const int st = it % DQ_STAGES;
       const uint32_t ph = (it / DQ_STAGES) & 1;
       uint4 vals[8];
-      if (row_ok) {
-        dequant_row64<FMT>(w, row, kb * DQ_BK, vals);
+      if (FMT == QFMT_I2S) {
+        if (row_ok) dequant_row64<FMT, false>(w, row, kb * DQ_BK, nullptr, vals);
       } else {
+        // Codebook of this row for this k-block. The 32 rows of a warp usually use a short run of
+        // consecutive codebooks: keep up to CB_SLOTS of them in a per-warp shared-memory table so
+        // the 64 look-ups per row are shared-memory reads; wider spreads gather from global memory.
+        int cbi = -1;
+        if (row_ok) {
+          const long long blk = (row * w.K + (long long)kb * DQ_BK) / w.block_size;
+          cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
+        }
+        const int hi = __reduce_max_sync(0xffffffffu, cbi);
+        const int lo = __reduce_min_sync(0xffffffffu, row_ok ? cbi : 0x7fffffff);
+        if (hi >= 0 && hi - lo < S::CB_SLOTS) {
+          if (lo < cached_lo || hi > cached_hi) {
+            __syncwarp();
+            const int last = min(lo + S::CB_SLOTS, w.n_codebooks) - 1;
+            const int n_vec = (last - lo + 1) * CBSZ / 8;   // codebooks are 32- or 512-byte records
+            const uint4* src = reinterpret_cast<const uint4*>(cb_global + (long long)lo * CBSZ);
+            for (int i = lane; i < n_vec; i += 32) reinterpret_cast<uint4*>(warp_cb)[i] = __ldg(src + i);
+            cached_lo = lo;
+            cached_hi = last;
+            __syncwarp();
+          }
+          if (row_ok) dequant_row64<FMT, true>(w, row, kb * DQ_BK, warp_cb + (cbi - cached_lo) * CBSZ, vals);
+        } else if (row_ok) {
+          dequant_row64<FMT, false>(w, row, kb * DQ_BK, cb_global + (long long)cbi * CBSZ, vals);
+        }
+      }
+      if (!row_ok) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) vals[c] = make_uint4(0, 0, 0, 0);
       }
@@ -219,7 +255,7 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, DequantWeights w,
             if (m < M) {
               const float val = __uint_as_float(v[j]);
               const long long off = (long long)m * ld_out + row;
-              if (out_f32) {
+              if (out_f32 || n_peers > 0) {
                 if (n_peers > 0) {
                   for (int p = 0; p < n_peers; ++p) atomicAdd(reinterpret_cast<float*>(peers.p[p]) + off, val);
                 } else {
@@ -264,7 +300,13 @@ __global__ void dequant_full_kernel(DequantWeights w, __nv_bfloat16* __restrict_
     const long long row = i / (w.K / 64);
     const int k0 = (int)(i % (w.K / 64)) * 64;
     uint4 vals[8];
-    dequant_row64<FMT>(w, row, k0, vals);
+    const unsigned short* cb = nullptr;
+    if (FMT != QFMT_I2S) {
+      const long long blk = (row * w.K + k0) / w.block_size;
+      const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
+      cb = reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * ((FMT == QFMT_OIL4) ? 16 : 256);
+    }
+    dequant_row64<FMT, false>(w, row, k0, cb, vals);
     uint4* dst = reinterpret_cast<uint4*>(out + row * w.K + k0);
 #pragma unroll
     for (int c = 0; c < 8; ++c) dst[c] = vals[c];

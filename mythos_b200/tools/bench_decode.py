@@ -35,6 +35,7 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=0, help="use only this many layers (0 = all)")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0 = preset)")
     ap.add_argument("--repeat", type=int, default=3)
+    ap.add_argument("--no-graph", action="store_true", help="launch decode steps one by one (for launch lists)")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -67,7 +68,7 @@ def main(argv=None) -> int:
     prompts = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g, dtype=torch.int32)
     ttfts, rates = [], []
     for it in range(a.repeat):
-        res = eng.generate(prompts, max_new_tokens=a.new, use_graph=True)
+        res = eng.generate(prompts, max_new_tokens=a.new, use_graph=not a.no_graph)
         t = torch.tensor([res.stats.ttft_s, res.stats.decode_s], device=dev, dtype=torch.float64)
         if world > 1:
             import torch.distributed as dist

@@ -16,14 +16,16 @@ def _close(a, b, rtol=2e-2, atol=2e-2):
 
 
 @pytest.mark.parametrize("fmt", ["oil8", "oil4", "i2s"])
-@pytest.mark.parametrize("M", [1, 16, 64, 200])
-def test_dequant_gemm_matches_dequantised_matmul(fmt, M):
+@pytest.mark.parametrize("M,group", [(1, 4), (16, 1), (64, 64), (200, 4), (32, 3)])
+def test_dequant_gemm_matches_dequantised_matmul(fmt, M, group):
     from mythos_b200.infer.quant_weights import QuantLinear
 
     torch.manual_seed(M)
     N, K = 384, 512
     w = torch.randn(N, K, device="cuda") * 0.02
-    q = QuantLinear.from_float(w, fmt, block_size=256, codebook_group=4)
+    # group 1 spreads a warp's rows over more codebooks than its shared-memory table holds (global
+    # gathers); 3/4/64 exercise the cached path with moving and fixed windows
+    q = QuantLinear.from_float(w, fmt, block_size=256, codebook_group=group)
     deq = q.dequantize().float()
     ref_deq = q._dequantize_reference().float()
     assert torch.equal(deq, ref_deq.to(torch.bfloat16).float())
@@ -41,6 +43,12 @@ def test_dequant_gemm_matches_dequantised_matmul(fmt, M):
     C.finalize_acc(acc, None, out)
     _close(out, x.float() @ deq.t(), atol=1e-2)
     assert float(acc.abs().max()) == 0.0
+    # fused all-reduce output: partial tiles are added into every listed accumulator (here: two
+    # local buffers standing in for two ranks)
+    accs = [torch.zeros(M, N, device="cuda") for _ in range(2)]
+    assert q.matmul(x, peer_ptrs=[a.data_ptr() for a in accs]) is None
+    for a in accs:
+        _close(a, x.float() @ deq.t(), atol=1e-2)
 
 
 def test_quantisation_error_is_small_and_gemv_matches():
