@@ -491,7 +491,7 @@ void kv_append(const Tensor& k, const Tensor& v, Tensor& k_cache, Tensor& v_cach
 
 void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
                        const Tensor& context_lens, Tensor& out, Tensor& scratch, Tensor& counters, int64_t splits,
-                       double scale) {
+                       double scale, const OptTensor& status) {
   chk_c(q, BF16, "q");
   chk_c(k_cache, BF16, "k_cache");
   chk_c(v_cache, BF16, "v_cache");
@@ -507,7 +507,8 @@ void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
   mb::paged_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int>(),
                         context_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(),
                         counters.data_ptr<int>(), (int)B, (int)H, (int)Hkv, (int)D, (int)k_cache.size(1),
-                        (int)block_table.size(1), (int)splits, (float)scale, cur_stream());
+                        (int)block_table.size(1), (int)k_cache.size(0), (int)splits, (float)scale,
+                        status_ptr(status), cur_stream());
 }
 
 void sample_tokens(const Tensor& logits, const OptTensor& history, const OptTensor& allow_mask, double temperature,

@@ -170,8 +170,8 @@ void kv_append(const void* k, const void* v, void* k_cache, void* v_cache, const
 // decoding: partials in `scratch` (>= batch*heads*splits*(head_dim+2) floats), combined in-kernel.
 void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                        const int* context_lens, void* out, float* scratch, int* counters, int batch, int heads,
-                       int kv_heads, int head_dim, int page_size, int max_pages, int splits, float scale,
-                       cudaStream_t stream);
+                       int kv_heads, int head_dim, int page_size, int max_pages, int cache_pages, int splits,
+                       float scale, int* status, cudaStream_t stream);
 // Greedy / temperature / top-k / top-p / repetition-penalty sampling of one token per row.
 struct SamplerArgs {
   float temperature, top_p, repetition_penalty;

@@ -3,7 +3,12 @@
 //   kv_append          scatter new K/V vectors into 16-token (or any size) pages through a block table
 //   paged_attn_decode  one query token per sequence against its paged context: split-KV flash
 //                      decoding, all query heads of a GQA group share each K/V load, the partial
-//                      results of the splits are merged by the last CTA to finish (no waiting)
+//                      results of the splits are merged by the last CTA to finish (no waiting).
+//                      16-token pages take the tensor-core path: each warp streams whole pages
+//                      through its own TMA ring (the kernel is bound by the KV bytes in flight)
+//                      and does QK^T and PV with warp-level MMAs (the query group is 1-8 rows, so
+//                      the arithmetic is far below the memory time either way); other page sizes
+//                      use the scalar kernel.
 //   i2s_gemv           single-token GEMV over packed I2_S trits
 //
 // Reference counterparts: PagedAttention::forward (src/inference_opt.cpp:58-107, no causal mask,
@@ -13,6 +18,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "host_util.h"
+#include "tc.cuh"
 
 namespace mb {
 namespace {
@@ -33,6 +39,62 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv
     const long long dst = ((long long)page * page_size + pos % page_size) * row + c;
     stg8(k_cache, dst, ldg8(k, (long long)t * kv_tok_stride + c));
     stg8(v_cache, dst, ldg8(v, (long long)t * kv_tok_stride + c));
+  }
+}
+
+// Merge `nstate` online-softmax states of a CTA (s_m/s_l: [nstate][gstride]; s_acc: state s at
+// s_acc + s * acc_stride, laid out [gstride][D]) for the G heads of one (sequence, kv head), publish the partial result of
+// this split, and let the last CTA of the (sequence, kv head) combine all splits into `out`.
+template <int D>
+__device__ __forceinline__ void merge_and_finish(const float* s_m, const float* s_l, const float* s_acc,
+                                                 long long acc_stride, int nstate, int gstride, int G, int* s_last, float* __restrict__ scratch,
+                                                 int* __restrict__ counters, __nv_bfloat16* __restrict__ out, int b,
+                                                 int hkv, int split, int heads, int kv_heads, int splits) {
+  const int stride = D + 2;
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+    for (int s = 0; s < nstate; ++s) M = fmaxf(M, s_m[s * gstride + g]);
+    float L = 0.f, A = 0.f;
+    for (int s = 0; s < nstate; ++s) {
+      const float ms = s_m[s * gstride + g];
+      if (ms == -INFINITY) continue;   // empty state: its accumulator may hold anything
+      const float w = exp2f(ms - M);
+      L += w * s_l[s * gstride + g];
+      A += w * s_acc[s * acc_stride + (long long)g * D + d];
+    }
+    float* part = scratch + (((long long)b * heads + hkv * G + g) * splits + split) * stride;
+    part[d] = A;
+    if (d == 0) {
+      part[D] = M;
+      part[D + 1] = L;
+    }
+  }
+  // the last CTA of this (sequence, kv head) merges the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&counters[b * kv_heads + hkv], 1);
+    *s_last = (prev == splits - 1) ? 1 : 0;
+    if (*s_last) counters[b * kv_heads + hkv] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    const float* base = scratch + ((long long)b * heads + hkv * G + g) * splits * stride;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, base[s * stride + D]);
+    float L = 0.f, A = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = base[s * stride + D];
+      if (ms == -INFINITY) continue;
+      const float w = exp2f(ms - M);
+      L += w * base[s * stride + D + 1];
+      A += w * base[s * stride + d];
+    }
+    out[((long long)b * heads + hkv * G + g) * D + d] = __float2bfloat16(L > 0.f ? A / L : 0.f);
   }
 }
 
@@ -69,35 +131,48 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
   const int* bt = block_table + (long long)b * max_pages;
   // Every lane of a warp runs the same number of iterations (the shuffles below need the full
-  // warp); a token slot past the end of the range contributes nothing.
-  for (int tb = t0 + warp * TPW; tb < t1; tb += 4 * TPW) {
-    const int t = tb + sub;
-    const bool valid = t < t1;
-    float kf[8], vf[8];
-    if (valid) {
-      const int page = bt[t / page_size];
-      const long long off = ((long long)page * page_size + t % page_size) * row + (long long)hkv * D + li * 8;
-      unpack8(ldg8(k_cache, off), kf);
-      unpack8(ldg8(v_cache, off), vf);
-    } else {
+  // warp); a token slot past the end of the range contributes nothing. Each iteration first issues
+  // the K/V loads of U token slots, then does the arithmetic, so a warp keeps 2*U 16-byte loads
+  // per lane in flight: decode attention is bound by how much of the KV stream is in flight.
+  constexpr int U = 4;
+  for (int tb = t0 + warp * TPW; tb < t1; tb += 4 * TPW * U) {
+    bf16x8 kq[U], vq[U];
+    bool valid[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) kf[i] = vf[i] = 0.f;
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + u * 4 * TPW + sub;
+      valid[u] = t < t1;
+      if (valid[u]) {
+        const int page = bt[t / page_size];
+        const long long off = ((long long)page * page_size + t % page_size) * row + (long long)hkv * D + li * 8;
+        kq[u] = ldg8(k_cache, off);
+        vq[u] = ldg8(v_cache, off);
+      } else {
+        const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        kq[u] = vq[u] = pack8(z);
+      }
     }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.f;
+    for (int u = 0; u < U; ++u) {
+      float kf[8], vf[8];
+      unpack8(kq[u], kf);
+      unpack8(vq[u], vf);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s += qv[g][i] * kf[i];
+      for (int g = 0; g < G; ++g) {
+        float s = 0.f;
 #pragma unroll
-      for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (valid) {
-        s *= scale_log2;
-        const float mn = fmaxf(m[g], s);
-        const float a = exp2f(m[g] - mn), p = exp2f(s - mn);
-        l[g] = l[g] * a + p;
+        for (int i = 0; i < 8; ++i) s += qv[g][i] * kf[i];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * a + p * vf[i];
-        m[g] = mn;
+        for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid[u]) {
+          s *= scale_log2;
+          const float mn = fmaxf(m[g], s);
+          const float a = exp2f(m[g] - mn), p = exp2f(s - mn);
+          l[g] = l[g] * a + p;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * a + p * vf[i];
+          m[g] = mn;
+        }
       }
     }
   }
@@ -113,50 +188,201 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int i = 0; i < 8; ++i) s_acc[st][g][li * 8 + i] = acc[g][i];
   }
   __syncthreads();
-  // merge the CTA's states: thread d handles column d of every head of the group
-  const int stride = D + 2;
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx % D;
-    float M = -INFINITY;
-    for (int s = 0; s < NSTATE; ++s) M = fmaxf(M, s_m[s][g]);
-    float L = 0.f, A = 0.f;
-    for (int s = 0; s < NSTATE; ++s) {
-      const float w = (s_m[s][g] == -INFINITY) ? 0.f : exp2f(s_m[s][g] - M);
-      L += w * s_l[s][g];
-      A += w * s_acc[s][g][d];
-    }
-    float* part = scratch + (((long long)b * heads + hkv * G + g) * splits + split) * stride;
-    part[d] = A;
-    if (d == 0) {
-      part[D] = M;
-      part[D + 1] = L;
-    }
+  merge_and_finish<D>(&s_m[0][0], &s_l[0][0], &s_acc[0][0][0], (long long)G * D, NSTATE, G, G, &s_last, scratch, counters, out, b, hkv,
+                      split, heads, kv_heads, splits);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core decode attention for 16-token pages.
+//
+// grid (batch, kv_heads, splits), 4 warps. A warp owns every fourth page of the split and streams
+// them through a private ring of PD_STAGES shared-memory stages filled by TMA (K and V of one page
+// and one kv head: two [16 tokens x 64 dims] 128B-swizzled boxes each). Per page the warp computes
+// S = Q K^T with m16n8k16 MMAs (the G <= 8 query heads of the group are rows 0..G-1 of the 16-row
+// A operand, loaded once into registers), an online softmax on the accumulator fragments, and
+// O += P V with the V fragments read through ldmatrix.trans. Nothing but the page bytes moves.
+constexpr int PD_STAGES = 3;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int D>
+struct PdSmem {
+  static constexpr int CHUNKS = D / 64;                 // 64-dim boxes per K or V page
+  static constexpr int TILE = 16 * 128;                 // one box: 16 tokens x 128 B
+  static constexpr int STAGE = 2 * CHUNKS * TILE;       // K + V
+  static constexpr int WARP_BYTES = PD_STAGES * STAGE;
+  static constexpr int OFF_BAR = 4 * WARP_BYTES;
+  static constexpr int OFF_MERGE = OFF_BAR + 4 * PD_STAGES * 8 + 16;   // s_m[4][8], s_l[4][8]
+  static constexpr int BYTES = OFF_MERGE + 64 * 4 + 1024;
+  static_assert(8 * D * 4 <= WARP_BYTES, "a warp's output state is staged in its own (drained) ring");
+};
+
+template <int D>
+__global__ void __launch_bounds__(128)
+paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                        const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_table,
+                        const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
+                        float* __restrict__ scratch, int* __restrict__ counters, int heads, int kv_heads, int G,
+                        int max_pages, int splits, float scale_log2, int* status) {
+  using S = PdSmem<D>;
+  constexpr int KS = D / 16;   // k-steps of Q K^T
+  constexpr int NT = D / 8;    // n-tiles of P V
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
+  uint8_t* wsm = smem + warp * S::WARP_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR) + warp * PD_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::OFF_BAR + 4 * PD_STAGES * 8);
+  int* s_last = const_cast<int*>(abort_flag) + 1;
+  float* s_m = reinterpret_cast<float*>(smem + S::OFF_MERGE);
+  float* s_l = s_m + 32;
+  float* w_acc = reinterpret_cast<float*>(wsm);   // this warp's [8][D] output state, written after its ring drained
+
+  if (threadIdx.x == 0) *abort_flag = 0;
+  if (lane == 0) {
+    for (int s = 0; s < PD_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
   }
-  // the last CTA of this (sequence, kv head) merges the splits
-  __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    const int prev = atomicAdd(&counters[b * kv_heads + hkv], 1);
-    s_last = (prev == splits - 1) ? 1 : 0;
-    if (s_last) counters[b * kv_heads + hkv] = 0;  // ready for the next launch
+
+  const int ctx = context_lens[b];
+  const int n_pages = (ctx + 15) >> 4;
+  const int per = (n_pages + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(n_pages, p0 + per);
+  const int my_pages = (p1 - p0 - warp + 3) >> 2;   // pages p0 + warp, p0 + warp + 4, ... (<= 0: none)
+  const int* bt = block_table + (long long)b * max_pages;
+
+  auto issue = [&](int i) {   // lane 0: load the warp's i-th page into stage i % PD_STAGES
+    const int st = i % PD_STAGES;
+    const int page = bt[p0 + warp + 4 * i];
+    uint8_t* dst = wsm + st * S::STAGE;
+    mbar_arrive_expect_tx(&full[st], S::STAGE);
+#pragma unroll
+    for (int c = 0; c < S::CHUNKS; ++c) {
+      tma_load_2d(dst + c * S::TILE, &tm_k, &full[st], hkv * D + c * 64, page * 16);
+      tma_load_2d(dst + (S::CHUNKS + c) * S::TILE, &tm_v, &full[st], hkv * D + c * 64, page * 16);
+    }
+  };
+  if (lane == 0)
+    for (int i = 0; i < PD_STAGES && i < my_pages; ++i) issue(i);
+
+  // Q fragments: row r = lane / 4 of the group (zero rows beyond G), columns 2t, 2t+1 (+8) of each k-step
+  const int r = lane >> 2, t = lane & 3;
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+    if (r < G) {
+      const __nv_bfloat16* qp = q + ((long long)b * heads + hkv * G + r) * D + ks * 16 + 2 * t;
+      qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  // per-lane ldmatrix row selectors
+  const int k_tok = ((lane >> 4) << 3) + (lane & 7), k_unit = (lane >> 3) & 1;   // K: matrices by (token half, unit)
+  const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7), v_unit = lane >> 4;   // V: matrices by (unit, token half)
+  const uint32_t wsm_addr = smem_u32(wsm);
+  bool ok = true;
+  for (int i = 0; i < my_pages; ++i) {
+    const int st = i % PD_STAGES;
+    ok = mbar_wait(&full[st], (i / PD_STAGES) & 1, abort_flag, status, 70);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const uint32_t kbase = wsm_addr + st * S::STAGE, vbase = kbase + S::CHUNKS * S::TILE;
+    // ---- S = Q K^T : two n-tiles of 8 tokens
+    float sc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int unit = ((ks & 3) << 1) + k_unit;
+      uint32_t kb[4];
+      ldmatrix_x4(kbase + (ks >> 2) * S::TILE + k_tok * 128 + ((unit ^ (k_tok & 7)) << 4), kb);
+      mma_bf16_16816(sc[0], qa[ks], kb[0], kb[1]);
+      mma_bf16_16816(sc[1], qa[ks], kb[2], kb[3]);
+    }
+    // ---- online softmax on rows 0..7 (fragment elements 0, 1); tokens past the context are masked
+    const int tok0 = (p0 + warp + 4 * i) * 16 + 2 * t;
+    float pv[2][2];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float v = (tok0 + j * 8 + e < ctx) ? sc[j][e] * scale_log2 : -INFINITY;
+        pv[j][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);   // finite: every page of the range holds a valid token
+    const float alpha = exp2f(m_run - m_new);
+    float psum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pv[j][e] = exp2f(pv[j][e] - m_new);
+        psum += pv[j][e];
+      }
+    l_run = l_run * alpha + psum;
+    m_run = m_new;
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(pv[0][0], pv[0][1]);
+    pa[1] = 0u;
+    pa[2] = pack_bf16x2(pv[1][0], pv[1][1]);
+    pa[3] = 0u;
+    // ---- O = O * alpha + P V
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      const int unit = ((np & 3) << 1) + v_unit;
+      uint32_t vb[4];
+      ldmatrix_x4_trans(vbase + (np >> 2) * S::TILE + v_tok * 128 + ((unit ^ (v_tok & 7)) << 4), vb);
+      o[2 * np][0] *= alpha;
+      o[2 * np][1] *= alpha;
+      o[2 * np + 1][0] *= alpha;
+      o[2 * np + 1][1] *= alpha;
+      mma_bf16_16816(o[2 * np], pa, vb[0], vb[1]);
+      mma_bf16_16816(o[2 * np + 1], pa, vb[2], vb[3]);
+    }
+    __syncwarp();
+    if (lane == 0 && i + PD_STAGES < my_pages) issue(i + PD_STAGES);
+  }
+
+  // ---- publish the warp's state (rows 0..G-1), merge warps, then splits
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (t == 0) {
+    s_m[warp * 8 + r] = ok ? m_run : -INFINITY;   // a warp that gave up contributes nothing
+    s_l[warp * 8 + r] = l_run;
+  }
+  if (ok) {   // every load this warp issued has landed and been consumed
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      *reinterpret_cast<float2*>(&w_acc[r * D + n * 8 + 2 * t]) = make_float2(o[n][0], o[n][1]);
   }
   __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx % D;
-    const float* base = scratch + ((long long)b * heads + hkv * G + g) * splits * stride;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, base[s * stride + D]);
-    float L = 0.f, A = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = base[s * stride + D];
-      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-      L += w * base[s * stride + D + 1];
-      A += w * base[s * stride + d];
-    }
-    out[((long long)b * heads + hkv * G + g) * D + d] = __float2bfloat16(L > 0.f ? A / L : 0.f);
-  }
+  merge_and_finish<D>(s_m, s_l, reinterpret_cast<const float*>(smem), S::WARP_BYTES / 4, 4, 8, G, s_last, scratch, counters, out, b, hkv, split, heads, kv_heads,
+                      splits);
 }
 
 // One warp per output row; x staged in shared memory as fp32.
@@ -209,14 +435,40 @@ void kv_append(const void* k, const void* v, void* k_cache, void* v_cache, const
 
 void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                        const int* context_lens, void* out, float* scratch, int* counters, int batch, int heads,
-                       int kv_heads, int head_dim, int page_size, int max_pages, int splits, float scale,
-                       cudaStream_t stream) {
+                       int kv_heads, int head_dim, int page_size, int max_pages, int cache_pages, int splits,
+                       float scale, int* status, cudaStream_t stream) {
   MB_REQUIRE(heads % kv_heads == 0, "paged_attn_decode: heads must be a multiple of kv_heads");
-  MB_REQUIRE(splits >= 1, "paged_attn_decode: need at least one split");
+  MB_REQUIRE(splits >= 1, "paged_attn_decode: splits must be positive");
   if (batch == 0) return;
   const int G = heads / kv_heads;
   const dim3 grid(batch, kv_heads, splits);
   const float sl2 = scale * 1.4426950408889634f;
+  if (page_size == 16 && G <= 8 && (head_dim == 64 || head_dim == 128)) {
+    // K / V cache as [cache_pages * 16 tokens, kv_heads * head_dim]; one box = 16 tokens x 64 dims
+    uint64_t dims[2] = {(uint64_t)kv_heads * head_dim, (uint64_t)cache_pages * 16};
+    uint64_t strides[1] = {(uint64_t)kv_heads * head_dim * 2};
+    uint32_t box[2] = {64, 16};
+    const CUtensorMap tk = make_tensor_map(k_cache, TmaDType::BF16, 2, dims, strides, box, true);
+    const CUtensorMap tv = make_tensor_map(v_cache, TmaDType::BF16, 2, dims, strides, box, true);
+#define MB_PDM(DD)                                                                                                 \
+  do {                                                                                                             \
+    static bool configured = false;                                                                                \
+    if (!configured) {                                                                                             \
+      MB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_mma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         PdSmem<DD>::BYTES));                                                      \
+      configured = true;                                                                                           \
+    }                                                                                                              \
+    paged_decode_mma_kernel<DD><<<grid, 128, PdSmem<DD>::BYTES, stream>>>(                                         \
+        tk, tv, (const __nv_bfloat16*)q, block_table, context_lens, (__nv_bfloat16*)out, scratch, counters, heads, \
+        kv_heads, G, max_pages, splits, sl2, status);                                                              \
+  } while (0)
+    if (head_dim == 128) MB_PDM(128);
+    else MB_PDM(64);
+#undef MB_PDM
+    count_launch();
+    check_launch();
+    return;
+  }
 #define MB_PD(GG, DD)                                                                                         \
   paged_decode_kernel<GG, DD><<<grid, 128, 0, stream>>>(                                                      \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,     \
@@ -225,12 +477,12 @@ void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
     if (G == 1) MB_PD(1, 128);
     else if (G == 2) MB_PD(2, 128);
     else if (G == 4) MB_PD(4, 128);
-    else MB_REQUIRE(false, "paged_attn_decode: GQA group must be 1, 2 or 4");
+    else MB_REQUIRE(false, "paged_attn_decode: GQA group must be 1, 2 or 4 for this page size");
   } else if (head_dim == 64) {
     if (G == 1) MB_PD(1, 64);
     else if (G == 2) MB_PD(2, 64);
     else if (G == 4) MB_PD(4, 64);
-    else MB_REQUIRE(false, "paged_attn_decode: GQA group must be 1, 2 or 4");
+    else MB_REQUIRE(false, "paged_attn_decode: GQA group must be 1, 2 or 4 for this page size");
   } else {
     MB_REQUIRE(false, "paged_attn_decode: head_dim must be 64 or 128");
   }

@@ -15,9 +15,11 @@ namespace mb {
 namespace {
 
 // ------------------------------------------------------------------------------ RoPE
-// One thread per (token, 8-wide group of pairs); loops over heads so each cos/sin is computed once.
+// One thread per (token, 8-wide group of pairs) loops over a chunk of heads (blockIdx.y picks the
+// chunk), so each cos/sin is computed once per chunk; few-token launches (decode) use many chunks.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict__ pos, int tokens, int heads,
-                            int head_dim, long long token_stride, float log2_theta, int inverse) {
+                            int heads_per_chunk, int head_dim, long long token_stride, float log2_theta,
+                            int inverse) {
   const int half = head_dim >> 1;
   const int groups = half >> 3;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -33,7 +35,9 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
     if (inverse) sn[i] = -sn[i];
   }
   __nv_bfloat16* base = x + (long long)t * token_stride;
-  for (int h = 0; h < heads; ++h) {
+  const int h_begin = blockIdx.y * heads_per_chunk;
+  const int h_end = min(heads, h_begin + heads_per_chunk);
+  for (int h = h_begin; h < h_end; ++h) {
     __nv_bfloat16* hp = base + (long long)h * head_dim;
     float a[8], b[8];
     unpack8(ldg8(hp, g * 8), a);
@@ -262,8 +266,14 @@ void rope_apply(void* x, const int* pos, int tokens, int heads, int head_dim, lo
   MB_REQUIRE(token_stride % 8 == 0, "rope: token stride must be a multiple of 8 elements");
   if (tokens == 0) return;
   const long long work = (long long)tokens * (head_dim / 16);
-  rope_kernel<<<ceil_div(work, 128), 128, 0, stream>>>((__nv_bfloat16*)x, pos, tokens, heads, head_dim, token_stride,
-                                                       log2f(theta), inverse ? 1 : 0);
+  // enough head chunks to put about two waves of threads on the machine
+  long long chunks = ((long long)sm_count() * 2048 + work - 1) / work;
+  if (chunks > heads) chunks = heads;
+  if (chunks < 1) chunks = 1;
+  const int hpc = (int)((heads + chunks - 1) / chunks);
+  const dim3 grid((unsigned)ceil_div(work, 128), (unsigned)((heads + hpc - 1) / hpc));
+  rope_kernel<<<grid, 128, 0, stream>>>((__nv_bfloat16*)x, pos, tokens, heads, hpc, head_dim, token_stride,
+                                        log2f(theta), inverse ? 1 : 0);
   count_launch();
   check_launch();
 }

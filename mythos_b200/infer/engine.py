@@ -27,7 +27,7 @@ from ..models.config import TransformerConfig
 from ..ops import functional as F
 from ..ops import native
 from .kv_paged import PagedKVCache
-from .quant_weights import QuantLinear
+from .quant_weights import QuantLinear, reserve_accumulator
 from .sampler import SamplerConfig, sample
 
 
@@ -181,9 +181,8 @@ class InferenceEngine:
             q = qkv[:, : H * D].unflatten(-1, (H, D))
             k = qkv[:, H * D:(H + Hkv) * D].unflatten(-1, (Hkv, D))
             v = qkv[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
-            if cfg.rope_theta > 0:
-                C.rope(q, pos, cfg.rope_theta, False)
-                C.rope(k, pos, cfg.rope_theta, False)
+            if cfg.rope_theta > 0:   # q and k heads are adjacent in the fused projection: one launch
+                C.rope(qkv[:, : (H + Hkv) * D].unflatten(-1, (H + Hkv, D)), pos, cfg.rope_theta, False)
             C.kv_append(k, v, self.cache.k[li], self.cache.v[li], table, pos, seq_ids)
             if prefill_shape is not None:
                 B, S = prefill_shape
@@ -197,7 +196,8 @@ class InferenceEngine:
             else:
                 o = torch.empty(T, H, D, device=self.device, dtype=torch.bfloat16)
                 C.paged_attn_decode(q.contiguous(), self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
-                                    self._scratch, self._counters, self._splits, scale)
+                                    self._scratch, self._counters, self._splits, scale,
+                                    native.status_word(self.device))
                 o = o.view(T, H * D)
             a = self._row_parallel(L.o, o)
             n, stream = F.rmsnorm(a, L.ffn_norm, cfg.norm_eps, stream)
@@ -221,8 +221,11 @@ class InferenceEngine:
         return _gather_columns(lg, self.tp)
 
     def _prepare_decode_scratch(self, batch: int, max_ctx: int):
-        splits = max(1, min(32, (2 * self._sms) // max(1, batch * self.hkv_local), (max_ctx + 255) // 256))
+        pairs = max(1, batch * self.hkv_local)
+        splits = max(1, min(32, (6 * self._sms + pairs - 1) // pairs, (max_ctx + 255) // 256))
         self._splits = splits
+        widest = max([self.head.N] + [max(L.qkv.N, L.o.N, L.up.N, L.down.N) for L in self.layers])
+        reserve_accumulator(self.device, min(batch, 256) * widest)
         need = batch * self.h_local * splits * (self.cfg.head_dim + 2)
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, device=self.device, dtype=torch.float32)

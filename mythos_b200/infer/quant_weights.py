@@ -21,6 +21,26 @@ from ..ops import native, reference as ref
 QFMT = {"oil8": 3, "oil4": 2, "i2s": 1}
 DECODE_MAX_TOKENS = 256
 
+# fp32 split-K accumulators, one per device, kept all-zero between uses (the finalize kernel zeroes
+# what it reads). Grown outside CUDA-graph capture only.
+_ACC: dict = {}
+_SMS: dict = {}
+
+
+def reserve_accumulator(device, numel: int) -> None:
+    """Make the split-K accumulator of ``device`` hold at least ``numel`` floats."""
+    device = torch.device(device)
+    cur = _ACC.get(device)
+    if cur is None or cur.numel() < numel:
+        _ACC[device] = torch.zeros(numel, device=device, dtype=torch.float32)
+
+
+def _sm_count(device) -> int:
+    device = torch.device(device)
+    if device not in _SMS:
+        _SMS[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SMS[device]
+
 
 def _pack_nibbles(idx: torch.Tensor) -> torch.Tensor:
     a = idx.reshape(-1, 2)
@@ -69,6 +89,30 @@ class QuantLinear:
         packed = idx if fmt == "oil8" else _pack_nibbles(idx)
         return cls(fmt, N, K, block_size, packed.contiguous(), codebooks=codebooks.to(torch.bfloat16).contiguous(),
                    cb_map=cb_map)
+
+    @classmethod
+    def random(cls, fmt: str, N: int, K: int, block_size: int = 256, codebook_group: int = 128, device="cuda",
+               generator=None, std: float = 0.02) -> "QuantLinear":
+        """Synthetic weights directly in storage format: N(0, std) quantile codebooks with uniform
+        random indices (OIL8 / OIL4), trits drawn with p = (0.25, 0.5, 0.25) and an absmean-like
+        scale per block (I2_S). No fp32 matrix is ever materialised."""
+        n = N * K
+        nb = n // block_size
+        dev = torch.device(device)
+        if fmt == "i2s":
+            u = torch.rand(n, device=dev, generator=generator)
+            codes = (u >= 0.25).to(torch.uint8) + (u >= 0.75).to(torch.uint8)      # 0: -1, 1: 0, 2: +1
+            scales = torch.full((nb,), std * 0.8, device=dev, dtype=torch.float32)
+            return cls(fmt, N, K, block_size, _pack_trits(codes), scales=scales)
+        size = 256 if fmt == "oil8" else 16
+        g = max(1, codebook_group)
+        n_cb = (nb + g - 1) // g
+        base = cbk.quantile_codebook(size, std, fp16=(fmt == "oil4")).to(dev)
+        codebooks = base[None].repeat(n_cb, 1).to(torch.bfloat16).contiguous()
+        cb_map = (torch.arange(nb, device=dev) // g).to(torch.int32) if g > 1 else None
+        idx = torch.randint(0, size, (n,), device=dev, generator=generator, dtype=torch.uint8)
+        packed = idx if fmt == "oil8" else _pack_nibbles(idx)
+        return cls(fmt, N, K, block_size, packed.contiguous(), codebooks=codebooks, cb_map=cb_map)
 
     @classmethod
     def from_oil_linear(cls, mod, rows: slice | None = None) -> "QuantLinear":
@@ -143,6 +187,19 @@ class QuantLinear:
         if M <= DECODE_MAX_TOKENS:
             if out is None:
                 out = torch.empty(M, self.N, device=x.device, dtype=torch.bfloat16)
+            # One CTA covers 128 output features. Too few of them to fill the GPU (narrow or
+            # tensor-parallel layers): split K across CTAs into the fp32 accumulator instead.
+            n_ctas = (self.N + 127) // 128
+            if n_ctas * 4 < 3 * _sm_count(x.device) and self.K >= 1024 and out.is_contiguous():
+                if not torch.cuda.is_current_stream_capturing():
+                    reserve_accumulator(x.device, M * self.N)
+                acc = _ACC.get(x.device)
+                if acc is not None and acc.numel() >= M * self.N:
+                    acc = acc[: M * self.N].view(M, self.N)
+                    C.dequant_gemm(x, self.packed, self.codebooks, self.cb_map, self.scales, QFMT[self.fmt], self.N,
+                                   self.K, self.block_size, acc, [], k_splits, st)
+                    C.finalize_acc(acc, None, out)
+                    return out
             C.dequant_gemm(x, self.packed, self.codebooks, self.cb_map, self.scales, QFMT[self.fmt], self.N, self.K,
                            self.block_size, out, [], 1, st)
             return out

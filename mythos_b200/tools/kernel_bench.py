@@ -52,6 +52,41 @@ class Timer:
         return times[len(times) // 2]
 
 
+def graph_time(t: Timer, fn) -> float:
+    """Median milliseconds of ``fn`` alone for launches of a few microseconds, where eager timing
+    would measure the CPU launch path: replay a CUDA graph of [L2 flush, fn] and subtract the
+    replay time of a graph holding only the flush."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(1, t.warmup)):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    buf = t.buf if t.buf is not None else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    g_full, g_flush = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_full):
+        buf.zero_()
+        fn()
+    with torch.cuda.graph(g_flush):
+        buf.zero_()
+
+    def med(g):
+        times = []
+        for _ in range(t.warmup + t.iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        times = sorted(times[t.warmup:])
+        return times[len(times) // 2]
+
+    return max(1e-6, med(g_full) - med(g_flush))
+
+
 def bench_gemm(t: Timer, M, N, K, layout="kk", epi=0):
     from mythos_b200.ops import functional as F
 
@@ -124,6 +159,42 @@ def bench_memory_bound(t: Timer, name: str, rows: int, dim: int):
     return ms, nbytes / ms / 1e6, "GB/s"
 
 
+def bench_dequant_gemm(t: Timer, fmt: str, M: int, N: int, K: int, group: int = 128):
+    """Decode-shaped GEMM over packed weights; reported as packed weight bytes per second."""
+    from mythos_b200.infer.quant_weights import QuantLinear
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = QuantLinear.random(fmt, N, K, 256, group, device="cuda", generator=g)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    q.matmul(x, out=out)   # sizes the split-K accumulator outside graph capture
+    ms = graph_time(t, lambda: q.matmul(x, out=out))
+    return ms, q.packed.numel() / ms / 1e6, "GB/s"
+
+
+def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int):
+    """Split-KV decode attention over 16-token pages; reported as KV bytes per second."""
+    from mythos_b200.ops import native
+
+    C = native.require()
+    pages_per_seq = (ctx + 15) // 16
+    n_pages = B * pages_per_seq
+    kc = (torch.randn(n_pages, 16, Hkv, D, device="cuda") * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(n_pages, 16, Hkv, D, device="cuda") * 0.5).to(torch.bfloat16)
+    table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(B, pages_per_seq)
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    q = torch.randn(B, H, D, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    splits = max(1, min(32, (6 * sms + B * Hkv - 1) // (B * Hkv), (ctx + 255) // 256))
+    scratch = torch.empty(B * H * splits * (D + 2), device="cuda")
+    counters = torch.zeros(B * Hkv + 64, device="cuda", dtype=torch.int32)
+    st = native.status_word("cuda")
+    ms = graph_time(t, lambda: C.paged_attn_decode(q, kc, vc, table, lens, out, scratch, counters, splits,
+                                                   D ** -0.5, st))
+    return ms, 2.0 * B * ctx * Hkv * D * 2 / ms / 1e6, "GB/s"
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--kernel", default="all")
@@ -142,6 +213,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--fmt", default="oil8", choices=["oil8", "oil4", "i2s"])
+    ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 single-CTA kernel, 2 paired-SM kernel")
     args = ap.parse_args()
     from mythos_b200.ops import native
@@ -178,6 +251,18 @@ def main():
     if k in ("attn_bwd", "all"):
         report(f"attn_bwd_b{args.batch}_s{args.seq}_h{args.heads}_d128",
                bench_attn(t, args.batch, args.seq, args.heads, hkv, 128, True))
+    if k == "dequant_gemm":
+        report(f"dequant_gemm_{args.fmt}_{args.m}x{args.n}x{args.k}", bench_dequant_gemm(t, args.fmt, args.m, args.n, args.k))
+    if k == "all":
+        for fmt, M, N, K in [("oil8", 64, 28672, 4096), ("oil8", 64, 4096, 14336), ("oil4", 64, 6144, 4096),
+                             ("oil4", 64, 4096, 4096), ("i2s", 8, 6912, 2560), ("oil8", 64, 128256, 4096)]:
+            report(f"dequant_gemm_{fmt}_{M}x{N}x{K}", bench_dequant_gemm(t, fmt, M, N, K))
+    if k == "paged_decode":
+        report(f"paged_decode_b{args.batch}_ctx{args.ctx}_h{args.heads}_kv{hkv}_d{args.head_dim}",
+               bench_paged_decode(t, args.batch, args.ctx, args.heads, hkv, args.head_dim))
+    if k == "all":
+        for B, ctx, H, Hkv in [(64, 1024, 32, 8), (64, 1024, 4, 1), (8, 32768, 20, 20)]:
+            report(f"paged_decode_b{B}_ctx{ctx}_h{H}_kv{Hkv}_d128", bench_paged_decode(t, B, ctx, H, Hkv, 128))
     for name, r, d in [("rmsnorm", args.rows, args.dim), ("swiglu", args.rows, 11008), ("ce", 4096, 32000),
                        ("adamw", 16384, 4096), ("fake_quant", 16384, 4096)]:
         if k in (name, "all"):

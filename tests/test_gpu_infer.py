@@ -51,6 +51,25 @@ def test_dequant_gemm_matches_dequantised_matmul(fmt, M, group):
         _close(a, x.float() @ deq.t(), atol=1e-2)
 
 
+@pytest.mark.parametrize("fmt", ["oil8", "oil4", "i2s"])
+@pytest.mark.parametrize("M,N,K,bs,group", [(8, 512, 4096, 256, 128), (64, 1000, 2048, 64, 16), (130, 256, 1024, 128, 1),
+                                            (256, 384, 1536, 256, 7)])
+def test_dequant_gemm_deep_k_and_block_sizes(fmt, M, N, K, bs, group):
+    """Narrow, deep layers (automatic split-K through the fp32 accumulator), ragged N, every
+    supported quantisation block size, codebook windows that move along K."""
+    from mythos_b200.infer.quant_weights import QuantLinear
+
+    torch.manual_seed(N + K)
+    w = torch.randn(N, K, device="cuda") * 0.02
+    q = QuantLinear.from_float(w, fmt, block_size=bs, codebook_group=group)
+    deq = q.dequantize().float()
+    assert torch.equal(deq, q._dequantize_reference().float().to(torch.bfloat16).float())
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    ref = x.float() @ deq.t()
+    _close(q.matmul(x), ref, atol=2e-2)
+    _close(q.matmul(x), ref, atol=2e-2)   # the accumulator was left zeroed by the first call
+
+
 def test_quantisation_error_is_small_and_gemv_matches():
     from mythos_b200.infer.quant_weights import QuantLinear
     from mythos_b200.ops import native
@@ -67,17 +86,20 @@ def test_quantisation_error_is_small_and_gemv_matches():
     _close(y, qi.dequantize().float() @ x.float(), atol=5e-3)
 
 
-@pytest.mark.parametrize("H,Hkv,D", [(4, 4, 128), (8, 2, 128), (4, 2, 64)])
-def test_paged_decode_attention(H, Hkv, D):
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 128, 16), (8, 2, 128, 16), (4, 2, 64, 16), (32, 8, 128, 16),
+                                          (8, 1, 64, 16), (8, 2, 128, 8), (4, 2, 64, 32)])
+def test_paged_decode_attention(H, Hkv, D, page):
+    """16-token pages run the tensor-core kernel, other page sizes the scalar one. The cache starts
+    out holding stale finite values, so tokens past a sequence's length must be masked, not read."""
     from mythos_b200.ops import native, reference as ref
 
     C = native.require()
     torch.manual_seed(H * 7 + D)
-    B, page, max_pages = 3, 16, 24
+    B, max_pages = 3, 384 // page
     lens = [37, 200, 1]
     n_pages = B * max_pages
-    kc = torch.zeros(n_pages, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
-    vc = torch.zeros_like(kc)
+    kc = (torch.randn(n_pages, page, Hkv, D, device="cuda") * 4).to(torch.bfloat16)
+    vc = (torch.randn(n_pages, page, Hkv, D, device="cuda") * 4).to(torch.bfloat16)
     perm = torch.randperm(n_pages)[: B * max_pages].reshape(B, max_pages).to(torch.int32)
     table = perm.cuda()
     ks, vs = [], []
@@ -95,7 +117,8 @@ def test_paged_decode_attention(H, Hkv, D):
         out = torch.empty(B, H, D, device="cuda", dtype=torch.bfloat16)
         scratch = torch.empty(B * H * splits * (D + 2), device="cuda")
         counters = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
-        C.paged_attn_decode(q, kc, vc, table, ctx, out, scratch, counters, splits, 1.0 / math.sqrt(D))
+        C.paged_attn_decode(q, kc, vc, table, ctx, out, scratch, counters, splits, 1.0 / math.sqrt(D),
+                            native.status_word("cuda"))
         for b in range(B):
             o, _ = ref.attention(q[b][None, None], ks[b][None], vs[b][None], causal=False)
             _close(out[b], o[0, 0], atol=2e-2)
