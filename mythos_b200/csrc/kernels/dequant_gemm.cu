@@ -311,7 +311,6 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_cons
         uint4 r[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) r[j] = *reinterpret_cast<const uint4*>(raw + trow[j] * RB + q * 16);
-        mbar_arrive(&raw_empty[rs]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           if (!row_ok[j]) {
@@ -326,7 +325,6 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_cons
         uint2 r[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) r[j] = *reinterpret_cast<const uint2*>(raw + trow[j] * RB + q * 8);
-        mbar_arrive(&raw_empty[rs]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const uint32_t words[2] = {r[j].x, r[j].y};
@@ -351,7 +349,6 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_cons
         uint32_t r[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) r[j] = *reinterpret_cast<const uint32_t*>(raw + trow[j] * RB + q * 4);
-        mbar_arrive(&raw_empty[rs]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           uint32_t o[8];
@@ -365,6 +362,11 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_cons
           vals[j][1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
+
+      // The raw stage is released only here, after the look-ups consumed the index registers: an
+      // arrive issued right behind the shared loads does not wait for them, and the refill of the
+      // stage by TMA could overtake the tail of a wide load.
+      mbar_arrive_after(&raw_empty[rs], vals[0][0].x ^ vals[0][1].w ^ vals[1][0].x ^ vals[1][1].w);
 
       // ---- publish the bf16 tile
       ok = mbar_wait(&ab_empty[st], sph ^ 1, abort_flag, status, 65);
@@ -506,7 +508,9 @@ void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, 
   if (k_splits <= 0) {
     k_splits = 1;
     if (out_bf16 == nullptr) {
-      const int want = (sm_count() + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
+      // decode-sized tiles run two CTAs per SM: aim for two full CTAs per SM, else one
+      const int target = sm_count() * (mt <= 64 ? 2 : 1);
+      const int want = (target + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
       k_splits = want < 1 ? 1 : want;
       if (k_splits > kblocks / 4) k_splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
     }

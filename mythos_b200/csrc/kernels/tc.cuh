@@ -43,6 +43,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrive that is ordered after the production of `dep`: the value is an (unused) operand of the
+// instruction, so every load it was computed from has returned before the arrive issues. Use it to
+// release a shared-memory stage that was read with plain loads.
+__device__ __forceinline__ void mbar_arrive_after(uint64_t* bar, uint32_t dep) {
+  asm volatile("{\n.reg .b32 t;\nmov.b32 t, %1;\nmbarrier.arrive.shared::cta.b64 _, [%0];\n}"
+               ::"r"(smem_u32(bar)), "r"(dep) : "memory");
+}
 // One try: the thread may be suspended by the hardware for up to MB_TRY_WAIT_NS until the phase
 // completes, so a waiting warp does not compete for issue slots with the warps doing the work.
 #ifndef MB_TRY_WAIT_NS

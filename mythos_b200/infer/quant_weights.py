@@ -190,7 +190,7 @@ class QuantLinear:
             # One CTA covers 128 output features. Too few of them to fill the GPU (narrow or
             # tensor-parallel layers): split K across CTAs into the fp32 accumulator instead.
             n_ctas = (self.N + 127) // 128
-            if n_ctas * 4 < 3 * _sm_count(x.device) and self.K >= 1024 and out.is_contiguous():
+            if n_ctas * 2 < 3 * _sm_count(x.device) and self.K >= 1024 and out.is_contiguous():
                 if not torch.cuda.is_current_stream_capturing():
                     reserve_accumulator(x.device, M * self.N)
                 acc = _ACC.get(x.device)
