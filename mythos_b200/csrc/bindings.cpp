@@ -422,7 +422,8 @@ mb::DequantWeights to_weights(const Tensor& packed, const OptTensor& codebooks, 
 // accumulators of all ranks (fused all-reduce), in which case `out` is ignored.
 void dequant_gemm(const Tensor& x, const Tensor& packed, const OptTensor& codebooks, const OptTensor& cb_map,
                   const OptTensor& scales, int64_t fmt, int64_t N, int64_t K, int64_t block_size, OptTensor out,
-                  const std::vector<int64_t>& peer_ptrs, int64_t k_splits, const OptTensor& status) {
+                  const std::vector<int64_t>& peer_ptrs, int64_t k_splits, const OptTensor& status,
+                  int64_t peer_bf16_offset) {
   chk(x, BF16, "x");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.size(1) == K, "dequant_gemm: x must be [M, K]");
   const auto w = to_weights(packed, codebooks, cb_map, scales, fmt, N, K, block_size);
@@ -443,7 +444,27 @@ void dequant_gemm(const Tensor& x, const Tensor& packed, const OptTensor& codebo
   const mb::PeerPtrs pp = to_peers(peer_ptrs);
   c10::cuda::CUDAGuard guard(x.device());
   mb::dequant_gemm(x.data_ptr(), x.stride(0), (int)x.size(0), w, o16, o32, peer_ptrs.empty() ? nullptr : &pp,
-                   (int)peer_ptrs.size(), ld, (int)k_splits, status_ptr(status), cur_stream());
+                   (int)peer_ptrs.size(), ld, (int)k_splits, status_ptr(status), cur_stream(), peer_bf16_offset);
+}
+
+void tp_push(Tensor& acc, const std::vector<int64_t>& ptrs, int64_t rank, int64_t slot_off) {
+  chk_c(acc, F32, "acc");
+  c10::cuda::CUDAGuard guard(acc.device());
+  mb::tp_push(acc.data_ptr<float>(), to_peers(ptrs), (int)ptrs.size(), (int)rank, slot_off, acc.numel(), cur_stream());
+}
+void tp_reduce_slots(const Tensor& staging, int64_t slots, int64_t slot_stride, const OptTensor& residual, Tensor& out) {
+  chk_c(staging, BF16, "staging");
+  chk_c(out, BF16, "out");
+  TORCH_CHECK(staging.numel() >= (slots - 1) * slot_stride + out.numel(), "tp_reduce_slots: staging too small");
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::tp_reduce_slots(staging.data_ptr(), (int)slots, slot_stride, cptr(residual), out.data_ptr(), out.numel(),
+                      cur_stream());
+}
+// part_ptrs / out_ptrs: every rank's partial and output buffer; n elements of each take part.
+void tp_allreduce_pull(const std::vector<int64_t>& part_ptrs, const std::vector<int64_t>& out_ptrs, int64_t rank,
+                       int64_t n) {
+  TORCH_CHECK(part_ptrs.size() == out_ptrs.size(), "tp_allreduce_pull: peer lists differ in length");
+  mb::tp_allreduce_pull(to_peers(part_ptrs), to_peers(out_ptrs), (int)part_ptrs.size(), (int)rank, n, cur_stream());
 }
 
 void finalize_acc(Tensor& acc, const OptTensor& residual, Tensor& out) {
@@ -492,7 +513,9 @@ void kv_append(const Tensor& k, const Tensor& v, Tensor& k_cache, Tensor& v_cach
 void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
                        const Tensor& context_lens, Tensor& out, Tensor& scratch, Tensor& counters, int64_t splits,
                        double scale, const OptTensor& status) {
-  chk_c(q, BF16, "q");
+  chk(q, BF16, "q");
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2),
+              "paged_attn_decode: q must be [batch, heads, head_dim] with contiguous heads");
   chk_c(k_cache, BF16, "k_cache");
   chk_c(v_cache, BF16, "v_cache");
   chk_c(block_table, I32, "block_table");
@@ -508,7 +531,7 @@ void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                         context_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(),
                         counters.data_ptr<int>(), (int)B, (int)H, (int)Hkv, (int)D, (int)k_cache.size(1),
                         (int)block_table.size(1), (int)k_cache.size(0), (int)splits, (float)scale,
-                        status_ptr(status), cur_stream());
+                        status_ptr(status), cur_stream(), q.stride(0));
 }
 
 void sample_tokens(const Tensor& logits, const OptTensor& history, const OptTensor& allow_mask, double temperature,
@@ -613,7 +636,12 @@ PYBIND11_MODULE(_C, m) {
   m.def("oil_codebook_stats", &oil_codebook_stats);
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("flash_attn_bwd", &flash_attn_bwd);
-  m.def("dequant_gemm", &dequant_gemm);
+  m.def("dequant_gemm", &dequant_gemm, py::arg("x"), py::arg("packed"), py::arg("codebooks"), py::arg("cb_map"),
+        py::arg("scales"), py::arg("fmt"), py::arg("N"), py::arg("K"), py::arg("block_size"), py::arg("out"),
+        py::arg("peer_ptrs"), py::arg("k_splits"), py::arg("status"), py::arg("peer_bf16_offset") = -1);
+  m.def("tp_push", &tp_push);
+  m.def("tp_reduce_slots", &tp_reduce_slots);
+  m.def("tp_allreduce_pull", &tp_allreduce_pull);
   m.def("finalize_acc", &finalize_acc);
   m.def("dequant_to_bf16", &dequant_to_bf16);
   m.def("i2s_gemv", &i2s_gemv);

@@ -137,6 +137,13 @@ void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream);
 // dst_r[i] += part[i] on every rank r (fp32 peer reductions).
 void peer_add_f32(const float* part, const PeerPtrs& dst, int n_peers, long long n, cudaStream_t stream);
 // Column all-gather by peer stores: dst_r[b, rank*cols + j] = src[b, j] on every rank r.
+// Tensor-parallel all-reduce building blocks (bf16 activations, see comm.cu).
+void tp_push(float* acc, const PeerPtrs& dst, int n_peers, int rank, long long slot_off, long long n,
+             cudaStream_t stream);
+void tp_reduce_slots(const void* staging, int slots, long long slot_stride, const void* residual, void* out,
+                     long long n, cudaStream_t stream);
+void tp_allreduce_pull(const PeerPtrs& part, const PeerPtrs& out, int n_peers, int rank, long long n,
+                       cudaStream_t stream);
 void peer_gather_cols(const void* src, const PeerPtrs& dst, int n_peers, int rank, long long rows, int cols,
                       cudaStream_t stream);
 
@@ -154,7 +161,8 @@ struct DequantWeights {
 // out_f32 / into every buffer of `peers` (fused all-reduce; buffers must hold zeros or a residual).
 // k_splits <= 0 picks enough splits to fill the GPU.
 void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, void* out_bf16, float* out_f32,
-                  const PeerPtrs* peers, int n_peers, long long ld_out, int k_splits, int* status, cudaStream_t stream);
+                  const PeerPtrs* peers, int n_peers, long long ld_out, int k_splits, int* status, cudaStream_t stream,
+                  long long peer_bf16_offset = -1);
 // out = bf16(acc (+ residual)); acc is reset to zero for its next accumulation.
 void finalize_acc(float* acc, const void* residual, void* out, long long n, cudaStream_t stream);
 // Whole-matrix dequantisation into a bf16 scratch buffer (prefill path).
@@ -171,7 +179,7 @@ void kv_append(const void* k, const void* v, void* k_cache, void* v_cache, const
 void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                        const int* context_lens, void* out, float* scratch, int* counters, int batch, int heads,
                        int kv_heads, int head_dim, int page_size, int max_pages, int cache_pages, int splits,
-                       float scale, int* status, cudaStream_t stream);
+                       float scale, int* status, cudaStream_t stream, long long q_tok_stride = 0);
 // Greedy / temperature / top-k / top-p / repetition-penalty sampling of one token per row.
 struct SamplerArgs {
   float temperature, top_p, repetition_penalty;

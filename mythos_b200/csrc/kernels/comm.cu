@@ -239,6 +239,91 @@ __global__ void peer_gather_cols_kernel(const __nv_bfloat16* __restrict__ src, P
   }
 }
 
+
+// ---- tensor-parallel all-reduce of bf16 activations over peer memory
+//
+// One-shot (few tokens, latency bound): every rank stores its partial into slot `rank` of every
+// peer's staging buffer (tp_push_kernel, or the dequant-GEMM epilogue directly), one barrier, then
+// every rank sums the W slots of its own staging buffer (tp_reduce_slots_kernel). One NVLink hop.
+//
+// Two-shot (prefill-sized, bandwidth bound): after a barrier every rank pulls ITS slice of the
+// elements from all W partial buffers with peer loads, sums in fp32 and stores the bf16 result into
+// every peer's output buffer (tp_allreduce_pull_kernel); a second barrier publishes the result.
+// Each element crosses NVLink once in each direction per rank pair, the minimum for an all-reduce.
+
+// acc fp32 [n] (zeroed afterwards) -> bf16 -> dst_p[slot_off + i] for every peer p.
+__global__ void tp_push_kernel(float* __restrict__ acc, PeerPtrs dst, int n_peers, int rank, long long slot_off,
+                               long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float4* a = reinterpret_cast<float4*>(acc) + 2 * i;
+    const float4 lo = a[0], hi = a[1];
+    a[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    const bf16x8 v = pack8(f);
+    for (int p = 0; p < n_peers; ++p) stg8(dst.p[(rank + p) % n_peers], slot_off + i * 8, v);
+  }
+}
+
+// Loads of memory that another GPU wrote (or owns) bypass L1: a line cached by an earlier round
+// would otherwise be served stale. L2 is the coherence point for NVLink traffic.
+__device__ __forceinline__ bf16x8 ld_l2_8(const void* base, long long elem_index) {
+  const uint4 v = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem_index));
+  return *reinterpret_cast<const bf16x8*>(&v);
+}
+
+// out[i] = bf16(sum_s staging[s * slot_stride + i] (+ residual[i]))
+__global__ void tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, int slots, long long slot_stride,
+                                       const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
+                                       long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bf16x8 v[MAX_PEERS];
+#pragma unroll
+    for (int s = 0; s < MAX_PEERS; ++s)
+      if (s < slots) v[s] = ld_l2_8(staging, s * slot_stride + i * 8);   // all loads in flight before the adds
+#pragma unroll
+    for (int s = 0; s < MAX_PEERS; ++s)
+      if (s < slots) {
+        float f[8];
+        unpack8(v[s], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    if (residual) {
+      float f[8];
+      unpack8(ldg8(residual, i * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+    stg8(out, i * 8, pack8(acc));
+  }
+}
+
+// Elements [begin8, end8) (units of 8) are this rank's slice: out_p[i] = bf16(sum_q part_q[i]) for
+// every p. Partials are summed in rank order, so the value does not depend on which rank owns it.
+__global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peers, int rank, long long begin8,
+                                         long long end8) {
+  for (long long i = begin8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bf16x8 v[MAX_PEERS];
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; ++q)
+      if (q < n_peers) v[q] = ld_l2_8(part.p[q], i * 8);
+#pragma unroll
+    for (int q = 0; q < MAX_PEERS; ++q)
+      if (q < n_peers) {
+        float f[8];
+        unpack8(v[q], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    const bf16x8 r = pack8(acc);
+    for (int p = 0; p < n_peers; ++p) stg8(out.p[(rank + p) % n_peers], i * 8, r);
+  }
+}
+
 }  // namespace
 
 void peer_add_f32(const float* part, const PeerPtrs& dst, int n_peers, long long n, cudaStream_t stream) {
@@ -260,6 +345,48 @@ void peer_gather_cols(const void* src, const PeerPtrs& dst, int n_peers, int ran
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;
   peer_gather_cols_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)src, dst, n_peers, rank, rows, cols);
+  count_launch();
+  check_launch();
+}
+
+void tp_push(float* acc, const PeerPtrs& dst, int n_peers, int rank, long long slot_off, long long n,
+             cudaStream_t stream) {
+  MB_REQUIRE(n % 8 == 0 && slot_off % 8 == 0, "tp_push: counts and offsets must be multiples of 8");
+  if (n == 0) return;
+  long long g = (n / 8 + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  tp_push_kernel<<<(int)g, 256, 0, stream>>>(acc, dst, n_peers, rank, slot_off, n / 8);
+  count_launch();
+  check_launch();
+}
+
+void tp_reduce_slots(const void* staging, int slots, long long slot_stride, const void* residual, void* out,
+                     long long n, cudaStream_t stream) {
+  MB_REQUIRE(n % 8 == 0 && slot_stride % 8 == 0, "tp_reduce_slots: counts and strides must be multiples of 8");
+  if (n == 0) return;
+  long long g = (n / 8 + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  tp_reduce_slots_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)staging, slots, slot_stride,
+                                                     (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n / 8);
+  count_launch();
+  check_launch();
+}
+
+void tp_allreduce_pull(const PeerPtrs& part, const PeerPtrs& out, int n_peers, int rank, long long n,
+                       cudaStream_t stream) {
+  MB_REQUIRE(n % 8 == 0, "tp_allreduce_pull: element count must be a multiple of 8");
+  MB_REQUIRE(n_peers >= 1 && n_peers <= MAX_PEERS, "tp_allreduce_pull: bad peer count");
+  const long long n8 = n / 8;
+  const long long per = (n8 + n_peers - 1) / n_peers;
+  const long long begin = per * rank < n8 ? per * rank : n8;
+  const long long end = begin + per < n8 ? begin + per : n8;
+  if (end <= begin) return;
+  long long g = (end - begin + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  tp_allreduce_pull_kernel<<<(int)g, 256, 0, stream>>>(part, out, n_peers, rank, begin, end);
   count_launch();
   check_launch();
 }

@@ -11,17 +11,18 @@
 //          raw reads and tile writes are bank-conflict free.
 //   1 thread: tcgen05.mma A(smem) x B(smem) -> TMEM, commit frees the A/B stage.
 // The packed weights are read from HBM exactly once, which is what a decode step is bound by.
-// Look-up tables live in shared memory: OIL8 keeps up to 8 (4 in the two-CTAs-per-SM plan)
-// consecutive 256-entry codebooks per warp (its 16 rows rarely span more; wider spreads gather
+// Look-up tables live in shared memory: OIL8 keeps up to 8 consecutive 256-entry codebooks per warp (its 16 rows rarely span more; wider spreads gather
 // from global memory); OIL4 and I2_S
 // keep a private 16-entry table per thread and row, interleaved so that every lane reads its own
 // bank (OIL4: the row's codebook; I2_S: nibble -> two scaled trits).
 // Split-K CTAs fill the machine when N is small (tensor-parallel shards) and combine with fp32
 // reductions.
 //
-// Fused collective: with `peers` set, every CTA adds its fp32 partial tile straight into the
-// accumulation buffer of EVERY rank (peer red.add over NVLink), so a row-parallel projection
-// leaves the all-reduced result on all ranks without a separate collective.
+// Fused collective: with `peers` set, the epilogue writes over NVLink instead of to local memory.
+// Either every CTA adds its fp32 partial tile into the accumulation buffer of EVERY rank (peer
+// red.add), or (peer_bf16_offset >= 0, single K split) it stores the bf16 tile into this rank's
+// slot of every rank's staging buffer, the first half of a one-shot all-reduce whose second half
+// is a local sum over the slots after one barrier.
 //
 // Semantics follow the reference reader's dequantisation (src/oil_format.cpp:434-455) followed
 // by a GEMM; the reference's own quantised "GEMMs" (src/kernel_oil8.cpp:14-71,
@@ -63,7 +64,7 @@ DqPlan dq_plan(int fmt, int mt) {
   p.raw_stage_bytes = DQ_BM * dq_raw_row_bytes(fmt);
   p.ab_stage_bytes = DQ_BM * DQ_BK * 2 + mt * DQ_BK * 2;
   p.ab_stages = two ? 2 : (mt > 128 ? 3 : DQ_MAX_AB);
-  p.cb_slots = two ? 4 : 8;
+  p.cb_slots = 8;
   // look-up tables: OIL8 8 warps x slots x 512 B; OIL4 2 rows x 16 x 256 halfwords; I2_S 2 x 16 x 256 words
   const int lut = fmt == QFMT_OIL8 ? 8 * p.cb_slots * 512 : (fmt == QFMT_OIL4 ? 16384 : 32768);
   const int fixed = p.ab_stages * p.ab_stage_bytes + lut + 1024 /*barriers*/ + 1024 /*alignment*/;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(DQ_THREADS, 2)
 dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
                     DequantWeights w, DqPlan plan, int M, int mt, int k_splits,
                     __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32, PeerPtrs peers, int n_peers,
-                    long long ld_out, int* status) {
+                    long long peer_bf16_offset, long long ld_out, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem + plan.off_bar);
@@ -408,7 +409,11 @@ dequant_gemm_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_cons
             if (m < M) {
               const float val = __uint_as_float(v[j]);
               const long long off = (long long)m * ld_out + row;
-              if (n_peers > 0) {
+              if (n_peers > 0 && peer_bf16_offset >= 0) {
+                const __nv_bfloat16 b = __float2bfloat16(val);   // this rank's slot in every peer's staging buffer
+                for (int p = 0; p < n_peers; ++p)
+                  reinterpret_cast<__nv_bfloat16*>(peers.p[p])[peer_bf16_offset + off] = b;
+              } else if (n_peers > 0) {
                 for (int p = 0; p < n_peers; ++p) atomicAdd(reinterpret_cast<float*>(peers.p[p]) + off, val);
               } else if (out_f32) {
                 atomicAdd(out_f32 + off, val);
@@ -493,7 +498,8 @@ __global__ void dequant_full_kernel(DequantWeights w, __nv_bfloat16* __restrict_
 }  // namespace
 
 void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, void* out_bf16, float* out_f32,
-                  const PeerPtrs* peers, int n_peers, long long ld_out, int k_splits, int* status, cudaStream_t stream) {
+                  const PeerPtrs* peers, int n_peers, long long ld_out, int k_splits, int* status, cudaStream_t stream,
+                  long long peer_bf16_offset) {
   MB_REQUIRE(w.K % 64 == 0, "dequant_gemm: K must be a multiple of 64");
   MB_REQUIRE(w.block_size % 64 == 0 && w.K % w.block_size == 0,
              "dequant_gemm: quantisation blocks must be multiples of 64 weights and tile the rows");
@@ -507,16 +513,16 @@ void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, 
   const int kblocks = w.K / DQ_BK;
   if (k_splits <= 0) {
     k_splits = 1;
-    if (out_bf16 == nullptr) {
-      // decode-sized tiles run two CTAs per SM: aim for two full CTAs per SM, else one
-      const int target = sm_count() * (mt <= 64 ? 2 : 1);
-      const int want = (target + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
+    if (out_bf16 == nullptr && peer_bf16_offset < 0) {
+      const int want = (sm_count() + n_tiles * m_tiles - 1) / (n_tiles * m_tiles);
       k_splits = want < 1 ? 1 : want;
       if (k_splits > kblocks / 4) k_splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
     }
   }
   if (k_splits > kblocks) k_splits = kblocks;
   MB_REQUIRE(out_bf16 == nullptr || k_splits == 1, "dequant_gemm: split-K needs the fp32 accumulate output");
+  MB_REQUIRE(peer_bf16_offset < 0 || (n_peers > 0 && k_splits == 1),
+             "dequant_gemm: bf16 peer stores need peers and a single K split");
   const DqPlan plan = dq_plan(w.fmt, mt);
   MB_REQUIRE(plan.raw_stages >= 2, "dequant_gemm: shared-memory plan has no room for the index ring");
   CUtensorMap tx, tw;
@@ -547,7 +553,8 @@ void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, 
       configured = true;                                                                                            \
     }                                                                                                               \
     dequant_gemm_kernel<F><<<grid, DQ_THREADS, plan.total, stream>>>(                                                \
-        tx, tw, w, plan, M, mt, k_splits, (__nv_bfloat16*)out_bf16, out_f32, pp, n_peers, ld_out, status);          \
+        tx, tw, w, plan, M, mt, k_splits, (__nv_bfloat16*)out_bf16, out_f32, pp, n_peers, peer_bf16_offset, ld_out,    \
+        status);          \
   } while (0)
   if (w.fmt == QFMT_OIL8) MB_DQ_LAUNCH(QFMT_OIL8);
   else if (w.fmt == QFMT_OIL4) MB_DQ_LAUNCH(QFMT_OIL4);

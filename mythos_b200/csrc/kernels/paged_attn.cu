@@ -105,7 +105,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                     const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ scratch,
                     int* __restrict__ counters, int heads, int kv_heads, int page_size, int max_pages, int splits,
-                    float scale_log2) {
+                    float scale_log2, long long q_tok_stride) {
   constexpr int LPT = D / 8;        // lanes per token (each lane holds 8 elements)
   constexpr int TPW = 32 / LPT;     // tokens per warp iteration
   constexpr int NSTATE = 4 * TPW;   // online-softmax states per CTA
@@ -123,7 +123,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   float qv[G][8], acc[G][8], m[G], l[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    unpack8(ldg8(q, ((long long)b * heads + hkv * G + g) * D + li * 8), qv[g]);
+    unpack8(ldg8(q, (long long)b * q_tok_stride + (long long)(hkv * G + g) * D + li * 8), qv[g]);
     m[g] = -INFINITY;
     l[g] = 0.f;
 #pragma unroll
@@ -236,7 +236,7 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                         const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_table,
                         const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ scratch, int* __restrict__ counters, int heads, int kv_heads, int G,
-                        int max_pages, int splits, float scale_log2, int* status) {
+                        int max_pages, int splits, float scale_log2, long long q_tok_stride, int* status) {
   using S = PdSmem<D>;
   constexpr int KS = D / 16;   // k-steps of Q K^T
   constexpr int NT = D / 8;    // n-tiles of P V
@@ -287,7 +287,7 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
   for (int ks = 0; ks < KS; ++ks) {
     qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
     if (r < G) {
-      const __nv_bfloat16* qp = q + ((long long)b * heads + hkv * G + r) * D + ks * 16 + 2 * t;
+      const __nv_bfloat16* qp = q + (long long)b * q_tok_stride + (long long)(hkv * G + r) * D + ks * 16 + 2 * t;
       qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
       qa[ks][2] = *reinterpret_cast<const uint32_t*>(qp + 8);
     }
@@ -436,7 +436,9 @@ void kv_append(const void* k, const void* v, void* k_cache, void* v_cache, const
 void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                        const int* context_lens, void* out, float* scratch, int* counters, int batch, int heads,
                        int kv_heads, int head_dim, int page_size, int max_pages, int cache_pages, int splits,
-                       float scale, int* status, cudaStream_t stream) {
+                       float scale, int* status, cudaStream_t stream, long long q_tok_stride) {
+  if (q_tok_stride <= 0) q_tok_stride = (long long)heads * head_dim;
+  MB_REQUIRE(q_tok_stride % 8 == 0, "paged_attn_decode: query token stride must be a multiple of 8 elements");
   MB_REQUIRE(heads % kv_heads == 0, "paged_attn_decode: heads must be a multiple of kv_heads");
   MB_REQUIRE(splits >= 1, "paged_attn_decode: splits must be positive");
   if (batch == 0) return;
@@ -460,7 +462,7 @@ void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
     }                                                                                                              \
     paged_decode_mma_kernel<DD><<<grid, 128, PdSmem<DD>::BYTES, stream>>>(                                         \
         tk, tv, (const __nv_bfloat16*)q, block_table, context_lens, (__nv_bfloat16*)out, scratch, counters, heads, \
-        kv_heads, G, max_pages, splits, sl2, status);                                                              \
+        kv_heads, G, max_pages, splits, sl2, q_tok_stride, status);                                                              \
   } while (0)
     if (head_dim == 128) MB_PDM(128);
     else MB_PDM(64);
@@ -472,7 +474,8 @@ void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
 #define MB_PD(GG, DD)                                                                                         \
   paged_decode_kernel<GG, DD><<<grid, 128, 0, stream>>>(                                                      \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,     \
-      context_lens, (__nv_bfloat16*)out, scratch, counters, heads, kv_heads, page_size, max_pages, splits, sl2)
+      context_lens, (__nv_bfloat16*)out, scratch, counters, heads, kv_heads, page_size, max_pages, splits, sl2,   \
+      q_tok_stride)
   if (head_dim == 128) {
     if (G == 1) MB_PD(1, 128);
     else if (G == 2) MB_PD(2, 128);

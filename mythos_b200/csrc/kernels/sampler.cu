@@ -181,6 +181,71 @@ sampler_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int vocab
   }
 }
 
+// ---- plain greedy decoding (no penalty, mask or log-probability): argmax over the row, spread
+// over several CTAs per row. Each CTA folds its chunk into one 64-bit key (order-preserving image of
+// the value in the high word, inverted index in the low word, so ties go to the smallest index),
+// atomicMax-es it into the row's slot, and the last CTA of the row writes the token and clears the
+// slot for the next launch.
+constexpr int ARGMAX_MAX_ROWS = 4096;
+static __device__ unsigned long long g_argmax_key[ARGMAX_MAX_ROWS];
+static __device__ int g_argmax_count[ARGMAX_MAX_ROWS];
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+  const uint32_t b = __float_as_uint(v);
+  const uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return ((unsigned long long)ord << 32) | (uint32_t)(0xFFFFFFFFu - (uint32_t)idx);
+}
+
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int vocab, int chunks,
+                   int* __restrict__ out_tokens) {
+  __shared__ unsigned long long s_key[8];
+  const int row = blockIdx.x, chunk = blockIdx.y, tid = threadIdx.x;
+  const __nv_bfloat16* lp = logits + (long long)row * ld;
+  const int vec = vocab >> 3;                                   // whole 8-element groups
+  const int per = (vec + chunks - 1) / chunks;
+  const int v0 = chunk * per, v1 = min(vec, v0 + per);
+  unsigned long long best = 0ull;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(lp) & 15) == 0);
+  for (int g = v0 + tid; g < v1; g += blockDim.x) {
+    float f[8];
+    if (aligned) {
+      unpack8(ldg8(lp, (long long)g * 8), f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __bfloat162float(lp[g * 8 + j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned long long k = argmax_key(f[j], g * 8 + j);
+      best = k > best ? k : best;
+    }
+  }
+  if (chunk == chunks - 1)                                      // ragged tail of the row
+    for (int i = vec * 8 + tid; i < vocab; i += blockDim.x) {
+      const unsigned long long k = argmax_key(__bfloat162float(lp[i]), i);
+      best = k > best ? k : best;
+    }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((tid & 31) == 0) s_key[tid >> 5] = best;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) best = s_key[w] > best ? s_key[w] : best;
+    atomicMax(&g_argmax_key[row], best);
+    __threadfence();
+    if (atomicAdd(&g_argmax_count[row], 1) == chunks - 1) {
+      __threadfence();
+      const unsigned long long k = atomicExch(&g_argmax_key[row], 0ull);
+      g_argmax_count[row] = 0;
+      out_tokens[row] = (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
+    }
+  }
+}
+
 }  // namespace
 
 void sample_tokens(const void* logits, long long ld, int rows, int vocab, const int* history, int history_len,
@@ -188,6 +253,19 @@ void sample_tokens(const void* logits, long long ld, int rows, int vocab, const 
                    cudaStream_t stream) {
   (void)scratch;
   if (rows == 0) return;
+  const bool plain_greedy = a.temperature < 1e-5f && allow_mask == nullptr && out_logprob == nullptr &&
+                            !(history_len > 0 && a.repetition_penalty != 1.f);
+  if (plain_greedy && rows <= ARGMAX_MAX_ROWS) {
+    int chunks = (2 * sm_count() + rows - 1) / rows;
+    const int max_chunks = (vocab / 8 + 2047) / 2048;          // at least 8 vectors per thread
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    argmax_rows_kernel<<<dim3(rows, chunks), 256, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, chunks,
+                                                               out_tokens);
+    count_launch();
+    check_launch();
+    return;
+  }
   const size_t smem = (size_t)((vocab + 31) / 32) * 4;
   MB_REQUIRE(smem <= 48 * 1024, "sample_tokens: vocabulary too large for the repetition bitmap");
   sampler_kernel<<<rows, SAMP_THREADS, smem, stream>>>((const __nv_bfloat16*)logits, ld, vocab, history, history_len,

@@ -48,9 +48,18 @@ class GenerationResult:
     stats: GenerationStats = field(default_factory=GenerationStats)
 
 
+ONESHOT_MAX_TOKENS = 256   # up to this many tokens a row-parallel sum takes the one-barrier path
+
+
 class TPContext:
-    """Tensor-parallel state of one rank: symmetric fp32 accumulators (double-buffered), a
-    symmetric logits buffer and a flag barrier whose epoch lives on the device."""
+    """Tensor-parallel state of one rank: the symmetric buffers of the two all-reduce paths, a
+    symmetric logits buffer and a flag barrier whose epoch lives on the device.
+
+    One-shot path (decode): ``staging[b]`` holds one bf16 slot per rank; every rank writes its
+    partial into its slot on all peers, one barrier, then sums its own slots. Two staging buffers
+    alternate, so a peer may already write the next partial while this rank still sums.
+    Two-shot path (prefill): partials sit in ``part``; after a barrier each rank pulls its slice
+    from all peers, sums and stores the result into every peer's ``out[b]``; a second barrier."""
 
     def __init__(self, group, device, max_tokens: int, hidden: int, vocab_shard: int, max_batch: int):
         import torch.distributed as dist
@@ -60,7 +69,12 @@ class TPContext:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
-        self.acc = [symm.make_buffer(max_tokens * hidden, torch.float32, device, group).zero_() for _ in range(2)]
+        self.slot_stride = ONESHOT_MAX_TOKENS * hidden
+        self.staging = [symm.make_buffer(self.world * self.slot_stride, torch.bfloat16, device, group).zero_()
+                        for _ in range(2)]
+        big = max(max_tokens, ONESHOT_MAX_TOKENS) * hidden
+        self.part = symm.make_buffer(big, torch.bfloat16, device, group)
+        self.out = [symm.make_buffer(big, torch.bfloat16, device, group) for _ in range(2)]
         self.logits = symm.make_buffer(max_batch * vocab_shard * self.world, torch.bfloat16, device, group)
         self.barrier = symm.FlagBarrier(device, group, device_epoch=True)
         self.which = 0
@@ -147,23 +161,35 @@ class InferenceEngine:
 
     # ------------------------------------------------------------------ building blocks
     def _row_parallel(self, lin: QuantLinear, x: torch.Tensor) -> torch.Tensor:
-        """x [T, K_local] @ W_shard^T, summed over ranks -> bf16 [T, d]."""
+        """x [T, K_local] @ W_shard^T, summed over ranks -> bf16 [T, d] (the all-reduce runs in this
+        framework's own kernels over peer memory)."""
         if self.tp is None:
             return lin.matmul(x)
-        tp = self.tp
-        T = x.shape[0]
-        buf = tp.acc[tp.which]
+        tp, C = self.tp, native.require()
+        T, n = x.shape[0], x.shape[0] * lin.N
+        b = tp.which
         tp.which ^= 1
-        if lin.dense is not None or T > 256:
-            # prefill-sized: local dense GEMM into fp32, then peer adds of the whole tile
-            part = F.gemm(x, lin.dequantize(), epi=F.EPI_F32)
-            _peer_add(part, buf.ptrs)
-        else:
-            lin.matmul(x, peer_ptrs=buf.ptrs)
+        if lin.dense is None and T <= ONESHOT_MAX_TOKENS:
+            stage = tp.staging[b]
+            slot_off = tp.rank * tp.slot_stride
+            if lin.K // 64 <= 16:
+                # short reduction: one K split, the GEMM epilogue stores straight into the peers' slots
+                lin.matmul(x, peer_ptrs=stage.ptrs, k_splits=1, peer_bf16_offset=slot_off)
+            else:
+                # split-K into the local fp32 accumulator, then one kernel converts and pushes it
+                acc = lin.matmul_acc(x)
+                C.tp_push(acc, stage.ptrs, tp.rank, slot_off)
+            tp.barrier.sync()
+            out = torch.empty(T, lin.N, device=x.device, dtype=torch.bfloat16)
+            C.tp_reduce_slots(stage.tensor, tp.world, tp.slot_stride, None, out)
+            return out
+        # prefill-sized: local GEMM into the symmetric partial buffer, two-shot all-reduce
+        part = tp.part.tensor[:n].view(T, lin.N)
+        lin.matmul(x, out=part)
         tp.barrier.sync()
-        out = torch.empty(T, lin.N, device=x.device, dtype=torch.bfloat16)
-        native.require().finalize_acc(buf.tensor[: T * lin.N], None, out)
-        return out
+        C.tp_allreduce_pull(tp.part.ptrs, tp.out[b].ptrs, tp.rank, n)
+        tp.barrier.sync()
+        return tp.out[b].tensor[:n].view(T, lin.N)
 
     def _forward(self, ids, pos, seq_ids, ctx_lens, prefill_shape=None):
         """ids/pos/seq_ids: int32 [T]; ctx_lens int32 [B] (decode). Returns final hidden [T, d]."""
@@ -195,7 +221,7 @@ class InferenceEngine:
                 o = o.view(T, H * D)
             else:
                 o = torch.empty(T, H, D, device=self.device, dtype=torch.bfloat16)
-                C.paged_attn_decode(q.contiguous(), self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
+                C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
                                     self._scratch, self._counters, self._splits, scale,
                                     native.status_word(self.device))
                 o = o.view(T, H * D)
@@ -412,11 +438,6 @@ def _shard_cols(mod, rank: int, world: int) -> QuantLinear:
     orig = (rows * blocks_per_row + cols).reshape(-1)
     cmap = orig.to(torch.int32) if mod.cb_map is None else mod.cb_map[orig]
     return QuantLinear.from_float(ws, mod.fmt, bs, 1, mod.codebooks.float(), cmap.contiguous())
-
-
-def _peer_add(part: torch.Tensor, ptrs) -> None:
-    """Add an fp32 tile into every rank's accumulator (prefill-sized row-parallel outputs)."""
-    native.require().peer_add_f32(part.contiguous(), list(ptrs))
 
 
 def _gather_columns(lg: torch.Tensor, tp: TPContext) -> torch.Tensor:

@@ -27,16 +27,23 @@ _ACC: dict = {}
 _SMS: dict = {}
 
 
+def _norm_device(device) -> torch.device:
+    d = torch.device(device)
+    if d.type == "cuda" and d.index is None:
+        d = torch.device("cuda", torch.cuda.current_device())
+    return d
+
+
 def reserve_accumulator(device, numel: int) -> None:
     """Make the split-K accumulator of ``device`` hold at least ``numel`` floats."""
-    device = torch.device(device)
+    device = _norm_device(device)
     cur = _ACC.get(device)
     if cur is None or cur.numel() < numel:
         _ACC[device] = torch.zeros(numel, device=device, dtype=torch.float32)
 
 
 def _sm_count(device) -> int:
-    device = torch.device(device)
+    device = _norm_device(device)
     if device not in _SMS:
         _SMS[device] = torch.cuda.get_device_properties(device).multi_processor_count
     return _SMS[device]
@@ -168,9 +175,11 @@ class QuantLinear:
         flat_cb = self.codebooks.float().reshape(-1)
         return flat_cb[cbi.repeat_interleave(self.block_size)[:n] * size + idx].reshape(self.N, self.K)
 
-    def matmul(self, x: torch.Tensor, out=None, peer_ptrs=None, k_splits: int = 0) -> torch.Tensor:
-        """``x [M, K] @ W^T -> [M, N]`` (bf16). With ``peer_ptrs`` the fp32 partial result is added
-        into every listed accumulation buffer instead (fused all-reduce) and ``None`` is returned."""
+    def matmul(self, x: torch.Tensor, out=None, peer_ptrs=None, k_splits: int = 0,
+               peer_bf16_offset: int = -1) -> torch.Tensor:
+        """``x [M, K] @ W^T -> [M, N]`` (bf16). With ``peer_ptrs`` the partial result goes to the
+        listed peer buffers instead and ``None`` is returned: added as fp32 into every buffer, or,
+        with ``peer_bf16_offset >= 0``, stored as bf16 at that element offset of every buffer."""
         M = x.shape[0]
         if not x.is_cuda:
             return (x.float() @ self._dequantize_reference().t().float() if self.dense is None
@@ -182,7 +191,7 @@ class QuantLinear:
         st = native.status_word(x.device)
         if peer_ptrs is not None:
             C.dequant_gemm(x, self.packed, self.codebooks, self.cb_map, self.scales, QFMT[self.fmt], self.N, self.K,
-                           self.block_size, None, list(peer_ptrs), k_splits, st)
+                           self.block_size, None, list(peer_ptrs), k_splits, st, peer_bf16_offset)
             return None
         if M <= DECODE_MAX_TOKENS:
             if out is None:
@@ -190,10 +199,10 @@ class QuantLinear:
             # One CTA covers 128 output features. Too few of them to fill the GPU (narrow or
             # tensor-parallel layers): split K across CTAs into the fp32 accumulator instead.
             n_ctas = (self.N + 127) // 128
-            if n_ctas * 2 < 3 * _sm_count(x.device) and self.K >= 1024 and out.is_contiguous():
+            if n_ctas * 4 < 3 * _sm_count(x.device) and self.K >= 1024 and out.is_contiguous():
                 if not torch.cuda.is_current_stream_capturing():
                     reserve_accumulator(x.device, M * self.N)
-                acc = _ACC.get(x.device)
+                acc = _ACC.get(_norm_device(x.device))
                 if acc is not None and acc.numel() >= M * self.N:
                     acc = acc[: M * self.N].view(M, self.N)
                     C.dequant_gemm(x, self.packed, self.codebooks, self.cb_map, self.scales, QFMT[self.fmt], self.N,
@@ -204,3 +213,14 @@ class QuantLinear:
                            self.block_size, out, [], 1, st)
             return out
         return F.gemm(x, self.dequantize(), out=out)
+
+    def matmul_acc(self, x: torch.Tensor) -> torch.Tensor:
+        """Split-K product left in the device's fp32 accumulator: returns the ``[M, N]`` view, which
+        the caller must consume with a kernel that zeroes it again (finalize / tp_push)."""
+        M = x.shape[0]
+        if not torch.cuda.is_current_stream_capturing():
+            reserve_accumulator(x.device, M * self.N)
+        acc = _ACC[_norm_device(x.device)][: M * self.N].view(M, self.N)
+        native.require().dequant_gemm(x, self.packed, self.codebooks, self.cb_map, self.scales, QFMT[self.fmt],
+                                      self.N, self.K, self.block_size, acc, [], 0, native.status_word(x.device))
+        return acc

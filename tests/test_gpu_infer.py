@@ -70,6 +70,44 @@ def test_dequant_gemm_deep_k_and_block_sizes(fmt, M, N, K, bs, group):
     _close(q.matmul(x), ref, atol=2e-2)   # the accumulator was left zeroed by the first call
 
 
+def test_tp_allreduce_kernels_with_emulated_ranks():
+    """The tensor-parallel all-reduce kernels, with the ranks' buffers living on one GPU and the
+    ranks' launches issued one after another (no kernel waits on another)."""
+    from mythos_b200.infer.quant_weights import QuantLinear
+    from mythos_b200.ops import native
+
+    C = native.require()
+    torch.manual_seed(5)
+    W, M, N, K = 4, 24, 256, 512
+    stride = 32 * N
+    lin = [QuantLinear.from_float(torch.randn(N, K, device="cuda") * 0.02, "oil8", 256, 4) for _ in range(W)]
+    xs = [torch.randn(M, K, device="cuda").to(torch.bfloat16) for _ in range(W)]
+    parts = [xs[r].float() @ lin[r].dequantize().float().t() for r in range(W)]
+    want = sum(p.to(torch.bfloat16).float() for p in parts)
+    # one-shot: the GEMM epilogue (ranks 0, 1) or the push kernel (ranks 2, 3) fills slot r of every staging buffer
+    staging = [torch.zeros(W * stride, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    ptrs = [t.data_ptr() for t in staging]
+    for r in range(W):
+        if r < 2:
+            lin[r].matmul(xs[r], peer_ptrs=ptrs, k_splits=1, peer_bf16_offset=r * stride)
+        else:
+            acc = lin[r].matmul_acc(xs[r])
+            C.tp_push(acc, ptrs, r, r * stride)
+            assert float(acc.abs().max()) == 0.0
+    for r in range(W):
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        C.tp_reduce_slots(staging[r], W, stride, None, out)
+        _close(out, want, atol=2e-2)
+    # two-shot: every rank owns a slice, pulls it from all partial buffers and stores it everywhere
+    pbuf = [p.to(torch.bfloat16).contiguous() for p in parts]
+    obuf = [torch.zeros(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    for r in range(W):
+        C.tp_allreduce_pull([t.data_ptr() for t in pbuf], [t.data_ptr() for t in obuf], r, M * N)
+    for r in range(W):
+        _close(obuf[r], want, atol=2e-2)
+        assert torch.equal(obuf[r], obuf[0])
+
+
 def test_quantisation_error_is_small_and_gemv_matches():
     from mythos_b200.infer.quant_weights import QuantLinear
     from mythos_b200.ops import native
@@ -160,6 +198,20 @@ def test_sampler_modes():
     mask[:, 17] = 1
     t = sample(logits, SamplerConfig(temperature=0.0), allow_mask=mask)
     assert (t == 17).all()
+
+
+@pytest.mark.parametrize("rows,V", [(3, 128256), (64, 32000), (2, 128259), (5, 100)])
+def test_greedy_argmax_many_ctas_per_row(rows, V):
+    from mythos_b200.infer.sampler import SamplerConfig, sample
+
+    torch.manual_seed(rows + V)
+    logits = (torch.randn(rows, V, device="cuda") * 3).to(torch.bfloat16)
+    logits[0, V - 1] = 40.0            # maximum in the ragged tail
+    logits[rows - 1, :] = -1.0         # all equal: the first index wins
+    for _ in range(3):                 # the per-row slots clean themselves between launches
+        t = sample(logits, SamplerConfig(temperature=0.0))
+        assert torch.equal(t.long(), logits.float().argmax(-1))
+    assert int(t[0]) == V - 1 and int(t[rows - 1]) == 0
 
 
 def test_engine_greedy_matches_full_recompute():
