@@ -201,7 +201,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 // S = Q K^T with m16n8k16 MMAs (the G <= 8 query heads of the group are rows 0..G-1 of the 16-row
 // A operand, loaded once into registers), an online softmax on the accumulator fragments, and
 // O += P V with the V fragments read through ldmatrix.trans. Nothing but the page bytes moves.
-constexpr int PD_STAGES = 3;
+constexpr int PD_STAGES = 2;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"

@@ -27,7 +27,7 @@ from ..models.config import TransformerConfig
 from ..ops import functional as F
 from ..ops import native
 from .kv_paged import PagedKVCache
-from .quant_weights import QuantLinear, reserve_accumulator
+from .quant_weights import QFMT, QuantLinear, reserve_accumulator
 from .sampler import SamplerConfig, sample
 
 
@@ -151,6 +151,41 @@ class InferenceEngine:
             eng.head = QuantLinear.from_oil_linear(head_mod)
         else:
             eng.head = _shard_rows_multi(head_mod, [(0, head_mod.out_features)], r, W)
+        return eng
+
+    @classmethod
+    def random(cls, cfg: TransformerConfig, seed: int = 0, **kw) -> "InferenceEngine":
+        """Synthetic engine for benchmarks: every matrix is created directly in its storage format
+        (quantile codebooks with uniform-random indices, trits with p = 0.25/0.5/0.25), shard by
+        shard, so a large model never exists in fp32. Embeddings are random bf16."""
+        eng = cls(cfg, **kw)
+        dev, W, r = eng.device, eng.world, eng.rank
+        g = torch.Generator(device=dev).manual_seed(seed * 1000 + r)
+        D, d = cfg.head_dim, cfg.hidden_size
+        bs, grp = cfg.oil_block_size, cfg.codebook_group
+        f = cfg.ffn_hidden_size
+        ge = torch.Generator(device=dev).manual_seed(seed)           # replicated tensors: same on every rank
+
+        def mk(fmt, N, K):
+            if fmt not in QFMT:
+                return QuantLinear.from_float(torch.randn(N, K, device=dev, generator=g) * 0.02, "bf16")
+            return QuantLinear.random(fmt, N, K, bs if K % bs == 0 else 64, grp, device=dev, generator=g)
+
+        af = cfg.attn_format or cfg.weight_format
+        ff = cfg.ffn_format or cfg.weight_format
+        eng.embed = (torch.randn(cfg.vocab_size, d, device=dev, generator=ge) * 0.02).to(torch.bfloat16)
+        eng.final_norm = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        for _ in range(cfg.num_layers):
+            L = _Layer()
+            L.attn_norm = torch.ones(d, device=dev, dtype=torch.bfloat16)
+            L.ffn_norm = torch.ones(d, device=dev, dtype=torch.bfloat16)
+            L.qkv = mk(af, (eng.h_local + 2 * eng.hkv_local) * D, d)
+            L.o = mk(af, d, eng.h_local * D)
+            L.up = mk(ff, (2 if cfg.gated_ffn else 1) * f // W, d)
+            L.down = mk(ff, d, f // W)
+            eng.layers.append(L)
+        hf = cfg.weight_format if cfg.embed_format in ("fp32", "fp16", "bf16") else cfg.embed_format
+        eng.head = mk(hf, cfg.vocab_size // W, d)
         return eng
 
     def weight_bytes(self) -> int:

@@ -22,7 +22,6 @@ import torch
 
 def main(argv=None) -> int:
     from ..infer.engine import InferenceEngine, TPContext
-    from ..models import DenseModel
     from ..models.config import NAMED_CONFIGS
     from ..ops import native
 
@@ -57,12 +56,9 @@ def main(argv=None) -> int:
         tp = TPContext(dist.group.WORLD, dev, max_tokens=max(a.batch * a.prompt, 256), hidden=cfg.hidden_size,
                        vocab_shard=cfg.vocab_size // world, max_batch=a.batch)
     torch.manual_seed(1234)
-    # build layer by layer on the GPU, pack, and drop the fp32 weights: an 8B fp32 model does not need to exist at once
-    with torch.device(dev):
-        model = DenseModel(cfg)
-    eng = InferenceEngine.from_model(model, device=dev, max_batch=a.batch, max_seq_len=cfg.max_seq_len, tp=tp)
+    # weights are created shard by shard directly in their storage format
+    eng = InferenceEngine.random(cfg, seed=1234, device=dev, max_batch=a.batch, max_seq_len=cfg.max_seq_len, tp=tp)
     wbytes = eng.weight_bytes()
-    del model
     torch.cuda.empty_cache()
     g = torch.Generator().manual_seed(7)
     prompts = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g, dtype=torch.int32)
@@ -81,7 +77,8 @@ def main(argv=None) -> int:
         ttfts.sort()
         print(json.dumps({"metric": "decode tok/s and p50 TTFT", "preset": a.preset, "tp": world, "batch": a.batch,
                           "prompt": a.prompt, "new_tokens": a.new, "layers": cfg.num_layers,
-                          "full_depth": not a.layers, "decode_tok_s": max(rates), "p50_ttft_s": ttfts[len(ttfts) // 2],
+                          "full_depth": cfg.num_layers == NAMED_CONFIGS[a.preset]().num_layers, "decode_tok_s": max(rates), "decode_tok_s_runs": [round(r, 1) for r in rates],
+                          "p50_ttft_s": ttfts[len(ttfts) // 2],
                           "weight_bytes_per_rank": wbytes, "kv_bytes_per_rank": eng.cache.size_bytes(),
                           "data": "random-init weights in format, uniform-random prompts, greedy"}))
     if world > 1:

@@ -172,7 +172,7 @@ def bench_dequant_gemm(t: Timer, fmt: str, M: int, N: int, K: int, group: int = 
     return ms, q.packed.numel() / ms / 1e6, "GB/s"
 
 
-def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int):
+def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int, splits: int = 0):
     """Split-KV decode attention over 16-token pages; reported as KV bytes per second."""
     from mythos_b200.ops import native
 
@@ -186,7 +186,8 @@ def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int):
     q = torch.randn(B, H, D, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    splits = max(1, min(32, (6 * sms + B * Hkv - 1) // (B * Hkv), (ctx + 255) // 256))
+    if splits <= 0:
+        splits = max(1, min(32, (6 * sms + B * Hkv - 1) // (B * Hkv), (ctx + 255) // 256))
     scratch = torch.empty(B * H * splits * (D + 2), device="cuda")
     counters = torch.zeros(B * Hkv + 64, device="cuda", dtype=torch.int32)
     st = native.status_word("cuda")
@@ -215,6 +216,7 @@ def main():
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--fmt", default="oil8", choices=["oil8", "oil4", "i2s"])
     ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--splits", type=int, default=0, help="KV splits of paged_decode (0 = the engine's choice)")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 single-CTA kernel, 2 paired-SM kernel")
     args = ap.parse_args()
     from mythos_b200.ops import native
@@ -258,8 +260,8 @@ def main():
                              ("oil4", 64, 4096, 4096), ("i2s", 8, 6912, 2560), ("oil8", 64, 128256, 4096)]:
             report(f"dequant_gemm_{fmt}_{M}x{N}x{K}", bench_dequant_gemm(t, fmt, M, N, K))
     if k == "paged_decode":
-        report(f"paged_decode_b{args.batch}_ctx{args.ctx}_h{args.heads}_kv{hkv}_d{args.head_dim}",
-               bench_paged_decode(t, args.batch, args.ctx, args.heads, hkv, args.head_dim))
+        report(f"paged_decode_b{args.batch}_ctx{args.ctx}_h{args.heads}_kv{hkv}_d{args.head_dim}_splits{args.splits}",
+               bench_paged_decode(t, args.batch, args.ctx, args.heads, hkv, args.head_dim, args.splits))
     if k == "all":
         for B, ctx, H, Hkv in [(64, 1024, 32, 8), (64, 1024, 4, 1), (8, 32768, 20, 20)]:
             report(f"paged_decode_b{B}_ctx{ctx}_h{H}_kv{Hkv}_d128", bench_paged_decode(t, B, ctx, H, Hkv, 128))
