@@ -212,3 +212,28 @@ def test_attention_qkv_forward_backward(B, S, H, Hkv):
     orf.backward(do.float())
     _close(o, orf, atol=2e-2)
     _close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
+
+
+def test_b200_backend_surface_matches_host():
+    from mythos_b200.utils import backend as bk
+
+    dev, host = bk.B200Backend(), bk.HostBackend()
+    assert dev.is_available() and isinstance(bk.select_optimal_backend(), bk.B200Backend)
+    torch.manual_seed(0)
+    A = torch.randn(64, 128, device="cuda").to(torch.bfloat16)
+    B = torch.randn(128, 96, device="cuda").to(torch.bfloat16)
+    C = torch.zeros(64, 96, device="cuda")
+    dev.gemm(1.0, A, B, 0.0, C)
+    assert (C - A.float() @ B.float()).abs().max() < 0.5
+    y = torch.zeros(64, device="cuda")
+    dev.gemv(1.0, A, torch.ones(128, device="cuda", dtype=torch.bfloat16), 0.0, y)
+    assert (y - A.float().sum(1)).abs().max() < 0.5
+    x = torch.randn(32, 256, device="cuda").to(torch.bfloat16)
+    g = torch.ones(256, device="cuda", dtype=torch.bfloat16)
+    for name, args in (("softmax", (x,)), ("rms_norm", (x, g)), ("relu", (x,)), ("gelu", (x,)), ("silu", (x,))):
+        a = getattr(dev, name)(*args).float()
+        b = getattr(host, name)(*[t.float() for t in args]).float()
+        assert (a - b).abs().max() < 3e-2, name
+    assert dev.memory_free() > 0 and dev.memory_total() >= dev.memory_free()
+    r = bk.benchmark_operation(dev, "gemm", 1024, 3)
+    assert r["gflops"] > 1000
