@@ -1,0 +1,53 @@
+import os
+
+import torch
+
+from mythos_b200.infer.kv_stores import KVCache, PagedKVCache1T
+
+
+def test_contiguous_cache_fp_and_int8():
+    torch.manual_seed(0)
+    for int8 in (False, True):
+        c = KVCache(2, 16, 2, 64, int8=int8)
+        k1, v1 = torch.randn(1, 2, 5, 64), torch.randn(1, 2, 5, 64)
+        for layer in range(2):
+            c.append(layer, k1, v1)
+        assert c.context_len() == 5
+        k2 = torch.randn(1, 2, 1, 64)
+        for layer in range(2):
+            c.append(layer, k2, k2)
+        ka, va = c.get_all(1)
+        want = torch.cat([k1, k2], dim=2)
+        tol = 0.0 if not int8 else float(want.abs().max()) / 127 * 0.51
+        assert ka.shape == (1, 2, 6, 64) and (ka - want).abs().max() <= tol + 1e-7
+        kr, _ = c.get_range(0, 2, 4)
+        assert (kr - k1[:, :, 2:4]).abs().max() <= tol + 1e-7
+        c.resize(32)
+        assert c.max_seq == 32 and c.context_len() == 6 and (c.get_all(0)[0] - want).abs().max() <= tol + 1e-7
+        c.clear()
+        assert c.context_len() == 0
+    assert KVCache(1, 8, 1, 64, int8=True).size_bytes() < KVCache(1, 8, 1, 64).size_bytes() / 3
+
+
+def test_sparse_store_spills_and_reloads(tmp_path):
+    torch.manual_seed(1)
+    s = PagedKVCache1T(1, 2, 8, block_size=16, fanout=64, max_resident=2, spill_dir=str(tmp_path))
+    assert s.capacity_tokens() == 64 ** 3 * 16
+    pos = [0, 5, 17, 40, 1_000_000, 3_000_017]
+    data = {p: (torch.randn(2, 8), torch.randn(2, 8)) for p in pos}
+    for p in pos:
+        s.append(0, p, *data[p])
+    assert len(s.resident) == 2 and s.stats["evictions"] >= 3
+    assert any(f.startswith("paged_kv_l0_b") for f in os.listdir(tmp_path))
+    for p in pos:
+        assert s.verify_retrieval(0, p, *data[p])
+    assert s.stats["reloads"] >= 3
+    k, v = s.get_range(0, 0, 20)
+    assert torch.equal(k[5], data[5][0]) and torch.equal(k[17], data[17][0]) and float(k[1].abs().sum()) == 0.0
+    assert s.flush_to_disk() == 2 and len(s.resident) == 0
+    assert s.verify_retrieval(0, 1_000_000, *data[1_000_000])
+    try:
+        s.append(0, 64 ** 3 * 16, *data[0])
+        assert False
+    except ValueError:
+        pass
