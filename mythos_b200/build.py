@@ -149,9 +149,27 @@ def build_host(verbose: bool = False) -> Path:
     return target
 
 
+def build_capi(verbose: bool = False) -> Path:
+    """C API (oil_model_load / oil_generate): a bridge library that embeds or joins CPython."""
+    target = PKG / "liboil_capi.so"
+    src = CSRC / "capi" / "oil_c_api.cpp"
+    if not src.exists():
+        return target
+    if _newer(target, [src, CSRC / "capi" / "oil_c_api.h"]):
+        libdir = sysconfig.get_config_var("LIBDIR") or "/usr/lib"
+        ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", sysconfig.get_paths()["include"], "-I",
+              str(CSRC / "capi"), str(src), "-o", str(target), "-L", libdir, f"-lpython{ver}", "-ldl", "-lm",
+              "-Wl,-rpath," + libdir])
+        if verbose:
+            print("g++ oil_c_api.cpp")
+    return target
+
+
 def build_all(verbose: bool = False) -> dict:
     objs = build_kernels(verbose)
-    out = {"binding": build_binding(objs, verbose), "kernels_c": build_kernel_clib(objs), "host": build_host(verbose)}
+    out = {"binding": build_binding(objs, verbose), "kernels_c": build_kernel_clib(objs), "host": build_host(verbose),
+           "capi": build_capi(verbose)}
     return out
 
 

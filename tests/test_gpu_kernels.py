@@ -237,3 +237,41 @@ def test_b200_backend_surface_matches_host():
     assert dev.memory_free() > 0 and dev.memory_total() >= dev.memory_free()
     r = bk.benchmark_operation(dev, "gemm", 1024, 3)
     assert r["gflops"] > 1000
+
+
+def test_kernel_c_abi_through_ctypes():
+    """libmythos_kernels.so: the launchers behind a plain C ABI, called with raw device pointers."""
+    import ctypes
+    import os
+
+    import mythos_b200
+
+    path = os.path.join(os.path.dirname(mythos_b200.__file__), "libmythos_kernels.so")
+    if not os.path.exists(path):
+        pytest.skip("libmythos_kernels.so not built")
+    lib = ctypes.CDLL(path)
+    lib.mythos_last_error.restype = ctypes.c_char_p
+    vp, ll, i32, f32 = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
+    torch.manual_seed(0)
+    x = torch.randn(64, 512, device="cuda").to(torch.bfloat16)
+    g = (torch.rand(512, device="cuda") + 0.5).to(torch.bfloat16)
+    y = torch.empty_like(x)
+    stream = vp(torch.cuda.current_stream().cuda_stream)
+    lib.mythos_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp]
+    rc = lib.mythos_rmsnorm_fwd(x.data_ptr(), None, g.data_ptr(), y.data_ptr(), None, None, 64, 512, 1e-5, stream)
+    assert rc == 0, lib.mythos_last_error()
+    torch.cuda.synchronize()
+    want = ref.rmsnorm(x, g, 1e-5)[0]
+    assert (y.float() - want.float()).abs().max() < 3e-2
+    a = torch.randn(128, 256, device="cuda").to(torch.bfloat16)
+    b = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    c = torch.empty(128, 64, device="cuda", dtype=torch.bfloat16)
+    lib.mythos_gemm_bf16.argtypes = [vp, ll, i32, vp, ll, i32, vp, ll, i32, i32, i32, i32, f32, vp, vp]
+    rc = lib.mythos_gemm_bf16(a.data_ptr(), 256, 0, b.data_ptr(), 256, 0, c.data_ptr(), 64, 128, 64, 256, 0, 1.0,
+                              None, stream)
+    assert rc == 0, lib.mythos_last_error()
+    torch.cuda.synchronize()
+    assert (c.float() - a.float() @ b.float().t()).abs().max() < 0.5
+    rc = lib.mythos_gemm_bf16(a.data_ptr(), 255, 0, b.data_ptr(), 256, 0, c.data_ptr(), 64, 128, 64, 256, 0, 1.0,
+                              None, stream)
+    assert rc != 0 and len(lib.mythos_last_error()) > 0        # misaligned row stride is reported, not launched
