@@ -245,6 +245,7 @@ def test_kernel_c_abi_through_ctypes():
     import os
 
     import mythos_b200
+    from mythos_b200.ops import reference as ref
 
     path = os.path.join(os.path.dirname(mythos_b200.__file__), "libmythos_kernels.so")
     if not os.path.exists(path):
