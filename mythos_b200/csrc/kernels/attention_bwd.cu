@@ -10,7 +10,10 @@
 // The same shared tiles serve as K-major operands in one product and MN-major in another, so
 // nothing is transposed in memory. Two compute warpgroups split the 64 query columns of a step
 // (32 each), so every SM sub-partition has two warps to hide TMEM-load and exp latency behind one
-// another. dQ is accumulated in an fp32 scratch buffer with bulk tensor reductions and converted
+// another. Q / dO tiles go through a three-stage ring so the load of step n+2 is issued while
+// step n computes (with two stages its latency sat on the critical path), and the MMA thread polls
+// "scores of the next step can be issued" and "dV/dK/dQ of this step can be issued" independently
+// instead of waiting for them in a fixed order. dQ is accumulated in an fp32 scratch buffer with bulk tensor reductions and converted
 // to bf16 by a second kernel. Replaces the reference's four O(S^2 D) scalar loops
 // (src/autograd.cpp:463-584).
 #include "api.h"
@@ -35,16 +38,16 @@ struct BwCfg {
   static constexpr int KV_BYTES = BW_KV * BW_D * 2;      // 32 KB, two 64-wide chunks of [128 x 128 B]
   static constexpr int QT_BYTES = BW_Q * BW_D * 2;       // 16 KB, two chunks of [64 x 128 B]
   static constexpr int STAGE_BYTES = 2 * QT_BYTES;       // Q + dO
+  static constexpr int STAGES = 3;
   static constexpr int PT_BYTES = BW_KV * BW_Q * 2;      // 16 KB
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = KV_BYTES;
   static constexpr int OFF_ST = 2 * KV_BYTES;
-  static constexpr int OFF_PT = OFF_ST + 2 * STAGE_BYTES;
+  static constexpr int OFF_PT = OFF_ST + STAGES * STAGE_BYTES;
   static constexpr int OFF_DST = OFF_PT + PT_BYTES;
-  static constexpr int OFF_STATS = OFF_DST + PT_BYTES;   // [8 warps][2 parity][lse 32 | delta 32] floats
-  static constexpr int OFF_DQ = OFF_STATS + 8 * 2 * 64 * 4;   // [8 warps][32 q][32 d] fp32 staging for the dQ reduce
+  static constexpr int OFF_DQ = OFF_DST + PT_BYTES;      // [8 warps][32 q][32 d] fp32 staging for the dQ reduce
   static constexpr int OFF_BAR = OFF_DQ + BW_Q * BW_D * 4;
-  static constexpr int NUM_BARS = 10;
+  static constexpr int NUM_BARS = 12;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256, COL_DQT = 384;
@@ -62,16 +65,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* kv_full = bars;         // K and V landed
-  uint64_t* q_full = bars + 1;      // [2] Q and dO of a step landed
-  uint64_t* q_empty = bars + 3;     // [2] the MMAs reading that stage completed
-  uint64_t* s_full = bars + 5;      // S^T and dP^T of a step computed
-  uint64_t* sp_free = bars + 6;     // compute threads hold S^T/dP^T in registers
-  uint64_t* pds_full = bars + 7;    // P^T and dS^T written to shared memory
-  uint64_t* mma_done = bars + 8;    // dV, dK, dQ^T products of a step completed
-  uint64_t* dq_free = bars + 9;     // compute threads drained dQ^T
+  uint64_t* q_full = bars + 1;      // [3] Q and dO of a step landed
+  uint64_t* q_empty = bars + 4;     // [3] the MMAs reading that stage completed
+  uint64_t* s_full = bars + 7;      // S^T and dP^T of a step computed
+  uint64_t* sp_free = bars + 8;     // compute threads hold S^T/dP^T in registers
+  uint64_t* pds_full = bars + 9;    // P^T and dS^T written to shared memory
+  uint64_t* mma_done = bars + 10;   // dV, dK, dQ^T products of a step completed
+  uint64_t* dq_free = bars + 11;    // compute threads drained dQ^T
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
-  float* stats = reinterpret_cast<float*>(smem + Cfg::OFF_STATS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvt = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -84,7 +86,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
     }
@@ -118,8 +120,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tma_load_4d(smem + Cfg::OFF_V + c * (BW_KV * 128), &tm_v, kv_full, c * 64, hkv, kv0, b);
       }
       for (int n = 0; n < N; ++n) {
-        const int st = n & 1;
-        const uint32_t ph = (n >> 1) & 1;
+        const int st = n % Cfg::STAGES;
+        const uint32_t ph = (n / Cfg::STAGES) & 1;
         if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, status, 21)) break;
         const int h = hkv * group + n / per_head;
         const int q0 = (i_start + n % per_head) * BW_Q;
@@ -144,7 +146,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const uint32_t pt_addr = smem_u32(smem + Cfg::OFF_PT);
       const uint32_t dst_addr = smem_u32(smem + Cfg::OFF_DST);
       auto issue_scores = [&](int n) {
-        const uint32_t qa = st_addr + (n & 1) * Cfg::STAGE_BYTES;
+        const uint32_t qa = st_addr + (n % Cfg::STAGES) * Cfg::STAGE_BYTES;
         const uint32_t doa = qa + Cfg::QT_BYTES;
 #pragma unroll
         for (int k = 0; k < BW_D / 16; ++k) {
@@ -166,33 +168,51 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         issue_scores(0);
       }
-      for (int n = 0; n < N && ok; ++n) {
-        if (n + 1 < N) {
-          const int st = (n + 1) & 1;
-          if (!mbar_wait(&q_full[st], ((n + 1) >> 1) & 1, abort_flag, status, 24)) { ok = false; break; }
-          if (!mbar_wait(sp_free, n & 1, abort_flag, status, 25)) { ok = false; break; }
+      // Two independent streams of work share this thread: the scores of step ns (need Q/dO of
+      // that step and the S/dP accumulators, which the compute threads release once per step) and
+      // the dV/dK/dQ products of step nm (need P/dS in shared memory and the drained dQ
+      // accumulator). Each is issued the moment its inputs are ready.
+      int ns = 1, nm = 0;
+      long long t_idle = clock64();
+      while (ok && nm < N) {
+        bool progressed = false;
+        if (ns < N && mbar_test_wait(&q_full[ns % Cfg::STAGES], (ns / Cfg::STAGES) & 1) &&
+            mbar_test_wait(sp_free, (ns - 1) & 1)) {
           tc_fence_after();
-          issue_scores(n + 1);
+          issue_scores(ns);
+          ++ns;
+          progressed = true;
         }
-        if (!mbar_wait(pds_full, n & 1, abort_flag, status, 26)) { ok = false; break; }
-        if (n > 0 && !mbar_wait(dq_free, (n - 1) & 1, abort_flag, status, 27)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t qa = st_addr + (n & 1) * Cfg::STAGE_BYTES;
-        const uint32_t doa = qa + Cfg::QT_BYTES;
+        if (mbar_test_wait(pds_full, nm & 1) && (nm == 0 || mbar_test_wait(dq_free, (nm - 1) & 1))) {
+          tc_fence_after();
+          const uint32_t qa = st_addr + (nm % Cfg::STAGES) * Cfg::STAGE_BYTES;
+          const uint32_t doa = qa + Cfg::QT_BYTES;
 #pragma unroll
-        for (int k = 0; k < BW_Q / 16; ++k)  // dV += P^T dO
-          umma_f16(tmem_base + Cfg::COL_DV, umma_desc_sw128(pt_addr + k * 32, 0, 1024),
-                   umma_desc_sw128(doa + k * 2048, BW_Q * 128, 1024), IDESC_ACC, (n > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BW_Q / 16; ++k)  // dV += P^T dO
+            umma_f16(tmem_base + Cfg::COL_DV, umma_desc_sw128(pt_addr + k * 32, 0, 1024),
+                     umma_desc_sw128(doa + k * 2048, BW_Q * 128, 1024), IDESC_ACC, (nm > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < BW_Q / 16; ++k)  // dK += dS^T Q
-          umma_f16(tmem_base + Cfg::COL_DK, umma_desc_sw128(dst_addr + k * 32, 0, 1024),
-                   umma_desc_sw128(qa + k * 2048, BW_Q * 128, 1024), IDESC_ACC, (n > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BW_Q / 16; ++k)  // dK += dS^T Q
+            umma_f16(tmem_base + Cfg::COL_DK, umma_desc_sw128(dst_addr + k * 32, 0, 1024),
+                     umma_desc_sw128(qa + k * 2048, BW_Q * 128, 1024), IDESC_ACC, (nm > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < BW_KV / 16; ++k)  // dQ^T = K^T dS^T
-          umma_f16(tmem_base + Cfg::COL_DQT, umma_desc_sw128(k_addr + k * 2048, BW_KV * 128, 1024),
-                   umma_desc_sw128(dst_addr + k * 2048, BW_KV * 128, 1024), IDESC_DQT, k > 0 ? 1u : 0u);
-        umma_commit(mma_done);
-        umma_commit(&q_empty[n & 1]);
+          for (int k = 0; k < BW_KV / 16; ++k)  // dQ^T = K^T dS^T
+            umma_f16(tmem_base + Cfg::COL_DQT, umma_desc_sw128(k_addr + k * 2048, BW_KV * 128, 1024),
+                     umma_desc_sw128(dst_addr + k * 2048, BW_KV * 128, 1024), IDESC_DQT, k > 0 ? 1u : 0u);
+          umma_commit(mma_done);
+          umma_commit(&q_empty[nm % Cfg::STAGES]);
+          ++nm;
+          progressed = true;
+        }
+        if (progressed) {
+          t_idle = clock64();
+        } else if (*abort_flag) {
+          ok = false;
+        } else if (clock64() - t_idle > MB_WAIT_LIMIT_CYCLES) {
+          *abort_flag = 1;
+          if (status) atomicCAS(status, 0, ST_TIMEOUT | (24 << 16));
+          ok = false;
+        }
       }
     }
   } else {
@@ -230,21 +250,27 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     };
 
+    float nx_lse = INFINITY, nx_dl = 0.f;
+    if (N > 0) {
+      const int q1 = i_start * BW_Q + wg * BW_QH + lane;
+      const long long off1 = ((long long)b * heads + hkv * group) * seq;
+      nx_lse = (q1 < seq) ? __ldg(lse + off1 + q1) * LOG2E : INFINITY;
+      nx_dl = (q1 < seq) ? __ldg(delta + off1 + q1) : 0.f;
+    }
     for (int n = 0; n < N && ok; ++n) {
       const int h = hkv * group + n / per_head;
       const int q0 = (i_start + n % per_head) * BW_Q;
-      // Each warp stages lse / delta of this query tile in its own shared-memory slot
-      // (double-buffered by step parity), so no CTA-wide barrier is needed here.
-      float* st_lse = stats + (cw * 2 + (n & 1)) * 64;
-      float* st_dl = st_lse + 32;
+      // lane i holds lse / delta of query column i of this warpgroup's 32 columns; the loop below
+      // broadcasts them with shuffles. The values of the next step are fetched now, a step ahead.
       const int qc0 = q0 + wg * BW_QH;   // first query row of this warpgroup's columns
-      {
-        const long long off = ((long long)b * heads + h) * seq;
-        const int q = qc0 + lane;
-        st_lse[lane] = (q < seq) ? lse[off + q] * LOG2E : INFINITY;
-        st_dl[lane] = (q < seq) ? delta[off + q] : 0.f;
+      const float my_lse = nx_lse, my_dl = nx_dl;
+      if (n + 1 < N) {
+        const int h1 = hkv * group + (n + 1) / per_head;
+        const int q1 = (i_start + (n + 1) % per_head) * BW_Q + wg * BW_QH + lane;
+        const long long off1 = ((long long)b * heads + h1) * seq;
+        nx_lse = (q1 < seq) ? __ldg(lse + off1 + q1) * LOG2E : INFINITY;
+        nx_dl = (q1 < seq) ? __ldg(delta + off1 + q1) : 0.f;
       }
-      __syncwarp();
 
       ok = mbar_wait(s_full, n & 1, abort_flag, status, 28);
       ok = __all_sync(0xffffffffu, ok);
@@ -261,11 +287,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const bool diag = causal && (qc0 < kv0 + BW_KV);
 #pragma unroll
       for (int i = 0; i < BW_QH; ++i) {
-        const float e = fmaf(s[i], scale_log2, -st_lse[i]);
+        const float e = fmaf(s[i], scale_log2, -__shfl_sync(0xffffffffu, my_lse, i));
         float p = ((i & 3) == 3) ? poly_exp2(e) : fast_exp2(e);
         if (diag && (kv_row > qc0 + i)) p = 0.f;
         s[i] = p;
-        d[i] = p * (d[i] - st_dl[i]) * scale;
+        d[i] = p * (d[i] - __shfl_sync(0xffffffffu, my_dl, i)) * scale;
       }
       if (n > 0) {
         ok = mbar_wait(mma_done, (n - 1) & 1, abort_flag, status, 29);
