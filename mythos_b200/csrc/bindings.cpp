@@ -467,6 +467,27 @@ void tp_allreduce_pull(const std::vector<int64_t>& part_ptrs, const std::vector<
   mb::tp_allreduce_pull(to_peers(part_ptrs), to_peers(out_ptrs), (int)part_ptrs.size(), (int)rank, n, cur_stream());
 }
 
+// x [M, K] @ w [N, K]^T with the output rows scattered to their owner ranks (fused reduce-scatter).
+void gemm_reduce_scatter(const Tensor& x, const Tensor& w, const std::vector<int64_t>& slot_ptrs, int64_t rank,
+                         int64_t rows_per_rank, int64_t slot_stride, const OptTensor& status) {
+  chk(x, BF16, "x");
+  chk(w, BF16, "w");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1) && x.stride(1) == 1 && w.stride(1) == 1,
+              "gemm_reduce_scatter: x [M, K], w [N, K]");
+  const mb::PeerPtrs pp = to_peers(slot_ptrs);
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::gemm_bf16_2cta_scatter(x.data_ptr(), x.stride(0), false, w.data_ptr(), w.stride(0), false, nullptr, w.size(0),
+                             (int)x.size(0), (int)w.size(0), (int)x.size(1), mb::EPI_BF16, 1.0f, status_ptr(status),
+                             cur_stream(), &pp, (int)slot_ptrs.size(), rows_per_rank, rank * slot_stride);
+}
+void tp_reduce_slots_bcast(const Tensor& staging, int64_t slots, int64_t slot_stride,
+                           const std::vector<int64_t>& out_ptrs, int64_t rank, int64_t out_off, int64_t n) {
+  chk_c(staging, BF16, "staging");
+  c10::cuda::CUDAGuard guard(staging.device());
+  mb::tp_reduce_slots_bcast(staging.data_ptr(), (int)slots, slot_stride, to_peers(out_ptrs), (int)out_ptrs.size(),
+                            (int)rank, out_off, n, cur_stream());
+}
+
 void finalize_acc(Tensor& acc, const OptTensor& residual, Tensor& out) {
   chk_c(acc, F32, "acc");
   chk_c(out, BF16, "out");
@@ -642,6 +663,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("tp_push", &tp_push);
   m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("tp_allreduce_pull", &tp_allreduce_pull);
+  m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
+  m.def("tp_reduce_slots_bcast", &tp_reduce_slots_bcast);
   m.def("finalize_acc", &finalize_acc);
   m.def("dequant_to_bf16", &dequant_to_bf16);
   m.def("i2s_gemv", &i2s_gemv);

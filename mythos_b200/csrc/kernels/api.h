@@ -20,6 +20,13 @@ void gemm_bf16(const void* A, long long lda, bool a_mn, const void* B, long long
 // Paired-SM variant (cta_group::2, 256x256 tile per 2-CTA cluster); same contract.
 void gemm_bf16_2cta(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
                     long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream);
+struct PeerPtrs;
+// Same kernel with a fused reduce-scatter epilogue (bf16): output row m goes to rank m / rows_per_rank,
+// at scatter[rank] + slot_off + (m % rows_per_rank) * ldc, a peer store from the epilogue.
+void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
+                            long long ldc, int M, int N, int K, int epi, float alpha, int* status,
+                            cudaStream_t stream, const PeerPtrs* scatter, int n_scatter, long long rows_per_rank,
+                            long long slot_off);
 double gemm_2cta_waves(int M, int N, int sms);
 // 0 = choose per problem, 1 = always the single-CTA kernel, 2 = the paired kernel whenever it applies.
 void set_gemm_mode(int mode);
@@ -144,6 +151,10 @@ void tp_reduce_slots(const void* staging, int slots, long long slot_stride, cons
                      long long n, cudaStream_t stream);
 void tp_allreduce_pull(const PeerPtrs& part, const PeerPtrs& out, int n_peers, int rank, long long n,
                        cudaStream_t stream);
+// Second half of the fused GEMM -> reduce-scatter: sum the `slots` partials of this rank's rows
+// (local staging) and store the bf16 result at out_p + out_off for every peer p (all-gather by stores).
+void tp_reduce_slots_bcast(const void* staging, int slots, long long slot_stride, const PeerPtrs& out, int n_peers,
+                           int rank, long long out_off, long long n, cudaStream_t stream);
 void peer_gather_cols(const void* src, const PeerPtrs& dst, int n_peers, int rank, long long rows, int cols,
                       cudaStream_t stream);
 

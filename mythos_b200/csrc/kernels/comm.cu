@@ -300,6 +300,28 @@ __global__ void tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging
   }
 }
 
+// out_p[out_off + i] = bf16(sum_s staging[s * slot_stride + i]) for every peer p.
+__global__ void tp_reduce_slots_bcast_kernel(const __nv_bfloat16* __restrict__ staging, int slots, long long slot_stride,
+                                             PeerPtrs out, int n_peers, int rank, long long out_off, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bf16x8 v[MAX_PEERS];
+#pragma unroll
+    for (int s = 0; s < MAX_PEERS; ++s)
+      if (s < slots) v[s] = ld_l2_8(staging, s * slot_stride + i * 8);
+#pragma unroll
+    for (int s = 0; s < MAX_PEERS; ++s)
+      if (s < slots) {
+        float f[8];
+        unpack8(v[s], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    const bf16x8 r = pack8(acc);
+    for (int p = 0; p < n_peers; ++p) stg8(out.p[(rank + p) % n_peers], out_off + i * 8, r);
+  }
+}
+
 // Elements [begin8, end8) (units of 8) are this rank's slice: out_p[i] = bf16(sum_q part_q[i]) for
 // every p. Partials are summed in rank order, so the value does not depend on which rank owns it.
 __global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peers, int rank, long long begin8,
@@ -370,6 +392,20 @@ void tp_reduce_slots(const void* staging, int slots, long long slot_stride, cons
   if (g > cap) g = cap;
   tp_reduce_slots_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)staging, slots, slot_stride,
                                                      (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n / 8);
+  count_launch();
+  check_launch();
+}
+
+void tp_reduce_slots_bcast(const void* staging, int slots, long long slot_stride, const PeerPtrs& out, int n_peers,
+                           int rank, long long out_off, long long n, cudaStream_t stream) {
+  MB_REQUIRE(n % 8 == 0 && slot_stride % 8 == 0 && out_off % 8 == 0,
+             "tp_reduce_slots_bcast: counts, strides and offsets must be multiples of 8");
+  if (n == 0) return;
+  long long g = (n / 8 + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  tp_reduce_slots_bcast_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)staging, slots, slot_stride, out,
+                                                           n_peers, rank, out_off, n / 8);
   count_launch();
   check_launch();
 }

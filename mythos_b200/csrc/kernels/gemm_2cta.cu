@@ -100,7 +100,8 @@ template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T_THREADS, 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Cout, int M, int N, int K, long long ldc, int tiles_m, int tiles_n, int k_splits,
-                 int epi, int vec_ok, float alpha, int* status) {
+                 int epi, int vec_ok, float alpha, int* status, PeerPtrs scatter, int n_scatter,
+                 long long rows_per_rank, long long slot_off) {
   using Cfg = Cfg2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -237,6 +238,12 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const int ncols = min(32, N - col);
           if (epi == EPI_BF16) {
             __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc + col;
+            if (n_scatter > 0) {
+              // fused reduce-scatter: the row block goes to the rank that owns these rows, into
+              // the slot of the sending rank (a peer store over NVLink, tile by tile)
+              const long long owner = row / rows_per_rank;
+              p = reinterpret_cast<__nv_bfloat16*>(scatter.p[owner]) + slot_off + (row - owner * rows_per_rank) * ldc + col;
+            }
             if (ncols == 32 && vec_ok) {
               uint4* p4 = reinterpret_cast<uint4*>(p);
 #pragma unroll
@@ -304,7 +311,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
 template <bool A_MN, bool B_MN>
 void launch2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int k_splits,
-             int epi, int vec_ok, float alpha, int* status, cudaStream_t stream) {
+             int epi, int vec_ok, float alpha, int* status, cudaStream_t stream, const PeerPtrs& scatter,
+             int n_scatter, long long rows_per_rank, long long slot_off) {
   auto kern = gemm_2cta_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -316,7 +324,8 @@ void launch2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N
   int clusters = sm_count() / 2;
   if (total < clusters) clusters = total;
   kern<<<clusters * 2, T_THREADS, Cfg2::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, k_splits, epi,
-                                                              vec_ok, alpha, status);
+                                                              vec_ok, alpha, status, scatter, n_scatter, rows_per_rank,
+                                                              slot_off);
   count_launch();
   check_launch();
 }
@@ -332,11 +341,25 @@ double gemm_2cta_waves(int M, int N, int sms) {
 
 void gemm_bf16_2cta(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
                     long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream) {
+  gemm_bf16_2cta_scatter(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, epi, alpha, status, stream, nullptr, 0, 0, 0);
+}
+
+void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
+                            long long ldc, int M, int N, int K, int epi, float alpha, int* status,
+                            cudaStream_t stream, const PeerPtrs* scatter, int n_scatter, long long rows_per_rank,
+                            long long slot_off) {
   MB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem");
+  PeerPtrs sc{};
+  if (n_scatter > 0) {
+    MB_REQUIRE(scatter != nullptr && epi == EPI_BF16, "gemm: scattered output needs peers and the bf16 epilogue");
+    MB_REQUIRE(rows_per_rank > 0 && (long long)n_scatter * rows_per_rank >= M, "gemm: scattered rows exceed the peers");
+    MB_REQUIRE((slot_off * 2) % 16 == 0, "gemm: slot offset must keep 16-byte alignment");
+    sc = *scatter;
+  }
   MB_REQUIRE(!(a_mn && !b_mn), "gemm: MN-major A with K-major B is not instantiated");
   MB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: operand row strides must be multiples of 8 elements");
   const int esz = (epi == EPI_BF16) ? 2 : 4;
-  const int vec_ok = ((ldc * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+  const int vec_ok = ((ldc * esz) % 16 == 0 && (n_scatter > 0 || (reinterpret_cast<uintptr_t>(C) & 15) == 0)) ? 1 : 0;
   const int kblocks = (K + T_BK - 1) / T_BK;
   int k_splits = 1;
   if (epi == EPI_F32_ATOMIC) {
@@ -359,9 +382,15 @@ void gemm_bf16_2cta(const void* A, long long lda, bool a_mn, const void* B, long
   bstr[0] = (uint64_t)ldb * 2;
   const CUtensorMap ta = make_tensor_map(A, TmaDType::BF16, 2, adims, astr, abox, true);
   const CUtensorMap tb = make_tensor_map(B, TmaDType::BF16, 2, bdims, bstr, bbox, true);
-  if (!a_mn && !b_mn) launch2<false, false>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream);
-  else if (!a_mn && b_mn) launch2<false, true>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream);
-  else launch2<true, true>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream);
+  if (!a_mn && !b_mn)
+    launch2<false, false>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream, sc, n_scatter,
+                          rows_per_rank, slot_off);
+  else if (!a_mn && b_mn)
+    launch2<false, true>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream, sc, n_scatter,
+                         rows_per_rank, slot_off);
+  else
+    launch2<true, true>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream, sc, n_scatter,
+                        rows_per_rank, slot_off);
 }
 
 }  // namespace mb

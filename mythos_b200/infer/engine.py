@@ -218,7 +218,19 @@ class InferenceEngine:
             out = torch.empty(T, lin.N, device=x.device, dtype=torch.bfloat16)
             C.tp_reduce_slots(stage.tensor, tp.world, tp.slot_stride, None, out)
             return out
-        # prefill-sized: local GEMM into the symmetric partial buffer, two-shot all-reduce
+        if T % (tp.world * 256) == 0 and lin.N >= 256 and lin.N % 8 == 0:
+            # GEMM with a fused reduce-scatter epilogue: every 256-row output tile is stored
+            # straight into the owner rank's slot for this rank while the GEMM is still running;
+            # after one barrier each rank sums its slots and stores the result to all peers.
+            rows = T // tp.world
+            n_slot = rows * lin.N
+            w = lin.dense if lin.dense is not None else lin.dequantize()
+            C.gemm_reduce_scatter(x, w, tp.part.ptrs, tp.rank, rows, n_slot, native.status_word(x.device))
+            tp.barrier.sync()
+            C.tp_reduce_slots_bcast(tp.part.tensor, tp.world, n_slot, tp.out[b].ptrs, tp.rank, tp.rank * n_slot, n_slot)
+            tp.barrier.sync()
+            return tp.out[b].tensor[:n].view(T, lin.N)
+        # other sizes: local GEMM into the symmetric partial buffer, two-shot all-reduce
         part = tp.part.tensor[:n].view(T, lin.N)
         lin.matmul(x, out=part)
         tp.barrier.sync()

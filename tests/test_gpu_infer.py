@@ -98,6 +98,21 @@ def test_tp_allreduce_kernels_with_emulated_ranks():
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         C.tp_reduce_slots(staging[r], W, stride, None, out)
         _close(out, want, atol=2e-2)
+    # GEMM with fused reduce-scatter epilogue, then reduce + broadcast
+    Wg, T, Ng, Kg = 2, 1024, 512, 256
+    rows, n_slot = T // Wg, (T // Wg) * Ng
+    xg = [torch.randn(T, Kg, device="cuda").to(torch.bfloat16) for _ in range(Wg)]
+    wg = [(torch.randn(Ng, Kg, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(Wg)]
+    partg = [torch.zeros(Wg * n_slot, device="cuda", dtype=torch.bfloat16) for _ in range(Wg)]
+    outg = [torch.zeros(T, Ng, device="cuda", dtype=torch.bfloat16) for _ in range(Wg)]
+    for r in range(Wg):
+        C.gemm_reduce_scatter(xg[r], wg[r], [t.data_ptr() for t in partg], r, rows, n_slot, native.status_word("cuda"))
+    for r in range(Wg):
+        C.tp_reduce_slots_bcast(partg[r], Wg, n_slot, [t.data_ptr() for t in outg], r, r * n_slot, n_slot)
+    wantg = sum((xg[r].float() @ wg[r].float().t()).to(torch.bfloat16).float() for r in range(Wg))
+    for r in range(Wg):
+        _close(outg[r], wantg, atol=3e-2)
+        assert torch.equal(outg[r], outg[0])
     # two-shot: every rank owns a slice, pulls it from all partial buffers and stores it everywhere
     pbuf = [p.to(torch.bfloat16).contiguous() for p in parts]
     obuf = [torch.zeros(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(W)]
