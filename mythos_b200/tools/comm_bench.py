@@ -1,0 +1,201 @@
+"""Fused compute + collective paths against their NCCL equivalents and the NVLink roofline.
+
+Launch with torchrun on N >= 2 GPUs of one node:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m mythos_b200.tools.comm_bench
+
+Every case is timed with CUDA events on the launching stream after warm-up, bracketed by a process
+group barrier, and reported as the maximum over ranks. For each fused path the line gives the bytes
+that have to cross NVLink per rank and direction, the time that would take at the measured peer-copy
+rate (770 GB/s per direction per GPU), the compute time at the measured GEMM rate where there is a
+GEMM, the roofline (the slower of the two) and achieved / roofline.
+
+Cases: ZeRO gradient reduce-scatter + norm (own kernel vs ``reduce_scatter_tensor``), ZeRO AdamW +
+STE + all-gather (own kernel vs AdamW kernel + ``all_gather_into_tensor`` + local re-quantisation),
+tensor-parallel one-shot all-reduce of a decode-sized activation (own kernels vs ``all_reduce``),
+tensor-parallel GEMM with fused reduce-scatter + reduce/broadcast (vs GEMM + ``all_reduce``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+NVLINK_GBS = 770.0      # measured peer copy, per direction per GPU
+GEMM_TFLOPS = 1654.5    # measured cuBLAS bf16 burst
+HBM_GBS = 6549.4        # measured copy bandwidth
+
+
+def _time(fn, group, iters: int, warmup: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t)
+
+
+def main(argv=None) -> int:
+    from ..ops import functional as F
+    from ..ops import native
+    from ..parallel import symm
+
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--params", type=int, default=256 << 20, help="flat parameter count of the ZeRO cases")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args(argv)
+    rank, local, W = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD
+    C = native.require()
+    st = native.status_word(dev)
+    rows = []
+
+    def report(name, ms, nvlink_bytes, flops=0.0, baseline_ms=None, hbm_bytes=0.0):
+        t_link = nvlink_bytes / NVLINK_GBS / 1e6          # ms
+        t_math = flops / GEMM_TFLOPS / 1e9                # ms
+        t_hbm = hbm_bytes / HBM_GBS / 1e6                 # ms, local memory traffic of this rank
+        roof = max(t_link, t_math, t_hbm)
+        bound = "nvlink" if roof == t_link else ("compute" if roof == t_math else "hbm")
+        row = {"case": name, "ranks": W, "ms": round(ms, 4), "nvlink_MB_per_rank_dir": round(nvlink_bytes / 1e6, 2),
+               "roofline_ms": round(roof, 4), "bound": bound, "achieved_over_roofline": round(roof / ms, 3)}
+        if baseline_ms is not None:
+            row["nccl_ms"] = round(baseline_ms, 4)
+            row["speedup_vs_nccl"] = round(baseline_ms / ms, 3)
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+
+    bar = symm.FlagBarrier(dev, group)
+
+    # ---------------------------------------------------------------- ZeRO reduce-scatter + norm
+    n = a.params // (256 * W) * (256 * W)
+    shard = n // W
+    gbuf = symm.make_buffer(n, torch.float32, dev, group)
+    gbuf.tensor.normal_()
+    gshard = torch.empty(shard, device=dev)
+    part = torch.zeros(1, device=dev)
+
+    def rs_fused():
+        bar.sync()
+        C.zero_reduce_scatter(gbuf.ptrs, gshard, rank * shard, part)
+        bar.sync(part)
+
+    def rs_nccl():
+        dist.reduce_scatter_tensor(gshard, gbuf.tensor, op=dist.ReduceOp.SUM, group=group)
+        F.sumsq(gshard, part)
+        dist.all_reduce(part, group=group)
+
+    t_f, t_n = _time(rs_fused, group, a.iters, a.warmup), _time(rs_nccl, group, a.iters, a.warmup)
+    # local memory: this rank's slice is read by every rank (W reads) and the result written once
+    report("zero_reduce_scatter_norm_fp32", t_f, shard * 4.0 * (W - 1), baseline_ms=t_n, hbm_bytes=shard * 4.0 * (W + 1))
+
+    # ---------------------------------------------------------------- ZeRO AdamW + STE + all-gather
+    cbuf = symm.make_buffer(n, torch.bfloat16, dev, group)
+    master = torch.randn(shard, device=dev) * 0.02
+    m, v = torch.zeros(shard, device=dev), torch.zeros(shard, device=dev)
+    from ..oil.codebook import quantile_codebook
+
+    nseg = n // 256
+    seg_fmt = torch.ones(nseg, device=dev, dtype=torch.uint8)                       # every segment OIL8
+    seg_cb = (torch.arange(nseg, device=dev) // 128).to(torch.int32)
+    cb8 = quantile_codebook(256).to(dev)[None].repeat((nseg + 127) // 128, 1).contiguous()
+    cb4 = torch.zeros(1, 16, device=dev)
+    gnorm = torch.zeros(1, device=dev)
+
+    def ag_fused():
+        C.zero_adamw_ste_allgather(master, m, v, gshard, cbuf.ptrs, rank * shard, seg_fmt, seg_cb, cb8, cb4, bar.slots,
+                                   gnorm, 1.0, 1e-4, 0.9, 0.95, 1e-8, 0.1, 10, 1.0, rank)
+        bar.sync()
+
+    full = torch.empty(n, device=dev)
+    qout = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    clip = torch.ones(1, device=dev)
+
+    def ag_nccl():
+        F.adamw_step(master, m, v, gshard, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=10,
+                     clip_coef=clip)
+        dist.all_gather_into_tensor(full, master, group=group)
+        C.oil_fake_quant(full, cb8, seg_cb, 256, qout, None)
+
+    t_f, t_n = _time(ag_fused, group, a.iters, a.warmup), _time(ag_nccl, group, a.iters, a.warmup)
+    # local memory: p, m, v, g read and p, m, v written in fp32, plus the bf16 image written by all W ranks
+    report("zero_adamw_ste_allgather_bf16", t_f, shard * 2.0 * (W - 1), baseline_ms=t_n,
+           hbm_bytes=shard * (28.0 + 2.0 * W))
+    del gbuf, cbuf, full, qout
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- TP one-shot all-reduce (decode)
+    T, N = 64, 4096
+    stride = 256 * N
+    staging = symm.make_buffer(W * stride, torch.bfloat16, dev, group).zero_()
+    acc = torch.randn(T, N, device=dev)
+    out = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
+    fbar = symm.FlagBarrier(dev, group)
+
+    def tp_oneshot():
+        C.tp_push(acc, staging.ptrs, rank, rank * stride)
+        fbar.sync()
+        C.tp_reduce_slots(staging.tensor, W, stride, None, out)
+
+    xb = torch.randn(T, N, device=dev).to(torch.bfloat16)
+
+    def tp_nccl():
+        dist.all_reduce(xb, group=group)
+
+    t_f, t_n = _time(tp_oneshot, group, a.iters * 5, a.warmup), _time(tp_nccl, group, a.iters * 5, a.warmup)
+    report("tp_allreduce_oneshot_64x4096_bf16", t_f, T * N * 2.0 * (W - 1), baseline_ms=t_n)
+
+    # ---------------------------------------------------------------- TP GEMM + fused reduce-scatter (prefill)
+    Tp, K = 8192 * W if W <= 4 else 65536, 4096 // W * 2
+    Tp = Tp // (W * 256) * (W * 256)
+    rows_per = Tp // W
+    n_slot = rows_per * N
+    partb = symm.make_buffer(W * n_slot, torch.bfloat16, dev, group)
+    outb = symm.make_buffer(Tp * N, torch.bfloat16, dev, group)
+    x = (torch.randn(Tp, K, device=dev) * 0.1).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(torch.bfloat16)
+
+    def tp_fused_gemm():
+        C.gemm_reduce_scatter(x, w, partb.ptrs, rank, rows_per, n_slot, st)
+        fbar.sync()
+        C.tp_reduce_slots_bcast(partb.tensor, W, n_slot, outb.ptrs, rank, rank * n_slot, n_slot)
+        fbar.sync()
+
+    yb = torch.empty(Tp, N, device=dev, dtype=torch.bfloat16)
+
+    def tp_gemm_nccl():
+        F.gemm(x, w, out=yb)
+        dist.all_reduce(yb, group=group)
+
+    t_f, t_n = _time(tp_fused_gemm, group, a.iters, a.warmup), _time(tp_gemm_nccl, group, a.iters, a.warmup)
+    # reduce-scatter then all-gather: each direction carries (W-1)/W of the output twice
+    report(f"tp_gemm_reduce_scatter_allgather_{Tp}x{N}x{K}", t_f, 2.0 * Tp * N * 2.0 * (W - 1) / W,
+           flops=2.0 * Tp * N * K, baseline_ms=t_n)
+    del partb, outb
+    torch.cuda.empty_cache()
+
+    if rank == 0:
+        print(json.dumps({"summary": rows}))
+    native.check_status(dev)
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
