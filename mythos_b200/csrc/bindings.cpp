@@ -488,6 +488,47 @@ void tp_reduce_slots_bcast(const Tensor& staging, int64_t slots, int64_t slot_st
                             (int)rank, out_off, n, cur_stream());
 }
 
+void sum_residual_rmsnorm(OptTensor acc, const OptTensor& slots, int64_t n_slots, int64_t slot_stride,
+                          const OptTensor& residual, const Tensor& gamma, Tensor& stream_out, Tensor& normed,
+                          double eps) {
+  chk_c(gamma, BF16, "gamma");
+  chk_c(stream_out, BF16, "stream_out");
+  chk_c(normed, BF16, "normed");
+  if (acc.has_value()) chk_c(*acc, F32, "acc");
+  if (slots.has_value()) chk_c(*slots, BF16, "slots");
+  if (residual.has_value()) chk_c(*residual, BF16, "residual");
+  const int64_t dim = normed.size(-1), rows = normed.numel() / dim;
+  TORCH_CHECK(stream_out.numel() == normed.numel() && gamma.numel() == dim, "sum_residual_rmsnorm: shape mismatch");
+  c10::cuda::CUDAGuard guard(normed.device());
+  mb::sum_residual_rmsnorm(acc.has_value() ? acc->data_ptr<float>() : nullptr, cptr(slots), (int)n_slots, slot_stride,
+                           cptr(residual), gamma.data_ptr(), stream_out.data_ptr(), normed.data_ptr(), (int)rows,
+                           (int)dim, (float)eps, cur_stream());
+}
+void qkv_rope_append(Tensor& acc, const Tensor& pos, const Tensor& seq_ids, const Tensor& block_table, Tensor& q_out,
+                     Tensor& k_cache, Tensor& v_cache, double theta) {
+  chk_c(acc, F32, "acc");
+  chk_c(pos, I32, "pos");
+  chk_c(seq_ids, I32, "seq_ids");
+  chk_c(block_table, I32, "block_table");
+  chk_c(q_out, BF16, "q_out");
+  chk_c(k_cache, BF16, "k_cache");
+  chk_c(v_cache, BF16, "v_cache");
+  const int64_t T = q_out.size(0), H = q_out.size(1), D = q_out.size(2), Hkv = k_cache.size(2);
+  TORCH_CHECK(acc.numel() == T * (H + 2 * Hkv) * D, "qkv_rope_append: accumulator shape mismatch");
+  c10::cuda::CUDAGuard guard(acc.device());
+  mb::qkv_rope_append(acc.data_ptr<float>(), pos.data_ptr<int>(), seq_ids.data_ptr<int>(), block_table.data_ptr<int>(),
+                      q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), (int)T, (int)H, (int)Hkv, (int)D,
+                      (int)k_cache.size(1), (int)block_table.size(1), (float)theta, cur_stream());
+}
+void finalize_gate(Tensor& acc, Tensor& out, int64_t kind) {
+  chk_c(acc, F32, "acc");
+  chk_c(out, BF16, "out");
+  const int64_t ffn = out.size(-1), rows = out.numel() / ffn;
+  TORCH_CHECK(acc.numel() == 2 * out.numel(), "finalize_gate: accumulator must be [rows, 2 * ffn]");
+  c10::cuda::CUDAGuard guard(acc.device());
+  mb::finalize_gate(acc.data_ptr<float>(), out.data_ptr(), rows, (int)ffn, (int)kind, cur_stream());
+}
+
 void finalize_acc(Tensor& acc, const OptTensor& residual, Tensor& out) {
   chk_c(acc, F32, "acc");
   chk_c(out, BF16, "out");
@@ -663,6 +704,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("tp_push", &tp_push);
   m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("tp_allreduce_pull", &tp_allreduce_pull);
+  m.def("sum_residual_rmsnorm", &sum_residual_rmsnorm);
+  m.def("qkv_rope_append", &qkv_rope_append);
+  m.def("finalize_gate", &finalize_gate);
   m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
   m.def("tp_reduce_slots_bcast", &tp_reduce_slots_bcast);
   m.def("finalize_acc", &finalize_acc);

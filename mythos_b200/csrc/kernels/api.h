@@ -112,6 +112,20 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
                             long long kv_tok_stride, long long dq_tok_stride, long long dkv_tok_stride, bool causal,
                             float scale, int* status, cudaStream_t stream);
 
+// ---- fused decode epilogues (decode_fused.cu)
+// Exactly one of `acc` (fp32 [rows, dim], zeroed) / `slots` (n_slots bf16 partials, slot_stride apart) is summed,
+// `residual` (may be null) is added, the bf16 result goes to stream_out and its RMS-normalised image to normed.
+void sum_residual_rmsnorm(float* acc, const void* slots, int n_slots, long long slot_stride, const void* residual,
+                          const void* gamma, void* stream_out, void* normed, int rows, int dim, float eps,
+                          cudaStream_t stream);
+// acc fp32 [tokens, (heads + 2 kv_heads) * head_dim] (zeroed): Q rotated -> q_out bf16 [tokens, heads, head_dim];
+// K rotated and V -> their cache pages. theta <= 0 disables the rotation.
+void qkv_rope_append(float* acc, const int* pos, const int* seq_ids, const int* block_table, void* q_out,
+                     void* k_cache, void* v_cache, int tokens, int heads, int kv_heads, int head_dim, int page_size,
+                     int max_pages, float theta, cudaStream_t stream);
+// acc fp32 [rows, 2 * ffn] (zeroed) -> act(gate) * up, bf16 [rows, ffn]; kind 0 SiLU, 1 squared ReLU.
+void finalize_gate(float* acc, void* out, long long rows, int ffn, int kind, cudaStream_t stream);
+
 // ---- peer-memory collectives fused with compute (comm.cu)
 constexpr int MAX_PEERS = 16;
 struct PeerPtrs {

@@ -110,6 +110,7 @@ class InferenceEngine:
         self._sms = sm
         self._scratch = None
         self._counters = None
+        self.fused_decode = True     # decode steps use the fused epilogue kernels when the model allows
 
     # ------------------------------------------------------------------ weights
     @classmethod
@@ -238,8 +239,74 @@ class InferenceEngine:
         tp.barrier.sync()
         return tp.out[b].tensor[:n].view(T, lin.N)
 
+    def _row_parallel_norm(self, lin: QuantLinear, x, gamma, stream):
+        """Decode-sized row-parallel projection fused with what follows it: returns
+        ``(rmsnorm(stream + x W^T) * gamma, stream + x W^T)``. The sum over K splits (and over
+        ranks under tensor parallelism), the residual add and the normalisation are one kernel."""
+        C, tp = native.require(), self.tp
+        T = x.shape[0]
+        normed = torch.empty(T, lin.N, device=x.device, dtype=torch.bfloat16)
+        new_stream = torch.empty_like(normed)
+        if tp is None:
+            acc = lin.matmul_acc(x)
+            C.sum_residual_rmsnorm(acc, None, 0, 0, stream, gamma, new_stream, normed, self.cfg.norm_eps)
+            return normed, new_stream
+        b = tp.which
+        tp.which ^= 1
+        stage = tp.staging[b]
+        slot_off = tp.rank * tp.slot_stride
+        if lin.K // 64 <= 16:
+            lin.matmul(x, peer_ptrs=stage.ptrs, k_splits=1, peer_bf16_offset=slot_off)
+        else:
+            C.tp_push(lin.matmul_acc(x), stage.ptrs, tp.rank, slot_off)
+        tp.barrier.sync()
+        C.sum_residual_rmsnorm(None, stage.tensor, tp.world, tp.slot_stride, stream, gamma, new_stream, normed,
+                               self.cfg.norm_eps)
+        return normed, new_stream
+
+    def _fused_decode_ok(self, T: int) -> bool:
+        cfg = self.cfg
+        return (T <= ONESHOT_MAX_TOKENS and cfg.hidden_size % 8 == 0 and cfg.hidden_size <= 16384
+                and all(m.dense is None for L in self.layers for m in (L.qkv, L.o, L.up, L.down))
+                and (not cfg.gated_ffn or cfg.activation in ("silu", "relu2")))
+
+    def _forward_decode(self, ids, pos, seq_ids, ctx_lens):
+        """Decode step with the fused epilogue kernels: per layer QKV GEMM -> (finalize + RoPE + KV
+        append) -> paged attention -> o GEMM -> (sum + residual + RMSNorm) -> up GEMM -> (finalize +
+        gate) -> down GEMM -> (sum + residual + RMSNorm of the next layer)."""
+        cfg, C = self.cfg, native.require()
+        D, H, Hkv = cfg.head_dim, self.h_local, self.hkv_local
+        T = ids.numel()
+        scale = 1.0 / math.sqrt(D)
+        table = self.cache.block_table
+        dev = self.device
+        x = torch.empty(T, cfg.hidden_size, device=dev, dtype=torch.bfloat16)
+        C.embedding_fwd(ids, self.embed, x)
+        n, stream = F.rmsnorm(x, self.layers[0].attn_norm, cfg.norm_eps, None)
+        st = native.status_word(dev)
+        for li, L in enumerate(self.layers):
+            acc = L.qkv.matmul_acc(n)
+            q = torch.empty(T, H, D, device=dev, dtype=torch.bfloat16)
+            C.qkv_rope_append(acc, pos, seq_ids, table, q, self.cache.k[li], self.cache.v[li], cfg.rope_theta)
+            o = torch.empty(T, H, D, device=dev, dtype=torch.bfloat16)
+            C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o, self._scratch,
+                                self._counters, self._splits, scale, st)
+            n, stream = self._row_parallel_norm(L.o, o.view(T, H * D), L.ffn_norm, stream)
+            if cfg.gated_ffn:
+                acc = L.up.matmul_acc(n)
+                h = torch.empty(T, L.up.N // 2, device=dev, dtype=torch.bfloat16)
+                C.finalize_gate(acc, h, 0 if cfg.activation == "silu" else 1)
+            else:
+                u = L.up.matmul(n)
+                h = F.relu2(u) if cfg.activation == "relu2" else F.activation(u, cfg.activation)
+            gamma = self.layers[li + 1].attn_norm if li + 1 < len(self.layers) else self.final_norm
+            n, stream = self._row_parallel_norm(L.down, h, gamma, stream)
+        return n
+
     def _forward(self, ids, pos, seq_ids, ctx_lens, prefill_shape=None):
         """ids/pos/seq_ids: int32 [T]; ctx_lens int32 [B] (decode). Returns final hidden [T, d]."""
+        if prefill_shape is None and self.fused_decode and self._fused_decode_ok(ids.numel()):
+            return self._forward_decode(ids, pos, seq_ids, ctx_lens)
         cfg, C = self.cfg, native.require()
         D, H, Hkv = cfg.head_dim, self.h_local, self.hkv_local
         scale = 1.0 / math.sqrt(D)

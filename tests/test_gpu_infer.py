@@ -229,6 +229,64 @@ def test_greedy_argmax_many_ctas_per_row(rows, V):
     assert int(t[0]) == V - 1 and int(t[rows - 1]) == 0
 
 
+def test_fused_decode_epilogue_kernels():
+    from mythos_b200.ops import native, reference as ref
+
+    C = native.require()
+    torch.manual_seed(7)
+    # sum (+ residual) + RMSNorm from an fp32 accumulator and from bf16 slots
+    T, N = 5, 2560
+    acc = torch.randn(T, N, device="cuda")
+    res = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    g = (torch.rand(N, device="cuda") + 0.5).to(torch.bfloat16)
+    want_stream = (acc + res.float()).to(torch.bfloat16)
+    want_norm = ref.rmsnorm(want_stream, g, 1e-5)[0]
+    stream, normed = torch.empty_like(res), torch.empty_like(res)
+    C.sum_residual_rmsnorm(acc.clone(), None, 0, 0, res, g, stream, normed, 1e-5)
+    assert torch.equal(stream, want_stream)
+    _close(normed, want_norm, atol=2e-2)
+    a2 = acc.clone()
+    C.sum_residual_rmsnorm(a2, None, 0, 0, None, g, stream, normed, 1e-5)
+    assert float(a2.abs().max()) == 0.0 and torch.equal(stream, acc.to(torch.bfloat16))
+    slots = torch.randn(3, 8, N, device="cuda").to(torch.bfloat16)        # 3 ranks, slot stride 8 rows
+    C.sum_residual_rmsnorm(None, slots, 3, 8 * N, res, g, stream, normed, 1e-5)
+    want = (slots[:, :T].float().sum(0) + res.float()).to(torch.bfloat16)
+    assert torch.equal(stream, want)
+    _close(normed, ref.rmsnorm(want, g, 1e-5)[0], atol=2e-2)
+    # finalize + gate
+    f = 384
+    acc = torch.randn(T, 2 * f, device="cuda")
+    gu = acc.to(torch.bfloat16)
+    out = torch.empty(T, f, device="cuda", dtype=torch.bfloat16)
+    C.finalize_gate(acc, out, 0)
+    _close(out, ref.swiglu(gu), atol=2e-2)
+    assert float(acc.abs().max()) == 0.0
+    acc = torch.randn(T, 2 * f, device="cuda")
+    gu = acc.to(torch.bfloat16).float()
+    C.finalize_gate(acc, out, 1)
+    _close(out, torch.relu(gu[:, :f]) ** 2 * gu[:, f:], atol=3e-2)
+    # finalize + RoPE + KV append against the separate kernels
+    H, Hkv, D, page, max_pages = 4, 2, 128, 16, 4
+    Tt = 3
+    acc = torch.randn(Tt, (H + 2 * Hkv) * D, device="cuda")
+    qkv = acc.to(torch.bfloat16)
+    pos = torch.tensor([5, 17, 0], device="cuda", dtype=torch.int32)
+    sid = torch.arange(Tt, device="cuda", dtype=torch.int32)
+    table = torch.randperm(Tt * max_pages).view(Tt, max_pages).to(torch.int32).cuda()
+    kc = torch.zeros(Tt * max_pages, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc)
+    q = torch.empty(Tt, H, D, device="cuda", dtype=torch.bfloat16)
+    C.qkv_rope_append(acc, pos, sid, table, q, kc, vc, 10000.0)
+    ref_qk = qkv[:, : (H + Hkv) * D].clone().unflatten(-1, (H + Hkv, D))
+    C.rope(ref_qk, pos, 10000.0, False)
+    C.kv_append(ref_qk[:, H:].contiguous(), qkv[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D)).contiguous(), kc2, vc2,
+                table, pos, sid)
+    _close(q, ref_qk[:, :H], atol=2e-2)
+    _close(kc, kc2, atol=2e-2)
+    assert torch.equal(vc, vc2) and float(acc.abs().max()) == 0.0
+
+
 def test_engine_greedy_matches_full_recompute():
     from mythos_b200.infer.engine import InferenceEngine
     from mythos_b200.models import DenseModel, TransformerConfig
@@ -247,6 +305,11 @@ def test_engine_greedy_matches_full_recompute():
     res = eng.generate(prompts, max_new_tokens=new, use_graph=False)
     res_g = eng.generate(prompts, max_new_tokens=new, use_graph=True)
     assert res.tokens == res_g.tokens
+    eng.fused_decode = False            # the unfused kernel sequence decodes (nearly) the same tokens
+    res_u = eng.generate(prompts, max_new_tokens=new, use_graph=False)
+    eng.fused_decode = True
+    same = sum(a == b for ra, rb in zip(res.tokens, res_u.tokens) for a, b in zip(ra, rb))
+    assert same >= B * new - 2
     seq = prompts.cuda()
     agree = 0
     with torch.no_grad():
