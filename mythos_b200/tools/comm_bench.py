@@ -177,6 +177,14 @@ def main(argv=None) -> int:
         C.tp_reduce_slots_bcast(partb.tensor, W, n_slot, outb.ptrs, rank, rank * n_slot, n_slot)
         fbar.sync()
 
+    partc = symm.make_buffer(Tp * N, torch.bfloat16, dev, group)
+
+    def tp_gemm_pull():        # unfused variant of the own path: local GEMM, then pull-sum-store between two barriers
+        F.gemm(x, w, out=partc.tensor.view(Tp, N))
+        fbar.sync()
+        C.tp_allreduce_pull(partc.ptrs, outb.ptrs, rank, Tp * N)
+        fbar.sync()
+
     yb = torch.empty(Tp, N, device=dev, dtype=torch.bfloat16)
 
     def tp_gemm_nccl():
@@ -184,10 +192,15 @@ def main(argv=None) -> int:
         dist.all_reduce(yb, group=group)
 
     t_f, t_n = _time(tp_fused_gemm, group, a.iters, a.warmup), _time(tp_gemm_nccl, group, a.iters, a.warmup)
+    t_p = _time(tp_gemm_pull, group, a.iters, a.warmup)
+    t_g = _time(lambda: F.gemm(x, w, out=yb), group, a.iters, a.warmup)
+    report(f"tp_gemm_then_pull_allreduce_{Tp}x{N}x{K}", t_p, 2.0 * Tp * N * 2.0 * (W - 1) / W, flops=2.0 * Tp * N * K,
+           baseline_ms=t_n)
+    report(f"gemm_alone_{Tp}x{N}x{K}", t_g, 0.0, flops=2.0 * Tp * N * K)
     # reduce-scatter then all-gather: each direction carries (W-1)/W of the output twice
     report(f"tp_gemm_reduce_scatter_allgather_{Tp}x{N}x{K}", t_f, 2.0 * Tp * N * 2.0 * (W - 1) / W,
            flops=2.0 * Tp * N * K, baseline_ms=t_n)
-    del partb, outb
+    del partb, outb, partc
     torch.cuda.empty_cache()
 
     if rank == 0:
