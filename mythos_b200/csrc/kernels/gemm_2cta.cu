@@ -33,7 +33,9 @@ struct Cfg2 {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = T_STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * T_STAGES + 4;
-  static constexpr int SMEM_BYTES = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
+  static constexpr int EPI_STAGE_OFFSET = BAR_OFFSET + 256;       // [4 epilogue warps][32 rows][128 B]
+  static constexpr int SMEM_BYTES = EPI_STAGE_OFFSET + 4 * 4096 + 1024;
+  static_assert(NUM_BARS * 8 + 16 <= 256, "barrier region");
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
 };
 
@@ -234,16 +236,46 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col = wi.n0 + c * 32;
+        if (n_scatter > 0) {
+          // Fused reduce-scatter (bf16): the rows go to the rank that owns them, into the slot of
+          // the sending rank. A thread holds one row; stored from registers, every warp store would
+          // be 32 separate 16-byte peer writes. The warp therefore transposes 32 rows x 64 columns
+          // through shared memory and writes full 128-byte lines over NVLink.
+          uint8_t* stg = smem + Cfg::EPI_STAGE_OFFSET + q * 4096;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 0]), alpha * __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 2]), alpha * __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 4]), alpha * __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(alpha * __uint_as_float(r[8 * j + 6]), alpha * __uint_as_float(r[8 * j + 7]));
+            const int piece = (c & 1) * 4 + j;
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((piece ^ (lane & 7)) << 4)) = v;
+          }
+          if (c & 1) {
+            __syncwarp();
+            const int col0 = wi.n0 + (c - 1) * 32;
+            const int row0 = wi.m0 + (int)cta * 128 + q * 32;
+            if (col0 < N && row0 < M) {
+              const long long owner = row0 / rows_per_rank;   // 256-row tiles never straddle two owners
+              __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(scatter.p[owner]) + slot_off +
+                                    (row0 - owner * rows_per_rank) * ldc + col0;
+#pragma unroll
+              for (int it = 0; it < 8; ++it) {
+                const int rr = it * 4 + (lane >> 3), piece = lane & 7;
+                if (row0 + rr < M)
+                  *reinterpret_cast<uint4*>(base + (long long)rr * ldc + piece * 8) =
+                      *reinterpret_cast<const uint4*>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
+              }
+            }
+            __syncwarp();
+          }
+          continue;
+        }
         if (row < M && col < N) {
           const int ncols = min(32, N - col);
           if (epi == EPI_BF16) {
             __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc + col;
-            if (n_scatter > 0) {
-              // fused reduce-scatter: the row block goes to the rank that owns these rows, into
-              // the slot of the sending rank (a peer store over NVLink, tile by tile)
-              const long long owner = row / rows_per_rank;
-              p = reinterpret_cast<__nv_bfloat16*>(scatter.p[owner]) + slot_off + (row - owner * rows_per_rank) * ldc + col;
-            }
             if (ncols == 32 && vec_ok) {
               uint4* p4 = reinterpret_cast<uint4*>(p);
 #pragma unroll
@@ -354,6 +386,8 @@ void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void*
     MB_REQUIRE(scatter != nullptr && epi == EPI_BF16, "gemm: scattered output needs peers and the bf16 epilogue");
     MB_REQUIRE(rows_per_rank > 0 && (long long)n_scatter * rows_per_rank >= M, "gemm: scattered rows exceed the peers");
     MB_REQUIRE((slot_off * 2) % 16 == 0, "gemm: slot offset must keep 16-byte alignment");
+    MB_REQUIRE(N % 64 == 0 && ldc % 8 == 0 && rows_per_rank % 256 == 0,
+               "gemm: scattered output needs N % 64 == 0, ldc % 8 == 0 and 256-row ownership blocks");
     sc = *scatter;
   }
   MB_REQUIRE(!(a_mn && !b_mn), "gemm: MN-major A with K-major B is not instantiated");

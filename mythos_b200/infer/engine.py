@@ -78,11 +78,17 @@ class TPContext:
         self.logits = symm.make_buffer(max_batch * vocab_shard * self.world, torch.bfloat16, device, group)
         self.barrier = symm.FlagBarrier(device, group, device_epoch=True)
         self.which = 0
-        # Prefill-sized row-parallel sums: False = local GEMM, then the pull all-reduce kernel (measured
-        # 0.58 ms for 16384 x 4096 x 4096 on 2 GPUs, against 0.64 ms for GEMM + NCCL all-reduce);
-        # True = GEMM whose epilogue stores each tile into the owner rank's slot (0.77 ms: 64-byte
-        # row segments from registers use NVLink poorly).
-        self.fused_reduce_scatter = False
+        # Prefill-sized row-parallel sums. True: GEMM whose epilogue stores each 256-row tile into the
+        # owner rank's slot in full 128-byte lines, then reduce + all-gather by peer stores. False:
+        # local GEMM, then the pull all-reduce kernel. Measured on B200: at 2 ranks (16384 x 4096 x
+        # 4096) fused 0.48 ms, pull 0.58 ms, GEMM + NCCL all-reduce 0.64 ms; at 8 ranks (65536 x 4096
+        # x 1024) fused 2.82 ms, pull 2.02 ms, NCCL 2.09 ms, and the TP8 time to first token is 0.33 s
+        # fused against 0.23 s pull. So the fused epilogue is the default at 2 ranks only.
+        # MYTHOS_TP_FUSED_RS=0/1 overrides.
+        import os
+
+        default = "1" if self.world <= 2 else "0"
+        self.fused_reduce_scatter = os.environ.get("MYTHOS_TP_FUSED_RS", default) != "0"
 
 
 class _Layer:
@@ -224,7 +230,7 @@ class InferenceEngine:
             out = torch.empty(T, lin.N, device=x.device, dtype=torch.bfloat16)
             C.tp_reduce_slots(stage.tensor, tp.world, tp.slot_stride, None, out)
             return out
-        if tp.fused_reduce_scatter and T % (tp.world * 256) == 0 and lin.N >= 256 and lin.N % 8 == 0:
+        if tp.fused_reduce_scatter and T % (tp.world * 256) == 0 and lin.N >= 256 and lin.N % 64 == 0:
             # GEMM with a fused reduce-scatter epilogue: every 256-row output tile is stored
             # straight into the owner rank's slot for this rank while the GEMM is still running;
             # after one barrier each rank sums its slots and stores the result to all peers.
