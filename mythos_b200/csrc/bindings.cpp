@@ -205,6 +205,32 @@ void cross_entropy_fwd(const Tensor& logits, const Tensor& targets, Tensor& loss
                         (int)logits.size(1), logits.stride(0), cur_stream());
 }
 
+void cross_entropy_shard_stats(const Tensor& logits, const Tensor& targets, Tensor& stats, int64_t vocab_offset,
+                               int64_t vocab_total) {
+  chk(logits, BF16, "logits");
+  chk_c(targets, I32, "targets");
+  chk_c(stats, F32, "stats");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "cross_entropy_shard_stats: logits must be [rows, vocab]");
+  TORCH_CHECK(stats.numel() == logits.size(0) * 3 && targets.numel() == logits.size(0),
+              "cross_entropy_shard_stats: stats must be [rows, 3] and targets [rows]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  mb::cross_entropy_shard_stats(logits.data_ptr(), targets.data_ptr<int>(), stats.data_ptr<float>(), (int)logits.size(0),
+                                (int)logits.size(1), logits.stride(0), (int)vocab_offset, (int)vocab_total, cur_stream());
+}
+void cross_entropy_shard_grad(Tensor& logits, const Tensor& targets, const Tensor& lse, int64_t vocab_offset,
+                              int64_t vocab_total, double grad_scale) {
+  chk(logits, BF16, "logits");
+  chk_c(targets, I32, "targets");
+  chk_c(lse, F32, "lse");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "cross_entropy_shard_grad: logits must be [rows, vocab]");
+  TORCH_CHECK(lse.numel() == logits.size(0) && targets.numel() == logits.size(0),
+              "cross_entropy_shard_grad: lse and targets must be [rows]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  mb::cross_entropy_shard_grad(logits.data_ptr(), targets.data_ptr<int>(), lse.data_ptr<float>(), (int)logits.size(0),
+                               (int)logits.size(1), logits.stride(0), (int)vocab_offset, (int)vocab_total,
+                               (float)grad_scale, cur_stream());
+}
+
 void adamw_step(Tensor& p, Tensor& m, Tensor& v, const Tensor& g, OptTensor p_bf16, double lr, double beta1,
                 double beta2, double eps, double weight_decay, int64_t step, double grad_scale,
                 const OptTensor& clip_coef) {
@@ -545,6 +571,17 @@ void dequant_to_bf16(const Tensor& packed, const OptTensor& codebooks, const Opt
   mb::dequant_to_bf16(w, out.data_ptr(), cur_stream());
 }
 
+void dequant_gather_rows(const Tensor& ids, const Tensor& packed, const OptTensor& codebooks, const OptTensor& cb_map,
+                         const OptTensor& scales, int64_t fmt, int64_t N, int64_t K, int64_t block_size, Tensor& out) {
+  chk_c(ids, I32, "ids");
+  chk(out, BF16, "out");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == ids.numel() && out.size(1) == K && out.stride(1) == 1,
+              "dequant_gather_rows: out must be [tokens, K] with unit inner stride");
+  const auto w = to_weights(packed, codebooks, cb_map, scales, fmt, N, K, block_size);
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::dequant_gather_rows(w, ids.data_ptr<int>(), (int)ids.numel(), out.data_ptr(), out.stride(0), cur_stream());
+}
+
 void i2s_gemv(const Tensor& x, const Tensor& packed, const Tensor& scales, int64_t N, int64_t K, int64_t block_size,
               Tensor& y) {
   chk_c(x, BF16, "x");
@@ -594,6 +631,60 @@ void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                         counters.data_ptr<int>(), (int)B, (int)H, (int)Hkv, (int)D, (int)k_cache.size(1),
                         (int)block_table.size(1), (int)k_cache.size(0), (int)splits, (float)scale,
                         status_ptr(status), cur_stream(), q.stride(0));
+}
+
+void kv_append_int8(const Tensor& k, const Tensor& v, Tensor& k_cache, Tensor& v_cache, Tensor& k_scale, Tensor& v_scale,
+                    const Tensor& block_table, const Tensor& positions, const Tensor& seq_ids) {
+  chk(k, BF16, "k");
+  chk(v, BF16, "v");
+  chk_c(k_cache, torch::kInt8, "k_cache");
+  chk_c(v_cache, torch::kInt8, "v_cache");
+  chk_c(k_scale, F32, "k_scale");
+  chk_c(v_scale, F32, "v_scale");
+  chk_c(block_table, I32, "block_table");
+  chk_c(positions, I32, "positions");
+  chk_c(seq_ids, I32, "seq_ids");
+  TORCH_CHECK(k.dim() == 3 && k.stride(2) == 1 && k.stride(1) == k.size(2) && k.stride(0) == v.stride(0),
+              "kv_append_int8: k/v must be [tokens, kv_heads, head_dim] with a shared token stride");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(2) == k.size(1) && k_cache.size(3) == k.size(2),
+              "kv_append_int8: cache must be [pages, page_size, kv_heads, head_dim]");
+  const int64_t rows = k_cache.size(0) * k_cache.size(1) * k_cache.size(2);
+  TORCH_CHECK(k_scale.numel() == rows && v_scale.numel() == rows, "kv_append_int8: one scale per (token, kv head)");
+  c10::cuda::CUDAGuard guard(k.device());
+  mb::kv_append_int8(k.data_ptr(), v.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_scale.data_ptr<float>(),
+                     v_scale.data_ptr<float>(), block_table.data_ptr<int>(), positions.data_ptr<int>(),
+                     seq_ids.data_ptr<int>(), (int)k.size(0), (int)k.size(1), (int)k.size(2), (int)k_cache.size(1),
+                     (int)block_table.size(1), k.stride(0), cur_stream());
+}
+
+void paged_attn_decode_int8(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& k_scale,
+                            const Tensor& v_scale, const Tensor& block_table, const Tensor& context_lens, Tensor& out,
+                            Tensor& scratch, Tensor& counters, int64_t splits, double scale) {
+  chk(q, BF16, "q");
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2),
+              "paged_attn_decode_int8: q must be [batch, heads, head_dim] with contiguous heads");
+  chk_c(k_cache, torch::kInt8, "k_cache");
+  chk_c(v_cache, torch::kInt8, "v_cache");
+  chk_c(k_scale, F32, "k_scale");
+  chk_c(v_scale, F32, "v_scale");
+  chk_c(block_table, I32, "block_table");
+  chk_c(context_lens, I32, "context_lens");
+  chk_c(out, BF16, "out");
+  chk_c(scratch, F32, "scratch");
+  chk_c(counters, I32, "counters");
+  const int64_t B = q.size(0), H = q.size(1), D = q.size(2), Hkv = k_cache.size(2);
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(3) == D, "paged_attn_decode_int8: cache head_dim mismatch");
+  const int64_t rows = k_cache.size(0) * k_cache.size(1) * Hkv;
+  TORCH_CHECK(k_scale.numel() == rows && v_scale.numel() == rows,
+              "paged_attn_decode_int8: one scale per (token, kv head)");
+  TORCH_CHECK(scratch.numel() >= B * H * splits * (D + 2), "paged_attn_decode_int8: scratch too small");
+  TORCH_CHECK(counters.numel() >= B * Hkv, "paged_attn_decode_int8: counters too small");
+  c10::cuda::CUDAGuard guard(q.device());
+  mb::paged_attn_decode_int8(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_scale.data_ptr<float>(),
+                             v_scale.data_ptr<float>(), block_table.data_ptr<int>(), context_lens.data_ptr<int>(),
+                             out.data_ptr(), scratch.data_ptr<float>(), counters.data_ptr<int>(), (int)B, (int)H,
+                             (int)Hkv, (int)D, (int)k_cache.size(1), (int)block_table.size(1), (int)splits,
+                             (float)scale, cur_stream(), q.stride(0));
 }
 
 void sample_tokens(const Tensor& logits, const OptTensor& history, const OptTensor& allow_mask, double temperature,
@@ -689,6 +780,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);
   m.def("cross_entropy_fwd", &cross_entropy_fwd);
+  m.def("cross_entropy_shard_stats", &cross_entropy_shard_stats);
+  m.def("cross_entropy_shard_grad", &cross_entropy_shard_grad);
   m.def("adamw_step", &adamw_step);
   m.def("sumsq", &sumsq);
   m.def("oil_fake_quant", &oil_fake_quant);
@@ -711,9 +804,12 @@ PYBIND11_MODULE(_C, m) {
   m.def("tp_reduce_slots_bcast", &tp_reduce_slots_bcast);
   m.def("finalize_acc", &finalize_acc);
   m.def("dequant_to_bf16", &dequant_to_bf16);
+  m.def("dequant_gather_rows", &dequant_gather_rows);
   m.def("i2s_gemv", &i2s_gemv);
   m.def("kv_append", &kv_append);
   m.def("paged_attn_decode", &paged_attn_decode);
+  m.def("kv_append_int8", &kv_append_int8);
+  m.def("paged_attn_decode_int8", &paged_attn_decode_int8);
   m.def("sample_tokens", &sample_tokens);
   m.def("moe_topk", &moe_topk);
   m.def("moe_dispatch", &moe_dispatch);

@@ -72,6 +72,13 @@ void cross_entropy_fwd_bwd(void* logits, const int* targets, float* losses, int 
                            float grad_scale, cudaStream_t stream);
 void cross_entropy_fwd(const void* logits, const int* targets, float* losses, int rows, int vocab, long long ld,
                        cudaStream_t stream);
+// Vocabulary-parallel form: this rank holds logits columns [vocab_offset, vocab_offset + vocab).
+// stats[row] = {local max, local sum exp(x - max), target logit or 0}; after the ranks have merged
+// the records into lse[row], the second call overwrites the local logits with their gradient.
+void cross_entropy_shard_stats(const void* logits, const int* targets, float* stats, int rows, int vocab, long long ld,
+                               int vocab_offset, int vocab_total, cudaStream_t stream);
+void cross_entropy_shard_grad(void* logits, const int* targets, const float* lse, int rows, int vocab, long long ld,
+                              int vocab_offset, int vocab_total, float grad_scale, cudaStream_t stream);
 
 // ---- optimizer + STE fake-quant (optim.cu, quant.cu)
 struct AdamWArgs {
@@ -192,6 +199,9 @@ void dequant_gemm(const void* x, long long ldx, int M, const DequantWeights& w, 
 void finalize_acc(float* acc, const void* residual, void* out, long long n, cudaStream_t stream);
 // Whole-matrix dequantisation into a bf16 scratch buffer (prefill path).
 void dequant_to_bf16(const DequantWeights& w, void* out, cudaStream_t stream);
+// Embedding gather through the quantised table: out[t, :K] = dequant(W[clamp(ids[t]), :]).
+void dequant_gather_rows(const DequantWeights& w, const int* ids, int tokens, void* out, long long ld_out,
+                         cudaStream_t stream);
 
 // ---- inference: paged KV cache, decode attention, sampler (paged_attn.cu, sampler.cu)
 // Cache layout: k_cache / v_cache [num_pages, page_size, kv_heads, head_dim] bf16;
@@ -205,6 +215,16 @@ void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
                        const int* context_lens, void* out, float* scratch, int* counters, int batch, int heads,
                        int kv_heads, int head_dim, int page_size, int max_pages, int cache_pages, int splits,
                        float scale, int* status, cudaStream_t stream, long long q_tok_stride = 0);
+// int8 pages: k_cache / v_cache [num_pages, page_size, kv_heads, head_dim] int8 with one fp32 scale
+// (max|x| / 127) per (token, kv head) in k_scale / v_scale [num_pages * page_size, kv_heads].
+void kv_append_int8(const void* k, const void* v, void* k_cache, void* v_cache, float* k_scale, float* v_scale,
+                    const int* block_table, const int* positions, const int* seq_ids, int tokens, int kv_heads,
+                    int head_dim, int page_size, int max_pages, long long kv_tok_stride, cudaStream_t stream);
+void paged_attn_decode_int8(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                            const float* v_scale, const int* block_table, const int* context_lens, void* out,
+                            float* scratch, int* counters, int batch, int heads, int kv_heads, int head_dim,
+                            int page_size, int max_pages, int splits, float scale, cudaStream_t stream,
+                            long long q_tok_stride = 0);
 // Greedy / temperature / top-k / top-p / repetition-penalty sampling of one token per row.
 struct SamplerArgs {
   float temperature, top_p, repetition_penalty;

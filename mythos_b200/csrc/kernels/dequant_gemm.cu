@@ -448,6 +448,44 @@ __global__ void finalize_acc_kernel(float* __restrict__ acc, const __nv_bfloat16
   }
 }
 
+// The 16 weights that start at flat element ``elem`` (a multiple of 16), as two 16-byte bf16 words.
+template <int FMT>
+__device__ __forceinline__ void expand_unit(const DequantWeights& w, long long elem, uint4 (&vals)[2]) {
+  const long long blk = elem / w.block_size;
+  if (FMT == QFMT_OIL8) {
+    const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
+    oil8_expand16<false>(__ldg(reinterpret_cast<const uint4*>(w.packed + elem)),
+                         reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * 256, 0u, vals);
+  } else if (FMT == QFMT_OIL4) {
+    const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
+    const unsigned short* cb = reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * 16;
+    const uint2 r = __ldg(reinterpret_cast<const uint2*>(w.packed + elem / 2));
+    const uint32_t words[2] = {r.x, r.y};
+    uint32_t o[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+        o[4 * h + b] = (uint32_t)__ldg(cb + ((words[h] >> (8 * b)) & 0xF)) |
+                       ((uint32_t)__ldg(cb + ((words[h] >> (8 * b + 4)) & 0xF)) << 16);
+    vals[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    vals[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  } else {
+    const float scale = w.scales[blk];
+    const uint32_t neg = bf16_bits(-scale), pos = bf16_bits(scale);
+    const uint32_t r = __ldg(reinterpret_cast<const uint32_t*>(w.packed + elem / 4));
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t c0 = (r >> (4 * i)) & 3, c1 = (r >> (4 * i + 2)) & 3;
+      const uint32_t v0 = c0 == 0 ? neg : (c0 == 2 ? pos : 0u), v1 = c1 == 0 ? neg : (c1 == 2 ? pos : 0u);
+      o[i] = v0 | (v1 << 16);
+    }
+    vals[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    vals[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
 // Full dequantisation to bf16 (prefill path: dequantise once into scratch, then the dense GEMM).
 // One thread expands 16 weights.
 template <int FMT>
@@ -455,41 +493,28 @@ __global__ void dequant_full_kernel(DequantWeights w, __nv_bfloat16* __restrict_
   const long long units = (long long)w.N * w.K / 16;
   for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (long long)gridDim.x * blockDim.x) {
     const long long elem = u * 16;
-    const long long blk = elem / w.block_size;
     uint4 vals[2];
-    if (FMT == QFMT_OIL8) {
-      const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
-      oil8_expand16<false>(__ldg(reinterpret_cast<const uint4*>(w.packed + elem)),
-                           reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * 256, 0u, vals);
-    } else if (FMT == QFMT_OIL4) {
-      const int cbi = w.cb_map ? w.cb_map[blk] : (int)blk;
-      const unsigned short* cb = reinterpret_cast<const unsigned short*>(w.codebooks) + (long long)cbi * 16;
-      const uint2 r = __ldg(reinterpret_cast<const uint2*>(w.packed + elem / 2));
-      const uint32_t words[2] = {r.x, r.y};
-      uint32_t o[8];
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-          o[4 * h + b] = (uint32_t)__ldg(cb + ((words[h] >> (8 * b)) & 0xF)) |
-                         ((uint32_t)__ldg(cb + ((words[h] >> (8 * b + 4)) & 0xF)) << 16);
-      vals[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      vals[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    } else {
-      const float scale = w.scales[blk];
-      const uint32_t neg = bf16_bits(-scale), pos = bf16_bits(scale);
-      const uint32_t r = __ldg(reinterpret_cast<const uint32_t*>(w.packed + elem / 4));
-      uint32_t o[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t c0 = (r >> (4 * i)) & 3, c1 = (r >> (4 * i + 2)) & 3;
-        const uint32_t v0 = c0 == 0 ? neg : (c0 == 2 ? pos : 0u), v1 = c1 == 0 ? neg : (c1 == 2 ? pos : 0u);
-        o[i] = v0 | (v1 << 16);
-      }
-      vals[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      vals[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    }
+    expand_unit<FMT>(w, elem, vals);
     uint4* dst = reinterpret_cast<uint4*>(out + elem);
+    dst[0] = vals[0];
+    dst[1] = vals[1];
+  }
+}
+
+// Row gather through the quantised table: out[t, :] = dequant(W[ids[t], :]); ids are clamped to
+// [0, N-1]. One thread per 16 weights, 32 bytes stored per thread.
+template <int FMT>
+__global__ void dequant_rows_kernel(DequantWeights w, const int* __restrict__ ids, int tokens,
+                                    __nv_bfloat16* __restrict__ out, long long ld_out) {
+  const int upr = w.K / 16;
+  const long long units = (long long)tokens * upr;
+  for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(u / upr), c = (int)(u % upr);
+    int id = __ldg(ids + t);
+    id = id < 0 ? 0 : (id >= w.N ? w.N - 1 : id);
+    uint4 vals[2];
+    expand_unit<FMT>(w, (long long)id * w.K + (long long)c * 16, vals);
+    uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * ld_out + (long long)c * 16);
     dst[0] = vals[0];
     dst[1] = vals[1];
   }
@@ -586,6 +611,24 @@ void dequant_to_bf16(const DequantWeights& w, void* out, cudaStream_t stream) {
   else if (w.fmt == QFMT_OIL4) dequant_full_kernel<QFMT_OIL4><<<(int)g, 256, 0, stream>>>(w, (__nv_bfloat16*)out);
   else if (w.fmt == QFMT_I2S) dequant_full_kernel<QFMT_I2S><<<(int)g, 256, 0, stream>>>(w, (__nv_bfloat16*)out);
   else MB_REQUIRE(false, "dequant_to_bf16: unknown weight format");
+  count_launch();
+  check_launch();
+}
+
+void dequant_gather_rows(const DequantWeights& w, const int* ids, int tokens, void* out, long long ld_out,
+                         cudaStream_t stream) {
+  MB_REQUIRE(w.K % 64 == 0 && w.block_size % 64 == 0, "dequant_gather_rows: K and block size must be multiples of 64");
+  MB_REQUIRE(ld_out % 8 == 0 && ld_out >= w.K, "dequant_gather_rows: output row stride must be >= K and a multiple of 8");
+  const long long units = (long long)tokens * (w.K / 16);
+  if (units == 0) return;
+  long long g = (units + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  if (g > cap) g = cap;
+  __nv_bfloat16* o = (__nv_bfloat16*)out;
+  if (w.fmt == QFMT_OIL8) dequant_rows_kernel<QFMT_OIL8><<<(int)g, 256, 0, stream>>>(w, ids, tokens, o, ld_out);
+  else if (w.fmt == QFMT_OIL4) dequant_rows_kernel<QFMT_OIL4><<<(int)g, 256, 0, stream>>>(w, ids, tokens, o, ld_out);
+  else if (w.fmt == QFMT_I2S) dequant_rows_kernel<QFMT_I2S><<<(int)g, 256, 0, stream>>>(w, ids, tokens, o, ld_out);
+  else MB_REQUIRE(false, "dequant_gather_rows: unknown weight format");
   count_launch();
   check_launch();
 }

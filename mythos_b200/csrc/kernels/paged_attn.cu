@@ -42,6 +42,69 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv
   }
 }
 
+// int8 pages: every (token, kv head) row of head_dim values is stored as int8 with one fp32 scale
+// = max|x| / 127 (k_scale / v_scale: [pages * page_size, kv_heads]). The head_dim / 8 threads that
+// share a row find the maximum with shuffles; a thread quantises and stores 8 values (8 bytes).
+__global__ void kv_append_int8_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                      signed char* __restrict__ k_cache, signed char* __restrict__ v_cache,
+                                      float* __restrict__ k_scale, float* __restrict__ v_scale,
+                                      const int* __restrict__ block_table, const int* __restrict__ positions,
+                                      const int* __restrict__ seq_ids, int tokens, int kv_heads, int head_dim,
+                                      int page_size, int max_pages, long long kv_tok_stride) {
+  const int row = kv_heads * head_dim;
+  const int per_tok = row >> 3;
+  const int lpt = head_dim >> 3;      // 8 or 16 lanes per row, aligned inside the warp
+  const long long total = (long long)tokens * per_tok;
+  const long long padded = (total + 31) / 32 * 32;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < padded;
+       i += (long long)gridDim.x * blockDim.x) {
+    const bool valid = i < total;
+    const int t = valid ? (int)(i / per_tok) : 0, c = valid ? (int)(i % per_tok) * 8 : 0;
+    float kf[8], vf[8];
+    unpack8(ldg8(k, (long long)t * kv_tok_stride + c), kf);
+    unpack8(ldg8(v, (long long)t * kv_tok_stride + c), vf);
+    float ka = 0.f, va = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ka = fmaxf(ka, fabsf(kf[j]));
+      va = fmaxf(va, fabsf(vf[j]));
+    }
+    for (int o = lpt / 2; o > 0; o >>= 1) {
+      ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o));
+      va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o));
+    }
+    if (!valid) continue;
+    const int pos = positions[t], seq = seq_ids[t];
+    const int page = block_table[(long long)seq * max_pages + pos / page_size];
+    if (page < 0) continue;
+    const long long tokrow = (long long)page * page_size + pos % page_size;
+    const float kinv = ka > 0.f ? 127.f / ka : 0.f, vinv = va > 0.f ? 127.f / va : 0.f;
+    uint32_t kw[2] = {0u, 0u}, vw[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int kq = max(-127, min(127, __float2int_rn(kf[j] * kinv)));
+      const int vq = max(-127, min(127, __float2int_rn(vf[j] * vinv)));
+      kw[j >> 2] |= (uint32_t)(kq & 0xFF) << (8 * (j & 3));
+      vw[j >> 2] |= (uint32_t)(vq & 0xFF) << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint2*>(k_cache + tokrow * row + c) = make_uint2(kw[0], kw[1]);
+    *reinterpret_cast<uint2*>(v_cache + tokrow * row + c) = make_uint2(vw[0], vw[1]);
+    if ((c % head_dim) == 0) {
+      const int head = c / head_dim;
+      k_scale[tokrow * kv_heads + head] = ka / 127.f;
+      v_scale[tokrow * kv_heads + head] = va / 127.f;
+    }
+  }
+}
+
+__device__ __forceinline__ void unpack8_int8(uint2 w, float (&f)[8]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[j] = (float)(int)(signed char)((w.x >> (8 * j)) & 0xFF);
+    f[4 + j] = (float)(int)(signed char)((w.y >> (8 * j)) & 0xFF);
+  }
+}
+
 // Merge `nstate` online-softmax states of a CTA (s_m/s_l: [nstate][gstride]; s_acc: state s at
 // s_acc + s * acc_stride, laid out [gstride][D]) for the G heads of one (sequence, kv head), publish the partial result of
 // this split, and let the last CTA of the (sequence, kv head) combine all splits into `out`.
@@ -99,10 +162,14 @@ __device__ __forceinline__ void merge_and_finish(const float* s_m, const float* 
 }
 
 // grid (batch, kv_heads, splits); block 128 threads. G = query heads per kv head, D = head_dim.
-template <int G, int D>
+// INT8: the pages hold int8 rows with one fp32 scale per (token, kv head) in k_scale / v_scale; a
+// lane then loads 8 bytes per token instead of 16 and the scales are folded into the score and
+// into the probability.
+template <int G, int D, bool INT8>
 __global__ void __launch_bounds__(128)
-paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                    const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
+paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache_v,
+                    const void* __restrict__ v_cache_v, const float* __restrict__ k_scale,
+                    const float* __restrict__ v_scale, const int* __restrict__ block_table,
                     const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ scratch,
                     int* __restrict__ counters, int heads, int kv_heads, int page_size, int max_pages, int splits,
                     float scale_log2, long long q_tok_stride) {
@@ -119,6 +186,10 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int per = (ctx + splits - 1) / splits;
   const int t0 = split * per, t1 = min(ctx, t0 + per);
   const int row = kv_heads * D;
+  const __nv_bfloat16* k_cache = static_cast<const __nv_bfloat16*>(k_cache_v);
+  const __nv_bfloat16* v_cache = static_cast<const __nv_bfloat16*>(v_cache_v);
+  const signed char* k_cache8 = static_cast<const signed char*>(k_cache_v);
+  const signed char* v_cache8 = static_cast<const signed char*>(v_cache_v);
 
   float qv[G][8], acc[G][8], m[G], l[G];
 #pragma unroll
@@ -134,9 +205,11 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   // warp); a token slot past the end of the range contributes nothing. Each iteration first issues
   // the K/V loads of U token slots, then does the arithmetic, so a warp keeps 2*U 16-byte loads
   // per lane in flight: decode attention is bound by how much of the KV stream is in flight.
-  constexpr int U = 4;
+  constexpr int U = INT8 ? 8 : 4;   // int8 rows are half as long: twice the slots for the same bytes in flight
   for (int tb = t0 + warp * TPW; tb < t1; tb += 4 * TPW * U) {
     bf16x8 kq[U], vq[U];
+    uint2 k8[U], v8[U];
+    float ks[U], vs[U];
     bool valid[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -144,19 +217,34 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       valid[u] = t < t1;
       if (valid[u]) {
         const int page = bt[t / page_size];
-        const long long off = ((long long)page * page_size + t % page_size) * row + (long long)hkv * D + li * 8;
-        kq[u] = ldg8(k_cache, off);
-        vq[u] = ldg8(v_cache, off);
+        const long long tokrow = (long long)page * page_size + t % page_size;
+        const long long off = tokrow * row + (long long)hkv * D + li * 8;
+        if (INT8) {
+          k8[u] = __ldg(reinterpret_cast<const uint2*>(k_cache8 + off));
+          v8[u] = __ldg(reinterpret_cast<const uint2*>(v_cache8 + off));
+          ks[u] = __ldg(k_scale + tokrow * kv_heads + hkv);
+          vs[u] = __ldg(v_scale + tokrow * kv_heads + hkv);
+        } else {
+          kq[u] = ldg8(k_cache, off);
+          vq[u] = ldg8(v_cache, off);
+        }
       } else {
         const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         kq[u] = vq[u] = pack8(z);
+        k8[u] = v8[u] = make_uint2(0u, 0u);
+        ks[u] = vs[u] = 0.f;
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       float kf[8], vf[8];
-      unpack8(kq[u], kf);
-      unpack8(vq[u], vf);
+      if (INT8) {
+        unpack8_int8(k8[u], kf);
+        unpack8_int8(v8[u], vf);
+      } else {
+        unpack8(kq[u], kf);
+        unpack8(vq[u], vf);
+      }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         float s = 0.f;
@@ -165,12 +253,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
         for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (valid[u]) {
-          s *= scale_log2;
+          s *= INT8 ? scale_log2 * ks[u] : scale_log2;
           const float mn = fmaxf(m[g], s);
           const float a = exp2f(m[g] - mn), p = exp2f(s - mn);
           l[g] = l[g] * a + p;
+          const float pv = INT8 ? p * vs[u] : p;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * a + p * vf[i];
+          for (int i = 0; i < 8; ++i) acc[g][i] = acc[g][i] * a + pv * vf[i];
           m[g] = mn;
         }
       }
@@ -472,10 +561,9 @@ void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
     return;
   }
 #define MB_PD(GG, DD)                                                                                         \
-  paged_decode_kernel<GG, DD><<<grid, 128, 0, stream>>>(                                                      \
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,     \
-      context_lens, (__nv_bfloat16*)out, scratch, counters, heads, kv_heads, page_size, max_pages, splits, sl2,   \
-      q_tok_stride)
+  paged_decode_kernel<GG, DD, false><<<grid, 128, 0, stream>>>(                                               \
+      (const __nv_bfloat16*)q, k_cache, v_cache, nullptr, nullptr, block_table, context_lens,                 \
+      (__nv_bfloat16*)out, scratch, counters, heads, kv_heads, page_size, max_pages, splits, sl2, q_tok_stride)
   if (head_dim == 128) {
     if (G == 1) MB_PD(1, 128);
     else if (G == 2) MB_PD(2, 128);
@@ -490,6 +578,59 @@ void paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, 
     MB_REQUIRE(false, "paged_attn_decode: head_dim must be 64 or 128");
   }
 #undef MB_PD
+  count_launch();
+  check_launch();
+}
+
+void kv_append_int8(const void* k, const void* v, void* k_cache, void* v_cache, float* k_scale, float* v_scale,
+                    const int* block_table, const int* positions, const int* seq_ids, int tokens, int kv_heads,
+                    int head_dim, int page_size, int max_pages, long long kv_tok_stride, cudaStream_t stream) {
+  MB_REQUIRE(head_dim == 64 || head_dim == 128, "kv_append_int8: head_dim must be 64 or 128");
+  MB_REQUIRE(kv_tok_stride % 8 == 0, "kv_append_int8: token stride must be a multiple of 8 elements");
+  if (tokens == 0) return;
+  const long long work = ((long long)tokens * kv_heads * head_dim / 8 + 31) / 32 * 32;
+  long long g = (work + 255) / 256;
+  const long long cap = (long long)sm_count() * 16;
+  if (g > cap) g = cap;
+  kv_append_int8_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                                                    (signed char*)k_cache, (signed char*)v_cache, k_scale, v_scale,
+                                                    block_table, positions, seq_ids, tokens, kv_heads, head_dim,
+                                                    page_size, max_pages, kv_tok_stride);
+  count_launch();
+  check_launch();
+}
+
+void paged_attn_decode_int8(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                            const float* v_scale, const int* block_table, const int* context_lens, void* out,
+                            float* scratch, int* counters, int batch, int heads, int kv_heads, int head_dim,
+                            int page_size, int max_pages, int splits, float scale, cudaStream_t stream,
+                            long long q_tok_stride) {
+  if (q_tok_stride <= 0) q_tok_stride = (long long)heads * head_dim;
+  MB_REQUIRE(q_tok_stride % 8 == 0, "paged_attn_decode_int8: query token stride must be a multiple of 8 elements");
+  MB_REQUIRE(heads % kv_heads == 0, "paged_attn_decode_int8: heads must be a multiple of kv_heads");
+  MB_REQUIRE(splits >= 1, "paged_attn_decode_int8: splits must be positive");
+  if (batch == 0) return;
+  const int G = heads / kv_heads;
+  const dim3 grid(batch, kv_heads, splits);
+  const float sl2 = scale * 1.4426950408889634f;
+#define MB_PD8(GG, DD)                                                                                        \
+  paged_decode_kernel<GG, DD, true><<<grid, 128, 0, stream>>>(                                                \
+      (const __nv_bfloat16*)q, k_cache, v_cache, k_scale, v_scale, block_table, context_lens,                 \
+      (__nv_bfloat16*)out, scratch, counters, heads, kv_heads, page_size, max_pages, splits, sl2, q_tok_stride)
+  if (head_dim == 128) {
+    if (G == 1) MB_PD8(1, 128);
+    else if (G == 2) MB_PD8(2, 128);
+    else if (G == 4) MB_PD8(4, 128);
+    else MB_REQUIRE(false, "paged_attn_decode_int8: GQA group must be 1, 2 or 4");
+  } else if (head_dim == 64) {
+    if (G == 1) MB_PD8(1, 64);
+    else if (G == 2) MB_PD8(2, 64);
+    else if (G == 4) MB_PD8(4, 64);
+    else MB_REQUIRE(false, "paged_attn_decode_int8: GQA group must be 1, 2 or 4");
+  } else {
+    MB_REQUIRE(false, "paged_attn_decode_int8: head_dim must be 64 or 128");
+  }
+#undef MB_PD8
   count_launch();
   check_launch();
 }

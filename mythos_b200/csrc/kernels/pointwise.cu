@@ -199,11 +199,9 @@ __global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfl
 // One CTA per row. Pass 1: online max / sum-exp. Pass 2 (WRITE_GRAD): overwrite logits with
 // (softmax - onehot) * grad_scale. Targets are clamped to [0, vocab-1]; target < 0 with
 // ignore semantics is expressed by the caller through grad_scale.
-template <bool WRITE_GRAD>
-__global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
-                          float* __restrict__ losses, int vocab, long long ld, float grad_scale) {
-  __shared__ float scratch[32];
-  __nv_bfloat16* row = logits + (long long)blockIdx.x * ld;
+// Block-wide max and sum of exp(x - max) over one row of bf16 logits (online, one pass).
+__device__ __forceinline__ void row_max_sumexp(const __nv_bfloat16* __restrict__ row, int vocab, float* scratch,
+                                               float& gm, float& gs) {
   const int nchunk = vocab >> 3;
   float m = -INFINITY, s = 0.f;
   for (int ch = threadIdx.x; ch < nchunk; ch += blockDim.x) {
@@ -225,9 +223,19 @@ __global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, const int* __restr
     s = s * __expf(m - nm) + __expf(v - nm);
     m = nm;
   }
-  const float gm = block_max(m, scratch);
+  gm = block_max(m, scratch);
   s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
-  const float gs = block_sum(s, scratch);
+  gs = block_sum(s, scratch);
+}
+
+template <bool WRITE_GRAD>
+__global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                          float* __restrict__ losses, int vocab, long long ld, float grad_scale) {
+  __shared__ float scratch[32];
+  __nv_bfloat16* row = logits + (long long)blockIdx.x * ld;
+  const int nchunk = vocab >> 3;
+  float gm, gs;
+  row_max_sumexp(row, vocab, scratch, gm, gs);
   int tgt = targets[blockIdx.x];
   tgt = tgt < 0 ? 0 : (tgt >= vocab ? vocab - 1 : tgt);
   const float lse = gm + logf(gs);
@@ -250,6 +258,48 @@ __global__ void ce_kernel(__nv_bfloat16* __restrict__ logits, const int* __restr
       row[c] = __float2bfloat16((p - (c == tgt ? 1.f : 0.f)) * grad_scale);
     }
   }
+}
+
+// Vocabulary-parallel cross-entropy: every rank holds the columns [vocab_offset, vocab_offset +
+// vocab) of the logits. Step 1 (this kernel, one CTA per row) writes stats[row] = {local max, local
+// sum of exp(x - local max), target logit if this shard owns the target else 0}. The ranks then
+// exchange the 12-byte records, merge them (max, rescaled sums, target) into the global
+// log-sum-exp, and step 2 overwrites the local logits with their gradient.
+__global__ void ce_shard_stats_kernel(const __nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                                      float* __restrict__ stats, int vocab, long long ld, int vocab_offset,
+                                      int vocab_total) {
+  __shared__ float scratch[32];
+  const __nv_bfloat16* row = logits + (long long)blockIdx.x * ld;
+  float gm, gs;
+  row_max_sumexp(row, vocab, scratch, gm, gs);
+  if (threadIdx.x == 0) {
+    int tgt = targets[blockIdx.x];
+    tgt = tgt < 0 ? 0 : (tgt >= vocab_total ? vocab_total - 1 : tgt);
+    const int local = tgt - vocab_offset;
+    float* o = stats + (long long)blockIdx.x * 3;
+    o[0] = gm;
+    o[1] = gs;
+    o[2] = (local >= 0 && local < vocab) ? __bfloat162float(row[local]) : 0.f;
+  }
+}
+__global__ void ce_shard_grad_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                                     const float* __restrict__ lse, int vocab, long long ld, int vocab_offset,
+                                     int vocab_total, float grad_scale) {
+  __nv_bfloat16* row = logits + (long long)blockIdx.x * ld;
+  int tgt = targets[blockIdx.x];
+  tgt = tgt < 0 ? 0 : (tgt >= vocab_total ? vocab_total - 1 : tgt);
+  const int local = tgt - vocab_offset;     // outside [0, vocab) when another shard owns the target
+  const float l = lse[blockIdx.x];
+  const int nchunk = vocab >> 3;
+  for (int ch = threadIdx.x; ch < nchunk; ch += blockDim.x) {
+    float v[8];
+    unpack8(ldg8(row, ch * 8), v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = (__expf(v[k] - l) - ((ch * 8 + k) == local ? 1.f : 0.f)) * grad_scale;
+    stg8(row, ch * 8, pack8(v));
+  }
+  for (int c = nchunk * 8 + threadIdx.x; c < vocab; c += blockDim.x)
+    row[c] = __float2bfloat16((__expf(__bfloat162float(row[c]) - l) - (c == local ? 1.f : 0.f)) * grad_scale);
 }
 
 inline int ew_grid(long long work, int threads) {
@@ -383,6 +433,25 @@ void cross_entropy_fwd(const void* logits, const int* targets, float* losses, in
   MB_REQUIRE(ld % 8 == 0, "cross_entropy: row stride must be a multiple of 8 elements");
   if (rows == 0) return;
   ce_kernel<false><<<rows, 512, 0, stream>>>((__nv_bfloat16*)const_cast<void*>(logits), targets, losses, vocab, ld, 0.f);
+  count_launch();
+  check_launch();
+}
+
+void cross_entropy_shard_stats(const void* logits, const int* targets, float* stats, int rows, int vocab, long long ld,
+                               int vocab_offset, int vocab_total, cudaStream_t stream) {
+  MB_REQUIRE(ld % 8 == 0, "cross_entropy_shard_stats: row stride must be a multiple of 8 elements");
+  if (rows == 0) return;
+  ce_shard_stats_kernel<<<rows, 512, 0, stream>>>((const __nv_bfloat16*)logits, targets, stats, vocab, ld, vocab_offset,
+                                                  vocab_total);
+  count_launch();
+  check_launch();
+}
+void cross_entropy_shard_grad(void* logits, const int* targets, const float* lse, int rows, int vocab, long long ld,
+                              int vocab_offset, int vocab_total, float grad_scale, cudaStream_t stream) {
+  MB_REQUIRE(ld % 8 == 0, "cross_entropy_shard_grad: row stride must be a multiple of 8 elements");
+  if (rows == 0) return;
+  ce_shard_grad_kernel<<<rows, 512, 0, stream>>>((__nv_bfloat16*)logits, targets, lse, vocab, ld, vocab_offset,
+                                                 vocab_total, grad_scale);
   count_launch();
   check_launch();
 }

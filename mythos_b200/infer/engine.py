@@ -10,10 +10,12 @@ prefill, split-KV paged attention for decode) -> output projection -> RMSNorm ->
 projection -> SwiGLU / ReLU^2 gate -> down projection.
 
 Tensor parallelism (``tp``): attention heads and FFN columns are sharded; the two row-parallel
-projections of a layer add their fp32 partial tiles straight into every rank's accumulation
-buffer from the GEMM epilogue (peer ``red.add`` over NVLink), a flag barrier follows, and a small
-kernel turns the accumulator into the bf16 activation and clears it. No library collective runs
-inside a decode step. The lm_head is vocabulary-parallel; logits are gathered with peer stores.
+projections of a layer store their bf16 partials into this rank's slot on every peer (from the GEMM
+epilogue, or from a push kernel after split-K), a flag barrier follows, and the sum over slots is
+fused with the residual add and the next RMSNorm. Prefill-sized sums use a pull all-reduce kernel
+or a GEMM with a fused reduce-scatter epilogue. No library collective runs inside a step. The
+lm_head is vocabulary-parallel; logits are gathered with peer stores. An embedding table stored in
+an OIL format is expanded row by row inside the gather kernel.
 """
 from __future__ import annotations
 
@@ -91,13 +93,28 @@ class TPContext:
         self.fused_reduce_scatter = os.environ.get("MYTHOS_TP_FUSED_RS", default) != "0"
 
 
+def _embed_gather_ok(cfg: TransformerConfig) -> bool:
+    """The row-gather kernel expands 16 weights per thread and needs whole 64-weight blocks per row."""
+    return cfg.hidden_size % 64 == 0
+
+
+def _embed_block(cfg: TransformerConfig) -> int:
+    return cfg.oil_block_size if cfg.hidden_size % cfg.oil_block_size == 0 else 64
+
+
 class _Layer:
     __slots__ = ("attn_norm", "ffn_norm", "qkv", "o", "up", "down")
 
 
 class InferenceEngine:
     def __init__(self, cfg: TransformerConfig, device="cuda", max_batch: int = 64, max_seq_len: int | None = None,
-                 page_size: int = 16, tp: TPContext | None = None, kv_pages: int | None = None):
+                 page_size: int = 16, tp: TPContext | None = None, kv_pages: int | None = None,
+                 kv_dtype: str = "bf16"):
+        """``kv_dtype``: "bf16", or "int8" for pages of int8 rows with one scale per (token, kv head)
+        (half the KV bytes per decode step; the reference's block-quantised cache mode,
+        src/kv_cache.cpp:13-42, 78-137)."""
+        if kv_dtype not in ("bf16", "int8"):
+            raise ValueError(f"kv_dtype must be 'bf16' or 'int8', got {kv_dtype!r}")
         self.cfg, self.device, self.tp = cfg, torch.device(device), tp
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len or cfg.max_seq_len
@@ -110,9 +127,10 @@ class InferenceEngine:
         self.hkv_local = cfg.kv_heads // self.world
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.cache = PagedKVCache(cfg.num_layers, self.hkv_local, cfg.head_dim, kv_pages or max_batch * pages_per_seq,
-                                  page_size, max_batch, pages_per_seq, self.device)
+                                  page_size, max_batch, pages_per_seq, self.device,
+                                  dtype=torch.int8 if kv_dtype == "int8" else torch.bfloat16)
         self.layers: list[_Layer] = []
-        self.embed = None        # bf16 [V, d]
+        self.embed = None        # bf16 [V, d], or a QuantLinear when the table is stored in an OIL format
         self.final_norm = None
         self.head: QuantLinear | None = None
         self._graph = None
@@ -133,7 +151,11 @@ class InferenceEngine:
         dev = eng.device
         W, r = eng.world, eng.rank
         D, H, Hkv = cfg.head_dim, cfg.num_heads, cfg.kv_heads
-        eng.embed = model.tok_embeddings.weight.detach().to(dev, torch.bfloat16).contiguous()
+        if cfg.embed_format in QFMT and _embed_gather_ok(cfg):
+            eng.embed = QuantLinear.from_float(model.tok_embeddings.weight.detach().float().to(dev), cfg.embed_format,
+                                               _embed_block(cfg), cfg.codebook_group)
+        else:
+            eng.embed = model.tok_embeddings.weight.detach().to(dev, torch.bfloat16).contiguous()
         eng.final_norm = model.norm.weight.detach().to(dev, torch.bfloat16).contiguous()
         for blk in model.layers:
             L = _Layer()
@@ -185,7 +207,11 @@ class InferenceEngine:
 
         af = cfg.attn_format or cfg.weight_format
         ff = cfg.ffn_format or cfg.weight_format
-        eng.embed = (torch.randn(cfg.vocab_size, d, device=dev, generator=ge) * 0.02).to(torch.bfloat16)
+        if cfg.embed_format in QFMT and _embed_gather_ok(cfg):
+            eng.embed = QuantLinear.random(cfg.embed_format, cfg.vocab_size, d, _embed_block(cfg), grp, device=dev,
+                                           generator=ge)
+        else:
+            eng.embed = (torch.randn(cfg.vocab_size, d, device=dev, generator=ge) * 0.02).to(torch.bfloat16)
         eng.final_norm = torch.ones(d, device=dev, dtype=torch.bfloat16)
         for _ in range(cfg.num_layers):
             L = _Layer()
@@ -201,12 +227,20 @@ class InferenceEngine:
         return eng
 
     def weight_bytes(self) -> int:
-        n = self.head.nbytes() + self.embed.numel() * 2
+        n = self.head.nbytes()
+        n += self.embed.nbytes() if isinstance(self.embed, QuantLinear) else self.embed.numel() * 2
         for L in self.layers:
             n += L.qkv.nbytes() + L.o.nbytes() + L.up.nbytes() + L.down.nbytes()
         return n
 
     # ------------------------------------------------------------------ building blocks
+    def _embed(self, ids: torch.Tensor, x: torch.Tensor) -> None:
+        """Token rows into ``x``; a quantised table is expanded row by row inside the gather."""
+        if isinstance(self.embed, QuantLinear):
+            self.embed.gather_rows(ids, x)
+        else:
+            native.require().embedding_fwd(ids, self.embed, x)
+
     def _row_parallel(self, lin: QuantLinear, x: torch.Tensor) -> torch.Tensor:
         """x [T, K_local] @ W_shard^T, summed over ranks -> bf16 [T, d] (the all-reduce runs in this
         framework's own kernels over peer memory)."""
@@ -278,6 +312,7 @@ class InferenceEngine:
     def _fused_decode_ok(self, T: int) -> bool:
         cfg = self.cfg
         return (T <= ONESHOT_MAX_TOKENS and cfg.hidden_size % 8 == 0 and cfg.hidden_size <= 16384
+                and not self.cache.int8          # the fused QKV finalize writes bf16 pages
                 and all(m.dense is None for L in self.layers for m in (L.qkv, L.o, L.up, L.down))
                 and (not cfg.gated_ffn or cfg.activation in ("silu", "relu2")))
 
@@ -292,7 +327,7 @@ class InferenceEngine:
         table = self.cache.block_table
         dev = self.device
         x = torch.empty(T, cfg.hidden_size, device=dev, dtype=torch.bfloat16)
-        C.embedding_fwd(ids, self.embed, x)
+        self._embed(ids, x)
         n, stream = F.rmsnorm(x, self.layers[0].attn_norm, cfg.norm_eps, None)
         st = native.status_word(dev)
         for li, L in enumerate(self.layers):
@@ -323,7 +358,7 @@ class InferenceEngine:
         scale = 1.0 / math.sqrt(D)
         table = self.cache.block_table
         x = torch.empty(ids.numel(), cfg.hidden_size, device=self.device, dtype=torch.bfloat16)
-        C.embedding_fwd(ids, self.embed, x)
+        self._embed(ids, x)
         branch, stream = x, None
         for li, L in enumerate(self.layers):
             n, stream = F.rmsnorm(branch, L.attn_norm, cfg.norm_eps, stream)
@@ -334,7 +369,11 @@ class InferenceEngine:
             v = qkv[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
             if cfg.rope_theta > 0:   # q and k heads are adjacent in the fused projection: one launch
                 C.rope(qkv[:, : (H + Hkv) * D].unflatten(-1, (H + Hkv, D)), pos, cfg.rope_theta, False)
-            C.kv_append(k, v, self.cache.k[li], self.cache.v[li], table, pos, seq_ids)
+            if self.cache.int8:
+                C.kv_append_int8(k, v, self.cache.k[li], self.cache.v[li], self.cache.k_scale[li],
+                                 self.cache.v_scale[li], table, pos, seq_ids)
+            else:
+                C.kv_append(k, v, self.cache.k[li], self.cache.v[li], table, pos, seq_ids)
             if prefill_shape is not None:
                 B, S = prefill_shape
                 o = torch.empty(B, S, H, D, device=self.device, dtype=torch.bfloat16)
@@ -346,9 +385,14 @@ class InferenceEngine:
                 o = o.view(T, H * D)
             else:
                 o = torch.empty(T, H, D, device=self.device, dtype=torch.bfloat16)
-                C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
-                                    self._scratch, self._counters, self._splits, scale,
-                                    native.status_word(self.device))
+                if self.cache.int8:
+                    C.paged_attn_decode_int8(q, self.cache.k[li], self.cache.v[li], self.cache.k_scale[li],
+                                             self.cache.v_scale[li], table, ctx_lens, o, self._scratch,
+                                             self._counters, self._splits, scale)
+                else:
+                    C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
+                                        self._scratch, self._counters, self._splits, scale,
+                                        native.status_word(self.device))
                 o = o.view(T, H * D)
             a = self._row_parallel(L.o, o)
             n, stream = F.rmsnorm(a, L.ffn_norm, cfg.norm_eps, stream)

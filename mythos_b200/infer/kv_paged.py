@@ -54,6 +54,12 @@ class PagedKVCache:
         shape = (num_pages, page_size, kv_heads, head_dim)
         self.k = [torch.zeros(shape, device=self.device, dtype=dtype) for _ in range(num_layers)]
         self.v = [torch.zeros(shape, device=self.device, dtype=dtype) for _ in range(num_layers)]
+        # int8 pages carry one fp32 scale (max|x| / 127) per (token, kv head); the append kernel
+        # writes them and the decode kernel folds them into the score and the probability
+        self.int8 = dtype == torch.int8
+        srows = (num_pages * page_size, kv_heads)
+        self.k_scale = [torch.zeros(srows, device=self.device) for _ in range(num_layers)] if self.int8 else None
+        self.v_scale = [torch.zeros(srows, device=self.device) for _ in range(num_layers)] if self.int8 else None
         self.alloc = PageAllocator(num_pages)
         self.block_table_host = torch.full((max_seqs, max_pages_per_seq), -1, dtype=torch.int32)
         self.block_table = self.block_table_host.to(self.device)
@@ -138,7 +144,10 @@ class PagedKVCache:
         return self.alloc.used / max(1, self.alloc.num_pages)
 
     def size_bytes(self) -> int:
-        return 2 * self.num_layers * self.k[0].numel() * self.k[0].element_size()
+        n = 2 * self.num_layers * self.k[0].numel() * self.k[0].element_size()
+        if self.int8:
+            n += 2 * self.num_layers * self.k_scale[0].numel() * 4
+        return n
 
     def offload_sequence(self, seq: int):
         """Copy a sequence's pages to pinned host memory and release them. Returns a handle for
@@ -152,7 +161,12 @@ class PagedKVCache:
             hv = torch.empty_like(hk, pin_memory=self.device.type == "cuda")
             hk.copy_(self.k[layer][idx], non_blocking=True)
             hv.copy_(self.v[layer][idx], non_blocking=True)
-            host.append((hk, hv))
+            if self.int8:
+                ks = self.k_scale[layer].view(-1, self.page_size, self.kv_heads)[idx].cpu()
+                vs = self.v_scale[layer].view(-1, self.page_size, self.kv_heads)[idx].cpu()
+                host.append((hk, hv, ks, vs))
+            else:
+                host.append((hk, hv))
         if self.device.type == "cuda":
             torch.cuda.current_stream(self.device).synchronize()
         length = self.lens[seq]
@@ -164,16 +178,19 @@ class PagedKVCache:
         self.reserve(seq, handle["len"])
         pages = [int(p) for p in self.block_table_host[seq] if p >= 0]
         idx = torch.tensor(pages, device=self.device, dtype=torch.long)
-        for layer, (hk, hv) in enumerate(handle["pages"]):
-            self.k[layer][idx] = hk.to(self.device, non_blocking=True)
-            self.v[layer][idx] = hv.to(self.device, non_blocking=True)
+        for layer, rec in enumerate(handle["pages"]):
+            self.k[layer][idx] = rec[0].to(self.device, non_blocking=True)
+            self.v[layer][idx] = rec[1].to(self.device, non_blocking=True)
+            if self.int8:
+                self.k_scale[layer].view(-1, self.page_size, self.kv_heads)[idx] = rec[2].to(self.device)
+                self.v_scale[layer].view(-1, self.page_size, self.kv_heads)[idx] = rec[3].to(self.device)
         self.lens[seq] = handle["len"]
         return seq
 
     def save_pages(self, seq: int, path: str) -> None:
         """File tier: write a sequence's pages to ``path`` (torch.save of the offload handle)."""
         h = self.offload_sequence(seq)
-        torch.save({"len": h["len"], "pages": [(k.clone(), v.clone()) for k, v in h["pages"]]}, path)
+        torch.save({"len": h["len"], "pages": [tuple(t.clone() for t in rec) for rec in h["pages"]]}, path)
 
     def load_pages(self, path: str) -> int:
         return self.restore_sequence(torch.load(path))

@@ -157,6 +157,25 @@ class QuantLinear:
             return out
         return self._dequantize_reference().to(torch.bfloat16)
 
+    def gather_rows(self, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Embedding look-up through the quantised table: ``out[t] = dequant(W[ids[t]])`` (bf16
+        [tokens, K]); ids int32, clamped to the table. Only the addressed rows are expanded."""
+        ids = ids.reshape(-1)
+        if out is None:
+            out = torch.empty(ids.numel(), self.K, device=ids.device, dtype=torch.bfloat16)
+        if self.dense is not None:
+            if ids.is_cuda:
+                native.require().embedding_fwd(ids, self.dense, out)
+            else:
+                out.copy_(self.dense[ids.long().clamp(0, self.N - 1)])
+            return out
+        if ids.is_cuda:
+            native.require().dequant_gather_rows(ids, self.packed, self.codebooks, self.cb_map, self.scales,
+                                                 QFMT[self.fmt], self.N, self.K, self.block_size, out)
+        else:
+            out.copy_(self._dequantize_reference()[ids.long().clamp(0, self.N - 1)].to(torch.bfloat16))
+        return out
+
     def _dequantize_reference(self) -> torch.Tensor:
         n = self.N * self.K
         nb = n // self.block_size

@@ -190,3 +190,83 @@ def load_adapters(model, path: str) -> int:
                         plist[i].copy_(torch.from_numpy(v.copy()).view(plist[i].shape))
                         n += 1
     return n
+
+
+# ------------------------------------------------------------------------------------------ QLoRA
+def nf4_quantize(w: torch.Tensor, block: int = 64):
+    """NF4 with an affine map per block: the 16 NormalFloat levels (in [-1, 1]) are stretched onto
+    ``[min, max]`` of each block of ``block`` weights, every weight takes the nearest level, and two
+    4-bit codes share a byte (low nibble first). Returns (packed uint8 [n/2], lo [blocks], hi
+    [blocks]). Same scheme as the reference's QLoRA base (src/adapters/qlora.cpp:23-96)."""
+    flat = w.detach().float().reshape(-1)
+    pad = (-flat.numel()) % block
+    if pad:
+        flat = torch.cat([flat, flat[-1:].expand(pad)])
+    blocks = flat.view(-1, block)
+    lo, hi = blocks.amin(dim=1), blocks.amax(dim=1)
+    span = (hi - lo).clamp(min=1e-12)
+    levels = torch.tensor(NF4_LEVELS, device=w.device)
+    unit = (blocks - lo[:, None]) / span[:, None] * 2.0 - 1.0          # block mapped onto [-1, 1]
+    codes = (unit[..., None] - levels).abs().argmin(dim=-1).to(torch.uint8).view(-1)
+    packed = codes[0::2] | (codes[1::2] << 4)
+    return packed, lo, hi
+
+
+def nf4_dequantize(packed: torch.Tensor, lo: torch.Tensor, hi: torch.Tensor, numel: int, block: int = 64):
+    codes = torch.stack([packed & 0xF, packed >> 4], dim=1).reshape(-1).long()
+    levels = torch.tensor(NF4_LEVELS, device=packed.device)
+    unit = levels[codes].view(-1, block)
+    vals = (unit + 1.0) * 0.5 * (hi - lo)[:, None] + lo[:, None]
+    return vals.reshape(-1)[:numel]
+
+
+class QLoRALinear(nn.Module):
+    """Linear layer whose frozen base lives in packed NF4 (4.5 bits per weight with block 64) and
+    whose update is a trainable rank-``r`` pair: ``y = x deq(W)^T + (alpha / r) * (x A^T) B^T``.
+    A is uniform in +-1/sqrt(in), B starts at zero, so the layer starts out equal to its quantised
+    base. The reference's ``QLoRAAdapter`` is forward-only (GEMV); this one trains A and B (the
+    dequantised base is rebuilt per call in bf16 and is not kept)."""
+
+    def __init__(self, weight: torch.Tensor, rank: int = 8, alpha: float = 16.0, block: int = 64):
+        super().__init__()
+        self.out_features, self.in_features = weight.shape
+        self.rank, self.alpha, self.scale, self.block = rank, alpha, alpha / rank, block
+        packed, lo, hi = nf4_quantize(weight, block)
+        self.register_buffer("packed", packed)
+        self.register_buffer("lo", lo)
+        self.register_buffer("hi", hi)
+        bound = 1.0 / math.sqrt(self.in_features)
+        self.lora_A = nn.Parameter(torch.empty(rank, self.in_features, device=weight.device).uniform_(-bound, bound))
+        self.lora_B = nn.Parameter(torch.zeros(self.out_features, rank, device=weight.device))
+
+    def base_weight(self) -> torch.Tensor:
+        n = self.out_features * self.in_features
+        return nf4_dequantize(self.packed, self.lo, self.hi, n, self.block).view(self.out_features, self.in_features)
+
+    def base_bytes(self) -> int:
+        return self.packed.numel() + 4 * (self.lo.numel() + self.hi.numel())
+
+    def forward(self, x):
+        dt = torch.bfloat16 if x.is_cuda else x.dtype
+        w = self.base_weight().to(dt)
+        y = F.linear(x.to(dt), w)
+        delta = F.linear(F.linear(x.to(dt), self.lora_A.to(dt)), self.lora_B.to(dt))
+        return y + self.scale * delta
+
+    @torch.no_grad()
+    def merged_weight(self) -> torch.Tensor:
+        """fp32 ``deq(W) + (alpha / r) * B A`` for export."""
+        return self.base_weight() + self.scale * (self.lora_B.float() @ self.lora_A.float())
+
+    def adapter_state(self, prefix: str = "") -> dict:
+        """``qlora.A`` / ``qlora.B`` plus the packed base and its block ranges."""
+        return {f"{prefix}qlora.A": self.lora_A.detach().float().cpu(), f"{prefix}qlora.B": self.lora_B.detach().float().cpu(),
+                f"{prefix}qlora.packed": self.packed.cpu(), f"{prefix}qlora.lo": self.lo.cpu(),
+                f"{prefix}qlora.hi": self.hi.cpu()}
+
+    @torch.no_grad()
+    def load_adapter_state(self, state: dict, prefix: str = "") -> None:
+        self.lora_A.copy_(state[f"{prefix}qlora.A"])
+        self.lora_B.copy_(state[f"{prefix}qlora.B"])
+        for k in ("packed", "lo", "hi"):
+            getattr(self, k).copy_(state[f"{prefix}qlora.{k}"])

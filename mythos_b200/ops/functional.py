@@ -150,7 +150,14 @@ def layernorm(x, gamma, beta=None, eps: float = 1e-5):
 
 
 # --------------------------------------------------------------------------------------- attention
-_SUPPORTED_BWD_HEAD_DIMS = (128,)
+_SUPPORTED_BWD_HEAD_DIMS = (64, 128)     # 64 runs the 128-wide kernel on zero-padded heads
+
+
+def _pad_heads(t, width: int):
+    """[B, S, H, D] (any strides) -> contiguous [B, S, H, width] with zeros beyond D."""
+    out = t.new_zeros(*t.shape[:-1], width)
+    out[..., : t.shape[-1]].copy_(t)
+    return out
 
 
 class _AttentionFn(torch.autograd.Function):
@@ -197,8 +204,21 @@ class _AttentionFn(torch.autograd.Function):
         dq_accum = torch.empty(B * S * H * D, device=qkv.device, dtype=torch.float32)
         delta = torch.empty(B * H * S, device=qkv.device, dtype=torch.float32)
         do4 = do.reshape(B, S, H, D).contiguous()
-        C.flash_attn_bwd(q4, k4, v4, o, do4, lse, dq4, dk4, dv4, dq_accum, delta, causal, scale,
-                         native.status_word(qkv.device))
+        if D == 128:
+            C.flash_attn_bwd(q4, k4, v4, o, do4, lse, dq4, dk4, dv4, dq_accum, delta, causal, scale,
+                             native.status_word(qkv.device))
+        else:
+            # Zero columns change neither the scores nor o . do, so the padded problem has the same
+            # lse and delta; the gradients of the padding columns come out zero and are dropped.
+            P = 128
+            qp, kp, vp, op, dop = (_pad_heads(t, P) for t in (q4, k4, v4, o.view(B, S, H, D), do4))
+            dqp, dkp, dvp = torch.empty_like(qp), torch.empty_like(kp), torch.empty_like(vp)
+            dq_accum = torch.empty(B * S * H * P, device=qkv.device, dtype=torch.float32)
+            C.flash_attn_bwd(qp, kp, vp, op, dop, lse, dqp, dkp, dvp, dq_accum, delta, causal, scale,
+                             native.status_word(qkv.device))
+            dq4.copy_(dqp[..., :D])
+            dk4.copy_(dkp[..., :D])
+            dv4.copy_(dvp[..., :D])
         if theta > 0:
             flat = dqkv.view(B * S, W)
             C.rope(flat[:, : H * D].unflatten(-1, (H, D)), pos, theta, True)

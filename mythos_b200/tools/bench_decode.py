@@ -34,6 +34,7 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=0, help="use only this many layers (0 = all)")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0 = preset)")
     ap.add_argument("--repeat", type=int, default=3)
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "int8"], help="KV page storage")
     ap.add_argument("--no-graph", action="store_true", help="launch decode steps one by one (for launch lists)")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -57,7 +58,8 @@ def main(argv=None) -> int:
                        vocab_shard=cfg.vocab_size // world, max_batch=a.batch)
     torch.manual_seed(1234)
     # weights are created shard by shard directly in their storage format
-    eng = InferenceEngine.random(cfg, seed=1234, device=dev, max_batch=a.batch, max_seq_len=cfg.max_seq_len, tp=tp)
+    eng = InferenceEngine.random(cfg, seed=1234, device=dev, max_batch=a.batch, max_seq_len=cfg.max_seq_len, tp=tp,
+                                 kv_dtype=a.kv_dtype)
     wbytes = eng.weight_bytes()
     torch.cuda.empty_cache()
     g = torch.Generator().manual_seed(7)
@@ -79,7 +81,7 @@ def main(argv=None) -> int:
                           "prompt": a.prompt, "new_tokens": a.new, "layers": cfg.num_layers,
                           "full_depth": cfg.num_layers == NAMED_CONFIGS[a.preset]().num_layers, "decode_tok_s": max(rates), "decode_tok_s_runs": [round(r, 1) for r in rates],
                           "p50_ttft_s": ttfts[len(ttfts) // 2],
-                          "weight_bytes_per_rank": wbytes, "kv_bytes_per_rank": eng.cache.size_bytes(),
+                          "weight_bytes_per_rank": wbytes, "kv_bytes_per_rank": eng.cache.size_bytes(), "kv_dtype": a.kv_dtype,
                           "data": "random-init weights in format, uniform-random prompts, greedy"}))
     if world > 1:
         import torch.distributed as dist

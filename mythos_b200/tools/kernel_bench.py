@@ -172,8 +172,9 @@ def bench_dequant_gemm(t: Timer, fmt: str, M: int, N: int, K: int, group: int = 
     return ms, q.packed.numel() / ms / 1e6, "GB/s"
 
 
-def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int, splits: int = 0):
-    """Split-KV decode attention over 16-token pages; reported as KV bytes per second."""
+def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int, splits: int = 0, int8: bool = False):
+    """Split-KV decode attention over 16-token pages; reported as KV bytes per second (for int8
+    pages: the int8 rows plus their fp32 scales)."""
     from mythos_b200.ops import native
 
     C = native.require()
@@ -191,6 +192,24 @@ def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int, spl
     scratch = torch.empty(B * H * splits * (D + 2), device="cuda")
     counters = torch.zeros(B * Hkv + 64, device="cuda", dtype=torch.int32)
     st = native.status_word("cuda")
+    if int8:
+        k8 = torch.empty(n_pages, 16, Hkv, D, device="cuda", dtype=torch.int8)
+        v8 = torch.empty_like(k8)
+        ks = torch.empty(n_pages * 16, Hkv, device="cuda")
+        vs = torch.empty_like(ks)
+        # quantise the bf16 pages with the append kernel: token j of physical page p belongs to the
+        # sequence and logical page that map to p in the block table
+        flat = table.long().view(-1)
+        seq_of = torch.empty(n_pages, device="cuda", dtype=torch.int32)
+        lpage_of = torch.empty(n_pages, device="cuda", dtype=torch.int32)
+        seq_of[flat] = torch.arange(B, device="cuda", dtype=torch.int32).repeat_interleave(pages_per_seq)
+        lpage_of[flat] = torch.arange(pages_per_seq, device="cuda", dtype=torch.int32).repeat(B)
+        seq_ids = seq_of.repeat_interleave(16).contiguous()
+        pos = (lpage_of.repeat_interleave(16) * 16 + torch.arange(16, device="cuda", dtype=torch.int32).repeat(n_pages))
+        C.kv_append_int8(kc.view(-1, Hkv, D), vc.view(-1, Hkv, D), k8, v8, ks, vs, table, pos.contiguous(), seq_ids)
+        ms = graph_time(t, lambda: C.paged_attn_decode_int8(q, k8, v8, ks, vs, table, lens, out, scratch, counters,
+                                                            splits, D ** -0.5))
+        return ms, 2.0 * B * ctx * Hkv * (D + 4) / ms / 1e6, "GB/s"
     ms = graph_time(t, lambda: C.paged_attn_decode(q, kc, vc, table, lens, out, scratch, counters, splits,
                                                    D ** -0.5, st))
     return ms, 2.0 * B * ctx * Hkv * D * 2 / ms / 1e6, "GB/s"
@@ -259,12 +278,14 @@ def main():
         for fmt, M, N, K in [("oil8", 64, 28672, 4096), ("oil8", 64, 4096, 14336), ("oil4", 64, 6144, 4096),
                              ("oil4", 64, 4096, 4096), ("i2s", 8, 6912, 2560), ("oil8", 64, 128256, 4096)]:
             report(f"dequant_gemm_{fmt}_{M}x{N}x{K}", bench_dequant_gemm(t, fmt, M, N, K))
-    if k == "paged_decode":
-        report(f"paged_decode_b{args.batch}_ctx{args.ctx}_h{args.heads}_kv{hkv}_d{args.head_dim}_splits{args.splits}",
-               bench_paged_decode(t, args.batch, args.ctx, args.heads, hkv, args.head_dim, args.splits))
+    if k in ("paged_decode", "paged_decode_int8"):
+        report(f"{k}_b{args.batch}_ctx{args.ctx}_h{args.heads}_kv{hkv}_d{args.head_dim}_splits{args.splits}",
+               bench_paged_decode(t, args.batch, args.ctx, args.heads, hkv, args.head_dim, args.splits,
+                                  int8=k.endswith("int8")))
     if k == "all":
         for B, ctx, H, Hkv in [(64, 1024, 32, 8), (64, 1024, 4, 1), (8, 32768, 20, 20)]:
             report(f"paged_decode_b{B}_ctx{ctx}_h{H}_kv{Hkv}_d128", bench_paged_decode(t, B, ctx, H, Hkv, 128))
+        report("paged_decode_int8_b8_ctx32768_h32_kv8_d128", bench_paged_decode(t, 8, 32768, 32, 8, 128, int8=True))
     for name, r, d in [("rmsnorm", args.rows, args.dim), ("swiglu", args.rows, 11008), ("ce", 4096, 32000),
                        ("adamw", 16384, 4096), ("fake_quant", 16384, 4096)]:
         if k in (name, "all"):

@@ -62,6 +62,31 @@ except Exception as e:
 '''
 
 
+VOCAB_CE_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from mythos_b200.parallel.vocab_ce import vocab_parallel_cross_entropy
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+torch.manual_seed(0)
+rows, V = 24, 40 * world
+full = torch.randn(rows, V) * 3
+targets = torch.randint(-2, V + 3, (rows,), dtype=torch.int32)       # out-of-range ids are clamped
+ref_in = full.clone().requires_grad_(True)
+ref = torch.nn.functional.cross_entropy(ref_in, targets.long().clamp(0, V - 1))
+ref.backward()
+v = V // world
+shard = full[:, rank * v:(rank + 1) * v].clone().requires_grad_(True)
+loss = vocab_parallel_cross_entropy(shard, targets, dist.group.WORLD)
+loss.backward()
+ok = abs(loss.item() - ref.item()) < 1e-5 and torch.allclose(shard.grad, ref_in.grad[:, rank * v:(rank + 1) * v], atol=1e-6)
+flag = torch.tensor([1.0 if ok else 0.0]); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+if rank == 0 and flag.item() == 1.0:
+    print("VOCAB_CE_OK")
+dist.destroy_process_group()
+'''
+
+
 def _torchrun(n, code, port, timeout=240, extra_env=None):
     env = dict(os.environ, REPO_ROOT=ROOT, **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
@@ -73,6 +98,12 @@ def _torchrun(n, code, port, timeout=240, extra_env=None):
 def test_pipeline_1f1b_matches_single_process(stages):
     res = _torchrun(stages, PP_WORKER, 29700 + stages)
     assert "PP_OK" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_vocab_parallel_cross_entropy_matches_full_rows(world):
+    res = _torchrun(world, VOCAB_CE_WORKER, 29720 + world)
+    assert "VOCAB_CE_OK" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
 
 
 def test_missing_rank_is_detected_by_timeout_not_hang():

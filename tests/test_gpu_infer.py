@@ -325,3 +325,86 @@ def test_engine_greedy_matches_full_recompute():
             seq = torch.cat([seq, got[:, None]], dim=1)
     assert agree == B * new
     assert res.stats.ttft_s > 0 and res.stats.tokens_per_s > 0
+
+
+@pytest.mark.parametrize("fmt,K,bs", [("oil8", 4096, 256), ("oil4", 2048, 256), ("i2s", 2560, 256), ("oil8", 192, 64)])
+def test_embedding_gather_through_quantised_table(fmt, K, bs):
+    """Row gather that expands only the addressed rows, against the full dequantised table."""
+    from mythos_b200.infer.quant_weights import QuantLinear
+
+    g = torch.Generator(device="cuda").manual_seed(K)
+    V = 1000
+    table = QuantLinear.random(fmt, V, K, bs, 16, device="cuda", generator=g)
+    full = table.dequantize()
+    ids = torch.randint(-3, V + 3, (257,), device="cuda", dtype=torch.int32)
+    out = table.gather_rows(ids)
+    assert torch.equal(out, full[ids.long().clamp(0, V - 1)])
+    # into a strided destination (row stride larger than K)
+    wide = torch.zeros(ids.numel(), K + 64, device="cuda", dtype=torch.bfloat16)
+    table.gather_rows(ids, wide[:, :K])
+    assert torch.equal(wide[:, :K], out) and float(wide[:, K:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("H,Hkv,D,page", [(8, 2, 128, 16), (4, 4, 64, 16), (4, 1, 128, 32)])
+def test_int8_kv_append_and_decode(H, Hkv, D, page):
+    """int8 pages: the append kernel's scales and codes against abs-max / 127 rounding, and decode
+    attention over the int8 pages against fp32 attention over the dequantised values."""
+    from mythos_b200.ops import native, reference as ref
+
+    C = native.require()
+    torch.manual_seed(H + D + page)
+    B, max_pages = 3, 256 // page
+    lens = [37, 200, 1]
+    n_pages = B * max_pages
+    k8 = torch.randint(-128, 127, (n_pages, page, Hkv, D), device="cuda", dtype=torch.int8)   # stale contents
+    v8 = torch.randint(-128, 127, (n_pages, page, Hkv, D), device="cuda", dtype=torch.int8)
+    ksc = torch.rand(n_pages * page, Hkv, device="cuda")
+    vsc = torch.rand(n_pages * page, Hkv, device="cuda")
+    table = torch.randperm(n_pages).reshape(B, max_pages).to(torch.int32).cuda()
+    kd, vd = [], []
+    for b in range(B):
+        k = (torch.randn(lens[b], Hkv, D, device="cuda") * (1 + b)).to(torch.bfloat16)
+        v = torch.randn(lens[b], Hkv, D, device="cuda").to(torch.bfloat16)
+        if b == 0:
+            k[3, 0] = 0                      # an all-zero row quantises to zeros with scale 0
+        pos = torch.arange(lens[b], device="cuda", dtype=torch.int32)
+        sid = torch.full((lens[b],), b, device="cuda", dtype=torch.int32)
+        C.kv_append_int8(k, v, k8, v8, ksc, vsc, table, pos, sid)
+        rows = (table[b, (pos // page).long()].long() * page + (pos % page).long())
+        for src, q8, sc, sink in ((k, k8, ksc, kd), (v, v8, vsc, vd)):
+            amax = src.float().abs().amax(-1)
+            got_scale = sc[rows]
+            assert torch.allclose(got_scale, amax / 127.0, rtol=1e-6, atol=0)
+            deq = q8.view(-1, Hkv, D)[rows].float() * got_scale[..., None]
+            assert float((deq - src.float()).abs().max()) <= float(got_scale.max()) * 0.51 + 1e-6
+            sink.append(deq)
+    q = torch.randn(B, H, D, device="cuda").to(torch.bfloat16)
+    ctx = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    for splits in (1, 3):
+        out = torch.empty(B, H, D, device="cuda", dtype=torch.bfloat16)
+        scratch = torch.empty(B * H * splits * (D + 2), device="cuda")
+        counters = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
+        C.paged_attn_decode_int8(q, k8, v8, ksc, vsc, table, ctx, out, scratch, counters, splits, 1.0 / math.sqrt(D))
+        for b in range(B):
+            o, _ = ref.attention(q[b][None, None].float(), kd[b][None], vd[b][None], causal=False)
+            _close(out[b], o[0, 0], atol=2e-2)
+        assert int(counters.abs().sum()) == 0
+
+
+def test_engine_int8_kv_tracks_bf16_kv():
+    """Same weights, int8 against bf16 pages: the first decode steps pick (nearly) the same tokens."""
+    from mythos_b200.infer.engine import InferenceEngine
+    from mythos_b200.models import TransformerConfig
+
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=2, head_dim=128,
+                            ffn_hidden_size=512, max_seq_len=320, oil_block_size=256, codebook_group=2,
+                            embed_format="oil8")
+    prompts = torch.randint(0, cfg.vocab_size, (2, 128), generator=torch.Generator().manual_seed(3), dtype=torch.int32)
+    toks = {}
+    for kind in ("bf16", "int8"):
+        eng = InferenceEngine.random(cfg, seed=5, device="cuda", max_batch=4, max_seq_len=320, kv_dtype=kind)
+        assert eng.cache.int8 == (kind == "int8")
+        toks[kind] = eng.generate(prompts, max_new_tokens=6, use_graph=(kind == "int8")).tokens
+    assert eng.cache.size_bytes() < 0.6 * 2 * cfg.num_layers * eng.cache.k[0].numel() * 2
+    same = sum(a == b for ra, rb in zip(toks["bf16"], toks["int8"]) for a, b in zip(ra, rb))
+    assert same >= 6, toks
