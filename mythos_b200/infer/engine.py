@@ -140,6 +140,7 @@ class InferenceEngine:
         self._scratch = None
         self._counters = None
         self.fused_decode = True     # decode steps use the fused epilogue kernels when the model allows
+        self.last_prefix_hit = 0     # tokens of the latest start_sequence that came from shared pages
 
     # ------------------------------------------------------------------ weights
     @classmethod
@@ -515,26 +516,77 @@ class InferenceEngine:
 
     # ------------------------------------------------------------------ step-wise API (serving)
     @torch.no_grad()
+    def generate_stream(self, prompt_ids, detokenize, on_text, max_new_tokens: int = 32,
+                        sampler: SamplerConfig | None = None, eos_id: int | None = None) -> GenerationResult:
+        """One sequence, text delivered while it is generated: every sampled token goes through
+        ``detokenize(list[int]) -> str`` into a buffer that calls ``on_text`` when the text ends in
+        white space, punctuation, a closing bracket or a quote, and once more at the end (role of
+        the reference's ``generate_stream``, engines/inference/stream.cpp:35-48)."""
+        from .stream import StreamBuffer
+
+        buf = StreamBuffer(on_text)
+
+        def on_token(step, tok):
+            buf.append(detokenize([int(tok[0])]))
+
+        res = self.generate([list(prompt_ids)], max_new_tokens, sampler, stream_callback=on_token, eos_id=eos_id,
+                            use_graph=False)
+        buf.close()
+        return res
+
     def start_sequence(self, prompt_ids, reuse_prefix: bool = True):
         """Prefill one request. Returns ``(seq, logits)`` with the logits of the last prompt token
-        ([1, V]). A cached prefix (full pages of an earlier identical prompt head) is re-used only
-        when it covers the whole prompt but the last token, otherwise the prompt is recomputed."""
+        ([1, V]). With ``reuse_prefix`` the full pages of an earlier prompt with the same head are
+        mapped into the new sequence (their reference counts go up) and only the remaining tokens
+        are computed: their K/V are appended to fresh pages and their queries attend over the paged
+        cache (shared prefix + the new tokens before them) in chunks of at most ``max_batch``
+        tokens. Without a cached prefix the whole prompt runs through the flash-attention prefill."""
         ids = [int(t) for t in prompt_ids]
         cache = self.cache
         seq = cache.new_sequence()
-        cache.reserve(seq, len(ids))
-        cache.sync_tables()
         S = len(ids)
+        # at least the last token is always computed: its logits are the result
+        covered = cache.share_prefix(seq, ids[:-1]) if reuse_prefix and S > 1 else 0
+        cache.reserve(seq, S - covered)
+        cache.sync_tables()
         dev = self.device
         self._prepare_decode_scratch(self.max_batch, self.max_seq_len)
-        t = torch.tensor(ids, dtype=torch.int32, device=dev)
-        pos = torch.arange(S, device=dev, dtype=torch.int32)
-        sid = torch.full((S,), seq, device=dev, dtype=torch.int32)
-        h = self._forward(t, pos, sid, None, prefill_shape=(1, S))
-        cache.advance(seq, S)
+        self.last_prefix_hit = covered
+        if covered == 0:
+            t = torch.tensor(ids, dtype=torch.int32, device=dev)
+            pos = torch.arange(S, device=dev, dtype=torch.int32)
+            sid = torch.full((S,), seq, device=dev, dtype=torch.int32)
+            h = self._forward(t, pos, sid, None, prefill_shape=(1, S))
+            cache.advance(seq, S)
+        else:
+            h = self._extend_sequence(seq, ids[covered:])
         if reuse_prefix:
             cache.publish_prefix(seq, ids)
         return seq, self._logits(h[-1:].contiguous())
+
+    @torch.no_grad()
+    def _extend_sequence(self, seq: int, new_ids) -> torch.Tensor:
+        """Append ``new_ids`` to a sequence that already has tokens in the cache (pages reserved)
+        and return their hidden states. Token i of a chunk is a row of a decode batch whose block
+        table row is the sequence's and whose context length is its own position + 1, so the paged
+        decode kernel gives causal attention over prefix and chunk."""
+        cache, dev = self.cache, self.device
+        step = max(1, min(self.max_batch, ONESHOT_MAX_TOKENS))
+        h = None
+        for lo in range(0, len(new_ids), step):
+            chunk = new_ids[lo:lo + step]
+            n, base = len(chunk), cache.lens[seq]
+            t = torch.tensor(chunk, dtype=torch.int32, device=dev)
+            pos = torch.arange(base, base + n, device=dev, dtype=torch.int32)
+            rows = cache.block_table[seq:seq + 1].expand(n, -1).contiguous()
+            saved = cache.block_table
+            cache.block_table = rows
+            try:
+                h = self._forward(t, pos, torch.arange(n, device=dev, dtype=torch.int32), pos + 1, None)
+            finally:
+                cache.block_table = saved
+            cache.advance(seq, n)
+        return h
 
     @torch.no_grad()
     def decode(self, seqs, tokens):

@@ -24,12 +24,14 @@ class PageAllocator:
         self.num_pages = num_pages
         self.free = list(range(num_pages - 1, -1, -1))
         self.refs = [0] * num_pages
+        self.gen = [0] * num_pages      # bumped on every allocation: tells a re-used page from the original
 
     def alloc(self) -> int:
         if not self.free:
             raise MemoryError("KV cache is out of pages")
         p = self.free.pop()
         self.refs[p] = 1
+        self.gen[p] += 1
         return p
 
     def retain(self, p: int) -> None:
@@ -120,8 +122,11 @@ class PagedKVCache:
         reference counts go up) and return the number of tokens covered; else 0."""
         n_full = len(tokens) // self.page_size
         for n in range(n_full, 0, -1):
-            pages = self.prefix_index.get(self._prefix_key(tokens[: n * self.page_size]))
-            if pages is not None and all(self.alloc.refs[p] > 0 for p in pages):
+            entry = self.prefix_index.get(self._prefix_key(tokens[: n * self.page_size]))
+            # an entry is valid while every page is still held by someone and has not been handed
+            # out again since it was published
+            if entry is not None and all(self.alloc.refs[p] > 0 and self.alloc.gen[p] == g for p, g in entry):
+                pages = [p for p, _ in entry]
                 for i, p in enumerate(pages):
                     self.alloc.retain(p)
                     self.block_table_host[seq, i] = p
@@ -135,7 +140,7 @@ class PagedKVCache:
         if n_full == 0:
             return
         pages = [int(self.block_table_host[seq, i]) for i in range(n_full)]
-        self.prefix_index[self._prefix_key(tokens[: n_full * self.page_size])] = pages
+        self.prefix_index[self._prefix_key(tokens[: n_full * self.page_size])] = [(p, self.alloc.gen[p]) for p in pages]
         while len(self.prefix_index) > max_entries:
             self.prefix_index.popitem(last=False)
 

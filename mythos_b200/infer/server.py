@@ -204,9 +204,16 @@ class GenerationBackend:
         return bytes(i & 0xFF for i in ids).decode("utf-8", errors="replace")
 
     def stream(self, prompt: str, max_tokens: int = 64, temperature: float = 0.0, top_k: int = 40, top_p: float = 0.9,
-               seed: int = 0):
-        """Yields text pieces. Without a model it echoes the prompt word by word (what a server
-        started for tests without weights can do)."""
+               seed: int = 0, flush: str = "token"):
+        """Yields text pieces. ``flush="punctuation"`` regroups them so that a piece ends at white
+        space, punctuation, a closing bracket or a quote (the reference's stream buffer). Without a
+        model it echoes the prompt word by word (what a server started for tests without weights
+        can do)."""
+        if flush == "punctuation":
+            from .stream import buffered
+
+            yield from buffered(self.stream(prompt, max_tokens, temperature, top_k, top_p, seed))
+            return
         if self.model is None:
             for w in prompt.split()[:max_tokens]:
                 yield w + " "
@@ -215,6 +222,9 @@ class GenerationBackend:
 
         from .sampler import SamplerConfig, sample
 
+        from .stream import Utf8Assembler
+
+        utf8 = Utf8Assembler()
         cfg = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p, seed=seed)
         vocab = self.model.cfg.vocab_size
         ids = [min(t, vocab - 1) for t in self.encode(prompt)] or [0]
@@ -226,7 +236,16 @@ class GenerationBackend:
                 lg = logits.to(torch.bfloat16).contiguous() if logits.is_cuda else logits.float()
                 tok = sample(lg, cfg, step=step).to(torch.int32)
                 seq = torch.cat([seq, tok.view(1, 1).to(dev)], dim=1)
-                yield self.decode([int(tok[0])])
+                if self.tokenizer is not None:
+                    yield self.decode([int(tok[0])])
+                else:                      # byte-level ids: hold back unfinished multi-byte characters
+                    piece = utf8.feed(bytes([int(tok[0]) & 0xFF]))
+                    if piece:
+                        yield piece
+            if self.tokenizer is None:
+                tail = utf8.finish()
+                if tail:
+                    yield tail
 
     def complete(self, prompt: str, **kw) -> str:
         return "".join(self.stream(prompt, **kw))
@@ -289,6 +308,8 @@ def _make_handler(server: "HTTPServer"):
                 return
             kw = dict(max_tokens=int(req.get("max_tokens", 64)), temperature=float(req.get("temperature", 0.0)),
                       top_k=int(req.get("top_k", 40)), top_p=float(req.get("top_p", 0.9)), seed=int(req.get("seed", 0)))
+            if req.get("stream_flush") in ("token", "punctuation"):
+                kw["flush"] = req["stream_flush"]
             prompt = str(req.get("prompt", ""))
             if req.get("stream"):
                 self.send_response(200)

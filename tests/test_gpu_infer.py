@@ -408,3 +408,35 @@ def test_engine_int8_kv_tracks_bf16_kv():
     assert eng.cache.size_bytes() < 0.6 * 2 * cfg.num_layers * eng.cache.k[0].numel() * 2
     same = sum(a == b for ra, rb in zip(toks["bf16"], toks["int8"]) for a, b in zip(ra, rb))
     assert same >= 6, toks
+
+
+@pytest.mark.parametrize("kv_dtype", ["bf16", "int8"])
+def test_prefix_pages_are_shared_and_suffix_attends_over_them(kv_dtype):
+    """A second request with the same prompt head maps the cached pages and computes only the
+    rest through paged attention; its logits match a full recompute."""
+    from mythos_b200.infer.engine import InferenceEngine
+    from mythos_b200.models import TransformerConfig
+
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=2, head_dim=128,
+                            ffn_hidden_size=512, max_seq_len=512, oil_block_size=256, codebook_group=2)
+    eng = InferenceEngine.random(cfg, seed=11, device="cuda", max_batch=8, max_seq_len=512, kv_dtype=kv_dtype)
+    g = torch.Generator().manual_seed(1)
+    head = torch.randint(0, 512, (150,), generator=g).tolist()
+    a, b = head + [5, 6, 7], head + [9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20]
+    sa, la = eng.start_sequence(a)
+    assert eng.last_prefix_hit == 0
+    used = eng.cache.alloc.used
+    sb, lb = eng.start_sequence(b)                     # 150 // 16 = 9 full pages are shared
+    assert eng.last_prefix_hit == 144
+    assert eng.cache.alloc.used == used + (len(b) + 15) // 16 - 9
+    sc, lc = eng.start_sequence(b, reuse_prefix=False)  # full recompute of the same prompt
+    assert eng.last_prefix_hit == 0
+    tol = 6e-2 if kv_dtype == "bf16" else 1.5e-1
+    assert float((lb.float() - lc.float()).abs().max()) < tol
+    assert int(lb.float().argmax()) == int(lc.float().argmax()) or float((lb.float() - lc.float()).abs().max()) < 2e-2
+    # both sequences keep decoding after the shared pages
+    nb = eng.decode([sb, sc], [int(lb.float().argmax()), int(lc.float().argmax())])
+    assert float((nb[0].float() - nb[1].float()).abs().max()) < 2 * tol
+    for s in (sa, sb, sc):
+        eng.release(s)
+    assert eng.cache.alloc.used == 0

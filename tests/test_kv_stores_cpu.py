@@ -51,3 +51,34 @@ def test_sparse_store_spills_and_reloads(tmp_path):
         assert False
     except ValueError:
         pass
+
+
+def test_paged_cache_prefix_sharing_and_recycled_pages():
+    from mythos_b200.infer.kv_paged import PagedKVCache
+
+    c = PagedKVCache(num_layers=1, kv_heads=1, head_dim=8, num_pages=8, page_size=4, max_seqs=4, max_pages_per_seq=4,
+                     device="cpu", dtype=torch.float32)
+    toks = list(range(10))
+    a = c.new_sequence()
+    c.reserve(a, len(toks))
+    c.advance(a, len(toks))
+    c.publish_prefix(a, toks)                       # two full pages
+    assert c.alloc.used == 3
+    b = c.new_sequence()
+    assert c.share_prefix(b, toks[:9]) == 8 and c.lens[b] == 8
+    pages_a = [int(p) for p in c.block_table_host[a][:2]]
+    assert [int(p) for p in c.block_table_host[b][:2]] == pages_a and all(c.alloc.refs[p] == 2 for p in pages_a)
+    c.reserve(b, 2)
+    assert c.alloc.used == 4
+    c.free_sequence(a)
+    assert all(c.alloc.refs[p] == 1 for p in pages_a)   # still held by b
+    c.free_sequence(b)
+    assert c.alloc.used == 0
+    # the pages go to someone else: the published entry must not match them any more
+    d = c.new_sequence()
+    c.reserve(d, 16)
+    e = c.new_sequence()
+    assert c.share_prefix(e, toks[:9]) == 0
+    # int8 pages carry scales and count them
+    q = PagedKVCache(1, 2, 64, 4, 16, 2, 2, device="cpu", dtype=torch.int8)
+    assert q.int8 and q.k_scale[0].shape == (64, 2) and q.size_bytes() == 2 * (4 * 16 * 2 * 64 + 64 * 2 * 4)

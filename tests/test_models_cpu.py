@@ -219,3 +219,38 @@ def test_codebook_kmeans_ema_and_serialisation():
     ema = cbk.EMAState(books, decay=0.5)
     ema.update(books, torch.ones(1, 256), books * 2)
     assert torch.allclose(books, torch.sort(q * 2).values[None])
+
+
+def test_qlora_nf4_base_is_frozen_and_adapter_trains():
+    from mythos_b200.models.lora import NF4_LEVELS, QLoRALinear, nf4_dequantize, nf4_quantize
+
+    torch.manual_seed(0)
+    w = torch.randn(48, 128) * 0.05
+    packed, lo, hi = nf4_quantize(w, 64)
+    assert packed.dtype == torch.uint8 and packed.numel() == w.numel() // 2 and lo.numel() == w.numel() // 64
+    deq = nf4_dequantize(packed, lo, hi, w.numel(), 64).view_as(w)
+    # every block reproduces its extremes exactly (levels -1 and +1 map onto min and max)
+    blocks, dblocks = w.view(-1, 64), deq.view(-1, 64)
+    assert torch.allclose(dblocks.amax(1), blocks.amax(1)) and torch.allclose(dblocks.amin(1), blocks.amin(1))
+    # nearest-level error is at most half the widest gap between levels, scaled to the block range
+    gaps = torch.tensor(NF4_LEVELS).diff().max() / 2
+    assert float(((deq - w).abs().view(-1, 64) / ((hi - lo)[:, None] / 2)).max()) <= float(gaps) + 1e-6
+    q = QLoRALinear(w, rank=4, alpha=8.0)
+    assert q.base_bytes() < w.numel() * 4 / 6
+    x = torch.randn(5, 128)
+    assert torch.allclose(q(x), x @ q.base_weight().T, atol=1e-5)          # B = 0 at the start
+    before = q.packed.clone()
+    tgt = torch.randn(5, 48)
+    opt = torch.optim.Adam([p for p in q.parameters() if p.requires_grad], lr=1e-2)
+    first = None
+    for _ in range(40):
+        loss = ((q(x) - tgt) ** 2).mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        first = first if first is not None else loss.item()
+    assert loss.item() < 0.5 * first and torch.equal(q.packed, before)
+    assert torch.allclose(x @ q.merged_weight().T, q(x), atol=1e-4)
+    other = QLoRALinear(torch.zeros_like(w), rank=4, alpha=8.0)
+    other.load_adapter_state(q.adapter_state("m."), "m.")
+    assert torch.allclose(other(x), q(x), atol=1e-6)

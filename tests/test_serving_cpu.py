@@ -220,3 +220,35 @@ def test_tokenizer_metrics_importers_planner_eval(tmp_path):
     assert eval_classification([0, 1, 1], [0, 1, 0])["accuracy"] == pytest.approx(2 / 3)
     r = eval_perplexity(_tiny(), torch.randint(0, 256, (90,)), context=32, stride=16)
     assert r["tokens"] == 89 and r["perplexity"] > 1
+
+
+def test_stream_buffer_flushes_at_breaks_and_keeps_the_tail():
+    from mythos_b200.infer.stream import StreamBuffer, Utf8Assembler, buffered
+
+    got = []
+    buf = StreamBuffer(got.append)
+    for piece in ["Hel", "lo", ",", " wor", "ld", "!", " (ok", ")", " tail"]:
+        buf.append(piece)
+    assert got == ["Hello,", " world!", " (ok)"]
+    buf.close()
+    assert got[-1] == " tail" and buf.buffer == ""
+    assert list(buffered(iter(["a", "b ", "c"]))) == ["ab ", "c"]
+    long = StreamBuffer(got.append, max_chars=4)
+    long.append("abcdef")
+    assert got[-1] == "abcdef"
+    # a multi-byte character split over two chunks comes out whole
+    asm = Utf8Assembler()
+    raw = "naïve ☃".encode("utf-8")
+    text = "".join(asm.feed(raw[i:i + 1]) for i in range(len(raw))) + asm.finish()
+    assert text == "naïve ☃"
+    assert Utf8Assembler().feed(b"\xe2\x98") == ""
+
+
+def test_backend_stream_regroups_at_punctuation():
+    from mythos_b200.infer.server import GenerationBackend
+
+    be = GenerationBackend()                      # no model: echoes the prompt word by word
+    plain = list(be.stream("one two, three", max_tokens=8))
+    grouped = list(be.stream("one two, three", max_tokens=8, flush="punctuation"))
+    assert "".join(plain) == "".join(grouped)
+    assert all(g[-1] in " ,.!?" for g in grouped)
