@@ -28,6 +28,7 @@ import torch
 from ..models.config import TransformerConfig
 from ..ops import functional as F
 from ..ops import native
+from ..utils import trace
 from .kv_paged import PagedKVCache
 from .quant_weights import QFMT, QuantLinear, reserve_accumulator
 from .sampler import SamplerConfig, sample
@@ -451,9 +452,10 @@ class InferenceEngine:
         # ---- prefill
         ids_d = ids.to(dev).reshape(-1)
         pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
-        h = self._forward(ids_d, pos, seq_t.repeat_interleave(S), None, prefill_shape=(B, S))
-        last = h.view(B, S, -1)[:, -1, :].contiguous()
-        tok = sample(self._logits(last), sampler, step=0)
+        with trace.span("prefill", dev):
+            h = self._forward(ids_d, pos, seq_t.repeat_interleave(S), None, prefill_shape=(B, S))
+            last = h.view(B, S, -1)[:, -1, :].contiguous()
+            tok = sample(self._logits(last), sampler, step=0)
         for s in seqs:
             cache.advance(s, S)
         torch.cuda.synchronize(dev)

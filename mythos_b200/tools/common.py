@@ -10,11 +10,30 @@ from ..models.config import NAMED_CONFIGS, TransformerConfig
 
 
 def pick_device(arg: str | None) -> torch.device:
+    """``auto`` -> the CUDA device named by ``OIL_GPU_DEVICE`` (default 0) when there is one, else
+    the CPU; a number -> that CUDA device; anything else is passed to ``torch.device``."""
     if arg in (None, "", "auto"):
-        return torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        from ..utils import env
+
+        return env.current().default_device()
     if arg.isdigit():
         return torch.device("cuda", int(arg))
     return torch.device(arg)
+
+
+def runtime_setup(seed_default: int | None = None):
+    """Read the documented ``OIL_*`` variables and make them take effect (threads, log level,
+    verbose range timing, seed). Returns the settings; ``seed_default`` is the tool's own default
+    seed, which ``OIL_SEED`` replaces when it is set."""
+    import os
+
+    from ..utils import env
+
+    env.reset()
+    rt = env.current()
+    if seed_default is not None and "OIL_SEED" not in os.environ:
+        rt.seed = seed_default
+    return rt.apply()
 
 
 def load_json_config(path: str | None) -> dict:

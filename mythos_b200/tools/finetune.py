@@ -22,7 +22,7 @@ def main(argv=None) -> int:
     from ..train.bpe import BPETokenizer
     from ..train.data import TokenDataset
     from ..train.trainer import TrainConfig, Trainer
-    from .common import pick_device
+    from .common import pick_device, runtime_setup
 
     ap = argparse.ArgumentParser(prog="oil-finetune", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -42,8 +42,11 @@ def main(argv=None) -> int:
     ap.add_argument("--grad-threshold", type=float, default=0.0)
     ap.add_argument("--log-interval", type=int, default=10)
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
-    ap.add_argument("--seed", type=int, default=42)
+    ap.add_argument("--seed", type=int, default=None, help="default: OIL_SEED, else 42")
     a = ap.parse_args(argv)
+    rt = runtime_setup(seed_default=42)
+    if a.seed is None:
+        a.seed = rt.seed
     device = pick_device(a.device)
     torch.manual_seed(a.seed)
     model, _ = load_model(a.model, device=device)

@@ -27,7 +27,7 @@ def build_parser():
     ap.add_argument("--top-k", type=int, default=40)
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--repetition-penalty", type=float, default=1.0)
-    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--seed", type=int, default=None, help="default: OIL_SEED, else 0")
     ap.add_argument("--batch-size", type=int, default=1)
     ap.add_argument("--output", "-o", default=None)
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
@@ -80,9 +80,12 @@ def main(argv=None) -> int:
     from ..infer.sampler import SamplerConfig
     from ..oil.model_io import load_model
     from ..train.bpe import BPETokenizer
-    from .common import pick_device
+    from .common import pick_device, runtime_setup
 
     args = build_parser().parse_args(argv)
+    rt = runtime_setup(seed_default=0)
+    if args.seed is None:
+        args.seed = rt.seed
     path = args.model or args.model_pos
     if not path:
         print("usage: oil-infer <model.oil> [prompt]", file=sys.stderr)

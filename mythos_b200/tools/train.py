@@ -48,7 +48,7 @@ def build_parser():
     ap.add_argument("--save-interval", type=int, default=0)
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
     ap.add_argument("--resume", default=None)
-    ap.add_argument("--seed", type=int, default=42)
+    ap.add_argument("--seed", type=int, default=None, help="default: OIL_SEED, else 42")
     ap.add_argument("--logdir", default=None, help="write TensorBoard events + JSONL here")
     ap.add_argument("--verbose", action="store_true")
     return ap
@@ -60,9 +60,12 @@ def main(argv=None) -> int:
     from ..train.bpe import BPETokenizer
     from ..train.data import TokenDataset, ZipfStream
     from ..train.trainer import TrainConfig, Trainer
-    from .common import load_json_config, model_config_from, pick_device
+    from .common import load_json_config, model_config_from, pick_device, runtime_setup
 
     args = build_parser().parse_args(argv)
+    rt = runtime_setup(seed_default=42)
+    if args.seed is None:
+        args.seed = rt.seed
     cfgj = load_json_config(args.config)
     tj = cfgj.get("training", {})
     device = pick_device(args.device)
@@ -125,6 +128,10 @@ def main(argv=None) -> int:
     for w in writers:
         w.close()
     print(f"saved {args.model} sha256 {file_sha256(args.model)} final loss {metrics.loss:.4f}")
+    if rt.verbose:      # OIL_VERBOSE=1: device time per phase, from CUDA events recorded around the ranges
+        from ..utils import trace
+
+        print(trace.format_summary(trace.summary()))
     return 0
 
 

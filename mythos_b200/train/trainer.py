@@ -29,6 +29,7 @@ import torch
 from ..models.layers import OILLinear
 from ..ops import functional as F
 from ..ops import native
+from ..utils import trace
 from . import sched
 from .param_store import ParamStore
 
@@ -115,7 +116,8 @@ class Trainer:
         tokens = ids.numel() * (self.dp.world_size if self.dp is not None else 1)
         loss_scale = 1.0 / tokens
         if self._stale:
-            self._refresh()
+            with trace.span("requantize", self.device):
+                self._refresh()
         st.zero_grad()
         total = None
         for i in range(n_micro):
@@ -124,18 +126,21 @@ class Trainer:
             if xi.device != self.device:
                 xi = xi.to(self.device, non_blocking=True)
                 ti = ti.to(self.device, non_blocking=True)
-            loss = self.model(xi, ti, loss_scale=loss_scale)
-            loss.backward()
+            with trace.span("forward", self.device):
+                loss = self.model(xi, ti, loss_scale=loss_scale)
+            with trace.span("backward", self.device):
+                loss.backward()
             if not st.bound:
                 st.gather_autograd_grads()
             total = loss.detach() if total is None else total + loss.detach()
         self.step += 1
         lr = self.current_lr()
-        if self.dp is not None:
-            self.dp.step(self, lr)
-            total = self.dp.all_reduce_scalar(total)
-        else:
-            self._local_optimizer_step(lr, 0, st.total)
+        with trace.span("optimizer", self.device):
+            if self.dp is not None:
+                self.dp.step(self, lr)
+                total = self.dp.all_reduce_scalar(total)
+            else:
+                self._local_optimizer_step(lr, 0, st.total)
         self._stale = True
         if cfg.codebook_ema_interval and self.step % cfg.codebook_ema_interval == 0:
             self.update_codebooks()

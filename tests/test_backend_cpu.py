@@ -25,3 +25,36 @@ def test_host_backend_ops_and_probe():
     assert sel.name in ("host-fp32", "b200-sm100a")
     r = bk.benchmark_operation(b, "gemm", 64, 2)
     assert r["gflops"] > 0 and bk.benchmark_operation(b, "add", 64, 2)["gbs"] > 0
+
+
+def test_runtime_environment_variables_take_effect():
+    import logging
+
+    from mythos_b200.utils import env, trace
+
+    rt = env.RuntimeEnv.from_environ({"OIL_NUM_THREADS": "3", "OIL_SEED": "7", "OIL_LOG_LEVEL": "DEBUG",
+                                      "OIL_VERBOSE": "1", "OIL_GPU_DEVICE": "5", "OIL_MEMORY_POOL_SIZE": "junk"})
+    assert (rt.num_threads, rt.seed, rt.log_level, rt.verbose, rt.gpu_device) == (3, 7, "debug", True, 5)
+    assert rt.memory_pool_size == 64 << 20                   # unparsable values fall back to the default
+    before = torch.get_num_threads()
+    try:
+        rt.apply()
+        assert torch.get_num_threads() == 3 and trace.timing_enabled()
+        assert logging.getLogger("mythos_b200").level == logging.DEBUG
+        a = torch.rand(4)
+        rt.apply()
+        assert torch.equal(a, torch.rand(4))                 # the seed is applied
+        assert rt.default_device().type == ("cuda" if torch.cuda.is_available() else "cpu")
+        with trace.span("outer"):
+            with trace.span("inner"):
+                torch.ones(10).sum()
+        with trace.span("inner"):
+            pass
+        rows = trace.summary()
+        assert rows["inner"]["calls"] == 2 and rows["outer"]["calls"] == 1 and rows["outer"]["ms"] >= 0
+        assert "inner" in trace.format_summary(rows) and trace.summary() == {}
+    finally:
+        torch.set_num_threads(before)
+        trace.enable_timing(False)
+        logging.getLogger("mythos_b200").setLevel(logging.NOTSET)
+    assert env.RuntimeEnv.from_environ({}).seed == 42
