@@ -149,6 +149,19 @@ def build_host(verbose: bool = False) -> Path:
     return target
 
 
+def build_host_sanitized(out_dir) -> Path:
+    """The host runtime with AddressSanitizer and UndefinedBehaviorSanitizer (the reference's
+    ``-DOIL_SANITIZE=ON``, cmake/compiler.cmake:8-11). Load it through ``MYTHOS_HOST_LIB`` in a
+    process started with ``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``."""
+    hdir = CSRC / "host"
+    target = Path(out_dir) / "liboil_host_asan.so"
+    srcs = sorted(hdir.glob("*.cpp"))
+    _run(["g++", "-O1", "-g", "-std=c++17", "-fPIC", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+          "-fno-sanitize-recover=undefined", "-I", str(hdir), "-shared", "-o", str(target), *map(str, srcs), "-lpthread",
+          "-ldl"])
+    return target
+
+
 def build_capi(verbose: bool = False) -> Path:
     """C API (oil_model_load / oil_generate): a bridge library that embeds or joins CPython."""
     target = PKG / "liboil_capi.so"

@@ -15,7 +15,9 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "liboil_host.so")
+        # MYTHOS_HOST_LIB points at another build of the same library (the sanitizer build in the tests)
+        path = os.environ.get("MYTHOS_HOST_LIB") or os.path.join(
+            os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "liboil_host.so")
         if not os.path.exists(path):
             raise RuntimeError("liboil_host.so is not built; run `python -m mythos_b200.build`")
         L = ctypes.CDLL(path)

@@ -440,3 +440,53 @@ def test_prefix_pages_are_shared_and_suffix_attends_over_them(kv_dtype):
     for s in (sa, sb, sc):
         eng.release(s)
     assert eng.cache.alloc.used == 0
+
+
+def test_repeated_launches_are_bit_identical():
+    """Race check by repetition: kernels whose warps hand data to each other through shared-memory
+    rings and barriers (dequant GEMM, flash attention, paged decode with a split merge) must give
+    the same bits for the same inputs on every launch."""
+    from mythos_b200.infer.quant_weights import QuantLinear
+    from mythos_b200.ops import native
+
+    C = native.require()
+    st = native.status_word("cuda")
+    torch.manual_seed(0)
+
+    def repeat(fn, n):
+        ref = fn().clone()
+        return sum(0 if torch.equal(fn(), ref) else 1 for _ in range(n))
+
+    for fmt, M, N, K in [("oil8", 256, 256, 512), ("oil4", 2, 512, 256), ("i2s", 200, 384, 512), ("oil8", 64, 1024, 2048)]:
+        q = QuantLinear.from_float(torch.randn(N, K, device="cuda") * 0.02, fmt, block_size=256, codebook_group=2)
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        assert repeat(lambda: q.matmul(x, out=out, k_splits=1), 300) == 0, (fmt, M, N, K)
+    B, S, H, D = 2, 256, 2, 128
+    qkv = (torch.randn(B, S, 3 * H * D, device="cuda") * 0.5).to(torch.bfloat16)
+    q4, k4, v4 = (qkv[..., i * H * D:(i + 1) * H * D].unflatten(-1, (H, D)) for i in range(3))
+    o = torch.empty(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, H, S, device="cuda", dtype=torch.float32)
+
+    def fwd():
+        C.flash_attn_fwd(q4, k4, v4, o, lse, True, 1 / math.sqrt(D), st)
+        return o
+
+    assert repeat(fwd, 100) == 0
+    Hkv, page, ctx_len = 2, 16, 700
+    n_pages = 2 * 64
+    kc = torch.randn(n_pages, page, Hkv, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(n_pages, page, Hkv, D, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(2, 64)
+    lens = torch.tensor([ctx_len, 333], device="cuda", dtype=torch.int32)
+    qd = torch.randn(2, 4, D, device="cuda").to(torch.bfloat16)
+    od = torch.empty_like(qd)
+    scratch = torch.empty(2 * 4 * 4 * (D + 2), device="cuda")
+    counters = torch.zeros(2 * Hkv, device="cuda", dtype=torch.int32)
+
+    def dec():
+        C.paged_attn_decode(qd, kc, vc, table, lens, od, scratch, counters, 4, 1 / math.sqrt(D), st)
+        return od
+
+    assert repeat(dec, 200) == 0
+    native.check_status("cuda")

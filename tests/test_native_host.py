@@ -1,6 +1,7 @@
 """The C++ host runtime against its Python twins: container reader/writer, SHA-256, sidecar check,
 BPE, RNG, page allocator."""
 import hashlib
+import os
 
 import numpy as np
 import pytest
@@ -98,3 +99,106 @@ def test_native_rng_and_pages():
     assert got == {0, 1, 2}
     with pytest.raises(MemoryError):
         pages.alloc()
+
+
+ASAN_WORKER = r'''
+import os, random, sys
+import numpy as np
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from mythos_b200.oil import native_io
+from mythos_b200.oil.container import OILError
+
+work = sys.argv[1]
+assert native_io.lib()._name.endswith("liboil_host_asan.so")     # the sanitizer build is the one in use
+random.seed(0)
+opened = rejected = 0
+
+def try_read(path):
+    global opened, rejected
+    try:
+        r = native_io.NativeReader(path)
+    except OILError:
+        rejected += 1
+        return
+    opened += 1
+    try:
+        for name in r.tensor_names():
+            try:
+                r.read_tensor(name)
+                r.tensor_sha256(name)
+            except OILError:
+                pass
+    finally:
+        r.close()
+
+for fname in sorted(os.listdir(work)):
+    if not fname.endswith(".oil"):
+        continue
+    raw = open(os.path.join(work, fname), "rb").read()
+    try_read(os.path.join(work, fname))
+    cuts = sorted(set(list(range(0, min(len(raw), 160), 3)) + [len(raw) * i // 23 for i in range(23)] + [len(raw) - 1]))
+    for cut in cuts:                                   # truncation anywhere must be an error, not a bad read
+        p = os.path.join(work, "cut.bin")
+        open(p, "wb").write(raw[:cut])
+        try_read(p)
+    for _ in range(150):                               # corrupt sizes / counts / offsets in the tables
+        b = bytearray(raw)
+        pos = random.randrange(0, min(len(b), 400))
+        b[pos] = random.choice([0x00, 0xFF, 0x7F, 0x80, b[pos] ^ (1 << random.randrange(8))])
+        p = os.path.join(work, "flip.bin")
+        open(p, "wb").write(bytes(b))
+        try_read(p)
+    idx = os.path.join(work, fname + "idx")
+    if os.path.exists(idx):
+        rawi = open(idx, "rb").read()
+        for cut in range(0, len(rawi), 7):
+            p = os.path.join(work, "cut.oilidx")
+            open(p, "wb").write(rawi[:cut])
+            try:
+                native_io.idx_check(p)
+            except OILError:
+                pass
+text = (b"the quick brown fox jumps over the lazy dog. " * 40) + bytes(range(256))
+bpe = native_io.NativeBPE.train(text, 300)
+assert bpe.decode(bpe.encode(text)) == text
+assert bpe.decode(bpe.encode(b"")) == b""
+rng = native_io.NativeRNG(7)
+assert rng.fill_uniform(1000, -1.0, 1.0).shape == (1000,)
+pool = native_io.NativePageAllocator(4)
+pages = [pool.alloc() for _ in range(4)]
+for p in pages:
+    pool.release(p)
+assert pool.used == 0
+assert native_io.sha256(b"abc").hex().startswith("ba7816bf")
+print("ASAN_OK", opened, rejected)
+'''
+
+
+def test_host_runtime_under_address_and_ub_sanitizers(tmp_path):
+    """Truncated and bit-flipped containers, sidecars, BPE, RNG and the page pool through the host
+    library built with -fsanitize=address,undefined: every malformed file must end in an OILError
+    (or a clean read), never in an out-of-bounds access."""
+    import subprocess
+    import sys
+
+    from mythos_b200 import build
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.oil.model_io import save_model
+
+    asan = subprocess.run(["gcc", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    if not os.path.isabs(asan) or not os.path.exists(asan):
+        pytest.skip("no AddressSanitizer runtime in this toolchain")
+    lib = build.build_host_sanitized(tmp_path)
+    torch.manual_seed(0)
+    work = tmp_path / "files"
+    work.mkdir()
+    for fmt in ("oil8", "oil4", "i2s", "fp16"):
+        cfg = TransformerConfig(vocab_size=32, hidden_size=32, num_layers=1, num_heads=2, head_dim=16,
+                                ffn_hidden_size=64, max_seq_len=16, weight_format=fmt, oil_block_size=32)
+        save_model(DenseModel(cfg), str(work / f"{fmt}.oil"))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, REPO_ROOT=root, LD_PRELOAD=asan, MYTHOS_HOST_LIB=str(lib),
+               ASAN_OPTIONS="detect_leaks=0:abort_on_error=0:exitcode=66", UBSAN_OPTIONS="halt_on_error=1:exitcode=67")
+    res = subprocess.run([sys.executable, "-c", ASAN_WORKER, str(work)], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0 and "ASAN_OK" in res.stdout, res.stdout[-1500:] + res.stderr[-4000:]
