@@ -531,20 +531,30 @@ void sum_residual_rmsnorm(OptTensor acc, const OptTensor& slots, int64_t n_slots
                            (int)dim, (float)eps, cur_stream());
 }
 void qkv_rope_append(Tensor& acc, const Tensor& pos, const Tensor& seq_ids, const Tensor& block_table, Tensor& q_out,
-                     Tensor& k_cache, Tensor& v_cache, double theta) {
+                     Tensor& k_cache, Tensor& v_cache, double theta, OptTensor k_scale, OptTensor v_scale) {
   chk_c(acc, F32, "acc");
   chk_c(pos, I32, "pos");
   chk_c(seq_ids, I32, "seq_ids");
   chk_c(block_table, I32, "block_table");
   chk_c(q_out, BF16, "q_out");
-  chk_c(k_cache, BF16, "k_cache");
-  chk_c(v_cache, BF16, "v_cache");
+  const bool int8 = k_scale.has_value();
+  TORCH_CHECK(int8 == v_scale.has_value(), "qkv_rope_append: give both scale tensors or neither");
+  chk_c(k_cache, int8 ? torch::kInt8 : BF16, "k_cache");
+  chk_c(v_cache, int8 ? torch::kInt8 : BF16, "v_cache");
   const int64_t T = q_out.size(0), H = q_out.size(1), D = q_out.size(2), Hkv = k_cache.size(2);
   TORCH_CHECK(acc.numel() == T * (H + 2 * Hkv) * D, "qkv_rope_append: accumulator shape mismatch");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(3) == D, "qkv_rope_append: cache must be [pages, page, kv_heads, D]");
+  if (int8) {
+    chk_c(*k_scale, F32, "k_scale");
+    chk_c(*v_scale, F32, "v_scale");
+    const int64_t rows = k_cache.size(0) * k_cache.size(1) * Hkv;
+    TORCH_CHECK(k_scale->numel() == rows && v_scale->numel() == rows, "qkv_rope_append: one scale per (token, kv head)");
+  }
   c10::cuda::CUDAGuard guard(acc.device());
   mb::qkv_rope_append(acc.data_ptr<float>(), pos.data_ptr<int>(), seq_ids.data_ptr<int>(), block_table.data_ptr<int>(),
                       q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), (int)T, (int)H, (int)Hkv, (int)D,
-                      (int)k_cache.size(1), (int)block_table.size(1), (float)theta, cur_stream());
+                      (int)k_cache.size(1), (int)block_table.size(1), (float)theta, cur_stream(),
+                      int8 ? k_scale->data_ptr<float>() : nullptr, int8 ? v_scale->data_ptr<float>() : nullptr);
 }
 void finalize_gate(Tensor& acc, Tensor& out, int64_t kind) {
   chk_c(acc, F32, "acc");
@@ -659,7 +669,8 @@ void kv_append_int8(const Tensor& k, const Tensor& v, Tensor& k_cache, Tensor& v
 
 void paged_attn_decode_int8(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& k_scale,
                             const Tensor& v_scale, const Tensor& block_table, const Tensor& context_lens, Tensor& out,
-                            Tensor& scratch, Tensor& counters, int64_t splits, double scale) {
+                            Tensor& scratch, Tensor& counters, int64_t splits, double scale,
+                            const OptTensor& status) {
   chk(q, BF16, "q");
   TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2),
               "paged_attn_decode_int8: q must be [batch, heads, head_dim] with contiguous heads");
@@ -683,8 +694,8 @@ void paged_attn_decode_int8(const Tensor& q, const Tensor& k_cache, const Tensor
   mb::paged_attn_decode_int8(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_scale.data_ptr<float>(),
                              v_scale.data_ptr<float>(), block_table.data_ptr<int>(), context_lens.data_ptr<int>(),
                              out.data_ptr(), scratch.data_ptr<float>(), counters.data_ptr<int>(), (int)B, (int)H,
-                             (int)Hkv, (int)D, (int)k_cache.size(1), (int)block_table.size(1), (int)splits,
-                             (float)scale, cur_stream(), q.stride(0));
+                             (int)Hkv, (int)D, (int)k_cache.size(1), (int)block_table.size(1), (int)k_cache.size(0),
+                             (int)splits, (float)scale, status_ptr(status), cur_stream(), q.stride(0));
 }
 
 void sample_tokens(const Tensor& logits, const OptTensor& history, const OptTensor& allow_mask, double temperature,
@@ -798,7 +809,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("tp_allreduce_pull", &tp_allreduce_pull);
   m.def("sum_residual_rmsnorm", &sum_residual_rmsnorm);
-  m.def("qkv_rope_append", &qkv_rope_append);
+  m.def("qkv_rope_append", &qkv_rope_append, py::arg("acc"), py::arg("pos"), py::arg("seq_ids"), py::arg("block_table"),
+        py::arg("q_out"), py::arg("k_cache"), py::arg("v_cache"), py::arg("theta"), py::arg("k_scale") = py::none(),
+        py::arg("v_scale") = py::none());
   m.def("finalize_gate", &finalize_gate);
   m.def("gemm_reduce_scatter", &gemm_reduce_scatter);
   m.def("tp_reduce_slots_bcast", &tp_reduce_slots_bcast);
@@ -809,7 +822,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("kv_append", &kv_append);
   m.def("paged_attn_decode", &paged_attn_decode);
   m.def("kv_append_int8", &kv_append_int8);
-  m.def("paged_attn_decode_int8", &paged_attn_decode_int8);
+  m.def("paged_attn_decode_int8", &paged_attn_decode_int8, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"),
+        py::arg("k_scale"), py::arg("v_scale"), py::arg("block_table"), py::arg("context_lens"), py::arg("out"),
+        py::arg("scratch"), py::arg("counters"), py::arg("splits"), py::arg("scale"), py::arg("status") = py::none());
   m.def("sample_tokens", &sample_tokens);
   m.def("moe_topk", &moe_topk);
   m.def("moe_dispatch", &moe_dispatch);

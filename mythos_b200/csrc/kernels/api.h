@@ -129,7 +129,8 @@ void sum_residual_rmsnorm(float* acc, const void* slots, int n_slots, long long 
 // K rotated and V -> their cache pages. theta <= 0 disables the rotation.
 void qkv_rope_append(float* acc, const int* pos, const int* seq_ids, const int* block_table, void* q_out,
                      void* k_cache, void* v_cache, int tokens, int heads, int kv_heads, int head_dim, int page_size,
-                     int max_pages, float theta, cudaStream_t stream);
+                     int max_pages, float theta, cudaStream_t stream, float* k_scale = nullptr,
+                     float* v_scale = nullptr);   // scales given: k_cache / v_cache are int8 pages
 // acc fp32 [rows, 2 * ffn] (zeroed) -> act(gate) * up, bf16 [rows, ffn]; kind 0 SiLU, 1 squared ReLU.
 void finalize_gate(float* acc, void* out, long long rows, int ffn, int kind, cudaStream_t stream);
 
@@ -223,8 +224,8 @@ void kv_append_int8(const void* k, const void* v, void* k_cache, void* v_cache, 
 void paged_attn_decode_int8(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                             const float* v_scale, const int* block_table, const int* context_lens, void* out,
                             float* scratch, int* counters, int batch, int heads, int kv_heads, int head_dim,
-                            int page_size, int max_pages, int splits, float scale, cudaStream_t stream,
-                            long long q_tok_stride = 0);
+                            int page_size, int max_pages, int cache_pages, int splits, float scale, int* status,
+                            cudaStream_t stream, long long q_tok_stride = 0);
 // Greedy / temperature / top-k / top-p / repetition-penalty sampling of one token per row.
 struct SamplerArgs {
   float temperature, top_p, repetition_penalty;

@@ -92,20 +92,27 @@ sum_residual_rmsnorm_kernel(float* __restrict__ acc, const __nv_bfloat16* __rest
 
 // One thread per (token, head slot, 8-wide group of the first half of the head): handles the pair
 // group (d, d + D/2). Head slots [0, H) are Q, [H, H + Hkv) K, [H + Hkv, H + 2 Hkv) V.
+// With k_cache8 / v_cache8 set the pages are int8: the head_dim / 16 threads of a head slot (adjacent
+// lanes, aligned in the warp) find max|x| with shuffles and store 8 + 8 bytes each plus one fp32
+// scale = max|x| / 127 per (token, kv head). Every lane of a warp reaches the shuffles: lanes past
+// the end of the work carry zeros and store nothing.
 __global__ void qkv_rope_append_kernel(float* __restrict__ acc, const int* __restrict__ pos,
                                        const int* __restrict__ seq_ids, const int* __restrict__ block_table,
                                        __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
-                                       __nv_bfloat16* __restrict__ v_cache, int tokens, int heads, int kv_heads,
+                                       __nv_bfloat16* __restrict__ v_cache, signed char* __restrict__ k_cache8,
+                                       signed char* __restrict__ v_cache8, float* __restrict__ k_scale,
+                                       float* __restrict__ v_scale, int tokens, int heads, int kv_heads,
                                        int head_dim, int page_size, int max_pages, float log2_theta) {
   const int half = head_dim >> 1, groups = half >> 3, slots = heads + 2 * kv_heads;
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (gid >= (long long)tokens * slots * groups) return;
+  const long long raw_gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool valid = raw_gid < (long long)tokens * slots * groups;
+  const long long gid = valid ? raw_gid : 0;
   const int g = (int)(gid % groups);
   const int hs = (int)((gid / groups) % slots);
   const int t = (int)(gid / ((long long)groups * slots));
   float* src = acc + ((long long)t * slots + hs) * head_dim;
   float a[8], b[8];
-  {
+  if (valid) {
     float4* pa = reinterpret_cast<float4*>(src + g * 8);
     float4* pb = reinterpret_cast<float4*>(src + half + g * 8);
     const float4 a0 = pa[0], a1 = pa[1], b0 = pb[0], b1 = pb[1];
@@ -113,6 +120,9 @@ __global__ void qkv_rope_append_kernel(float* __restrict__ acc, const int* __res
     pa[0] = z; pa[1] = z; pb[0] = z; pb[1] = z;
     a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
     b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = b[i] = 0.f;
   }
   const int p = pos[t];
   if (hs < heads + kv_heads && log2_theta > 0.f) {   // Q and K are rotated
@@ -130,18 +140,47 @@ __global__ void qkv_rope_append_kernel(float* __restrict__ acc, const int* __res
       b[i] = rb;
     }
   }
-  __nv_bfloat16* dst;
-  if (hs < heads) {
-    dst = q_out + ((long long)t * heads + hs) * head_dim;
-  } else {
-    const int seq = seq_ids[t];
-    const int page = block_table[(long long)seq * max_pages + p / page_size];
-    if (page < 0) return;
-    const bool is_k = hs < heads + kv_heads;
-    const int kvh = is_k ? hs - heads : hs - heads - kv_heads;
-    dst = (is_k ? k_cache : v_cache) +
-          (((long long)page * page_size + p % page_size) * kv_heads + kvh) * head_dim;
+  float amax = 0.f;
+  if (k_cache8 != nullptr) {   // same for every thread of the grid
+    // quantise what the bf16 path would have stored
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] = __bfloat162float(__float2bfloat16(a[i]));
+      b[i] = __bfloat162float(__float2bfloat16(b[i]));
+      amax = fmaxf(amax, fmaxf(fabsf(a[i]), fabsf(b[i])));
+    }
+    for (int o = groups >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   }
+  if (!valid) return;
+  if (hs < heads) {
+    __nv_bfloat16* dst = q_out + ((long long)t * heads + hs) * head_dim;
+    stg8(dst, g * 8, pack8(a));
+    stg8(dst, half + g * 8, pack8(b));
+    return;
+  }
+  const int seq = seq_ids[t];
+  const int page = block_table[(long long)seq * max_pages + p / page_size];
+  if (page < 0) return;
+  const bool is_k = hs < heads + kv_heads;
+  const int kvh = is_k ? hs - heads : hs - heads - kv_heads;
+  const long long row = ((long long)page * page_size + p % page_size) * kv_heads + kvh;
+  if (k_cache8 != nullptr) {
+    const float inv = amax > 0.f ? 127.f / amax : 0.f;
+    uint32_t wa[2] = {0u, 0u}, wb[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int qa = max(-127, min(127, __float2int_rn(a[i] * inv)));
+      const int qb = max(-127, min(127, __float2int_rn(b[i] * inv)));
+      wa[i >> 2] |= (uint32_t)(qa & 0xFF) << (8 * (i & 3));
+      wb[i >> 2] |= (uint32_t)(qb & 0xFF) << (8 * (i & 3));
+    }
+    signed char* dst8 = (is_k ? k_cache8 : v_cache8) + row * head_dim;
+    *reinterpret_cast<uint2*>(dst8 + g * 8) = make_uint2(wa[0], wa[1]);
+    *reinterpret_cast<uint2*>(dst8 + half + g * 8) = make_uint2(wb[0], wb[1]);
+    if (g == 0) (is_k ? k_scale : v_scale)[row] = amax / 127.f;
+    return;
+  }
+  __nv_bfloat16* dst = (is_k ? k_cache : v_cache) + row * head_dim;
   stg8(dst, g * 8, pack8(a));
   stg8(dst, half + g * 8, pack8(b));
 }
@@ -191,13 +230,19 @@ void sum_residual_rmsnorm(float* acc, const void* slots, int n_slots, long long 
 
 void qkv_rope_append(float* acc, const int* pos, const int* seq_ids, const int* block_table, void* q_out,
                      void* k_cache, void* v_cache, int tokens, int heads, int kv_heads, int head_dim, int page_size,
-                     int max_pages, float theta, cudaStream_t stream) {
+                     int max_pages, float theta, cudaStream_t stream, float* k_scale, float* v_scale) {
   MB_REQUIRE(head_dim % 16 == 0, "qkv_rope_append: head_dim must be a multiple of 16");
+  const bool int8 = k_scale != nullptr;
+  MB_REQUIRE(int8 == (v_scale != nullptr), "qkv_rope_append: int8 pages need both scale arrays");
+  MB_REQUIRE(!int8 || head_dim == 64 || head_dim == 128 || head_dim == 256,
+             "qkv_rope_append: int8 pages need head_dim / 16 lanes per head to be a power of two up to 16");
   if (tokens == 0) return;
   const long long work = (long long)tokens * (heads + 2 * kv_heads) * (head_dim / 16);
   qkv_rope_append_kernel<<<(unsigned)ceil_div(work, 128), 128, 0, stream>>>(
-      acc, pos, seq_ids, block_table, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tokens,
-      heads, kv_heads, head_dim, page_size, max_pages, theta > 0.f ? log2f(theta) : 0.f);
+      acc, pos, seq_ids, block_table, (__nv_bfloat16*)q_out, int8 ? nullptr : (__nv_bfloat16*)k_cache,
+      int8 ? nullptr : (__nv_bfloat16*)v_cache, int8 ? (signed char*)k_cache : nullptr,
+      int8 ? (signed char*)v_cache : nullptr, k_scale, v_scale, tokens, heads, kv_heads, head_dim, page_size, max_pages,
+      theta > 0.f ? log2f(theta) : 0.f);
   count_launch();
   check_launch();
 }

@@ -15,6 +15,8 @@
 // no partial last block), flash_decoding (:594-664), KVCache::append (src/kv_cache.cpp:78-137),
 // i2s_gemv (src/kernel_i2s.cpp:32-40). Partial last pages and per-sequence context lengths are
 // handled here.
+#include <cuda_fp16.h>
+
 #include "api.h"
 #include "common.cuh"
 #include "host_util.h"
@@ -474,6 +476,234 @@ paged_decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_c
                       splits);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core decode attention over int8 pages (16-token pages, head_dim 128).
+//
+// Same grid, warp roles and split merge as the bf16 kernel above. A warp's 16 KB of shared memory
+// hold a ring of PD_STAGES raw stages (K and V of one page as [16 tokens x 128 B] int8 boxes,
+// filled by TMA) and one pair of expanded tiles (K and V as fp16 in the 128B-swizzled layout that
+// the ldmatrix addressing below expects). Per page the warp expands the raw stage (16 bytes per
+// lane and step: int8 -> fp16 is exact and costs one byte permute and one subtract per pair of
+// values), hands the raw stage back to TMA at once, and runs the same m16n8k16 products in fp16.
+// The fp32 scales (one per token and kv head) never touch the tiles: the K scale multiplies the
+// score, the V scale the probability, both in fp32 on the accumulator fragments.
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Four int8 in `w` -> two fp16x2 words (values 0,1 and 2,3). x ^ 0x80 is the value + 128 as an
+// unsigned byte u; 0x6400 | u is the fp16 number 1024 + u; subtracting 1152 leaves the value.
+__device__ __forceinline__ void int8x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t x = w ^ 0x80808080u;
+  uint32_t l = __byte_perm(x, 0x64646464u, 0x4140), h = __byte_perm(x, 0x64646464u, 0x4342);
+  const __half2 bias = __floats2half2_rn(1152.f, 1152.f);
+  __half2 lv = __hsub2(*reinterpret_cast<__half2*>(&l), bias), hv = __hsub2(*reinterpret_cast<__half2*>(&h), bias);
+  lo = *reinterpret_cast<uint32_t*>(&lv);
+  hi = *reinterpret_cast<uint32_t*>(&hv);
+}
+
+__global__ void __launch_bounds__(128)
+paged_decode_mma_int8_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                             const __nv_bfloat16* __restrict__ q, const float* __restrict__ k_scale,
+                             const float* __restrict__ v_scale, const int* __restrict__ block_table,
+                             const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
+                             float* __restrict__ scratch, int* __restrict__ counters, int heads, int kv_heads, int G,
+                             int max_pages, int splits, float scale_log2, long long q_tok_stride, int* status) {
+  constexpr int D = 128;
+  using S = PdSmem<D>;
+  constexpr int KS = D / 16, NT = D / 8;
+  constexpr int RAW_HALF = 16 * D;            // K (or V) of one page as int8
+  constexpr int RAW = 2 * RAW_HALF;
+  constexpr int CONV_OFF = PD_STAGES * RAW;   // expanded tiles behind the raw ring
+  static_assert(CONV_OFF + 2 * S::CHUNKS * S::TILE == S::WARP_BYTES, "raw ring + expanded tiles fill the warp's share");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
+  uint8_t* wsm = smem + warp * S::WARP_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR) + warp * PD_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::OFF_BAR + 4 * PD_STAGES * 8);
+  int* s_last = const_cast<int*>(abort_flag) + 1;
+  float* s_m = reinterpret_cast<float*>(smem + S::OFF_MERGE);
+  float* s_l = s_m + 32;
+  float* w_acc = reinterpret_cast<float*>(wsm);   // [8][D] output state, written after the ring drained
+
+  if (threadIdx.x == 0) *abort_flag = 0;
+  if (lane == 0) {
+    for (int s = 0; s < PD_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int ctx = context_lens[b];
+  const int n_pages = (ctx + 15) >> 4;
+  const int per = (n_pages + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(n_pages, p0 + per);
+  const int my_pages = (p1 - p0 - warp + 3) >> 2;
+  const int* bt = block_table + (long long)b * max_pages;
+
+  auto issue = [&](int i) {   // lane 0: the warp's i-th page into raw stage i % PD_STAGES
+    const int st = i % PD_STAGES;
+    const int page = bt[p0 + warp + 4 * i];
+    uint8_t* dst = wsm + st * RAW;
+    mbar_arrive_expect_tx(&full[st], RAW);
+    tma_load_2d(dst, &tm_k, &full[st], hkv * D, page * 16);
+    tma_load_2d(dst + RAW_HALF, &tm_v, &full[st], hkv * D, page * 16);
+  };
+  if (lane == 0)
+    for (int i = 0; i < PD_STAGES && i < my_pages; ++i) issue(i);
+
+  const int r = lane >> 2, t = lane & 3;
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+    if (r < G) {
+      const __nv_bfloat16* qp = q + (long long)b * q_tok_stride + (long long)(hkv * G + r) * D + ks * 16 + 2 * t;
+      qa[ks][0] = pack_f16x2(__bfloat162float(qp[0]), __bfloat162float(qp[1]));
+      qa[ks][2] = pack_f16x2(__bfloat162float(qp[8]), __bfloat162float(qp[9]));
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  const int k_tok = ((lane >> 4) << 3) + (lane & 7), k_unit = (lane >> 3) & 1;
+  const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7), v_unit = lane >> 4;
+  const uint32_t conv_addr = smem_u32(wsm) + CONV_OFF;
+  uint8_t* convk = wsm + CONV_OFF;
+  uint8_t* convv = convk + S::CHUNKS * S::TILE;
+  bool ok = true;
+  for (int i = 0; i < my_pages; ++i) {
+    const int st = i % PD_STAGES;
+    const int lpage = p0 + warp + 4 * i;
+    // scales of the four tokens this lane's score / probability fragments cover; issued before the
+    // wait so that their latency hides behind it. Tokens past the context are never used.
+    const long long tokrow0 = (long long)bt[lpage] * 16;
+    const int tok0 = lpage * 16 + 2 * t;
+    float ksc[2][2], vsc[2][2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool live = tok0 + j * 8 + e < ctx;
+        const long long idx = (tokrow0 + 2 * t + j * 8 + e) * kv_heads + hkv;
+        ksc[j][e] = live ? __ldg(k_scale + idx) : 0.f;
+        vsc[j][e] = live ? __ldg(v_scale + idx) : 0.f;
+      }
+    ok = mbar_wait(&full[st], (i / PD_STAGES) & 1, abort_flag, status, 71);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    // ---- expand the raw stage: chunk c = 16 dims of token c / 8
+    const uint8_t* rawk = wsm + st * RAW;
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const int c = lane + 32 * kk;
+      const int tok = c >> 3, g = c & 7;
+      const uint4 kr = *reinterpret_cast<const uint4*>(rawk + c * 16);
+      const uint4 vr = *reinterpret_cast<const uint4*>(rawk + RAW_HALF + c * 16);
+      uint4 k0, k1, v0, v1;
+      int8x4_to_f16x4(kr.x, k0.x, k0.y);
+      int8x4_to_f16x4(kr.y, k0.z, k0.w);
+      int8x4_to_f16x4(kr.z, k1.x, k1.y);
+      int8x4_to_f16x4(kr.w, k1.z, k1.w);
+      int8x4_to_f16x4(vr.x, v0.x, v0.y);
+      int8x4_to_f16x4(vr.y, v0.z, v0.w);
+      int8x4_to_f16x4(vr.z, v1.x, v1.y);
+      int8x4_to_f16x4(vr.w, v1.z, v1.w);
+      const int off = (g >> 2) * S::TILE + tok * 128;
+      const int u0 = (g & 3) << 1;
+      const int a0 = off + ((u0 ^ (tok & 7)) << 4), a1 = off + (((u0 + 1) ^ (tok & 7)) << 4);
+      *reinterpret_cast<uint4*>(convk + a0) = k0;
+      *reinterpret_cast<uint4*>(convk + a1) = k1;
+      *reinterpret_cast<uint4*>(convv + a0) = v0;
+      *reinterpret_cast<uint4*>(convv + a1) = v1;
+    }
+    __syncwarp();   // raw stage consumed by every lane; expanded tiles visible to the warp
+    if (lane == 0 && i + PD_STAGES < my_pages) issue(i + PD_STAGES);
+    const uint32_t kbase = conv_addr, vbase = conv_addr + S::CHUNKS * S::TILE;
+    // ---- S = Q K^T
+    float sc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int unit = ((ks & 3) << 1) + k_unit;
+      uint32_t kb[4];
+      ldmatrix_x4(kbase + (ks >> 2) * S::TILE + k_tok * 128 + ((unit ^ (k_tok & 7)) << 4), kb);
+      mma_f16_16816(sc[0], qa[ks], kb[0], kb[1]);
+      mma_f16_16816(sc[1], qa[ks], kb[2], kb[3]);
+    }
+    // ---- online softmax; the K scale enters here, the V scale goes into the probabilities
+    float pv[2][2];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float v = (tok0 + j * 8 + e < ctx) ? sc[j][e] * ksc[j][e] * scale_log2 : -INFINITY;
+        pv[j][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = exp2f(m_run - m_new);
+    float psum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pe = exp2f(pv[j][e] - m_new);   // 0 for masked tokens
+        psum += pe;
+        pv[j][e] = (tok0 + j * 8 + e < ctx) ? pe * vsc[j][e] : 0.f;
+      }
+    l_run = l_run * alpha + psum;
+    m_run = m_new;
+    uint32_t pa[4];
+    pa[0] = pack_f16x2(pv[0][0], pv[0][1]);
+    pa[1] = 0u;
+    pa[2] = pack_f16x2(pv[1][0], pv[1][1]);
+    pa[3] = 0u;
+    // ---- O = O * alpha + P V
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      const int unit = ((np & 3) << 1) + v_unit;
+      uint32_t vb[4];
+      ldmatrix_x4_trans(vbase + (np >> 2) * S::TILE + v_tok * 128 + ((unit ^ (v_tok & 7)) << 4), vb);
+      o[2 * np][0] *= alpha;
+      o[2 * np][1] *= alpha;
+      o[2 * np + 1][0] *= alpha;
+      o[2 * np + 1][1] *= alpha;
+      mma_f16_16816(o[2 * np], pa, vb[0], vb[1]);
+      mma_f16_16816(o[2 * np + 1], pa, vb[2], vb[3]);
+    }
+    __syncwarp();   // the expanded tiles are free for the next page
+  }
+
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (t == 0) {
+    s_m[warp * 8 + r] = ok ? m_run : -INFINITY;
+    s_l[warp * 8 + r] = l_run;
+  }
+  if (ok) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      *reinterpret_cast<float2*>(&w_acc[r * D + n * 8 + 2 * t]) = make_float2(o[n][0], o[n][1]);
+  }
+  __syncthreads();
+  merge_and_finish<D>(s_m, s_l, reinterpret_cast<const float*>(smem), S::WARP_BYTES / 4, 4, 8, G, s_last, scratch, counters, out, b, hkv,
+                      split, heads, kv_heads, splits);
+}
+
 // One warp per output row; x staged in shared memory as fp32.
 __global__ void i2s_gemv_kernel(const __nv_bfloat16* __restrict__ x, DequantWeights w, __nv_bfloat16* __restrict__ y) {
   extern __shared__ float xs[];
@@ -603,8 +833,8 @@ void kv_append_int8(const void* k, const void* v, void* k_cache, void* v_cache, 
 void paged_attn_decode_int8(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                             const float* v_scale, const int* block_table, const int* context_lens, void* out,
                             float* scratch, int* counters, int batch, int heads, int kv_heads, int head_dim,
-                            int page_size, int max_pages, int splits, float scale, cudaStream_t stream,
-                            long long q_tok_stride) {
+                            int page_size, int max_pages, int cache_pages, int splits, float scale, int* status,
+                            cudaStream_t stream, long long q_tok_stride) {
   if (q_tok_stride <= 0) q_tok_stride = (long long)heads * head_dim;
   MB_REQUIRE(q_tok_stride % 8 == 0, "paged_attn_decode_int8: query token stride must be a multiple of 8 elements");
   MB_REQUIRE(heads % kv_heads == 0, "paged_attn_decode_int8: heads must be a multiple of kv_heads");
@@ -613,6 +843,26 @@ void paged_attn_decode_int8(const void* q, const void* k_cache, const void* v_ca
   const int G = heads / kv_heads;
   const dim3 grid(batch, kv_heads, splits);
   const float sl2 = scale * 1.4426950408889634f;
+  if (page_size == 16 && G <= 8 && head_dim == 128) {
+    // K / V cache as [cache_pages * 16 tokens, kv_heads * 128] bytes; one box = 16 tokens x 128 B
+    uint64_t dims[2] = {(uint64_t)kv_heads * head_dim, (uint64_t)cache_pages * 16};
+    uint64_t strides[1] = {(uint64_t)kv_heads * head_dim};
+    uint32_t box[2] = {128, 16};
+    const CUtensorMap tk = make_tensor_map(k_cache, TmaDType::U8, 2, dims, strides, box, false);
+    const CUtensorMap tv = make_tensor_map(v_cache, TmaDType::U8, 2, dims, strides, box, false);
+    static bool configured = false;
+    if (!configured) {
+      MB_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_mma_int8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PdSmem<128>::BYTES));
+      configured = true;
+    }
+    paged_decode_mma_int8_kernel<<<grid, 128, PdSmem<128>::BYTES, stream>>>(
+        tk, tv, (const __nv_bfloat16*)q, k_scale, v_scale, block_table, context_lens, (__nv_bfloat16*)out, scratch,
+        counters, heads, kv_heads, G, max_pages, splits, sl2, q_tok_stride, status);
+    count_launch();
+    check_launch();
+    return;
+  }
 #define MB_PD8(GG, DD)                                                                                        \
   paged_decode_kernel<GG, DD, true><<<grid, 128, 0, stream>>>(                                                \
       (const __nv_bfloat16*)q, k_cache, v_cache, k_scale, v_scale, block_table, context_lens,                 \

@@ -314,7 +314,7 @@ class InferenceEngine:
     def _fused_decode_ok(self, T: int) -> bool:
         cfg = self.cfg
         return (T <= ONESHOT_MAX_TOKENS and cfg.hidden_size % 8 == 0 and cfg.hidden_size <= 16384
-                and not self.cache.int8          # the fused QKV finalize writes bf16 pages
+                and (not self.cache.int8 or cfg.head_dim in (64, 128, 256))
                 and all(m.dense is None for L in self.layers for m in (L.qkv, L.o, L.up, L.down))
                 and (not cfg.gated_ffn or cfg.activation in ("silu", "relu2")))
 
@@ -335,10 +335,16 @@ class InferenceEngine:
         for li, L in enumerate(self.layers):
             acc = L.qkv.matmul_acc(n)
             q = torch.empty(T, H, D, device=dev, dtype=torch.bfloat16)
-            C.qkv_rope_append(acc, pos, seq_ids, table, q, self.cache.k[li], self.cache.v[li], cfg.rope_theta)
             o = torch.empty(T, H, D, device=dev, dtype=torch.bfloat16)
-            C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o, self._scratch,
-                                self._counters, self._splits, scale, st)
+            if self.cache.int8:
+                ks, vs = self.cache.k_scale[li], self.cache.v_scale[li]
+                C.qkv_rope_append(acc, pos, seq_ids, table, q, self.cache.k[li], self.cache.v[li], cfg.rope_theta, ks, vs)
+                C.paged_attn_decode_int8(q, self.cache.k[li], self.cache.v[li], ks, vs, table, ctx_lens, o,
+                                         self._scratch, self._counters, self._splits, scale, st)
+            else:
+                C.qkv_rope_append(acc, pos, seq_ids, table, q, self.cache.k[li], self.cache.v[li], cfg.rope_theta)
+                C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o, self._scratch,
+                                    self._counters, self._splits, scale, st)
             n, stream = self._row_parallel_norm(L.o, o.view(T, H * D), L.ffn_norm, stream)
             if cfg.gated_ffn:
                 acc = L.up.matmul_acc(n)
@@ -390,7 +396,7 @@ class InferenceEngine:
                 if self.cache.int8:
                     C.paged_attn_decode_int8(q, self.cache.k[li], self.cache.v[li], self.cache.k_scale[li],
                                              self.cache.v_scale[li], table, ctx_lens, o, self._scratch,
-                                             self._counters, self._splits, scale)
+                                             self._counters, self._splits, scale, native.status_word(self.device))
                 else:
                     C.paged_attn_decode(q, self.cache.k[li], self.cache.v[li], table, ctx_lens, o,
                                         self._scratch, self._counters, self._splits, scale,

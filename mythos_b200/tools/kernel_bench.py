@@ -208,7 +208,7 @@ def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int, spl
         pos = (lpage_of.repeat_interleave(16) * 16 + torch.arange(16, device="cuda", dtype=torch.int32).repeat(n_pages))
         C.kv_append_int8(kc.view(-1, Hkv, D), vc.view(-1, Hkv, D), k8, v8, ks, vs, table, pos.contiguous(), seq_ids)
         ms = graph_time(t, lambda: C.paged_attn_decode_int8(q, k8, v8, ks, vs, table, lens, out, scratch, counters,
-                                                            splits, D ** -0.5))
+                                                            splits, D ** -0.5, st))
         return ms, 2.0 * B * ctx * Hkv * (D + 4) / ms / 1e6, "GB/s"
     ms = graph_time(t, lambda: C.paged_attn_decode(q, kc, vc, table, lens, out, scratch, counters, splits,
                                                    D ** -0.5, st))

@@ -285,6 +285,29 @@ def test_fused_decode_epilogue_kernels():
     _close(q, ref_qk[:, :H], atol=2e-2)
     _close(kc, kc2, atol=2e-2)
     assert torch.equal(vc, vc2) and float(acc.abs().max()) == 0.0
+    # the same epilogue writing int8 pages, against RoPE + the int8 append kernel
+    for D8, Tt8 in ((128, 3), (64, 5)):
+        acc = torch.randn(Tt8, (H + 2 * Hkv) * D8, device="cuda") * 2
+        qkv = acc.to(torch.bfloat16)
+        pos8 = torch.tensor([5, 17, 0, 33, 2][:Tt8], device="cuda", dtype=torch.int32)
+        sid8 = torch.arange(Tt8, device="cuda", dtype=torch.int32)
+        table8 = torch.randperm(Tt8 * max_pages).view(Tt8, max_pages).to(torch.int32).cuda()
+        shape8 = (Tt8 * max_pages, page, Hkv, D8)
+        k8, v8 = (torch.zeros(shape8, device="cuda", dtype=torch.int8) for _ in range(2))
+        k8r, v8r = torch.zeros_like(k8), torch.zeros_like(v8)
+        ks, vs, ksr, vsr = (torch.zeros(shape8[0] * page, Hkv, device="cuda") for _ in range(4))
+        q8 = torch.empty(Tt8, H, D8, device="cuda", dtype=torch.bfloat16)
+        C.qkv_rope_append(acc, pos8, sid8, table8, q8, k8, v8, 10000.0, ks, vs)
+        ref_qk = qkv[:, : (H + Hkv) * D8].clone().unflatten(-1, (H + Hkv, D8))
+        C.rope(ref_qk, pos8, 10000.0, False)
+        C.kv_append_int8(ref_qk[:, H:].contiguous(), qkv[:, (H + Hkv) * D8:].unflatten(-1, (Hkv, D8)).contiguous(),
+                         k8r, v8r, ksr, vsr, table8, pos8, sid8)
+        _close(q8, ref_qk[:, :H], atol=2e-2)
+        assert torch.equal(v8, v8r) and torch.equal(vs, vsr) and float(acc.abs().max()) == 0.0
+        # K goes through sincosf in one kernel and the RoPE kernel's own evaluation in the other:
+        # scales agree to bf16 rounding, codes to one step
+        assert torch.allclose(ks, ksr, rtol=1e-2, atol=1e-6)
+        assert int((k8.int() - k8r.int()).abs().max()) <= 2
 
 
 def test_engine_greedy_matches_full_recompute():
@@ -345,10 +368,12 @@ def test_embedding_gather_through_quantised_table(fmt, K, bs):
     assert torch.equal(wide[:, :K], out) and float(wide[:, K:].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("H,Hkv,D,page", [(8, 2, 128, 16), (4, 4, 64, 16), (4, 1, 128, 32)])
+@pytest.mark.parametrize("H,Hkv,D,page", [(8, 2, 128, 16), (32, 8, 128, 16), (8, 1, 128, 16), (3, 3, 128, 16),
+                                          (4, 4, 64, 16), (4, 1, 128, 32)])
 def test_int8_kv_append_and_decode(H, Hkv, D, page):
     """int8 pages: the append kernel's scales and codes against abs-max / 127 rounding, and decode
-    attention over the int8 pages against fp32 attention over the dequantised values."""
+    attention over the int8 pages against fp32 attention over the dequantised values. 16-token
+    pages with head_dim 128 run the tensor-core kernel, the other shapes the scalar one."""
     from mythos_b200.ops import native, reference as ref
 
     C = native.require()
@@ -384,11 +409,13 @@ def test_int8_kv_append_and_decode(H, Hkv, D, page):
         out = torch.empty(B, H, D, device="cuda", dtype=torch.bfloat16)
         scratch = torch.empty(B * H * splits * (D + 2), device="cuda")
         counters = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
-        C.paged_attn_decode_int8(q, k8, v8, ksc, vsc, table, ctx, out, scratch, counters, splits, 1.0 / math.sqrt(D))
+        C.paged_attn_decode_int8(q, k8, v8, ksc, vsc, table, ctx, out, scratch, counters, splits, 1.0 / math.sqrt(D),
+                                 native.status_word("cuda"))
         for b in range(B):
             o, _ = ref.attention(q[b][None, None].float(), kd[b][None], vd[b][None], causal=False)
             _close(out[b], o[0, 0], atol=2e-2)
         assert int(counters.abs().sum()) == 0
+    native.check_status("cuda")
 
 
 def test_engine_int8_kv_tracks_bf16_kv():
