@@ -252,3 +252,56 @@ def test_backend_stream_regroups_at_punctuation():
     grouped = list(be.stream("one two, three", max_tokens=8, flush="punctuation"))
     assert "".join(plain) == "".join(grouped)
     assert all(g[-1] in " ,.!?" for g in grouped)
+
+
+def test_reduced_precision_activation_wrappers_pool_and_stream_config():
+    import torch.nn as nn
+
+    from mythos_b200.infer.extras import (DecodeResult, FP8Inference, INT8Inference, InferenceMemoryPool, StreamConfig,
+                                          decode_with_config, fake_quant_fp8, fake_quant_int8, quantize_per_token_int8)
+
+    torch.manual_seed(0)
+    x = torch.randn(6, 64) * 3
+    q, s = quantize_per_token_int8(x)
+    assert q.dtype == torch.int8 and s.shape == (6, 1) and int(q.abs().max()) == 127
+    assert float((fake_quant_int8(x) - x).abs().max()) <= float(s.max()) * 0.5 + 1e-6
+    assert float((fake_quant_fp8(x) - x).abs().max()) <= 0.07 * float(x.abs().max())      # e4m3: 3 mantissa bits
+    assert torch.equal(fake_quant_int8(torch.zeros(2, 8)), torch.zeros(2, 8))
+    net = nn.Sequential(nn.Linear(64, 32), nn.ReLU(), nn.Linear(32, 8))
+    ref = net(x).detach()
+    for cls, tol in ((INT8Inference, 0.05), (FP8Inference, 0.15)):
+        w = cls(net)
+        y = w(x)
+        assert w.is_quantized and w.layers_seen == 2
+        err = float((y - ref).abs().max())
+        assert 0 < err < tol * float(ref.abs().max())
+    assert not any(m._forward_pre_hooks for m in net.modules())          # hooks are gone after the call
+
+    pool = InferenceMemoryPool(256, 3)
+    a, b, c = pool.alloc(), pool.alloc(), pool.alloc()
+    assert pool.used == 3 and pool.capacity == 3 and a.numel() == 256
+    with pytest.raises(MemoryError):
+        pool.alloc()
+    pool.free(b)
+    assert pool.used == 2 and pool.alloc().data_ptr() == b.data_ptr()
+    with pytest.raises(ValueError):
+        pool.free(torch.empty(256, dtype=torch.uint8))
+
+    text = "ab\ncdSTOPef"
+    vocab = sorted(set(text)) + ["<eos>"]
+
+    def step(ids):                                  # a model that recites `text`, then emits <eos>
+        k = len(ids) - 1
+        lg = torch.full((len(vocab),), -5.0)
+        lg[vocab.index(text[k]) if k < len(text) else len(vocab) - 1] = 5.0
+        return lg
+
+    detok = lambda ids: "".join(vocab[i] for i in ids)
+    pieces = []
+    r = decode_with_config(step, [0], StreamConfig(stream=True, max_tokens=50, eos_id=len(vocab) - 1), detok, pieces.append)
+    assert isinstance(r, DecodeResult) and r.text == text and r.finish_reason == "eos" and "".join(pieces) == text
+    assert len(r.logprobs) == len(text) and 1.0 <= r.perplexity < 1.01
+    assert decode_with_config(step, [0], StreamConfig(max_tokens=50, stop_on_newline=True), detok).text == "ab\n"
+    r = decode_with_config(step, [0], StreamConfig(max_tokens=50, stop_sequences=["STOP"]), detok)
+    assert r.text == "ab\ncd" and r.finish_reason == "stop"
+    assert decode_with_config(step, [0], StreamConfig(max_tokens=4), detok).finish_reason == "length"
