@@ -522,6 +522,78 @@ class InferenceEngine:
         return GenerationResult(tokens=[t.tolist() for t in toks], stats=stats)
 
 
+    # ------------------------------------------------------------------ text-level API
+    @classmethod
+    def load(cls, path: str, device="cuda", **kw) -> "InferenceEngine":
+        """Engine from an ``.oil`` file and its sibling ``.vocab`` tokenizer (byte-level ids when the
+        vocabulary file is missing): the reference's ``engine::InferenceEngine::load`` + ``init``
+        (engines/inference/inference.cpp)."""
+        import os
+
+        from ..oil.model_io import load_model
+        from ..train.bpe import BPETokenizer
+
+        model, _ = load_model(path, device=device)
+        kw.setdefault("max_seq_len", model.cfg.max_seq_len)
+        eng = cls.from_model(model, device=device, **kw)
+        vocab = (path[:-4] if path.endswith(".oil") else path) + ".vocab"
+        eng.tokenizer = BPETokenizer.load(vocab) if os.path.exists(vocab) else None
+        return eng
+
+    def encode(self, text: str) -> list:
+        tok = getattr(self, "tokenizer", None)
+        ids = tok.encode(text) if tok is not None else list(text.encode("utf-8"))
+        return [min(int(i), self.cfg.vocab_size - 1) for i in ids] or [0]
+
+    def decode_text(self, ids) -> str:
+        tok = getattr(self, "tokenizer", None)
+        if tok is not None:
+            return tok.decode(list(ids))
+        return bytes(int(i) & 0xFF for i in ids).decode("utf-8", errors="replace")
+
+    def generate_with_stats(self, prompt: str, max_new_tokens: int = 64, sampler: SamplerConfig | None = None):
+        """``(text, GenerationStats)``: tokens, seconds, tokens/s, KV bytes and KV utilisation of one
+        prompt (the reference's ``generate_with_stats`` / ``InferenceStats``)."""
+        ids = self.encode(prompt)
+        room = self.max_seq_len - len(ids)
+        if room < 1:
+            raise ValueError("prompt fills the engine's context")
+        tok = getattr(self, "tokenizer", None)
+        res = self.generate([ids], max_new_tokens=min(max_new_tokens, room), sampler=sampler,
+                            eos_id=tok.eos_id() if tok is not None else None)
+        new = res.tokens[0]
+        if tok is not None and tok.eos_id() in new:
+            new = new[: new.index(tok.eos_id())]
+        return self.decode_text(new), res.stats
+
+    def generate_text(self, prompt: str, max_new_tokens: int = 64, sampler: SamplerConfig | None = None) -> str:
+        return self.generate_with_stats(prompt, max_new_tokens, sampler)[0]
+
+    def generate_batch(self, prompts, max_new_tokens: int = 64, sampler: SamplerConfig | None = None) -> list:
+        """Texts for a list of prompts. Prompts that tokenise to the same length share one batched
+        prefill + decode (up to ``max_batch`` at a time); the reference loops over them one by one."""
+        enc = [self.encode(p) for p in prompts]
+        out = [None] * len(prompts)
+        by_len: dict[int, list[int]] = {}
+        for i, ids in enumerate(enc):
+            by_len.setdefault(len(ids), []).append(i)
+        for n, members in by_len.items():
+            for lo in range(0, len(members), self.max_batch):
+                group = members[lo:lo + self.max_batch]
+                res = self.generate([enc[i] for i in group], max_new_tokens=min(max_new_tokens, self.max_seq_len - n),
+                                    sampler=sampler)
+                for i, toks in zip(group, res.tokens):
+                    out[i] = self.decode_text(toks)
+        return out
+
+    def reset_context(self) -> None:
+        """Drop every live sequence and the prefix index (all pages return to the free list)."""
+        cache = self.cache
+        for s in range(cache.max_seqs):
+            if cache.active[s]:
+                cache.free_sequence(s)
+        cache.prefix_index.clear()
+
     # ------------------------------------------------------------------ step-wise API (serving)
     @torch.no_grad()
     def generate_stream(self, prompt_ids, detokenize, on_text, max_new_tokens: int = 32,

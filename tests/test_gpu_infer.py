@@ -517,3 +517,34 @@ def test_repeated_launches_are_bit_identical():
 
     assert repeat(dec, 200) == 0
     native.check_status("cuda")
+
+
+def test_engine_text_api_load_batch_stream_reset(tmp_path):
+    """load(.oil + .vocab) -> generate_with_stats / generate_batch / generate_stream / reset_context."""
+    from mythos_b200.infer.engine import InferenceEngine
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.oil.model_io import save_model
+    from mythos_b200.train.bpe import BPETokenizer
+
+    torch.manual_seed(0)
+    tok = BPETokenizer()
+    tok.train(b"the quick brown fox jumps over the lazy dog. " * 30, 300)
+    cfg = TransformerConfig(vocab_size=320, hidden_size=256, num_layers=2, num_heads=2, head_dim=128,
+                            ffn_hidden_size=512, max_seq_len=256, oil_block_size=256, codebook_group=2)
+    path = str(tmp_path / "m.oil")
+    save_model(DenseModel(cfg), path)
+    tok.save(str(tmp_path / "m.vocab"))
+    eng = InferenceEngine.load(path, device="cuda", max_batch=4)
+    assert eng.tokenizer is not None and eng.decode_text(eng.encode("the lazy dog")) == "the lazy dog"
+    text, stats = eng.generate_with_stats("the quick brown", max_new_tokens=8)
+    assert isinstance(text, str) and stats.new_tokens >= 1 and stats.ttft_s > 0 and stats.kv_bytes > 0
+    prompts = ["the quick brown", "the lazy dog jumps", "the quick brown"]
+    outs = eng.generate_batch(prompts, max_new_tokens=6)
+    assert len(outs) == 3 and outs[0] == outs[2] and all(isinstance(o, str) for o in outs)
+    pieces = []
+    res = eng.generate_stream(eng.encode("the quick"), eng.decode_text, pieces.append, max_new_tokens=8)
+    assert "".join(pieces) == "".join(eng.decode_text([t]) for t in res.tokens[0])
+    seq, _ = eng.start_sequence(eng.encode("the quick brown fox jumps over the lazy dog."))
+    assert eng.cache.alloc.used > 0
+    eng.reset_context()
+    assert eng.cache.alloc.used == 0 and not eng.cache.prefix_index
