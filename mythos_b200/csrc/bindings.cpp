@@ -530,6 +530,30 @@ void sum_residual_rmsnorm(OptTensor acc, const OptTensor& slots, int64_t n_slots
                            cptr(residual), gamma.data_ptr(), stream_out.data_ptr(), normed.data_ptr(), (int)rows,
                            (int)dim, (float)eps, cur_stream());
 }
+void tp_sum_residual_rmsnorm(OptTensor acc, const std::vector<int64_t>& staging_ptrs,
+                             const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t slot_stride, int64_t parity,
+                             int64_t max_rows, const OptTensor& residual, const Tensor& gamma, Tensor& stream_out,
+                             Tensor& normed, double eps, Tensor& epoch_dev, Tensor& arrive, int64_t limit_cycles,
+                             const OptTensor& status) {
+  chk_c(gamma, BF16, "gamma");
+  chk_c(stream_out, BF16, "stream_out");
+  chk_c(normed, BF16, "normed");
+  chk_c(epoch_dev, I32, "epoch_dev");
+  chk_c(arrive, I32, "arrive");
+  if (acc.has_value()) chk_c(*acc, F32, "acc");
+  if (residual.has_value()) chk_c(*residual, BF16, "residual");
+  const int64_t dim = normed.size(-1), rows = normed.numel() / dim;
+  TORCH_CHECK(stream_out.numel() == normed.numel() && gamma.numel() == dim, "tp_sum_residual_rmsnorm: shape mismatch");
+  TORCH_CHECK(!acc.has_value() || acc->numel() >= rows * dim, "tp_sum_residual_rmsnorm: accumulator too small");
+  TORCH_CHECK(staging_ptrs.size() == flag_ptrs.size() && !staging_ptrs.empty(),
+              "tp_sum_residual_rmsnorm: one staging and one flag pointer per rank");
+  c10::cuda::CUDAGuard guard(normed.device());
+  mb::tp_sum_residual_rmsnorm(acc.has_value() ? acc->data_ptr<float>() : nullptr, to_peers(staging_ptrs),
+                              to_peers(flag_ptrs), (int)rank, (int)staging_ptrs.size(), slot_stride, (int)parity,
+                              (int)max_rows, cptr(residual), gamma.data_ptr(), stream_out.data_ptr(), normed.data_ptr(),
+                              (int)rows, (int)dim, (float)eps, epoch_dev.data_ptr<int>(), arrive.data_ptr<int>(),
+                              limit_cycles, status_ptr(status), cur_stream());
+}
 void qkv_rope_append(Tensor& acc, const Tensor& pos, const Tensor& seq_ids, const Tensor& block_table, Tensor& q_out,
                      Tensor& k_cache, Tensor& v_cache, double theta, OptTensor k_scale, OptTensor v_scale) {
   chk_c(acc, F32, "acc");
@@ -809,6 +833,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("tp_allreduce_pull", &tp_allreduce_pull);
   m.def("sum_residual_rmsnorm", &sum_residual_rmsnorm);
+  m.def("tp_sum_residual_rmsnorm", &tp_sum_residual_rmsnorm);
   m.def("qkv_rope_append", &qkv_rope_append, py::arg("acc"), py::arg("pos"), py::arg("seq_ids"), py::arg("block_table"),
         py::arg("q_out"), py::arg("k_cache"), py::arg("v_cache"), py::arg("theta"), py::arg("k_scale") = py::none(),
         py::arg("v_scale") = py::none());

@@ -125,6 +125,14 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
 void sum_residual_rmsnorm(float* acc, const void* slots, int n_slots, long long slot_stride, const void* residual,
                           const void* gamma, void* stream_out, void* normed, int rows, int dim, float eps,
                           cudaStream_t stream);
+// Tensor-parallel form: pushes this rank's partial row (acc, may be null when the GEMM stored the slots)
+// into slot `rank` of every rank's staging buffer, signals and awaits per-row flags
+// (flags: int32 [2][world][max_rows] per rank), then sums the world's slots + residual and normalises.
+// epoch_dev / arrive: one int each in local device memory, both zero before the first call.
+void tp_sum_residual_rmsnorm(float* acc, const PeerPtrs& staging, const PeerPtrs& flags, int rank, int world,
+                             long long slot_stride, int parity, int max_rows, const void* residual, const void* gamma,
+                             void* stream_out, void* normed, int rows, int dim, float eps, int* epoch_dev, int* arrive,
+                             long long limit_cycles, int* status, cudaStream_t stream);
 // acc fp32 [tokens, (heads + 2 kv_heads) * head_dim] (zeroed): Q rotated -> q_out bf16 [tokens, heads, head_dim];
 // K rotated and V -> their cache pages. theta <= 0 disables the rotation.
 void qkv_rope_append(float* acc, const int* pos, const int* seq_ids, const int* block_table, void* q_out,

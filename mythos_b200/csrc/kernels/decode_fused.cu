@@ -9,6 +9,10 @@
 //                          and V written straight into their KV-cache pages         (replaces finalize,
 //                          RoPE and kv_append)
 //   finalize_gate          fp32 accumulator of the gate/up projection -> act(gate) * up (bf16)
+//   tp_sum_residual_rmsnorm   the tensor-parallel form of the first: push this rank's partial row to
+//                          every peer, signal a per-row flag, wait for the peers' flags of the same
+//                          row, then sum + residual + RMSNorm, all in one launch (replaces push
+//                          kernel, barrier kernel and sum kernel)
 //
 // Accumulators are zeroed as they are read (they are shared split-K scratch). Reference formulas:
 // rms_norm (src/math.cpp:182-205), RotaryEmbedding::apply (src/transformer.cpp:118-139), FFN
@@ -68,6 +72,132 @@ sum_residual_rmsnorm_kernel(float* __restrict__ acc, const __nv_bfloat16* __rest
         for (int j = 0; j < 8; ++j) x[j] += f[j];
       }
       // the stream is stored in bf16; normalise what is stored so both outputs agree
+      const bf16x8 h = pack8(x);
+      stg8(stream_out, e, h);
+      unpack8(h, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)dim + eps);
+#pragma unroll
+  for (int it = 0; it < SRN_MAX_VEC; ++it) {
+    const int v = threadIdx.x + it * SRN_THREADS;
+    if (v < nvec) {
+      float g[8], y[8];
+      unpack8(ldg8(gamma, (long long)v * 8), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = vals[it][j] * rstd * g[j];
+      stg8(normed, row * dim + (long long)v * 8, pack8(y));
+    }
+  }
+}
+
+__device__ __forceinline__ void st_release_sys_i32(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys_i32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Tensor-parallel sum of a decode-sized activation fused with the residual add and RMSNorm.
+// One CTA per row; rows are independent, so no CTA ever waits on another CTA of its own grid.
+//   1. (acc != null) the row of this rank's fp32 partial is rounded to bf16 and stored into slot
+//      `rank` of the staging buffer of every rank (acc is zeroed for the next split-K GEMM);
+//      with acc == null the GEMM before this launch has already stored the slots.
+//   2. thread r < world announces the row to rank r: flags[r][parity][rank][row] = epoch (release at
+//      system scope, after a system fence that covers the row's stores), then waits for
+//      flags[me][parity][r][row] >= epoch with a cycle limit; on expiry the status word is set
+//      and the row is left alone.
+//   3. the world's slots of the row are read through L2, summed with the residual, stored as the
+//      new residual stream and normalised.
+// The epoch lives on the device (one increment per launch, done by the CTA that is last to have
+// read it), so the launch can be replayed from a CUDA graph.
+__global__ void __launch_bounds__(SRN_THREADS)
+tp_sum_residual_rmsnorm_kernel(float* __restrict__ acc, PeerPtrs staging, PeerPtrs flags, int rank, int world,
+                               long long slot_stride, long long flag_base, int max_rows,
+                               const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma,
+                               __nv_bfloat16* __restrict__ stream_out, __nv_bfloat16* __restrict__ normed, int dim,
+                               float eps, int* epoch_dev, int* arrive, long long limit_cycles, int* status) {
+  __shared__ float scratch[32];
+  __shared__ int s_epoch, s_ok;
+  const long long row = blockIdx.x;
+  const int nvec = dim >> 3;
+  if (threadIdx.x == 0) {
+    const int e = *reinterpret_cast<volatile int*>(epoch_dev) + 1;
+    s_epoch = e;
+    s_ok = 1;
+    __threadfence();
+    if (atomicAdd(arrive, 1) == (int)gridDim.x - 1) {   // every CTA has read the old epoch
+      *arrive = 0;
+      *epoch_dev = e;
+    }
+  }
+  if (acc) {
+#pragma unroll
+    for (int it = 0; it < SRN_MAX_VEC; ++it) {
+      const int v = threadIdx.x + it * SRN_THREADS;
+      if (v < nvec) {
+        const long long e = row * dim + (long long)v * 8;
+        float4* a = reinterpret_cast<float4*>(acc + e);
+        const float4 lo = a[0], hi = a[1];
+        a[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const bf16x8 h = pack8(x);
+        for (int r = 0; r < world; ++r) {
+          const int dst = (rank + r) % world;
+          stg8(staging.p[dst], (long long)rank * slot_stride + e, h);
+        }
+      }
+    }
+  }
+  // The row's stores are ordered before the barrier (CTA scope); the signalling threads then fence at
+  // system scope before their release store, which carries the whole CTA's stores with it. A system
+  // fence in every thread costs about 5 us per launch here.
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const int r = threadIdx.x, e = s_epoch;
+    __threadfence_system();
+    st_release_sys_i32(reinterpret_cast<int*>(flags.p[r]) + flag_base + (long long)rank * max_rows + row, e);
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + flag_base + (long long)r * max_rows + row;
+    const long long t0 = clock64();
+    while (ld_acquire_sys_i32(mine) < e) {
+      if (clock64() - t0 > limit_cycles) {
+        if (status) atomicCAS(status, 0, 1 | (41 << 16));
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(staging.p[rank]);
+  float vals[SRN_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < SRN_MAX_VEC; ++it) {
+    const int v = threadIdx.x + it * SRN_THREADS;
+    if (v < nvec) {
+      const long long e = row * dim + (long long)v * 8;
+      float (&x)[8] = vals[it];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = 0.f;
+      for (int s = 0; s < world; ++s) {   // written by peers: read through L2
+        float f[8];
+        unpack8(ldcg8(slots, s * slot_stride + e), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] += f[j];
+      }
+      if (residual) {
+        float f[8];
+        unpack8(ldg8(residual, e), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] += f[j];
+      }
       const bf16x8 h = pack8(x);
       stg8(stream_out, e, h);
       unpack8(h, x);
@@ -224,6 +354,25 @@ void sum_residual_rmsnorm(float* acc, const void* slots, int n_slots, long long 
   sum_residual_rmsnorm_kernel<<<rows, SRN_THREADS, 0, stream>>>(
       acc, (const __nv_bfloat16*)slots, n_slots, slot_stride, (const __nv_bfloat16*)residual,
       (const __nv_bfloat16*)gamma, (__nv_bfloat16*)stream_out, (__nv_bfloat16*)normed, dim, eps);
+  count_launch();
+  check_launch();
+}
+
+void tp_sum_residual_rmsnorm(float* acc, const PeerPtrs& staging, const PeerPtrs& flags, int rank, int world,
+                             long long slot_stride, int parity, int max_rows, const void* residual, const void* gamma,
+                             void* stream_out, void* normed, int rows, int dim, float eps, int* epoch_dev, int* arrive,
+                             long long limit_cycles, int* status, cudaStream_t stream) {
+  MB_REQUIRE(world >= 1 && world <= MAX_PEERS, "tp_sum_residual_rmsnorm: world size out of range");
+  MB_REQUIRE(dim % 8 == 0 && dim <= SRN_THREADS * 8 * SRN_MAX_VEC, "tp_sum_residual_rmsnorm: unsupported row width");
+  MB_REQUIRE(slot_stride % 8 == 0 && slot_stride >= (long long)rows * dim,
+             "tp_sum_residual_rmsnorm: slot stride must hold the rows and be a multiple of 8");
+  MB_REQUIRE(rows <= max_rows && (parity == 0 || parity == 1), "tp_sum_residual_rmsnorm: rows exceed the flag array");
+  MB_REQUIRE(epoch_dev != nullptr && arrive != nullptr, "tp_sum_residual_rmsnorm: epoch and arrival counters are required");
+  if (rows == 0) return;
+  tp_sum_residual_rmsnorm_kernel<<<rows, SRN_THREADS, 0, stream>>>(
+      acc, staging, flags, rank, world, slot_stride, (long long)parity * world * max_rows, max_rows,
+      (const __nv_bfloat16*)residual, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)stream_out, (__nv_bfloat16*)normed,
+      dim, eps, epoch_dev, arrive, limit_cycles, status);
   count_launch();
   check_launch();
 }

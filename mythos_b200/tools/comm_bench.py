@@ -161,6 +161,37 @@ def main(argv=None) -> int:
     t_f, t_n = _time(tp_oneshot, group, a.iters * 5, a.warmup), _time(tp_nccl, group, a.iters * 5, a.warmup)
     report("tp_allreduce_oneshot_64x4096_bf16", t_f, T * N * 2.0 * (W - 1), baseline_ms=t_n)
 
+    # the same sum followed by residual add + RMSNorm: three kernels + barrier vs one signalled kernel
+    gamma = torch.ones(N, device=dev, dtype=torch.bfloat16)
+    resid = torch.randn(T, N, device=dev).to(torch.bfloat16)
+    s_out, n_out = torch.empty_like(resid), torch.empty_like(resid)
+    row_flags = symm.make_buffer(2 * W * 256, torch.int32, dev, group).zero_()
+    row_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    row_arrive = torch.zeros(1, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    dist.barrier(group=group)
+    parity = [0]
+
+    def tp_norm_unfused():
+        C.tp_push(acc, staging.ptrs, rank, rank * stride)
+        fbar.sync()
+        C.sum_residual_rmsnorm(None, staging.tensor, W, stride, resid, gamma, s_out, n_out, 1e-5)
+
+    def tp_norm_signalled():
+        C.tp_sum_residual_rmsnorm(acc, staging.ptrs, row_flags.ptrs, rank, stride, parity[0], 256, resid, gamma, s_out,
+                                  n_out, 1e-5, row_epoch, row_arrive, symm.DEFAULT_BARRIER_LIMIT_CYCLES, st)
+        parity[0] ^= 1
+
+    def tp_norm_nccl():
+        dist.all_reduce(xb, group=group)
+        F.rmsnorm(xb, gamma, 1e-5, resid)
+
+    t_u = _time(tp_norm_unfused, group, a.iters * 5, a.warmup)
+    t_s = _time(tp_norm_signalled, group, a.iters * 5, a.warmup)
+    t_n = _time(tp_norm_nccl, group, a.iters * 5, a.warmup)
+    report("tp_sum_residual_rmsnorm_push_barrier_sum_64x4096", t_u, T * N * 2.0 * (W - 1), baseline_ms=t_n)
+    report("tp_sum_residual_rmsnorm_row_signalled_64x4096", t_s, T * N * 2.0 * (W - 1), baseline_ms=t_n)
+
     # ---------------------------------------------------------------- TP GEMM + fused reduce-scatter (prefill)
     Tp, K = 8192 * W if W <= 4 else 65536, 4096 // W * 2
     Tp = Tp // (W * 256) * (W * 256)

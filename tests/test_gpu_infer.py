@@ -548,3 +548,53 @@ def test_engine_text_api_load_batch_stream_reset(tmp_path):
     assert eng.cache.alloc.used > 0
     eng.reset_context()
     assert eng.cache.alloc.used == 0 and not eng.cache.prefix_index
+
+
+def test_row_signalled_sum_norm_single_rank_and_timeout():
+    """The fused push + per-row flag + sum + residual + RMSNorm kernel with one rank (it signals and
+    awaits its own flags; the epoch advances on the device), then with a second "rank" whose flags
+    nobody sets: the bounded wait must give up and report instead of hanging."""
+    from mythos_b200.ops import native, reference as ref
+
+    C = native.require()
+    torch.manual_seed(3)
+    T, N, max_rows = 7, 2560, 16
+    g = (torch.rand(N, device="cuda") + 0.5).to(torch.bfloat16)
+    staging = torch.zeros(max_rows * N, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(2 * 1 * max_rows, device="cuda", dtype=torch.int32)
+    epoch = torch.zeros(1, device="cuda", dtype=torch.int32)
+    arrive = torch.zeros(1, device="cuda", dtype=torch.int32)
+    st = native.status_word("cuda")
+    for it in range(4):
+        acc = torch.randn(T, N, device="cuda")
+        res = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+        want_stream = (acc.to(torch.bfloat16).float() + res.float()).to(torch.bfloat16)
+        stream, normed = torch.empty_like(res), torch.empty_like(res)
+        C.tp_sum_residual_rmsnorm(acc, [staging.data_ptr()], [flags.data_ptr()], 0, max_rows * N, it & 1, max_rows, res, g,
+                                  stream, normed, 1e-5, epoch, arrive, 2_000_000_000, st)
+        assert torch.equal(stream, want_stream) and float(acc.abs().max()) == 0.0
+        _close(normed, ref.rmsnorm(want_stream, g, 1e-5)[0], atol=2e-2)
+        assert int(epoch) == it + 1 and int(arrive) == 0
+    native.check_status("cuda")
+    assert flags.view(2, max_rows)[:, :T].min().item() >= 3 and int(flags.view(2, max_rows)[:, T:].abs().sum()) == 0
+    # slots already stored by the producer (no accumulator): only signal, wait and reduce
+    staging.view(max_rows, N)[:T] = torch.ones(T, N, device="cuda", dtype=torch.bfloat16)
+    C.tp_sum_residual_rmsnorm(None, [staging.data_ptr()], [flags.data_ptr()], 0, max_rows * N, 0, max_rows, None, g, stream,
+                              normed, 1e-5, epoch, arrive, 2_000_000_000, st)
+    assert float((stream.float() - 1).abs().max()) == 0.0
+    # two ranks, the peer never signals: every row times out, outputs are left alone, status is set
+    staging2 = torch.zeros(2 * max_rows * N, device="cuda", dtype=torch.bfloat16)
+    peer_staging = torch.zeros_like(staging2)
+    fa = torch.zeros(2 * 2 * max_rows, device="cuda", dtype=torch.int32)
+    fb = torch.zeros_like(fa)
+    stream.fill_(7.0)
+    C.tp_sum_residual_rmsnorm(torch.randn(T, N, device="cuda"), [staging2.data_ptr(), peer_staging.data_ptr()],
+                              [fa.data_ptr(), fb.data_ptr()], 0, max_rows * N, 0, max_rows, None, g, stream, normed, 1e-5,
+                              epoch, arrive, 2_000_000, st)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="status 1"):
+        native.check_status("cuda")
+    native.check_status("cuda")  # cleared
+    assert float((stream.float() - 7).abs().max()) == 0.0
+    assert int(fb.view(2, 2, max_rows)[0, 0, :T].min()) == int(epoch)        # the peer was still signalled
+    assert float(peer_staging.view(2, max_rows, N)[0, :T].float().abs().max()) > 0   # and received the rows
