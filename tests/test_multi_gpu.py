@@ -101,9 +101,11 @@ dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_tensor_parallel_engine_matches_single_gpu():
+@pytest.mark.parametrize("row_flags", ["0", "1"])
+def test_tensor_parallel_engine_matches_single_gpu(row_flags):
+    """row_flags = 1: decode-sized sums run as the single-launch kernel with per-row flags."""
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, REPO_ROOT=root, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, REPO_ROOT=root, NCCL_NVLS_ENABLE="0", MYTHOS_TP_ROW_FLAGS=row_flags)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29621", "--no-python", sys.executable, "-c", TP_WORKER]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
