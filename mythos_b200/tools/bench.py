@@ -20,6 +20,7 @@ def main(argv=None) -> int:
     ap.add_argument("--inference", action="store_true")
     ap.add_argument("--model", default=None)
     ap.add_argument("--prompt", default="The quick brown fox")
+    ap.add_argument("--prompts", default=None, help="file with one prompt per line (each is timed; means are reported)")
     ap.add_argument("--batch-size", type=int, default=1)
     ap.add_argument("--max-tokens", type=int, default=128)
     ap.add_argument("--iterations", type=int, default=10)
@@ -39,9 +40,13 @@ def main(argv=None) -> int:
         device = pick_device(a.device)
         model, _ = load_model(a.model, device=device)
         model.eval()
-        text, stats = generate_text(model, None, a.prompt, a.max_tokens, SamplerConfig(temperature=0.0), device)
-        row = {"model": a.model, "tokens_per_s": stats["tokens_per_s"], "ttft_ms": stats["ttft_s"] * 1e3,
-               "ms_per_token": 1e3 / max(stats["tokens_per_s"], 1e-9),
+        prompts = [a.prompt]
+        if a.prompts:
+            prompts = [ln.rstrip("\n") for ln in open(a.prompts, encoding="utf-8") if ln.strip()] or prompts
+        runs = [generate_text(model, None, p, a.max_tokens, SamplerConfig(temperature=0.0), device)[1] for p in prompts]
+        stats = {k: sum(r[k] for r in runs) / len(runs) for k in ("tokens_per_s", "ttft_s")}
+        row = {"model": a.model, "prompts": len(prompts), "tokens_per_s": stats["tokens_per_s"],
+               "ttft_ms": stats["ttft_s"] * 1e3, "ms_per_token": 1e3 / max(stats["tokens_per_s"], 1e-9),
                "memory_mb": torch.cuda.max_memory_allocated() / 2 ** 20 if device.type == "cuda" else 0.0}
         line = ",".join(f"{v}" for v in row.values()) if a.csv else json.dumps(row)
         print(line)

@@ -40,6 +40,10 @@ def main(argv=None) -> int:
     ap.add_argument("--target-modules", default="q,v")
     ap.add_argument("--merge", action="store_true", help="fold adapters into the base before saving")
     ap.add_argument("--grad-threshold", type=float, default=0.0)
+    ap.add_argument("--freeze-base", action="store_true",
+                    help="full method: keep every linear weight fixed (norms and embeddings still train); "
+                         "adapter methods always freeze the base")
+    ap.add_argument("--save-interval", type=int, default=0, help="also save every N steps")
     ap.add_argument("--log-interval", type=int, default=10)
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
     ap.add_argument("--seed", type=int, default=None, help="default: OIL_SEED, else 42")
@@ -55,9 +59,17 @@ def main(argv=None) -> int:
     ids = np.minimum(np.asarray(tok.encode(open(a.data, "rb").read()), dtype=np.int32), model.cfg.vocab_size - 1)
     if a.method != "full":
         apply_lora(model, a.lora_rank, a.lora_alpha, tuple(a.target_modules.split(",")), dora=(a.method == "dora"))
+    elif a.freeze_base:
+        from ..models.layers import OILLinear
+
+        for m in model.modules():
+            if isinstance(m, OILLinear):
+                m.weight.requires_grad_(False)
     seq = min(a.seq_length, model.cfg.max_seq_len)
     tcfg = TrainConfig(batch_size=a.batch_size, seq_length=seq, epochs=a.epochs, max_steps=a.max_steps, lr=a.lr,
-                       weight_decay=0.0, warmup_steps=max(1, a.max_steps // 20), log_interval=a.log_interval)
+                       weight_decay=0.0, warmup_steps=max(1, a.max_steps // 20), log_interval=a.log_interval,
+                       save_interval=a.save_interval if a.method == "full" else 0,
+                       output_path=a.output if (a.method == "full" and a.save_interval) else "")
     tr = Trainer(model, tcfg, device=device)
     tr.log_callbacks.append(lambda m: print(f"step {m.step} loss {m.loss:.4f} gnorm {m.grad_norm:.3f}", flush=True))
     loader = TokenDataset(ids, a.batch_size, seq, seed=a.seed, pin=device.type == "cuda")
