@@ -31,12 +31,14 @@ def build_parser():
     ap.add_argument("--batch-size", type=int, default=1)
     ap.add_argument("--output", "-o", default=None)
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
-    ap.add_argument("--precision", default="auto")
+    ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "fp16", "bf16", "int8"],
+                    help="int8: int8 KV pages on the GPU engine, int8 activations on the CPU path; the other "
+                         "values keep the engine's bf16 compute (GPU) / fp32 reference ops (CPU)")
     ap.add_argument("--verbose", action="store_true")
     return ap
 
 
-def generate_text(model, tokenizer, prompt: str, max_tokens: int, sampler, device):
+def generate_text(model, tokenizer, prompt: str, max_tokens: int, sampler, device, precision: str = "auto"):
     """Returns (text, stats dict). CUDA: paged-KV engine; CPU: full-recompute loop on the reference ops."""
     from ..infer.sampler import sample
 
@@ -48,7 +50,8 @@ def generate_text(model, tokenizer, prompt: str, max_tokens: int, sampler, devic
 
         S = len(ids)
         eng = InferenceEngine.from_model(model, device=device, max_batch=1,
-                                         max_seq_len=min(model.cfg.max_seq_len, S + max_tokens) + 16)
+                                         max_seq_len=min(model.cfg.max_seq_len, S + max_tokens) + 16,
+                                         kv_dtype="int8" if precision == "int8" else "bf16")
         room = eng.max_seq_len - S
         res = eng.generate([ids], max_new_tokens=max(1, min(max_tokens, room)), sampler=sampler,
                            use_graph=sampler.greedy)
@@ -58,10 +61,15 @@ def generate_text(model, tokenizer, prompt: str, max_tokens: int, sampler, devic
         seq = torch.tensor([ids], dtype=torch.int32)
         new = []
         ttft = None
+        run = model
+        if precision == "int8":
+            from ..infer.extras import INT8Inference
+
+            run = INT8Inference(model)
         with torch.no_grad():
             for step in range(max_tokens):
                 window = seq[:, -model.cfg.max_seq_len:]
-                logits = model(window)[:, -1].float()
+                logits = run(window)[:, -1].float()
                 hist = seq[:, -64:].to(torch.int32)
                 tok = sample(logits, sampler, history=hist, step=step)
                 if ttft is None:
@@ -102,7 +110,7 @@ def main(argv=None) -> int:
         print(f"warning: {vocab} not found, using byte tokens", file=sys.stderr)
     sampler = SamplerConfig(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             repetition_penalty=args.repetition_penalty, seed=args.seed)
-    text, stats = generate_text(model, tokenizer, prompt, args.max_tokens, sampler, device)
+    text, stats = generate_text(model, tokenizer, prompt, args.max_tokens, sampler, device, args.precision)
     out = prompt + text
     if args.output:
         with open(args.output, "w") as f:

@@ -57,6 +57,7 @@ def test_infer_positional_and_flags(trained, capsys):
                        str(d / "gen.txt")]) == 0
     capsys.readouterr()
     assert (d / "gen.txt").read_text().strip() and first.strip()
+    assert infer.main([str(model), "the quick", "-t", "3", "--temperature", "0", "--gpu", "cpu", "--precision", "int8"]) == 0
 
 
 @pytest.mark.parametrize("method", ["lora", "qlora", "dora", "full"])
