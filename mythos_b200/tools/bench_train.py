@@ -1,0 +1,89 @@
+"""Training-step throughput of any named configuration on one GPU (tokens/s, CUDA events).
+
+    python -m mythos_b200.tools.bench_train --preset moe-8x --batch 16 --micro-batch 4 --seq 2048
+    python -m mythos_b200.tools.bench_train --preset bitnet-2.4b --lora-rank 16 --batch 4 --micro-batch 1 --seq 4096
+
+``bench.py`` at the repository root is the fixed headline benchmark (dense 1.3B, 1-8 GPUs); this
+tool covers the other training configurations: the 8-expert MoE (all experts local: routing,
+dispatch, grouped expert GEMMs and combine run through the same kernels as under expert
+parallelism, with the exchange buffers in local memory) and LoRA fine-tuning of q / v on a frozen
+quantised base. Synthetic seeded Zipf(1.1) tokens, random-init weights, optimizer step inside the
+timed region, W warm-up steps, K timed steps bracketed by synchronisation.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def main(argv=None) -> int:
+    from ..models import DenseModel
+    from ..models.config import NAMED_CONFIGS
+    from ..ops import native
+    from ..train.data import ZipfStream
+    from ..train.trainer import TrainConfig, Trainer
+
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--preset", default="moe-8x", choices=sorted(NAMED_CONFIGS))
+    ap.add_argument("--layers", type=int, default=0, help="use only this many layers (0 = all)")
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--micro-batch", type=int, default=4)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--lora-rank", type=int, default=0, help="> 0: freeze the base and train rank-r adapters")
+    ap.add_argument("--lora-targets", default="q,v")
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    native.require()
+    cfg = NAMED_CONFIGS[a.preset]()
+    if a.layers:
+        cfg.num_layers = a.layers
+    cfg.max_seq_len = max(a.seq, min(cfg.max_seq_len, a.seq))
+    torch.manual_seed(1234)
+    if cfg.num_experts > 0:
+        from ..models.moe import MoEModel as Model
+    else:
+        Model = DenseModel
+    with torch.device(dev):
+        model = Model(cfg)
+    if a.lora_rank > 0:
+        from ..models.lora import apply_lora
+
+        apply_lora(model, a.lora_rank, 2.0 * a.lora_rank, tuple(a.lora_targets.split(",")))
+    n_params = sum(p.numel() for p in model.parameters())
+    n_train = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    tr = Trainer(model, TrainConfig(batch_size=a.batch, micro_batch_size=a.micro_batch, seq_length=a.seq, lr=3e-4,
+                                    warmup_steps=100, max_steps=10000, max_grad_norm=1.0, codebook_ema_interval=0),
+                 device=dev)
+    stream = ZipfStream(cfg.vocab_size, a.batch, a.seq, s=1.1, seed=100)
+    batches = [tuple(t.to(dev) for t in stream.next_batch()) for _ in range(2)]
+    for i in range(a.warmup):
+        tr.train_step(*batches[i % 2])
+    torch.cuda.synchronize()
+    native.check_status(dev)
+    l0 = native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.steps):
+        loss = tr.train_step(*batches[i % 2])
+    e1.record()
+    torch.cuda.synchronize()
+    native.check_status(dev)
+    ms = e0.elapsed_time(e1) / a.steps
+    print(json.dumps({"metric": "train tokens/s (one GPU)", "preset": a.preset, "layers": cfg.num_layers,
+                      "value": a.batch * a.seq / (ms / 1e3), "ms_per_step": ms, "batch": a.batch,
+                      "micro_batch": a.micro_batch, "seq_len": a.seq, "steps": a.steps, "warmup": a.warmup,
+                      "parameters": n_params, "trainable_parameters": n_train, "lora_rank": a.lora_rank,
+                      "gpu_launches_per_step": (native.launch_count() - l0) // a.steps, "loss": float(loss),
+                      "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
+                      "data": "synthetic seeded Zipf(1.1) tokens, random-init weights"}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
