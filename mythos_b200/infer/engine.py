@@ -644,13 +644,20 @@ class InferenceEngine:
         mapped into the new sequence (their reference counts go up) and only the remaining tokens
         are computed: their K/V are appended to fresh pages and their queries attend over the paged
         cache (shared prefix + the new tokens before them) in chunks of at most ``max_batch``
-        tokens. Without a cached prefix the whole prompt runs through the flash-attention prefill."""
+        tokens. Without a cached prefix, or when the hit covers less than half of the prompt, the
+        whole prompt runs through the flash-attention prefill."""
         ids = [int(t) for t in prompt_ids]
         cache = self.cache
         seq = cache.new_sequence()
         S = len(ids)
         # at least the last token is always computed: its logits are the result
         covered = cache.share_prefix(seq, ids[:-1]) if reuse_prefix and S > 1 else 0
+        if 0 < covered < S // 2:
+            # A short hit is not worth it: the rest would go through the decode kernel in chunks of
+            # max_batch tokens, each chunk a full pass over the weights. Recompute the whole prompt.
+            cache.free_sequence(seq)
+            seq = cache.new_sequence()
+            covered = 0
         cache.reserve(seq, S - covered)
         cache.sync_tables()
         dev = self.device
