@@ -44,45 +44,35 @@ class DenseToMoEPruner:
         return experts
 
 
-_DTYPES = {0: torch.float32, 1: torch.float16, 2: torch.int8, 3: torch.uint8, 4: torch.int32, 5: torch.int64}
-_DTYPE_IDS = {v: k for k, v in _DTYPES.items()}
-
-
 def save_experts(tensors, path: str) -> None:
     """Expert tensor file: i32 count, then per tensor i32 rank, i64 dims[rank], u8 dtype, raw bytes
-    (the host tensor serialisation of the reference, src/tensor.cpp:297-334)."""
+    (the host tensor serialisation of the reference, src/tensor.cpp:297-334, with its ``DType``
+    numbering: int64 0, uint8 1, float16 5, float32 6; int32 tensors are widened to int64, other
+    types stored as float32)."""
+    from ..core import serialize_tensor
+
     with open(path, "wb") as f:
         f.write(struct.pack("<i", len(tensors)))
         for t in tensors:
-            t = t.detach().cpu().contiguous()
-            if t.dtype not in _DTYPE_IDS:
-                t = t.float()
-            f.write(struct.pack("<i", t.dim()))
-            f.write(struct.pack(f"<{t.dim()}q", *t.shape))
-            f.write(struct.pack("<B", _DTYPE_IDS[t.dtype]))
-            f.write(t.numpy().tobytes())
+            if t.dtype in (torch.int32, torch.int16, torch.int8):
+                t = t.long()
+            f.write(serialize_tensor(t))
 
 
 def load_experts(path: str) -> list[torch.Tensor]:
-    import numpy as np
+    from ..core import OilError, deserialize_tensor
 
-    out = []
-    with open(path, "rb") as f:
-        (n,) = struct.unpack("<i", f.read(4))
+    data = open(path, "rb").read()
+    if len(data) < 4:
+        raise ValueError(f"{path}: truncated expert file")
+    (n,) = struct.unpack_from("<i", data, 0)
+    out, off = [], 4
+    try:
         for _ in range(n):
-            (rank,) = struct.unpack("<i", f.read(4))
-            dims = struct.unpack(f"<{rank}q", f.read(8 * rank))
-            (dt,) = struct.unpack("<B", f.read(1))
-            dtype = _DTYPES[dt]
-            count = 1
-            for d in dims:
-                count *= d
-            raw = f.read(count * torch.empty((), dtype=dtype).element_size())
-            if len(raw) != count * torch.empty((), dtype=dtype).element_size():
-                raise ValueError(f"{path}: truncated expert file")
-            npdt = {torch.float32: np.float32, torch.float16: np.float16, torch.int8: np.int8, torch.uint8: np.uint8,
-                    torch.int32: np.int32, torch.int64: np.int64}[dtype]
-            out.append(torch.from_numpy(np.frombuffer(raw, dtype=npdt).copy()).view(*dims))
+            t, off = deserialize_tensor(data, off)
+            out.append(t)
+    except OilError as e:
+        raise ValueError(f"{path}: truncated expert file ({e})") from None
     return out
 
 

@@ -107,29 +107,42 @@ def apply_oil_update(module, grad: torch.Tensor, lr: float, blocks: torch.Tensor
 # --------------------------------------------------------------------------- CHPK checkpoints
 
 CHPK_MAGIC, CHPK_VERSION = 0x4B504843, 2
-_DT = {0: np.float32, 1: np.float16, 2: np.int8, 3: np.uint8, 4: np.int32, 5: np.int64}
-_DT_ID = {torch.float32: 0, torch.float16: 1, torch.int8: 2, torch.uint8: 3, torch.int32: 4, torch.int64: 5}
 
 
 def _write_tensor(f, t: torch.Tensor) -> None:
-    t = t.detach().cpu().contiguous()
-    if t.dtype not in _DT_ID:
-        t = t.float()
-    f.write(struct.pack("<i", t.dim()))
-    f.write(struct.pack(f"<{t.dim()}q", *t.shape))
-    f.write(struct.pack("<B", _DT_ID[t.dtype]))
-    f.write(t.numpy().tobytes())
+    """The reference's ``Tensor::serialize`` record (dtype byte in its ``DType`` numbering)."""
+    from ..core import serialize_tensor
+
+    if t.dtype in (torch.int32, torch.int16, torch.int8):
+        t = t.long()
+    f.write(serialize_tensor(t))
 
 
 def _read_tensor(f) -> torch.Tensor:
-    (rank,) = struct.unpack("<i", f.read(4))
-    dims = struct.unpack(f"<{rank}q", f.read(8 * rank)) if rank else ()
-    (dt,) = struct.unpack("<B", f.read(1))
-    n = int(np.prod(dims)) if rank else 1
-    raw = f.read(n * np.dtype(_DT[dt]).itemsize)
-    if len(raw) != n * np.dtype(_DT[dt]).itemsize:
+    from ..core import DType, dtype_bits
+
+    head = f.read(4)
+    if len(head) != 4:
         raise ValueError("truncated checkpoint")
-    return torch.from_numpy(np.frombuffer(raw, dtype=_DT[dt]).copy()).view(*dims)
+    (rank,) = struct.unpack("<i", head)
+    if not 0 <= rank <= 8:
+        raise ValueError(f"bad tensor rank {rank} in checkpoint")
+    rest = f.read(8 * rank + 1)
+    if len(rest) != 8 * rank + 1:
+        raise ValueError("truncated checkpoint")
+    dims = struct.unpack(f"<{rank}q", rest[:-1]) if rank else ()
+    try:
+        dt = DType(rest[-1])
+    except ValueError:
+        raise ValueError(f"unknown tensor dtype {rest[-1]} in checkpoint") from None
+    npdt = {DType.I64: np.int64, DType.U8: np.uint8, DType.F16: np.float16, DType.F32: np.float32}.get(dt)
+    if npdt is None:
+        raise ValueError(f"dtype {dt.name} has no dense form")
+    n = int(np.prod(dims)) if rank else 1
+    raw = f.read(n * dtype_bits(dt) // 8)
+    if len(raw) != n * dtype_bits(dt) // 8:
+        raise ValueError("truncated checkpoint")
+    return torch.from_numpy(np.frombuffer(raw, dtype=npdt).copy()).reshape(tuple(dims))
 
 
 def save_chpk(path: str, step: int, lr: float, params, m=None, v=None) -> None:

@@ -82,7 +82,10 @@ def test_moe_utilities(tmp_path):
     path = str(tmp_path / "experts.bin")
     me.save_experts(ts, path)
     back = me.load_experts(path)
-    assert all(a.dtype == b.dtype and torch.equal(a, b) for a, b in zip(ts, back))
+    assert back[0].dtype == torch.float32 and back[2].dtype == torch.float16 and back[1].dtype == torch.int64
+    assert all(torch.equal(a.to(b.dtype), b) for a, b in zip(ts, back))
+    raw = open(path, "rb").read()
+    assert raw[4 + 4 + 16] == 6          # float32 carries the reference's DType number
     drop = me.ExpertDropout(0.25)
     assert drop.get_active_count(8) == 6 and sum(drop.get_mask(8)) == 6
     bal = me.compute_balance([0, 1, 2, 3, 0, 1, 2, 3], 4)
