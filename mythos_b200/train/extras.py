@@ -109,69 +109,82 @@ def apply_oil_update(module, grad: torch.Tensor, lr: float, blocks: torch.Tensor
 CHPK_MAGIC, CHPK_VERSION = 0x4B504843, 2
 
 
-def _write_tensor(f, t: torch.Tensor) -> None:
-    """The reference's ``Tensor::serialize`` record (dtype byte in its ``DType`` numbering)."""
+def _write_record(f, name: str, t: torch.Tensor) -> None:
+    """``u32 name_len, name, u32 size, Tensor::serialize bytes`` (checkpoint.cpp:14-29)."""
     from ..core import serialize_tensor
 
     if t.dtype in (torch.int32, torch.int16, torch.int8):
         t = t.long()
-    f.write(serialize_tensor(t))
+    body = serialize_tensor(t)
+    if len(body) > 0xFFFFFFFF:
+        raise ValueError("tensor too large for the checkpoint format (> 4 GB)")
+    raw = name.encode()
+    f.write(struct.pack("<I", len(raw)) + raw + struct.pack("<I", len(body)) + body)
 
 
-def _read_tensor(f) -> torch.Tensor:
-    from ..core import DType, dtype_bits
+def _read_record(f, expected: str) -> torch.Tensor:
+    from ..core import OilError, deserialize_tensor
 
     head = f.read(4)
     if len(head) != 4:
-        raise ValueError("truncated checkpoint")
-    (rank,) = struct.unpack("<i", head)
-    if not 0 <= rank <= 8:
-        raise ValueError(f"bad tensor rank {rank} in checkpoint")
-    rest = f.read(8 * rank + 1)
-    if len(rest) != 8 * rank + 1:
-        raise ValueError("truncated checkpoint")
-    dims = struct.unpack(f"<{rank}q", rest[:-1]) if rank else ()
+        raise ValueError("corrupt checkpoint: name length")
+    (n,) = struct.unpack("<I", head)
+    name = f.read(n)
+    size = f.read(4)
+    if len(name) != n or len(size) != 4:
+        raise ValueError("corrupt checkpoint: tensor size")
+    if name.decode(errors="replace") != expected:
+        raise ValueError(f"checkpoint record {name!r} where {expected!r} was expected")
+    (nbytes,) = struct.unpack("<I", size)
+    body = f.read(nbytes)
+    if len(body) != nbytes:
+        raise ValueError("corrupt checkpoint: tensor data")
     try:
-        dt = DType(rest[-1])
-    except ValueError:
-        raise ValueError(f"unknown tensor dtype {rest[-1]} in checkpoint") from None
-    npdt = {DType.I64: np.int64, DType.U8: np.uint8, DType.F16: np.float16, DType.F32: np.float32}.get(dt)
-    if npdt is None:
-        raise ValueError(f"dtype {dt.name} has no dense form")
-    n = int(np.prod(dims)) if rank else 1
-    raw = f.read(n * dtype_bits(dt) // 8)
-    if len(raw) != n * dtype_bits(dt) // 8:
-        raise ValueError("truncated checkpoint")
-    return torch.from_numpy(np.frombuffer(raw, dtype=npdt).copy()).reshape(tuple(dims))
+        return deserialize_tensor(body)[0]
+    except OilError as e:
+        raise ValueError(f"corrupt checkpoint: {e}") from None
 
 
 def save_chpk(path: str, step: int, lr: float, params, m=None, v=None) -> None:
-    """u32 magic, u32 version, i64 step, f32 lr, u32 count, parameters, u8 has_moments, m list, v list."""
+    """The reference's dense-trainer checkpoint, byte for byte (engines/trainer/dense/
+    checkpoint.cpp:53-103): u32 magic "CHPK", u32 version 2, u32 step, f32 lr, u32 count, records
+    ``param_i``; u32 count, then per index the records ``m_i`` and ``v_i`` (zeros when the optimizer
+    has no state yet)."""
     params = list(params)
+    if not 0 <= step <= 0xFFFFFFFF:
+        raise ValueError("checkpoint: step exceeds the uint32 range")
+    m = list(m) if m is not None else [torch.zeros_like(p, dtype=torch.float32) for p in params]
+    v = list(v) if v is not None else [torch.zeros_like(p, dtype=torch.float32) for p in params]
     with open(path, "wb") as f:
-        f.write(struct.pack("<IIqfI", CHPK_MAGIC, CHPK_VERSION, step, lr, len(params)))
-        for p in params:
-            _write_tensor(f, p)
-        has = m is not None and v is not None
-        f.write(struct.pack("<B", 1 if has else 0))
-        if has:
-            for t in list(m) + list(v):
-                _write_tensor(f, t)
+        f.write(struct.pack("<IIIfI", CHPK_MAGIC, CHPK_VERSION, step, lr, len(params)))
+        for i, p in enumerate(params):
+            _write_record(f, f"param_{i}", p)
+        f.write(struct.pack("<I", len(params)))
+        for i in range(len(params)):
+            _write_record(f, f"m_{i}", m[i])
+            _write_record(f, f"v_{i}", v[i])
 
 
 def load_chpk(path: str):
     with open(path, "rb") as f:
-        magic, version, step, lr, n = struct.unpack("<IIqfI", f.read(24))
+        head = f.read(20)
+        if len(head) != 20:
+            raise ValueError(f"{path}: truncated checkpoint header")
+        magic, version, step, lr, n = struct.unpack("<IIIfI", head)
         if magic != CHPK_MAGIC:
             raise ValueError(f"{path}: not a CHPK checkpoint")
         if version > CHPK_VERSION:
             raise ValueError(f"{path}: checkpoint version {version} is newer than {CHPK_VERSION}")
-        params = [_read_tensor(f) for _ in range(n)]
+        params = [_read_record(f, f"param_{i}") for i in range(n)]
         m = v = None
-        flag = f.read(1)
-        if flag and flag[0] == 1:
-            m = [_read_tensor(f) for _ in range(n)]
-            v = [_read_tensor(f) for _ in range(n)]
+        if version >= 2:
+            cnt = f.read(4)
+            if len(cnt) == 4:
+                (num_opt,) = struct.unpack("<I", cnt)
+                m, v = [], []
+                for i in range(num_opt):
+                    m.append(_read_record(f, f"m_{i}"))
+                    v.append(_read_record(f, f"v_{i}"))
     return {"step": step, "lr": lr, "params": params, "m": m, "v": v}
 
 

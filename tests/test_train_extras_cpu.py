@@ -48,6 +48,19 @@ def test_chpk_round_trip(tmp_path):
     ck = ex.load_chpk(path)
     assert ck["step"] == 17 and abs(ck["lr"] - 1e-3) < 1e-9
     assert all(torch.equal(a, b) for a, b in zip(ps, ck["params"])) and torch.equal(ck["v"][1], v[1])
+    # byte layout of the reference writer: 20-byte header with a u32 step, then named records
+    import struct
+    raw = open(path, "rb").read()
+    assert struct.unpack_from("<IIIfI", raw, 0)[:3] == (0x4B504843, 2, 17) and struct.unpack_from("<I", raw, 16)[0] == 2
+    assert raw[20:24] == struct.pack("<I", 7) and raw[24:31] == b"param_0"
+    body = struct.unpack_from("<I", raw, 31)[0]
+    assert body == 4 + 2 * 8 + 1 + 12 * 4 and raw[35:39] == struct.pack("<i", 2) and raw[35 + 4 + 16] == 6
+    pos = [raw.index(struct.pack("<I", 3) + tag) for tag in (b"m_0", b"v_0", b"m_1", b"v_1")]
+    assert pos == sorted(pos) and pos[0] > raw.index(b"param_1")        # moments interleaved per parameter
+    ex.save_chpk(path, 3, 1e-2, ps)                      # no optimizer state yet: zeros are written
+    ck0 = ex.load_chpk(path)
+    assert ck0["step"] == 3 and all(float(t.abs().sum()) == 0 for t in ck0["m"] + ck0["v"])
+    ex.save_chpk(path, 17, 1e-3, ps, m, v)
     with open(path, "r+b") as f:
         f.write(b"XXXX")
     try:
