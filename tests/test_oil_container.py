@@ -155,3 +155,48 @@ def test_model_save_load_save_is_bit_exact(tmp_path, fmt):
     want = {"oil8": Format.OIL8, "oil4": Format.OIL4, "i2s": Format.TERNARY, "fp32": Format.FP32}[fmt]
     assert set(fmts) == {want}
     assert m2.cfg.weight_format == fmt and m2.cfg.oil_block_size == 64
+
+
+def test_reader_fuzz_only_raises_oil_errors(tmp_path):
+    """Truncations and byte flips in the header / tables: the Python reader either reads the file or
+    raises OILError, never an IndexError / struct.error / MemoryError from a wild size field."""
+    import random
+
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.oil.container import OILError, OILReader, read_idx_file
+    from mythos_b200.oil.model_io import save_model
+
+    random.seed(0)
+    torch.manual_seed(0)
+    rejected = 0
+    for fmt in ("oil8", "i2s"):
+        cfg = TransformerConfig(vocab_size=32, hidden_size=32, num_layers=1, num_heads=2, head_dim=16,
+                                ffn_hidden_size=64, max_seq_len=16, weight_format=fmt, oil_block_size=32)
+        p = str(tmp_path / f"{fmt}.oil")
+        save_model(DenseModel(cfg), p)
+        raw = open(p, "rb").read()
+        trials = [raw[:c] for c in list(range(0, 160, 5)) + [len(raw) * i // 11 for i in range(11)]]
+        for _ in range(80):
+            b = bytearray(raw)
+            pos = random.randrange(0, min(len(b), 400))
+            b[pos] = random.choice([0x00, 0xFF, 0x7F, 0x80, b[pos] ^ (1 << random.randrange(8))])
+            trials.append(bytes(b))
+        q = str(tmp_path / "trial.oil")
+        for t in trials:
+            open(q, "wb").write(t)
+            try:
+                r = OILReader(q)
+                for name in r.tensor_names():
+                    try:
+                        r.read_tensor(name)
+                    except OILError:
+                        rejected += 1
+            except OILError:
+                rejected += 1
+        rawi = open(p + "idx", "rb").read()
+        qi = str(tmp_path / "trial.oilidx")
+        for c in range(0, len(rawi) - 1, 9):
+            open(qi, "wb").write(rawi[:c])
+            with pytest.raises(OILError):
+                read_idx_file(qi)
+    assert rejected > 50
