@@ -112,6 +112,22 @@ def _embed_gather_ok(cfg: TransformerConfig) -> bool:
     return cfg.hidden_size % 64 == 0
 
 
+def _zero_ffn_padding(up: QuantLinear, down: QuantLinear, f_loc: int, f_pad: int, gated: bool) -> None:
+    """Set the padded FFN units of a shard to exact zeros: rows [f_loc, f_pad) of each half of the up
+    projection and columns [f_loc, f_pad) of the down projection. I2_S only (trit code 1 is zero
+    whatever the block scale; four trits per byte, so f_loc has to be a multiple of 4); codebook
+    formats have no exact zero."""
+    if up.fmt != "i2s" or down.fmt != "i2s" or f_loc % 4:
+        raise ValueError("padding an FFN shard needs I2_S weights and a shard width that is a multiple of 4; "
+                         "choose a tensor-parallel size whose FFN shard is a multiple of 64")
+    zero = 0x55                                            # 01 01 01 01
+    rows_up = up.packed.view(up.N, up.K // 4)
+    rows_up[f_loc:f_pad] = zero
+    if gated:
+        rows_up[f_pad + f_loc:2 * f_pad] = zero
+    down.packed.view(down.N, down.K // 4)[:, f_loc // 4:] = zero
+
+
 def _embed_block(cfg: TransformerConfig) -> int:
     return cfg.oil_block_size if cfg.hidden_size % cfg.oil_block_size == 0 else 64
 
@@ -207,8 +223,11 @@ class InferenceEngine:
         """Synthetic engine for benchmarks: every matrix is created directly in its storage format
         (quantile codebooks with uniform-random indices, trits with p = 0.25/0.5/0.25), shard by
         shard, so a large model never exists in fp32. Embeddings are random bf16."""
+        ffn_multiple = int(kw.pop("ffn_multiple", 64))
         eng = cls(cfg, **kw)
         dev, W, r = eng.device, eng.world, eng.rank
+        if cfg.ffn_hidden_size % W or ffn_multiple % 64:
+            raise ValueError("the FFN width must divide by the tensor-parallel size and ffn_multiple by 64")
         g = torch.Generator(device=dev).manual_seed(seed * 1000 + r)
         D, d = cfg.head_dim, cfg.hidden_size
         bs, grp = cfg.oil_block_size, cfg.codebook_group
@@ -234,8 +253,15 @@ class InferenceEngine:
             L.ffn_norm = torch.ones(d, device=dev, dtype=torch.bfloat16)
             L.qkv = mk(af, (eng.h_local + 2 * eng.hkv_local) * D, d)
             L.o = mk(af, d, eng.h_local * D)
-            L.up = mk(ff, (2 if cfg.gated_ffn else 1) * f // W, d)
-            L.down = mk(ff, d, f // W)
+            # The down projection's reduction length (this rank's FFN columns) has to be a multiple
+            # of 64 for the dequant GEMM; a shard that is not (6912 / 8 = 864) is padded with zero
+            # weights: zero rows of the up projection give act(0) * 0 = 0 and meet zero columns.
+            f_loc = f // W
+            f_pad = (f_loc + ffn_multiple - 1) // ffn_multiple * ffn_multiple
+            L.up = mk(ff, (2 if cfg.gated_ffn else 1) * f_pad, d)
+            L.down = mk(ff, d, f_pad)
+            if f_pad != f_loc:
+                _zero_ffn_padding(L.up, L.down, f_loc, f_pad, cfg.gated_ffn)
             eng.layers.append(L)
         hf = cfg.weight_format if cfg.embed_format in ("fp32", "fp16", "bf16") else cfg.embed_format
         eng.head = mk(hf, cfg.vocab_size // W, d)

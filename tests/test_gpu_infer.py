@@ -598,3 +598,42 @@ def test_row_signalled_sum_norm_single_rank_and_timeout():
     assert float((stream.float() - 7).abs().max()) == 0.0
     assert int(fb.view(2, 2, max_rows)[0, 0, :T].min()) == int(epoch)        # the peer was still signalled
     assert float(peer_staging.view(2, max_rows, N)[0, :T].float().abs().max()) > 0   # and received the rows
+
+
+def test_zero_padded_ffn_shard_equals_the_unpadded_one():
+    """An I2_S FFN shard whose width is not a multiple of the GEMM's K granule is padded with zero
+    trits; slicing the padding away again must not change the logits."""
+    from mythos_b200.infer.engine import InferenceEngine
+    from mythos_b200.infer.quant_weights import QuantLinear
+    from mythos_b200.models import TransformerConfig
+
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=2, head_dim=128,
+                            ffn_hidden_size=192, max_seq_len=256, activation="relu2", gated_ffn=True,
+                            weight_format="i2s", embed_format="fp16", oil_block_size=64)
+    f, fp = 192, 256
+    padded = InferenceEngine.random(cfg, seed=9, device="cuda", max_batch=4, max_seq_len=256, ffn_multiple=128)
+    sliced = InferenceEngine.random(cfg, seed=9, device="cuda", max_batch=4, max_seq_len=256, ffn_multiple=128)
+    for Lp, Ls in zip(padded.layers, sliced.layers):
+        assert Lp.up.N == 2 * fp and Lp.down.K == fp
+        up_rows = Lp.up.packed.view(2 * fp, -1)
+        assert int((up_rows[f:fp] != 0x55).sum()) == 0 and int((up_rows[fp + f:] != 0x55).sum()) == 0
+        assert int((Lp.down.packed.view(256, -1)[:, f // 4:] != 0x55).sum()) == 0
+        keep = torch.cat([up_rows[:f], up_rows[fp:fp + f]]).contiguous().view(-1)
+        up_scales = Lp.up.scales.view(2 * fp, -1)
+        Ls.up = QuantLinear("i2s", 2 * f, 256, 64, keep,
+                            scales=torch.cat([up_scales[:f], up_scales[fp:fp + f]]).contiguous().view(-1))
+        down_bytes = Lp.down.packed.view(256, -1)[:, : f // 4].contiguous().view(-1)
+        down_scales = Lp.down.scales.view(256, -1)[:, : f // 64].contiguous().view(-1)
+        Ls.down = QuantLinear("i2s", 256, f, 64, down_bytes, scales=down_scales)
+    prompt = torch.randint(0, 512, (40,), generator=torch.Generator().manual_seed(4)).tolist()
+    sp, lp = padded.start_sequence(prompt, reuse_prefix=False)
+    ss, ls = sliced.start_sequence(prompt, reuse_prefix=False)
+    assert float((lp.float() - ls.float()).abs().max()) < 2e-2 and int(lp.float().argmax()) == int(ls.float().argmax())
+    tok = int(lp.float().argmax())
+    dp, ds = padded.decode([sp], [tok]), sliced.decode([ss], [tok])
+    assert float((dp.float() - ds.float()).abs().max()) < 2e-2
+    with pytest.raises(ValueError, match="I2_S"):
+        InferenceEngine.random(TransformerConfig(vocab_size=512, hidden_size=256, num_layers=1, num_heads=2, head_dim=128,
+                                                 ffn_hidden_size=192, max_seq_len=64, weight_format="oil8",
+                                                 oil_block_size=64), seed=1, device="cuda", max_batch=2, max_seq_len=64,
+                               ffn_multiple=128)
