@@ -104,3 +104,20 @@ def test_codebook_engines_reduce_error():
         after = float(((d - w) ** 2).mean())
         assert after < before                       # Lloyd iterations lower the squared error
         assert E.compute_quant_error(w, d) == float((d - w).abs().max())
+
+
+def test_ffn_shard_padding_writes_exact_zero_trits():
+    from mythos_b200.infer.engine import _zero_ffn_padding
+    from mythos_b200.infer.quant_weights import QuantLinear
+
+    up = QuantLinear.random("i2s", 2 * 256, 256, 64, device="cpu", generator=torch.Generator().manual_seed(0))
+    down = QuantLinear.random("i2s", 256, 256, 64, device="cpu", generator=torch.Generator().manual_seed(1))
+    before_up, before_down = up._dequantize_reference().clone(), down._dequantize_reference().clone()
+    _zero_ffn_padding(up, down, 192, 256, True)
+    w, wd = up._dequantize_reference(), down._dequantize_reference()
+    assert float(w[192:256].abs().max()) == 0 and float(w[256 + 192:].abs().max()) == 0 and float(wd[:, 192:].abs().max()) == 0
+    assert torch.equal(w[:192], before_up[:192]) and torch.equal(w[256:256 + 192], before_up[256:256 + 192])
+    assert torch.equal(wd[:, :192], before_down[:, :192])
+    oil = QuantLinear.random("oil8", 256, 256, 64, 1, device="cpu", generator=torch.Generator().manual_seed(2))
+    with pytest.raises(ValueError, match="I2_S"):
+        _zero_ffn_padding(oil, down, 192, 256, False)
