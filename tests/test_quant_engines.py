@@ -2,6 +2,7 @@
 closed-form expectations and round trips."""
 import math
 
+import pytest
 import torch
 
 from mythos_b200.oil import engines as E
