@@ -49,6 +49,12 @@ def build_parser():
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
     ap.add_argument("--resume", default=None)
     ap.add_argument("--seed", type=int, default=None, help="default: OIL_SEED, else 42")
+    ap.add_argument("--streaming", action="store_true",
+                    help="read and tokenise --data in 4 MB chunks while training (the tokenizer is trained on the first chunk)")
+    ap.add_argument("--mask-prob", type=float, default=0.0, help="augmentation: input ids replaced by id 0")
+    ap.add_argument("--replace-prob", type=float, default=0.0, help="augmentation: input ids replaced by random ids")
+    ap.add_argument("--curriculum-epochs", type=int, default=0,
+                    help="grow the sequence length from a quarter to full over this many epochs")
     ap.add_argument("--logdir", default=None, help="write TensorBoard events + JSONL here")
     ap.add_argument("--verbose", action="store_true")
     return ap
@@ -73,10 +79,11 @@ def main(argv=None) -> int:
     tokenizer, tokens = None, None
     vocab = args.vocab_size
     if args.data:
-        text = open(args.data, "rb").read()
+        with open(args.data, "rb") as fh:
+            text = fh.read(4 << 20) if args.streaming else fh.read()
         tokenizer = BPETokenizer()
         tokenizer.train(text, max(256, vocab or 512))
-        tokens = np.asarray(tokenizer.encode(text), dtype=np.int32)
+        tokens = None if args.streaming else np.asarray(tokenizer.encode(text), dtype=np.int32)
         vocab = tokenizer.vocab_size
     cfg = model_config_from(args, cfgj, vocab or None)
     seq = args.seq_length or tj.get("seq_length") or min(cfg.max_seq_len, 512)
@@ -112,6 +119,10 @@ def main(argv=None) -> int:
         if len(loader) == 0:
             print("corpus is shorter than one batch; lower --batch-size / --seq-length", file=sys.stderr)
             return 2
+    elif args.streaming and args.data:
+        from ..train.data import StreamingTokenDataset
+
+        loader = StreamingTokenDataset(args.data, tokenizer, batch, seq, vocab_limit=cfg.vocab_size)
     else:
         stream = ZipfStream(cfg.vocab_size, batch, seq, seed=args.seed)
 
@@ -122,6 +133,12 @@ def main(argv=None) -> int:
 
         loader = _Synthetic()
         tcfg.epochs = 1
+    if args.mask_prob or args.replace_prob or args.curriculum_epochs:
+        from ..train.data import AugmentedLoader, Curriculum
+
+        cur = Curriculum(seq, args.curriculum_epochs) if args.curriculum_epochs else None
+        loader = AugmentedLoader(loader, cfg.vocab_size, args.mask_prob, args.replace_prob, curriculum=cur,
+                                 seed=args.seed)
     metrics = trainer.fit(loader)
     if tokenizer is not None:
         tokenizer.save(args.model[:-4] + ".vocab" if args.model.endswith(".oil") else args.model + ".vocab")

@@ -106,3 +106,16 @@ def test_convert_and_bench(trained, capsys):
                        "--output", str(d / "bench.json")]) == 0
     row = json.loads((d / "bench.json").read_text())
     assert row["prompts"] == 2 and row["tokens_per_s"] > 0 and row["ms_per_token"] > 0
+
+
+def test_train_streaming_with_augmentation_and_curriculum(tmp_path):
+    from mythos_b200.tools import train
+
+    data = tmp_path / "corpus.txt"
+    data.write_text(CORPUS * 3)
+    model = tmp_path / "s.oil"
+    rc = train.main(["--model", str(model), "--data", str(data), "--streaming", "--batch-size", "2", "--seq-length", "32",
+                     "--epochs", "2", "--max-steps", "8", "--vocab-size", "300", "--dim", "64", "--n-layers", "1",
+                     "--num-heads", "2", "--weight-format", "fp32", "--gpu", "cpu", "--mask-prob", "0.1",
+                     "--replace-prob", "0.05", "--curriculum-epochs", "2", "--log-interval", "4"])
+    assert rc == 0 and model.exists() and (tmp_path / "s.vocab").exists()

@@ -103,3 +103,34 @@ def test_dense_trainer_ema_and_resume(tmp_path):
     tr2.load_checkpoint(path)
     assert tr2.step == 12 and abs(tr2.lr - 3e-3) < 1e-9
     assert abs(tr2.train_step(x, y) - ref_loss) < 1e-5
+
+
+def test_streaming_loader_augmentation_and_curriculum(tmp_path):
+    from mythos_b200.train.data import Curriculum, StreamingTokenDataset, TokenDataset, augment_batch
+
+    text = bytes(range(32, 127)) * 400                         # 38,000 bytes, byte-level ids
+    p = tmp_path / "corpus.bin"
+    p.write_bytes(text)
+    for use_mmap in (False, True):
+        ds = StreamingTokenDataset(str(p), None, batch=4, seq=64, chunk_bytes=5000, prefetch=2, mmap=use_mmap)
+        batches = list(ds)
+        assert ds.chunks_read == 8 and len(batches) == (len(text) - 1) // 256
+        flat = torch.cat([b[0].reshape(-1) for b in batches])
+        assert torch.equal(flat, torch.tensor(list(text[: flat.numel()]), dtype=torch.int32))   # nothing lost at chunk seams
+        assert all(torch.equal(i.reshape(-1)[1:], t.reshape(-1)[:-1]) for i, t in batches)
+    whole = TokenDataset(list(text), 4, 64, shuffle=False, prefetch=0)
+    assert torch.equal(next(iter(whole))[0], batches[0][0])
+    g = torch.Generator().manual_seed(0)
+    ids, tgt = batches[0]
+    a_ids, a_tgt = augment_batch(ids, tgt, vocab=300, mask_prob=0.2, replace_prob=0.1, label_mask_prob=0.3, generator=g)
+    changed = (a_ids != ids).float().mean().item()
+    assert 0.15 < changed < 0.4 and 0.15 < (a_tgt == 0).float().mean().item() < 0.45 and int(a_ids.max()) < 300
+    assert torch.equal(augment_batch(ids, tgt, 300)[0], ids)
+    cur = Curriculum(64, total_epochs=4, min_fraction=0.25)
+    lens = []
+    for e in range(5):
+        cur.step(e)
+        lens.append(cur.length())
+    assert lens == [16, 32, 48, 64, 64] and cur.apply(ids, tgt)[0].shape == (4, 64)
+    cur.step(0)
+    assert cur.apply(ids, tgt)[1].shape == (4, 16)
