@@ -146,3 +146,23 @@ class ModelEvaluator:
         if choice_items is not None:
             out["multiple_choice_accuracy"] = eval_multiple_choice(self.model, choice_items)
         return out
+
+
+# Names of the reference's evaluation entry points (src/eval.cpp).
+eval_hellaswag = eval_multiple_choice
+
+
+def load_eval_tokens(path: str, tokenizer=None, max_tokens: int | None = None, vocab_size: int | None = None):
+    """Token ids of an evaluation text file: through ``tokenizer`` (anything with ``encode``), else
+    its raw bytes; clipped to ``vocab_size`` and truncated to ``max_tokens`` (``load_eval_tokens`` of
+    the reference)."""
+    import numpy as np
+
+    with open(path, "rb") as f:
+        data = f.read()
+    ids = np.asarray(tokenizer.encode(data) if tokenizer is not None else list(data), dtype=np.int32)
+    if vocab_size:
+        ids = np.minimum(ids, vocab_size - 1)
+    if max_tokens:
+        ids = ids[:max_tokens]
+    return torch.from_numpy(ids)

@@ -118,3 +118,8 @@ class JsonlLogger:
 
     def close(self) -> None:
         self._f.close()
+
+
+# The reference calls its JSONL writer ``WandBLogger`` (src/log_writer.cpp:88-121): same file
+# layout, ``wandb/<project>/<run>/metrics.json``, nothing is sent anywhere.
+WandBLogger = JsonlLogger
