@@ -15,6 +15,7 @@ import base64
 import hashlib
 import importlib.util
 import json
+import logging
 import os
 import socket
 import struct
@@ -189,8 +190,13 @@ class GenerationBackend:
     """Thread-safe text generation for the server: tokenises, runs the model, detokenises. With a
     CUDA model the continuous batcher is used; on CPU a plain recompute loop."""
 
-    def __init__(self, model=None, tokenizer=None, device="cpu", name="model"):
+    def __init__(self, model=None, tokenizer=None, device="cpu", name="model", use_engine: bool = False):
+        """``use_engine``: serve a CUDA model through the paged-KV ``InferenceEngine`` (one prefill,
+        then one decode step per token, shared prompt heads) instead of recomputing the sequence for
+        every token. Its building blocks are covered by the GPU tests; the combination inside the
+        server has not been run on a GPU yet, hence opt-in (``oil-serve --paged-engine``)."""
         self.model, self.tokenizer, self.device, self.name = model, tokenizer, device, name
+        self.use_engine = use_engine
         self._lock = threading.Lock()
 
     def encode(self, text: str) -> list[int]:
@@ -230,22 +236,54 @@ class GenerationBackend:
         ids = [min(t, vocab - 1) for t in self.encode(prompt)] or [0]
         with self._lock, torch.no_grad():
             dev = next(self.model.parameters()).device
+            engine = self._engine(dev) if (self.use_engine and dev.type == "cuda") else None
+            room = self.model.cfg.max_seq_len - len(ids)
+            kv_seq = None
+            if engine is not None and room > 1:
+                # paged-KV engine: one prefill (cached prompt heads are shared), then one decode
+                # step per token instead of recomputing the whole sequence
+                try:
+                    kv_seq, logits = engine.start_sequence(ids)
+                except Exception:          # the prompt does not fit the engine: use the recompute loop
+                    kv_seq, engine = None, None
             seq = torch.tensor([ids], dtype=torch.int32, device=dev)
-            for step in range(max_tokens):
-                logits = self.model(seq[:, -self.model.cfg.max_seq_len:])[:, -1]
-                lg = logits.to(torch.bfloat16).contiguous() if logits.is_cuda else logits.float()
-                tok = sample(lg, cfg, step=step).to(torch.int32)
-                seq = torch.cat([seq, tok.view(1, 1).to(dev)], dim=1)
-                if self.tokenizer is not None:
-                    yield self.decode([int(tok[0])])
-                else:                      # byte-level ids: hold back unfinished multi-byte characters
-                    piece = utf8.feed(bytes([int(tok[0]) & 0xFF]))
-                    if piece:
-                        yield piece
+            try:
+                for step in range(max_tokens if kv_seq is None else min(max_tokens, room - 1)):
+                    if kv_seq is None:
+                        logits = self.model(seq[:, -self.model.cfg.max_seq_len:])[:, -1]
+                    lg = logits.to(torch.bfloat16).contiguous() if logits.is_cuda else logits.float()
+                    tok = sample(lg, cfg, step=step).to(torch.int32)
+                    if kv_seq is None:
+                        seq = torch.cat([seq, tok.view(1, 1).to(dev)], dim=1)
+                    else:
+                        logits = engine.decode([kv_seq], [int(tok[0])])
+                    if self.tokenizer is not None:
+                        yield self.decode([int(tok[0])])
+                    else:                      # byte-level ids: hold back unfinished multi-byte characters
+                        piece = utf8.feed(bytes([int(tok[0]) & 0xFF]))
+                        if piece:
+                            yield piece
+            finally:                           # also when the consumer stops reading early
+                if kv_seq is not None:
+                    engine.release(kv_seq)
             if self.tokenizer is None:
                 tail = utf8.finish()
                 if tail:
                     yield tail
+
+    def _engine(self, dev):
+        """Inference engine over the served model (built on first use; None when it cannot be built,
+        e.g. for shapes the kernels do not cover: the recompute loop then serves the request)."""
+        if getattr(self, "_eng", None) is None and not getattr(self, "_eng_failed", False):
+            try:
+                from .engine import InferenceEngine
+
+                self._eng = InferenceEngine.from_model(self.model, device=dev, max_batch=8,
+                                                       max_seq_len=self.model.cfg.max_seq_len)
+            except Exception as e:
+                self._eng_failed = True
+                logging.getLogger("mythos_b200").warning("serving without the paged-KV engine: %s", e)
+        return getattr(self, "_eng", None)
 
     def complete(self, prompt: str, **kw) -> str:
         return "".join(self.stream(prompt, **kw))
@@ -538,6 +576,8 @@ def main(argv=None) -> int:
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--device", default="auto")
     ap.add_argument("--config", default=None)
+    ap.add_argument("--paged-engine", action="store_true",
+                    help="serve a CUDA model through the paged-KV inference engine instead of recomputing per token")
     a = ap.parse_args(argv)
     cfg = AppConfig.load(a.config) if a.config else AppConfig({"server": {"port": a.port}})
     backend = GenerationBackend()
@@ -550,7 +590,7 @@ def main(argv=None) -> int:
         model, _ = load_model(a.model, device=dev)
         vocab = (a.model[:-4] if a.model.endswith(".oil") else a.model) + ".vocab"
         tok = BPETokenizer.load(vocab) if os.path.exists(vocab) else None
-        backend = GenerationBackend(model.eval(), tok, dev, os.path.basename(a.model))
+        backend = GenerationBackend(model.eval(), tok, dev, os.path.basename(a.model), use_engine=a.paged_engine)
     srv = HTTPServer(backend, port=int(cfg.get("server.port", a.port)), host=a.host)
     srv.start()
     try:
