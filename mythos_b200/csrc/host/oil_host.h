@@ -1,7 +1,7 @@
 // C ABI of the host runtime library (liboil_host.so): the .oil container (mmap reader with an
 // O(1) block index, streaming writer, dequantisation of all six block formats), SHA-256, the
-// .oilidx sidecar check, the byte-level BPE tokenizer, the reference-compatible RNG and the KV
-// page allocator. Python reaches it through ctypes (mythos_b200/oil/native_io.py); C and C++
+// .oilidx sidecar check, the byte-level BPE tokenizer, the reference-compatible RNG, the KV
+// page allocator and the prefetching token-window loader. Python reaches it through ctypes (mythos_b200/oil/native_io.py); C and C++
 // programs include this header. Functions return 0 / a handle on success and a negative code /
 // null on failure; oil_last_error() describes the last failure of the calling thread.
 #pragma once
@@ -74,6 +74,16 @@ int32_t oil_pages_alloc(OilPages* p);              // -1 when exhausted
 void oil_pages_retain(OilPages* p, int32_t page);
 void oil_pages_release(OilPages* p, int32_t page);
 int32_t oil_pages_used(const OilPages* p);
+
+// ---- token-window loader: windows of seq + 1 tokens, optional per-epoch window shuffle, batches
+// prepared by a worker thread into a ring of `prefetch` slots (loader.cpp)
+typedef struct OilLoader OilLoader;
+OilLoader* oil_loader_create(const int32_t* tokens, int64_t n_tokens, int batch, int seq, int shuffle, uint64_t seed,
+                             int prefetch);
+int64_t oil_loader_num_batches(const OilLoader* L);
+void oil_loader_reset(OilLoader* L, int epoch);
+int oil_loader_next(OilLoader* L, int32_t* ids_out, int32_t* targets_out);   // 1, or 0 at the end of the epoch
+void oil_loader_free(OilLoader* L);
 
 #ifdef __cplusplus
 }

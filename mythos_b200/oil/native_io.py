@@ -74,6 +74,14 @@ def lib():
         L.oil_pages_retain.argtypes = [vp, ctypes.c_int32]
         L.oil_pages_release.argtypes = [vp, ctypes.c_int32]
         L.oil_pages_used.argtypes = [vp]
+        L.oil_loader_create.restype = vp
+        L.oil_loader_create.argtypes = [vp, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_uint64,
+                                        ctypes.c_int]
+        L.oil_loader_num_batches.restype = ctypes.c_int64
+        L.oil_loader_num_batches.argtypes = [vp]
+        L.oil_loader_reset.argtypes = [vp, ctypes.c_int]
+        L.oil_loader_next.argtypes = [vp, vp, vp]
+        L.oil_loader_free.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -259,3 +267,49 @@ class NativePageAllocator:
         if getattr(self, "_h", None):
             lib().oil_pages_free(self._h)
             self._h = None
+
+
+class NativeTokenLoader:
+    """``TokenDataset`` served by the C++ loader: a worker thread assembles ``[B, S]`` batches into a
+    ring while the training step runs; iteration copies a finished batch straight into (optionally
+    pinned) torch tensors. Window-level shuffle, deterministic in (seed, epoch); the permutation is
+    the runtime's own, not numpy's."""
+
+    def __init__(self, tokens, batch: int, seq: int, shuffle: bool = True, seed: int = 42, prefetch: int = 2,
+                 pin: bool = False):
+        import torch
+
+        arr = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        self.batch, self.seq = batch, seq
+        self._h = lib().oil_loader_create(arr.ctypes.data, arr.size, batch, seq, 1 if shuffle else 0, seed, prefetch)
+        if not self._h:
+            raise ValueError("NativeTokenLoader: need at least two tokens and positive batch / sequence sizes")
+        self.pin = bool(pin and torch.cuda.is_available())
+
+    def __len__(self) -> int:
+        return int(lib().oil_loader_num_batches(self._h))
+
+    def reset(self, epoch: int = 0) -> None:
+        lib().oil_loader_reset(self._h, epoch)
+
+    def __iter__(self):
+        import torch
+
+        while True:
+            ids = torch.empty(self.batch, self.seq, dtype=torch.int32, pin_memory=self.pin)
+            tgt = torch.empty(self.batch, self.seq, dtype=torch.int32, pin_memory=self.pin)
+            if not lib().oil_loader_next(self._h, ids.data_ptr(), tgt.data_ptr()):
+                return
+            yield ids, tgt
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().oil_loader_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+

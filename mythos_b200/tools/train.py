@@ -49,6 +49,7 @@ def build_parser():
     ap.add_argument("--gpu", "--device", dest="device", default="auto")
     ap.add_argument("--resume", default=None)
     ap.add_argument("--seed", type=int, default=None, help="default: OIL_SEED, else 42")
+    ap.add_argument("--python-loader", action="store_true", help="use the Python data loader instead of the C++ one")
     ap.add_argument("--streaming", action="store_true",
                     help="read and tokenise --data in 4 MB chunks while training (the tokenizer is trained on the first chunk)")
     ap.add_argument("--mask-prob", type=float, default=0.0, help="augmentation: input ids replaced by id 0")
@@ -115,7 +116,14 @@ def main(argv=None) -> int:
         f"gnorm {m.grad_norm:.3f} tok/s {m.tokens_per_sec:,.0f}", flush=True))
     print(f"model: {model.param_count():,} parameters, format {cfg.weight_format}, device {device}")
     if tokens is not None:
-        loader = TokenDataset(tokens, batch, seq, shuffle=True, seed=args.seed, pin=device.type == "cuda")
+        from ..oil import native_io
+
+        if native_io.available() and not args.python_loader:
+            # C++ loader: batches are assembled by a worker thread into a ring, copied into pinned tensors
+            loader = native_io.NativeTokenLoader(tokens, batch, seq, shuffle=True, seed=args.seed,
+                                                 pin=device.type == "cuda")
+        else:
+            loader = TokenDataset(tokens, batch, seq, shuffle=True, seed=args.seed, pin=device.type == "cuda")
         if len(loader) == 0:
             print("corpus is shorter than one batch; lower --batch-size / --seq-length", file=sys.stderr)
             return 2
