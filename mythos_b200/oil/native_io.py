@@ -90,7 +90,7 @@ def available() -> bool:
     try:
         lib()
         return True
-    except (RuntimeError, OSError):
+    except (RuntimeError, OSError, AttributeError):     # missing, unloadable, or an older build of the library
         return False
 
 
