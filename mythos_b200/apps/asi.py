@@ -574,10 +574,35 @@ class ToolUse:
 
     @staticmethod
     def _calc(expr: str) -> str:
-        if not re.fullmatch(r"[0-9+\-*/(). %]+", expr):
+        """+ - * / % and parentheses over numbers, evaluated by walking the syntax tree (no eval):
+        no names, calls or powers, at most 256 characters and 64 operations, results bounded."""
+        import ast
+        import operator
+
+        if len(expr) > 256 or not re.fullmatch(r"[0-9+\-*/(). %]+", expr) or "**" in expr:
             return "error: unsupported expression"
+        ops = {ast.Add: operator.add, ast.Sub: operator.sub, ast.Mult: operator.mul, ast.Div: operator.truediv,
+               ast.Mod: operator.mod, ast.FloorDiv: operator.floordiv}
+        budget = [64]
+
+        def ev(node):
+            budget[0] -= 1
+            if budget[0] < 0:
+                raise ValueError("expression too long")
+            if isinstance(node, ast.Constant) and isinstance(node.value, (int, float)):
+                return node.value
+            if isinstance(node, ast.UnaryOp) and isinstance(node.op, (ast.UAdd, ast.USub)):
+                v = ev(node.operand)
+                return -v if isinstance(node.op, ast.USub) else v
+            if isinstance(node, ast.BinOp) and type(node.op) in ops:
+                v = ops[type(node.op)](ev(node.left), ev(node.right))
+                if abs(v) > 1e300:
+                    raise ValueError("result out of range")
+                return v
+            raise ValueError("unsupported expression")
+
         try:
-            return str(eval(expr, {"__builtins__": {}}, {}))   # digits and operators only, checked above
+            return str(ev(ast.parse(expr.strip(), mode="eval").body))
         except Exception as e:                                  # noqa: BLE001
             return f"error: {e}"
 

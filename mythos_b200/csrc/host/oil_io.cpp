@@ -153,6 +153,8 @@ OilFile* oil_open(const char* path) {
     OilFile::T t;
     t.name.assign((const char*)f->data + o, ln); o += ln;
     t.start = rd<uint32_t>(f->data + o); t.count = rd<uint32_t>(f->data + o + 4); o += 8;
+    if ((uint64_t)t.start + (uint64_t)t.count > (uint64_t)nb)
+      return bad("tensor '" + t.name + "' refers to blocks beyond the block table");
     f->by_name[t.name] = (uint32_t)f->tensors.size();
     f->tensors.push_back(t);
   }
@@ -162,10 +164,10 @@ OilFile* oil_open(const char* path) {
     if (o + 8 > f->size) return bad("truncated in block " + std::to_string(b));
     f->nw[b] = rd<uint32_t>(f->data + o);
     const uint32_t cb = rd<uint32_t>(f->data + o + 4);
-    if (o + 12 + cb > f->size) return bad("truncated in block " + std::to_string(b));
+    if ((uint64_t)o + 12ull + cb > f->size) return bad("truncated in block " + std::to_string(b));
     const uint32_t ib = rd<uint32_t>(f->data + o + 8 + cb);
+    if ((uint64_t)o + 12ull + cb + ib > f->size) return bad("truncated in block " + std::to_string(b));
     o += 12ull + cb + ib;
-    if (o > f->size) return bad("truncated in block " + std::to_string(b));
   }
   f->off[nb] = o;
   return f;
@@ -220,10 +222,16 @@ int64_t oil_read_tensor_f32(const OilFile* f, const char* name, float* out, int6
     if (pos + n > capacity) return fail(-4, "output buffer too small");
     float* o = out + pos;
     const uint8_t fmt = f->fmt[b];
-    if (fmt == 3 && cbn >= 1028) {            // OIL8: magic + 256 f32
-      const float* c = (const float*)(cb + 4);
-      for (uint32_t j = 0; j < n && j < ibn; ++j) o[j] = c[idx[j]];
-    } else if (fmt == 2 && cbn >= 36) {       // OIL4: magic + 16 f16, even index in the low nibble
+    // bytes of index data that the block's format needs for n weights; the header's idx_bytes was
+    // checked against the file size in oil_open, so idx[0 .. ibn) is inside the mapping
+    const uint64_t bits = fmt == 3 ? 8 : fmt == 2 ? 4 : fmt == 1 ? 2 : fmt == 0 ? 1 : fmt == 4 ? 16 : 32;
+    if ((uint64_t)ibn < ((uint64_t)n * bits + 7) / 8)
+      return fail(-2, "block " + std::to_string(b) + " of '" + t.name + "': index data shorter than its weight count needs");
+    if ((fmt == 3 && cbn < 1028) || (fmt == 2 && cbn < 36))
+      return fail(-2, "block " + std::to_string(b) + " of '" + t.name + "': codebook too small for its format");
+    if (fmt == 3) {                           // OIL8: magic + 256 f32
+      for (uint32_t j = 0; j < n; ++j) o[j] = rd<float>(cb + 4 + 4u * idx[j]);
+    } else if (fmt == 2) {       // OIL4: magic + 16 f16, even index in the low nibble
       float c[16];
       for (int k = 0; k < 16; ++k) c[k] = half_to_float(rd<uint16_t>(cb + 4 + 2 * k));
       for (uint32_t j = 0; j < n; ++j) o[j] = c[(j & 1) ? (idx[j >> 1] >> 4) : (idx[j >> 1] & 0xF)];
@@ -238,7 +246,7 @@ int64_t oil_read_tensor_f32(const OilFile* f, const char* name, float* out, int6
     } else if (fmt == 4) {                    // FP16
       for (uint32_t j = 0; j < n; ++j) o[j] = half_to_float(rd<uint16_t>(idx + 2 * j));
     } else {                                  // FP32 (and unknown codes, as the reference)
-      if (ibn >= 4ull * n) memcpy(o, idx, 4ull * n); else memset(o, 0, 4ull * n);
+      memcpy(o, idx, 4ull * n);
     }
     pos += n;
   }
@@ -249,6 +257,7 @@ int oil_tensor_sha256(const OilFile* f, const char* name, uint8_t out[32]) {
   auto it = f->by_name.find(name);
   if (it == f->by_name.end()) return fail(-3, std::string("no tensor named ") + name);
   const auto& t = f->tensors[it->second];
+  if ((uint64_t)t.start + t.count >= f->off.size()) return fail(-2, std::string("tensor '") + name + "' refers to blocks beyond the block table");
   const uint64_t lo = f->off[t.start], hi = f->off[t.start + t.count];
   oil_sha256(f->data + lo, hi - lo, out);
   return 0;

@@ -51,13 +51,18 @@ extern "C" int mythos_rmsnorm_bwd_noalloc(const void* dy, const void* x, const v
   if (dim > MYTHOS_NOALLOC_MAX_DIM)
     return fail(MYTHOS_NOALLOC_E_TOO_LARGE, "dim " + std::to_string(dim) + " exceeds the built-in scratch (max " +
                                                 std::to_string(MYTHOS_NOALLOC_MAX_DIM) + ")");
-  if (rows == 0) return MYTHOS_NOALLOC_OK;
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != MYTHOS_NOALLOC_OK) return rc;
   const int n_partial = rows < MYTHOS_NOALLOC_PARTIALS ? rows : MYTHOS_NOALLOC_PARTIALS;
   try {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows == 0) {
+      // no rows: the gradient of gamma is zero. Overwrite mode still has to write it; a reduction
+      // over zero partial rows does exactly that (accumulate mode leaves dgamma as it is).
+      if (!accumulate) mb::rmsnorm_bwd_reduce(scratch, dgamma, 0, dim, false, s);
+      return MYTHOS_NOALLOC_OK;
+    }
     // Every one of the n_partial CTAs writes its full [dim] row of partial sums before the
     // reduction reads them, so stale contents of the shared array are never observed.
     mb::rmsnorm_bwd(dy, x, gamma, rstd, dx, scratch, rows, dim, n_partial, s);

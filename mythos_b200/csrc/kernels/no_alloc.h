@@ -23,7 +23,8 @@
 // The function calls no cudaMalloc / cudaFree and no allocating library routine. Inputs and
 // outputs are device pointers supplied by the caller: dy, x, dx are bf16 [rows, dim]; gamma is
 // bf16 [dim]; rstd is fp32 [rows] as produced by the forward pass; dgamma is fp32 [dim]
-// (overwritten, or added to when accumulate != 0). `stream` is a cudaStream_t (null = default).
+// (overwritten, or added to when accumulate != 0; with rows == 0 that means zeros, or no change).
+// `stream` is a cudaStream_t (null = default).
 // Returns 0 on success, a negative MYTHOS_NOALLOC_E_* code otherwise; mythos_noalloc_last_error()
 // gives the message of the last failure on the calling thread.
 #pragma once

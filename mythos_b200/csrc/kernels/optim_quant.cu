@@ -1,7 +1,9 @@
 // Optimizer and train-in-format kernels.
-//   * AdamW with decoupled decay, update  p -= lr*wd*p;  p -= lr*sqrt(bc2)/bc1 * m/(sqrt(v)+eps')
-//     written in the reference's form (src/optimizer.cpp:91-119):
-//     p -= lr * (m/bc1) / (sqrt(v/bc2) + eps).
+//   * AdamW with decoupled decay in the standard form: p -= lr*wd*p; p -= lr * (m/bc1) / (sqrt(v/bc2) + eps)
+//     with bc1 = 1-beta1^t, bc2 = 1-beta2^t. This deviates on purpose from the reference
+//     (src/optimizer.cpp:91-119), which computes lr*sqrt(bc2)/bc1 * m/(sqrt(v/bc2)+eps) and so applies
+//     the second-moment correction twice (a sqrt(1-beta2^t) smaller step early on, ~30x at t=1).
+//     The state files (.opt, CHPK) are interchangeable; the trajectories are not.
 //   * STE fake quantisation: nearest centroid in a sorted codebook (first minimum wins, as the
 //     brute-force search of src/codebook.cpp:172-186 does), I2_S ternary with absmean scale.
 //   * Codebook EMA statistics (counts / sums per centroid), src/codebook.cpp:137-170.

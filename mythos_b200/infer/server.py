@@ -234,11 +234,14 @@ class GenerationBackend:
         cfg = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p, seed=seed)
         vocab = self.model.cfg.vocab_size
         ids = [min(t, vocab - 1) for t in self.encode(prompt)] or [0]
+        # The backend lock is held per step (prefill, one token), never across a ``yield``: a client
+        # that reads slowly stalls only its own request; other requests interleave token by token.
         with self._lock, torch.no_grad():
             dev = next(self.model.parameters()).device
             engine = self._engine(dev) if (self.use_engine and dev.type == "cuda") else None
             room = self.model.cfg.max_seq_len - len(ids)
             kv_seq = None
+            logits = None
             if engine is not None and room > 1:
                 # paged-KV engine: one prefill (cached prompt heads are shared), then one decode
                 # step per token instead of recomputing the whole sequence
@@ -247,8 +250,9 @@ class GenerationBackend:
                 except Exception:          # the prompt does not fit the engine: use the recompute loop
                     kv_seq, engine = None, None
             seq = torch.tensor([ids], dtype=torch.int32, device=dev)
-            try:
-                for step in range(max_tokens if kv_seq is None else min(max_tokens, room - 1)):
+        try:
+            for step in range(max_tokens if kv_seq is None else min(max_tokens, room - 1)):
+                with self._lock, torch.no_grad():
                     if kv_seq is None:
                         logits = self.model(seq[:, -self.model.cfg.max_seq_len:])[:, -1]
                     lg = logits.to(torch.bfloat16).contiguous() if logits.is_cuda else logits.float()
@@ -257,19 +261,21 @@ class GenerationBackend:
                         seq = torch.cat([seq, tok.view(1, 1).to(dev)], dim=1)
                     else:
                         logits = engine.decode([kv_seq], [int(tok[0])])
-                    if self.tokenizer is not None:
-                        yield self.decode([int(tok[0])])
-                    else:                      # byte-level ids: hold back unfinished multi-byte characters
-                        piece = utf8.feed(bytes([int(tok[0]) & 0xFF]))
-                        if piece:
-                            yield piece
-            finally:                           # also when the consumer stops reading early
-                if kv_seq is not None:
+                    tok_id = int(tok[0])
+                if self.tokenizer is not None:
+                    yield self.decode([tok_id])
+                else:                      # byte-level ids: hold back unfinished multi-byte characters
+                    piece = utf8.feed(bytes([tok_id & 0xFF]))
+                    if piece:
+                        yield piece
+        finally:                           # also when the consumer stops reading early
+            if kv_seq is not None:
+                with self._lock:
                     engine.release(kv_seq)
-            if self.tokenizer is None:
-                tail = utf8.finish()
-                if tail:
-                    yield tail
+        if self.tokenizer is None:
+            tail = utf8.finish()
+            if tail:
+                yield tail
 
     def _engine(self, dev):
         """Inference engine over the served model (built on first use; None when it cannot be built,
@@ -329,6 +335,12 @@ def _make_handler(server: "HTTPServer"):
         def do_POST(self):
             try:
                 n = int(self.headers.get("Content-Length", "0"))
+                if n < 0:
+                    raise ValueError("negative Content-Length")
+                if n > server.max_body_bytes:
+                    self.close_connection = True          # the unread body must not be parsed as a request
+                    self._json(413, {"error": f"request body larger than {server.max_body_bytes} bytes"})
+                    return
                 raw = self.rfile.read(n) if n else b""
                 req = json.loads(raw.decode("utf-8") or "{}")
             except socket.timeout:
@@ -378,9 +390,10 @@ def _make_handler(server: "HTTPServer"):
 
 class HTTPServer:
     def __init__(self, backend: GenerationBackend | None = None, port: int = 0, host: str = "127.0.0.1",
-                 request_timeout: float = 30.0, logger: Logger | None = None):
+                 request_timeout: float = 30.0, logger: Logger | None = None, max_body_bytes: int = 8 << 20):
         self.backend = backend or GenerationBackend()
         self.host, self.port, self.request_timeout = host, port, request_timeout
+        self.max_body_bytes = max_body_bytes                # larger request bodies are answered with 413
         self.logger = logger or Logger.instance()
         self.plugins = PluginManager(self)
         self.started = time.time()

@@ -141,12 +141,17 @@ class NativeReader:
         out = np.empty(n, dtype=np.float32)
         got = lib().oil_read_tensor_f32(self._h, name.encode(), out.ctypes.data, n)
         if got < 0:
-            raise RuntimeError(lib().oil_last_error().decode())
+            from .container import OILError
+
+            raise OILError(lib().oil_last_error().decode())
         return out
 
     def tensor_sha256(self, name: str) -> bytes:
         out = ctypes.create_string_buffer(32)
-        lib().oil_tensor_sha256(self._h, name.encode(), out)
+        if lib().oil_tensor_sha256(self._h, name.encode(), out) != 0:
+            from .container import OILError
+
+            raise OILError(lib().oil_last_error().decode())
         return out.raw
 
 

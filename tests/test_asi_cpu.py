@@ -59,6 +59,9 @@ def test_safety_alignment_hitl_tools():
     assert al.value_alignment_score("happy to help, be careful") > al.value_alignment_score("attack and destroy")
     t = asi.ToolUse()
     assert t.call_tool("calculator", "2*(3+4)") == "14" and t.call_tool("calculator", "__import__('os')").startswith("error")
+    assert t.call_tool("calculator", "9**9**9**9").startswith("error")          # no powers, no unbounded work
+    assert t.call_tool("calculator", "-(7 % 4) + 10 / 4") == "-0.5" and t.call_tool("calculator", "1/0").startswith("error")
+    assert t.call_tool("calculator", "+".join(["1"] * 100)).startswith("error")
     assert t.call_tool("nope", "") .startswith("error") and "upper" in t.get_available_tools()
 
 

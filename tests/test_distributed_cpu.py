@@ -148,3 +148,43 @@ def test_checkpoint_written_for_one_layout_loads_into_another(tmp_path):
     batch = data.next_batch()
     l1, l2 = tr.train_step(*batch), tr2.train_step(*batch)
     assert abs(float(l1) - float(l2)) < 2e-3
+
+
+@pytest.mark.parametrize("fmt", ["oil8", "i2s"])
+def test_resume_restores_fp32_masters_of_quantised_layers(tmp_path, fmt):
+    """The .oil file stores centroids / trits; the fp32 master weights travel in the .master file, so
+    a resumed run has the same masters and follows the same trajectory as an uninterrupted one."""
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.train.data import ZipfStream
+    from mythos_b200.train.trainer import TrainConfig, Trainer
+
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=2, head_dim=16, ffn_hidden_size=64,
+                            max_seq_len=16, oil_block_size=32, weight_format=fmt)
+    tc = TrainConfig(batch_size=4, seq_length=16, lr=1e-2, warmup_steps=0)
+    torch.manual_seed(0)
+    tr = Trainer(DenseModel(cfg), tc, device="cpu")
+    data = ZipfStream(64, 4, 16, seed=0)
+    for _ in range(3):
+        tr.train_step(*data.next_batch())
+    path = str(tmp_path / "ck.oil")
+    tr.save_checkpoint(path)
+    assert os.path.exists(path + ".master")
+    torch.manual_seed(1)                                            # different initial weights
+    tr2 = Trainer(DenseModel(cfg), tc, device="cpu")
+    tr2.load_checkpoint(path)
+    quantised = [s for s in tr.store.slots if s.module is not None]
+    assert quantised
+    for s1, s2 in zip(tr.store.slots, tr2.store.slots):
+        a = tr.store.master[s1.offset:s1.offset + s1.numel]
+        b = tr2.store.master[s2.offset:s2.offset + s2.numel]
+        if s1.module is not None:
+            assert torch.equal(a, b), s1.name                       # not collapsed onto centroids
+            assert not torch.equal(a, s1.module.quantize_now(a.view(s1.param.shape)).reshape(-1).float())
+    for _ in range(4):                                              # the trajectories stay together
+        batch = data.next_batch()
+        l1, l2 = tr.train_step(*batch), tr2.train_step(*batch)
+        assert abs(float(l1) - float(l2)) < 1e-5
+    for s1, s2 in zip(tr.store.slots, tr2.store.slots):
+        if s1.module is not None:
+            assert torch.allclose(tr.store.master[s1.offset:s1.offset + s1.numel],
+                                  tr2.store.master[s2.offset:s2.offset + s2.numel], atol=1e-6)

@@ -50,6 +50,43 @@ def test_native_reader_and_writer_agree_with_python(tmp_path):
         native_io.NativeReader(str(bad))
 
 
+def test_native_reader_rejects_corrupt_block_ranges_and_sizes(tmp_path):
+    """A tensor entry that points past the block table, and a block whose weight count needs more
+    index bytes than the file holds, are errors (they used to index out of range / read past the
+    mapping)."""
+    import struct
+
+    from mythos_b200.oil import container as oc
+    from mythos_b200.oil.formats import Format
+
+    p = str(tmp_path / "g.oil")
+    oc.write_oil(p, [("w", [oc.BlockData(Format.FP32, 8, b"", np.arange(8, dtype=np.float32).tobytes())])])
+    raw = open(p, "rb").read()
+    o = 16 + struct.unpack_from("<I", raw, 12)[0]
+    nb = struct.unpack_from("<I", raw, o)[0]
+    fmt_byte = o + 4 + 4
+    t = o + 4 + 9 * nb + 4
+    ln = struct.unpack_from("<H", raw, t)[0]
+    start_off = t + 2 + ln
+    block0 = start_off + 8
+    for off in (start_off, start_off + 4):
+        b = bytearray(raw)
+        struct.pack_into("<I", b, off, 0x100000)
+        q = tmp_path / "range.oil"
+        q.write_bytes(bytes(b))
+        with pytest.raises(oc.OILError, match="beyond the block table"):
+            native_io.NativeReader(str(q))
+    b = bytearray(raw)
+    b[fmt_byte] = int(Format.FP16)
+    struct.pack_into("<I", b, block0, 50_000_000)
+    q = tmp_path / "size.oil"
+    q.write_bytes(bytes(b))
+    r = native_io.NativeReader(str(q))
+    with pytest.raises(oc.OILError, match="index data shorter"):
+        r.read_tensor("w")
+    r.close()
+
+
 def test_native_idx_check_names_the_corrupt_tensor(tmp_path):
     from mythos_b200.oil import container as oc
 
@@ -102,7 +139,7 @@ def test_native_rng_and_pages():
 
 
 ASAN_WORKER = r'''
-import os, random, sys
+import os, random, struct, sys
 import numpy as np
 sys.path.insert(0, os.environ["REPO_ROOT"])
 from mythos_b200.oil import native_io
@@ -148,6 +185,32 @@ for fname in sorted(os.listdir(work)):
         p = os.path.join(work, "flip.bin")
         open(p, "wb").write(bytes(b))
         try_read(p)
+    # structured corruption: the fields that size later reads, at their offsets in this file
+    u32 = lambda o: struct.unpack_from("<I", raw, o)[0]
+    o = 16 + u32(12)
+    nb = u32(o); fmt_table = o + 4; o = fmt_table + 9 * nb
+    nt = u32(o); o += 4
+    fields = [(fmt_table + 9 * i + 4, 1) for i in range(min(nb, 6))]          # per-block format byte
+    for _ in range(nt):
+        ln = struct.unpack_from("<H", raw, o)[0]; o += 2 + ln
+        fields += [(o, 4), (o + 4, 4)]; o += 8                                   # tensor start / count
+    for _ in range(min(nb, 6)):                                                  # block headers
+        cbn = u32(o + 4); ibn = u32(o + 8 + cbn)
+        fields += [(o, 4), (o + 4, 4), (o + 8 + cbn, 4)]                         # num_weights / cb / idx bytes
+        o += 12 + cbn + ibn
+    for pos, width in fields:
+        for val in (0, 1, 0x7F, 0xFF, 0x100000, 50_000_000, 0x7FFFFFFF, 0xFFFFFFFF):
+            for fmt_byte in ((None,) if width == 4 else (0, 1, 2, 3, 4, 5, 9)):
+                b = bytearray(raw)
+                if width == 4:
+                    struct.pack_into("<I", b, pos, val)
+                else:
+                    b[pos] = fmt_byte
+                p = os.path.join(work, "field.bin")
+                open(p, "wb").write(bytes(b))
+                try_read(p)
+            if width == 1:
+                break
     idx = os.path.join(work, fname + "idx")
     if os.path.exists(idx):
         rawi = open(idx, "rb").read()

@@ -70,6 +70,31 @@ def test_http_server_starts_without_a_model_on_port_zero():
     srv.stop()
 
 
+def test_http_server_rejects_oversized_and_negative_bodies_and_interleaves_streams():
+    import socket
+
+    from mythos_b200.infer.server import GenerationBackend, HTTPServer
+
+    backend = GenerationBackend(_tiny(), None, "cpu", "tiny")
+    srv = HTTPServer(backend, port=0, max_body_bytes=1024)
+    port = srv.start()
+    try:
+        for length, want in ((5000, b"413"), (-5, b"400")):
+            s = socket.create_connection(("127.0.0.1", port), timeout=10)
+            s.sendall(f"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Length: {length}\r\n\r\n".encode())
+            assert want in s.recv(4096).split(b"\r\n")[0]        # answered without waiting for a body
+            s.close()
+        # a generator that has yielded its first piece does not hold the backend lock
+        slow = backend.stream("ab", max_tokens=4)
+        next(slow)
+        assert backend._lock.acquire(timeout=1.0)
+        backend._lock.release()
+        assert isinstance(backend.complete("cd", max_tokens=2), str)   # a second request runs to the end meanwhile
+        assert len(list(slow)) >= 1
+    finally:
+        srv.stop()
+
+
 def test_websocket_handshake_frames_and_broadcast():
     from mythos_b200.infer import server as S
 

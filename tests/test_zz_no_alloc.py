@@ -66,6 +66,20 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
     assert prev_dg is not None
 
 
+def test_noalloc_with_zero_rows_writes_zeros_or_leaves_the_accumulator():
+    lib, fn = _lib()
+    t = torch.zeros(64, device="cuda", dtype=torch.bfloat16)
+    f = torch.zeros(1, device="cuda")
+    dg = torch.full((64,), 5.0, device="cuda")
+    args = (t.data_ptr(), t.data_ptr(), t.data_ptr(), f.data_ptr(), t.data_ptr(), dg.data_ptr(), 0, 64)
+    assert fn(*args, 1, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dg, torch.full((64,), 5.0, device="cuda"))       # accumulate: unchanged
+    assert fn(*args, 0, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dg, torch.zeros(64, device="cuda"))              # overwrite: the gradient is zero
+
+
 def test_noalloc_rejects_oversized_and_bad_arguments():
     lib, fn = _lib()
     t = torch.zeros(8, device="cuda", dtype=torch.bfloat16)
