@@ -9,6 +9,12 @@ Synthetic seeded Zipf(1.1) tokens, random-init N(0, 0.02) weights.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
 
+After the training measurement the same process group runs the second half of the headline metric:
+greedy decode of a Llama-3-8B-shaped model (mixed OIL4 attention / OIL8 FFN weights, paged bf16 KV
+with 16-token pages, batch 64, prompt 1024, 256 new tokens) with tensor parallelism over the N
+GPUs of the run; tokens/s, p50 time to first token and the fraction of the HBM bound are reported in
+the ``decode`` object of the same JSON line (``--no-decode`` skips it).
+
 Prints one JSON line on rank 0. ``--impl reference`` reports why the reference cannot run this
 configuration (CPU-only FP32 C++ engine without a Python package, a GPU path or multi-process
 communication).
@@ -92,6 +98,65 @@ def model_flops_per_token(cfg) -> float:
     return 6.0 * lin + 3.0 * attn
 
 
+def run_decode(world: int, rank: int, device, args, hbm_gbs: float) -> dict:
+    """TP = world decode benchmark of the Llama-3-8B-shaped mixed OIL4 / OIL8 model (the second half
+    of the headline metric). Device-side decode time, max over ranks; TTFT is prefill + first sample
+    around a device synchronise, p50 over the timed repeats, max over ranks."""
+    import torch
+
+    from mythos_b200.infer.engine import InferenceEngine, TPContext
+    from mythos_b200.models.config import NAMED_CONFIGS
+    from mythos_b200.ops import native
+
+    cfg = NAMED_CONFIGS["llama3-8b"]()
+    batch, prompt, new = args.decode_batch, args.decode_prompt, args.decode_new
+    cfg.max_seq_len = prompt + new + 16
+    tp = None
+    if world > 1:
+        import torch.distributed as dist
+
+        tp = TPContext(dist.group.WORLD, device, max_tokens=max(batch * prompt, 256), hidden=cfg.hidden_size,
+                       vocab_shard=cfg.vocab_size // world, max_batch=batch)
+    torch.manual_seed(1234)
+    eng = InferenceEngine.random(cfg, seed=1234, device=device, max_batch=batch, max_seq_len=cfg.max_seq_len, tp=tp,
+                                 kv_dtype="bf16")
+    wbytes = eng.weight_bytes()
+    torch.cuda.empty_cache()
+    g = torch.Generator().manual_seed(7)
+    prompts = torch.randint(0, cfg.vocab_size, (batch, prompt), generator=g, dtype=torch.int32)
+    ttfts, dec_s = [], []
+    launches0 = native.launch_count()
+    for it in range(args.decode_repeat + 1):                       # the first repeat is the warm-up
+        res = eng.generate(prompts, max_new_tokens=new, use_graph=True)
+        t = torch.tensor([res.stats.ttft_s, res.stats.decode_s], device=device, dtype=torch.float64)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if it > 0:
+            ttfts.append(float(t[0]))
+            dec_s.append(float(t[1]))
+    native.check_status(device)
+    ttfts.sort()
+    best = min(dec_s)
+    ms_step = best / (new - 1) * 1e3
+    # bytes one rank must stream per decode step: its weight shard once, its share of the KV pages
+    # at the mean context length of the decode phase
+    kv_per_tok = 2 * cfg.num_layers * (cfg.kv_dim // world if world <= cfg.kv_heads else cfg.head_dim) * 2
+    kv_bytes = batch * (prompt + new / 2) * kv_per_tok
+    bound_ms = (wbytes + kv_bytes) / (hbm_gbs * 1e9) * 1e3
+    return {"metric": "TP decode tok/s, p50 TTFT", "tp": world, "tok_s": batch * (new - 1) / best,
+            "p50_ttft_s": ttfts[len(ttfts) // 2], "ms_per_step": ms_step,
+            "config": {"model": "llama3-8b shape (32L d4096 32q/8kv ffn14336 v128256), OIL4 attention / OIL8 FFN + embeddings",
+                       "batch": batch, "prompt": prompt, "new_tokens": new, "kv": "paged bf16, 16-token pages",
+                       "sampling": "greedy", "decode": "CUDA-graph replay"},
+            "weight_bytes_per_rank": int(wbytes), "kv_bytes_read_per_step_per_rank": int(kv_bytes),
+            "hbm_bound_ms_per_step": bound_ms, "fraction_of_hbm_bound": bound_ms / ms_step,
+            "decode_s_runs": [round(x, 4) for x in dec_s],
+            "gpu_launches": int(native.launch_count() - launches0),
+            "data": "random-init weights in format, uniform-random prompts"}
+
+
 def run_reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a CPU-only FP32 C++ engine (no setup.py/pyproject: pip install fails; no GPU "
@@ -109,6 +174,11 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"],
                     help="data-parallel gradient path: fused peer-memory kernels or plain NCCL collectives")
+    ap.add_argument("--no-decode", action="store_true", help="skip the tensor-parallel decode measurement")
+    ap.add_argument("--decode-batch", type=int, default=64)
+    ap.add_argument("--decode-prompt", type=int, default=1024)
+    ap.add_argument("--decode-new", type=int, default=256)
+    ap.add_argument("--decode-repeat", type=int, default=2)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm()
@@ -207,6 +277,24 @@ def main() -> int:
         pass
     peak_tflops = peaks.get("bf16_tflops_sustained", 1400.0)
     mfu = value / world * model_flops_per_token(cfg) / (peak_tflops * 1e12)
+    peak_mem_gb = torch.cuda.max_memory_allocated(device) / 2 ** 30
+    flops_per_token = model_flops_per_token(cfg)
+
+    decode = None
+    if not args.no_decode:
+        # release the training state (weights, optimizer shards, activations cache) before the engine is built
+        import gc
+
+        del trainer, model, stream, dev_batches, host_batches, loss
+        if dp is not None:
+            dp.release()
+        dp = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            decode = run_decode(world, rank, device, args, float(peaks.get("hbm_gbs", 6650.0)))
+        except Exception as e:                                   # the training line must still be printed
+            decode = {"error": f"{type(e).__name__}: {e}"}
     if rank == 0:
         h2d = 2 * args.per_gpu_batch * SEQ * 4
         out = {
@@ -224,13 +312,15 @@ def main() -> int:
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": int(launches),
-            "model_flops_per_token": model_flops_per_token(cfg),
+            "model_flops_per_token": flops_per_token,
             "fraction_of_measured_bf16_sustained": mfu,
             "final_loss": last,
-            "peak_memory_gb": torch.cuda.max_memory_allocated(device) / 2 ** 30,
+            "peak_memory_gb": peak_mem_gb,
         }
+        if decode is not None:
+            out["decode"] = decode
         print(json.dumps(out))
-    if dp is not None:
+    if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()

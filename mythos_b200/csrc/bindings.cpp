@@ -52,6 +52,60 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, i
                 (int)M, (int)N, (int)K, (int)epi, (float)alpha, status_ptr(status), cur_stream());
 }
 
+// h[M,F] = silu(gate) * up and (optionally) the pre-activations gu[M,2F] from x[M,K] and w[2F,K].
+void gemm_swiglu_fwd(const Tensor& x, const Tensor& w, OptTensor gu, Tensor& h, const OptTensor& status) {
+  chk(x, BF16, "x");
+  chk(w, BF16, "w");
+  chk(h, BF16, "h");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && h.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && h.stride(1) == 1,
+              "gemm_swiglu_fwd: 2-D operands with unit inner stride");
+  const int64_t M = x.size(0), K = x.size(1), F = w.size(0) / 2;
+  TORCH_CHECK(w.size(1) == K && w.size(0) == 2 * F && h.size(0) == M && h.size(1) == F, "gemm_swiglu_fwd: shapes");
+  if (gu.has_value()) {
+    chk(*gu, BF16, "gu");
+    TORCH_CHECK(gu->dim() == 2 && gu->size(0) == M && gu->size(1) == 2 * F && gu->stride(1) == 1, "gemm_swiglu_fwd: gu");
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::gemm_swiglu_fwd(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), mptr(gu), gu.has_value() ? gu->stride(0) : 0,
+                      h.data_ptr(), h.stride(0), (int)M, (int)F, (int)K, status_ptr(status), cur_stream());
+}
+
+// dgu[M,2F] = SwiGLU backward of (dy[M,K] @ w_down[K,F]) at the saved pre-activations gu[M,2F].
+void gemm_swiglu_bwd(const Tensor& dy, const Tensor& w_down, const Tensor& gu, Tensor& dgu, const OptTensor& status) {
+  chk(dy, BF16, "dy");
+  chk(w_down, BF16, "w_down");
+  chk(gu, BF16, "gu");
+  chk(dgu, BF16, "dgu");
+  TORCH_CHECK(dy.dim() == 2 && w_down.dim() == 2 && gu.dim() == 2 && dgu.dim() == 2, "gemm_swiglu_bwd: 2-D operands");
+  TORCH_CHECK(dy.stride(1) == 1 && w_down.stride(1) == 1 && gu.stride(1) == 1 && dgu.stride(1) == 1,
+              "gemm_swiglu_bwd: unit inner stride");
+  const int64_t M = dy.size(0), K = dy.size(1), F = w_down.size(1);
+  TORCH_CHECK(w_down.size(0) == K && gu.size(0) == M && gu.size(1) == 2 * F && dgu.size(0) == M && dgu.size(1) == 2 * F,
+              "gemm_swiglu_bwd: shapes");
+  c10::cuda::CUDAGuard guard(dy.device());
+  mb::gemm_swiglu_bwd(dy.data_ptr(), dy.stride(0), w_down.data_ptr(), w_down.stride(0), gu.data_ptr(), gu.stride(0),
+                      dgu.data_ptr(), dgu.stride(0), (int)M, (int)F, (int)K, status_ptr(status), cur_stream());
+}
+
+// out[M,N] = x[M,K] w[N,K]^T with rotary embedding on the 128-wide heads in columns [0, rope_cols).
+void gemm_rope(const Tensor& x, const Tensor& w, Tensor& out, const Tensor& pos, const Tensor& cos_sin, int64_t rope_cols,
+               const OptTensor& status) {
+  chk(x, BF16, "x");
+  chk(w, BF16, "w");
+  chk(out, BF16, "out");
+  chk_c(pos, I32, "pos");
+  chk_c(cos_sin, F32, "cos_sin");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1,
+              "gemm_rope: 2-D operands with unit inner stride");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && out.size(0) == M && out.size(1) == N && pos.numel() == M, "gemm_rope: shapes");
+  TORCH_CHECK(cos_sin.dim() == 3 && cos_sin.size(1) == 64 && cos_sin.size(2) == 2, "gemm_rope: table must be [P, 64, 2]");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::gemm_rope(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), (int)M, (int)N,
+                (int)K, pos.data_ptr<int>(), cos_sin.data_ptr<float>(), (int)cos_sin.size(0), (int)rope_cols,
+                status_ptr(status), cur_stream());
+}
+
 void rmsnorm_fwd(const Tensor& x, const OptTensor& residual, const Tensor& gamma, Tensor& y, OptTensor resid_out,
                  OptTensor rstd, double eps) {
   chk_c(x, BF16, "x");
@@ -64,7 +118,11 @@ void rmsnorm_fwd(const Tensor& x, const OptTensor& residual, const Tensor& gamma
 }
 
 void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const Tensor& rstd, Tensor& dx,
-                 Tensor& dgamma_partial, Tensor& dgamma, bool accumulate) {
+                 Tensor& dgamma_partial, Tensor& dgamma, bool accumulate, const OptTensor& dres) {
+  if (dres.has_value()) {
+    chk_c(*dres, BF16, "dres");
+    TORCH_CHECK(dres->numel() == x.numel(), "rmsnorm_bwd: dres must have the shape of x");
+  }
   chk_c(dy, BF16, "dy");
   chk_c(x, BF16, "x");
   chk_c(gamma, BF16, "gamma");
@@ -77,7 +135,7 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, const T
   TORCH_CHECK(dgamma_partial.size(1) == dim, "rmsnorm_bwd: partial buffer must be [n_partial, dim]");
   c10::cuda::CUDAGuard guard(x.device());
   mb::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
-                  dgamma_partial.data_ptr<float>(), (int)rows, (int)dim, (int)n_partial, cur_stream());
+                  dgamma_partial.data_ptr<float>(), (int)rows, (int)dim, (int)n_partial, cur_stream(), cptr(dres));
   mb::rmsnorm_bwd_reduce(dgamma_partial.data_ptr<float>(), dgamma.data_ptr<float>(), (int)n_partial, (int)dim,
                          accumulate, cur_stream());
 }
@@ -799,7 +857,11 @@ PYBIND11_MODULE(_C, m) {
   m.doc() = "mythos_b200 sm_100a kernels";
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("rstd"), py::arg("dx"),
+        py::arg("dgamma_partial"), py::arg("dgamma"), py::arg("accumulate"), py::arg("dres") = py::none());
+  m.def("gemm_swiglu_fwd", &gemm_swiglu_fwd);
+  m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd);
+  m.def("gemm_rope", &gemm_rope);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("rope", &rope);
   m.def("swiglu_fused_fwd", &swiglu_fused_fwd);
@@ -859,6 +921,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("symm_barrier", &symm_barrier);
   m.def("zero_reduce_scatter", &zero_reduce_scatter);
   m.def("zero_adamw_ste_allgather", &zero_adamw_ste_allgather);
+  m.def("set_gemm_coalesced_epilogue", [](int64_t on) { mb::set_gemm_coalesced_epilogue((int)on); });
   m.def("set_gemm_mode", [](int64_t mode) { mb::set_gemm_mode((int)mode); });
   m.def("get_gemm_mode", []() { return (int64_t)mb::get_gemm_mode(); });
   m.def("launch_count", &launch_count);

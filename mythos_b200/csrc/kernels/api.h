@@ -3,6 +3,7 @@
 // All launchers are asynchronous on `stream`, bump the library's launch counter and throw
 // std::invalid_argument / mb::CudaError on bad arguments or launch failure.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -27,7 +28,35 @@ void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void*
                             long long ldc, int M, int N, int K, int epi, float alpha, int* status,
                             cudaStream_t stream, const PeerPtrs* scatter, int n_scatter, long long rows_per_rank,
                             long long slot_off);
+// Work folded into the paired kernel's epilogue (gemm_2cta.cu).
+enum : int { FUSE_NONE = 0, FUSE_SWIGLU_FWD = 1, FUSE_SWIGLU_BWD = 2, FUSE_ROPE = 3 };
+struct EpiFuse {
+  int F = 0;                              // SwiGLU: ffn width (number of gate columns)
+  const __nv_bfloat16* aux = nullptr;     // SWIGLU_BWD: saved gate|up pre-activations [M, 2F]
+  long long ld_aux = 0;
+  __nv_bfloat16* out2 = nullptr;          // SWIGLU_FWD: h = silu(gate) * up, [M, F]
+  long long ld_out2 = 0;
+  const int* pos = nullptr;               // ROPE: position of every row
+  const float2* cs = nullptr;             // ROPE: [max_pos, 64] (cos, sin) of pair j at angle pos * theta^(-2j/128)
+  int max_pos = 0;
+  int rope_cols = 0;                      // ROPE: columns [0, rope_cols) are rotated heads of 128
+};
+// gate_up[M, 2F] (may be null) and h[M, F] = silu(gate) * up from x[M, K] and the fused [2F, K] weight
+// (gate rows first), one launch; F must be a multiple of 128.
+void gemm_swiglu_fwd(const void* x, long long ldx, const void* w_gate_up, long long ldw, void* gate_up, long long ld_gu,
+                     void* h, long long ld_h, int M, int F, int K, int* status, cudaStream_t stream);
+// d_gate_up[M, 2F] from dy[M, K], the down-projection weight [K, F] and the saved pre-activations:
+// the dgrad GEMM dh = dy W_down with the SwiGLU backward applied in the epilogue.
+void gemm_swiglu_bwd(const void* dy, long long ld_dy, const void* w_down, long long ldw, const void* gate_up,
+                     long long ld_gu, void* d_gate_up, long long ld_dgu, int M, int F, int K, int* status,
+                     cudaStream_t stream);
+// out[M, N] = x[M, K] w[N, K]^T with the half-split rotary embedding applied to the heads (128 columns
+// each) in columns [0, rope_cols); cos_sin is the [max_pos, 64, 2] fp32 table.
+void gemm_rope(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int M, int N, int K,
+               const int* pos, const float* cos_sin, int max_pos, int rope_cols, int* status, cudaStream_t stream);
 double gemm_2cta_waves(int M, int N, int sms);
+// 1 (default): the paired kernel's plain epilogues store through a shared-memory transpose; 0: from registers.
+void set_gemm_coalesced_epilogue(int on);
 // 0 = choose per problem, 1 = always the single-CTA kernel, 2 = the paired kernel whenever it applies.
 void set_gemm_mode(int mode);
 int get_gemm_mode();
@@ -35,8 +64,9 @@ int get_gemm_mode();
 // ---- normalisation (norm.cu)
 void rmsnorm_fwd(const void* x, const void* residual, const void* gamma, void* y, void* resid_out, float* rstd,
                  int rows, int dim, float eps, cudaStream_t stream);
+// dres (bf16 [rows, dim], may be null): gradient arriving through the residual stream, added to dx.
 void rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, void* dx, float* dgamma_partial,
-                 int rows, int dim, int n_partial, cudaStream_t stream);
+                 int rows, int dim, int n_partial, cudaStream_t stream, const void* dres = nullptr);
 void rmsnorm_bwd_reduce(const float* dgamma_partial, float* dgamma, int n_partial, int dim, bool accumulate,
                         cudaStream_t stream);
 void layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int rows, int dim, float eps,

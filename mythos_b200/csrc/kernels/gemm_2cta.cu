@@ -33,8 +33,9 @@ struct Cfg2 {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = T_STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * T_STAGES + 4;
-  static constexpr int EPI_STAGE_OFFSET = BAR_OFFSET + 256;       // [4 epilogue warps][32 rows][128 B]
-  static constexpr int SMEM_BYTES = EPI_STAGE_OFFSET + 4 * 4096 + 1024;
+  static constexpr int EPI_STAGE_OFFSET = BAR_OFFSET + 256;       // [up to 8 epilogue warps][32 rows][128 B]
+  static constexpr int SMEM_BYTES = EPI_STAGE_OFFSET + 8 * 4096 + 1024;
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
   static_assert(NUM_BARS * 8 + 16 <= 256, "barrier region");
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
 };
@@ -98,12 +99,53 @@ __device__ __forceinline__ Work2 decode2(int w, int tiles_m, int tiles_n, int k_
   return {tm * T_BM, tn * T_BN, kb0, kb1};
 }
 
-template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T_THREADS, 1)
+__device__ __forceinline__ uint4 pack8_bf16(const float* v) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  return o;
+}
+__device__ __forceinline__ void unpack8_bf16(const uint4& q, float* v) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+// sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5 with the hardware tanh: one special-function op per element
+// (exp + reciprocal would be two, and the special-function pipe is what bounds these epilogues).
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
+
+// FUSE selects work folded into the epilogue (a separate instantiation each, so the plain GEMM's
+// code and register allocation are unaffected):
+//   FUSE_SWIGLU_FWD  gate/up projection: the pair's B halves are the gate rows [tn*128, +128) and the
+//                    up rows [F + tn*128, +128) of the [2F, K] weight, so every thread holds gate and
+//                    up of the same output element; writes both pre-activations and silu(g)*u.
+//   FUSE_SWIGLU_BWD  down-projection dgrad: the accumulator is dL/dh; the epilogue reads the saved
+//                    pre-activations and writes dL/dgate and dL/dup, dL/dh never reaches memory.
+//   FUSE_ROPE        QKV projection: columns [0, rope_cols) are heads of 128 that get the half-split
+//                    rotation by the row's position (table of cos/sin pairs) before the bf16 store.
+// The SwiGLU-backward epilogue waits on global loads (the saved pre-activations); it runs eight
+// epilogue warps (two per TMEM lane quarter, four 32-column chunks each) to have twice the loads in flight.
+template <int FUSE>
+__host__ __device__ constexpr int epi_warps() { return FUSE == FUSE_SWIGLU_BWD ? 8 : 4; }
+template <int FUSE>
+__host__ __device__ constexpr int cta_threads() { return 64 + 32 * epi_warps<FUSE>(); }
+static_assert(cta_threads<FUSE_NONE>() == T_THREADS, "plain kernel: producer + MMA + four epilogue warps");
+
+template <bool A_MN, bool B_MN, int FUSE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(cta_threads<FUSE>(), 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Cout, int M, int N, int K, long long ldc, int tiles_m, int tiles_n, int k_splits,
                  int epi, int vec_ok, float alpha, int* status, PeerPtrs scatter, int n_scatter,
-                 long long rows_per_rank, long long slot_off) {
+                 long long rows_per_rank, long long slot_off, EpiFuse fz) {
   using Cfg = Cfg2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -128,8 +170,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 8);   // leader: four epilogue warps of each CTA
-    mbar_init(&tempty[1], 8);
+    mbar_init(&tempty[0], 2 * epi_warps<FUSE>());   // leader: the epilogue warps of both CTAs
+    mbar_init(&tempty[1], 2 * epi_warps<FUSE>());
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -156,7 +198,8 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int w = cluster_id; w < total && ok; w += n_clusters) {
         const Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
-        const int my_m = wi.m0 + (int)cta * 128, my_n = wi.n0 + (int)cta * 128;
+        const int my_m = wi.m0 + (int)cta * 128;
+        const int my_n = (FUSE == FUSE_SWIGLU_FWD) ? (wi.n0 >> 1) + (int)cta * fz.F : wi.n0 + (int)cta * 128;
         for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, status, 51)) { ok = false; break; }
           const uint32_t lbar = map_to_cta(smem_u32(&full[stage]), 0);
@@ -230,6 +273,206 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = wi.m0 + (int)cta * 128 + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * T_BN + ((uint32_t)(q * 32) << 16);
+      if (FUSE == FUSE_SWIGLU_FWD) {
+        // accumulator columns [0,128) = gate, [128,256) = up of ffn columns (n0/2) .. (n0/2)+127.
+        // Stores go through the per-warp shared-memory tile so that a warp instruction writes 64
+        // contiguous bytes of 8 rows instead of 16 bytes of 32 rows (see FUSE_SWIGLU_BWD below).
+        uint8_t* sA = smem + Cfg::EPI_STAGE_OFFSET + q * 4096;
+        uint8_t* sB = sA + 2048;
+        const int row0 = wi.m0 + (int)cta * 128 + q * 32;
+        const int crow = lane >> 2, cpiece = lane & 3;
+        const int colg0 = wi.n0 >> 1;
+        __nv_bfloat16* gu_base = reinterpret_cast<__nv_bfloat16*>(Cout);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld32(t_row + c * 32, rg);
+          tmem_ld32(t_row + 128 + c * 32, ru);
+          tmem_ld_wait();
+          uint4 hq[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float g[8], u[8], h[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              g[i] = alpha * __uint_as_float(rg[8 * j + i]);
+              u[i] = alpha * __uint_as_float(ru[8 * j + i]);
+              h[i] = g[i] * sigmoid_fast(g[i]) * u[i];
+            }
+            const uint32_t off = lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+            *reinterpret_cast<uint4*>(sA + off) = pack8_bf16(g);
+            *reinterpret_cast<uint4*>(sB + off) = pack8_bf16(u);
+            hq[j] = pack8_bf16(h);
+          }
+          __syncwarp();
+          const int col = colg0 + c * 32 + cpiece * 8;
+          if (gu_base != nullptr) {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int rr = it * 8 + crow;
+              if (row0 + rr < M) {
+                const uint32_t off = rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4);
+                __nv_bfloat16* p = gu_base + (long long)(row0 + rr) * ldc + col;
+                *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(sA + off);
+                *reinterpret_cast<uint4*>(p + fz.F) = *reinterpret_cast<const uint4*>(sB + off);
+              }
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(sA + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = hq[j];
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + crow;
+            if (row0 + rr < M)
+              *reinterpret_cast<uint4*>(fz.out2 + (long long)(row0 + rr) * fz.ld_out2 + col) =
+                  *reinterpret_cast<const uint4*>(sA + rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4));
+          }
+          __syncwarp();
+        }
+      } else if (FUSE == FUSE_SWIGLU_BWD) {
+        // accumulator = dL/dh for ffn columns n0 .. n0+255; pre-activations come from fz.aux [M, 2F].
+        // A thread owns one accumulator row, but 32 rows x 16 bytes per instruction would make every
+        // global access of the warp 32 separate sectors, and this epilogue moves four times the bytes
+        // of a plain store. So global memory is touched in the transposed arrangement (4 lanes per
+        // row, 64 contiguous bytes, 8 rows per instruction) and a per-warp shared-memory tile
+        // (two 32 x 64-byte buffers, 16-byte pieces XOR-swizzled by row pair) converts between the two.
+        uint8_t* sA = smem + Cfg::EPI_STAGE_OFFSET + (warp - 2) * 4096;
+        uint8_t* sB = sA + 2048;
+        const int row0 = wi.m0 + (int)cta * 128 + q * 32;
+        const int cbase = ((warp - 2) >> 2) * 4;                // this warp's four chunks of the tile
+        const int nchunks = min(4, max(0, (fz.F - wi.n0) / 32 - cbase));
+        const int crow = lane >> 2, cpiece = lane & 3;          // coalesced phase: row within a group of 8, piece
+        uint4 pg[2][4], pu[2][4];                               // two chunks of pre-activations in flight
+        auto fetch = [&](int i, uint4* dg_, uint4* du_) {
+          const int col = wi.n0 + (cbase + i) * 32 + cpiece * 8;
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + crow;
+            const __nv_bfloat16* p = fz.aux + (long long)min(row0 + rr, M - 1) * fz.ld_aux + col;
+            dg_[it] = __ldg(reinterpret_cast<const uint4*>(p));
+            du_[it] = __ldg(reinterpret_cast<const uint4*>(p + fz.F));
+          }
+        };
+        if (nchunks > 0) fetch(0, pg[0], pu[0]);
+        if (nchunks > 1) fetch(1, pg[1], pu[1]);
+        {
+          // Pull the pre-activations of this CTA's NEXT tile into L2 now, a whole main loop ahead:
+          // the demand loads above then pay an L2 hit instead of a loaded-DRAM round trip.
+          const int w2 = w + n_clusters;
+          if (w2 < total) {
+            const Work2 nx = decode2(w2, tiles_m, tiles_n, k_splits, kblocks);
+            const int tid = (warp - 2) * 32 + lane;             // 256 threads, 1024 lines of 128 bytes
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int line = tid * 4 + i;
+              const int prow = nx.m0 + (int)cta * 128 + (line >> 3), seg = line & 7;
+              const int pcol = nx.n0 + (seg & 3) * 64;
+              if (prow < M && pcol < fz.F) {
+                const __nv_bfloat16* pp = fz.aux + (long long)prow * fz.ld_aux + pcol + (seg >> 2) * fz.F;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pp));
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (i >= nchunks) break;                              // uniform over the warp
+          const int c = cbase + i;
+          uint32_t r[32];
+          tmem_ld32(t_row + c * 32, r);
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + crow;
+            const uint32_t off = rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4);
+            *reinterpret_cast<uint4*>(sA + off) = pg[i & 1][it];
+            *reinterpret_cast<uint4*>(sB + off) = pu[i & 1][it];
+          }
+          __syncwarp();
+          uint4 gq[4], uq[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t off = lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+            gq[j] = *reinterpret_cast<const uint4*>(sA + off);
+            uq[j] = *reinterpret_cast<const uint4*>(sB + off);
+          }
+          __syncwarp();
+          if (i + 2 < nchunks) fetch(i + 2, pg[i & 1], pu[i & 1]);   // refill the buffer just consumed
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float g[8], u[8], dg[8], du[8];
+            unpack8_bf16(gq[j], g);
+            unpack8_bf16(uq[j], u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float dh = alpha * __uint_as_float(r[8 * j + e]);
+              const float sg = sigmoid_fast(g[e]);
+              const float silu = g[e] * sg;
+              dg[e] = dh * u[e] * (sg + silu * (1.f - sg));
+              du[e] = dh * silu;
+            }
+            const uint32_t off = lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+            *reinterpret_cast<uint4*>(sA + off) = pack8_bf16(dg);
+            *reinterpret_cast<uint4*>(sB + off) = pack8_bf16(du);
+          }
+          __syncwarp();
+          const int col = wi.n0 + c * 32 + cpiece * 8;
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rr = it * 8 + crow;
+            if (row0 + rr < M) {
+              const uint32_t off = rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4);
+              __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)(row0 + rr) * ldc + col;
+              *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(sA + off);
+              *reinterpret_cast<uint4*>(p + fz.F) = *reinterpret_cast<const uint4*>(sB + off);
+            }
+          }
+          __syncwarp();
+        }
+      } else if (FUSE == FUSE_ROPE) {
+        __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc;
+        int p = (row < M) ? fz.pos[row] : 0;
+        p = min(max(p, 0), fz.max_pos - 1);
+        const float4* cs_row = reinterpret_cast<const float4*>(fz.cs + (long long)p * 64);
+#pragma unroll 1
+        for (int hb = 0; hb < 2; ++hb) {
+          const int head_col = wi.n0 + hb * 128;
+          if (head_col >= N) break;
+          const bool rotate = head_col + 128 <= fz.rope_cols;
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t lo[32], hi[32];
+            tmem_ld32(t_row + hb * 128 + cc * 32, lo);
+            tmem_ld32(t_row + hb * 128 + 64 + cc * 32, hi);
+            tmem_ld_wait();
+            if (row < M) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float a[8], b[8];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                  float x0 = alpha * __uint_as_float(lo[8 * j + i]), x1 = alpha * __uint_as_float(lo[8 * j + i + 1]);
+                  float y0 = alpha * __uint_as_float(hi[8 * j + i]), y1 = alpha * __uint_as_float(hi[8 * j + i + 1]);
+                  if (rotate) {
+                    const float4 t = __ldg(cs_row + ((cc * 32 + 8 * j + i) >> 1));  // (cos, sin) of two pairs
+                    a[i] = x0 * t.x - y0 * t.y;
+                    b[i] = x0 * t.y + y0 * t.x;
+                    a[i + 1] = x1 * t.z - y1 * t.w;
+                    b[i + 1] = x1 * t.w + y1 * t.z;
+                  } else {
+                    a[i] = x0; b[i] = y0; a[i + 1] = x1; b[i + 1] = y1;
+                  }
+                }
+                *reinterpret_cast<uint4*>(c_row + head_col + cc * 32 + 8 * j) = pack8_bf16(a);
+                *reinterpret_cast<uint4*>(c_row + head_col + 64 + cc * 32 + 8 * j) = pack8_bf16(b);
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < T_BN / 32; ++c) {
         uint32_t r[32];
@@ -266,6 +509,58 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (row0 + rr < M)
                   *reinterpret_cast<uint4*>(base + (long long)rr * ldc + piece * 8) =
                       *reinterpret_cast<const uint4*>(stg + rr * 128 + ((piece ^ (rr & 7)) << 4));
+              }
+            }
+            __syncwarp();
+          }
+          continue;
+        }
+        if (vec_ok == 2 && col + 32 <= N && epi != EPI_F32_ATOMIC) {
+          // Full 32-column chunk (uniform over the warp): transpose through the warp's shared-memory
+          // tile so that every store instruction writes whole contiguous row segments (bf16: 64 bytes
+          // of 8 rows; fp32: 128 bytes of 4 rows) instead of 16 bytes of 32 different rows.
+          const int row0 = wi.m0 + (int)cta * 128 + q * 32;
+          uint8_t* stage = smem + Cfg::EPI_STAGE_OFFSET + q * 4096;
+          if (epi == EPI_BF16) {
+            uint8_t* sbuf = stage + (c & 1) * 2048;              // alternate halves: one warp barrier per chunk
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = alpha * __uint_as_float(r[8 * j + e]);
+              *reinterpret_cast<uint4*>(sbuf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = pack8_bf16(v);
+            }
+            __syncwarp();
+            const int crow = lane >> 2, cpiece = lane & 3;
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int rr = it * 8 + crow;
+              if (row0 + rr < M)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)(row0 + rr) * ldc + col +
+                                          cpiece * 8) =
+                    *reinterpret_cast<const uint4*>(sbuf + rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v = make_float4(alpha * __uint_as_float(r[4 * j]), alpha * __uint_as_float(r[4 * j + 1]),
+                                     alpha * __uint_as_float(r[4 * j + 2]), alpha * __uint_as_float(r[4 * j + 3]));
+              *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+            }
+            __syncwarp();
+            const int crow = lane >> 3, cpiece = lane & 7;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + crow;
+              if (row0 + rr < M) {
+                float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((cpiece ^ (rr & 7)) << 4));
+                float4* gp = reinterpret_cast<float4*>(reinterpret_cast<float*>(Cout) + (long long)(row0 + rr) * ldc + col +
+                                                       cpiece * 4);
+                if (epi == EPI_F32_ACC) {
+                  const float4 o = *gp;
+                  v = make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w);
+                }
+                *gp = v;
               }
             }
             __syncwarp();
@@ -341,11 +636,11 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  : "memory");
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int FUSE = FUSE_NONE>
 void launch2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int k_splits,
              int epi, int vec_ok, float alpha, int* status, cudaStream_t stream, const PeerPtrs& scatter,
-             int n_scatter, long long rows_per_rank, long long slot_off) {
-  auto kern = gemm_2cta_kernel<A_MN, B_MN>;
+             int n_scatter, long long rows_per_rank, long long slot_off, const EpiFuse& fz = EpiFuse{}) {
+  auto kern = gemm_2cta_kernel<A_MN, B_MN, FUSE>;
   static bool configured = false;
   if (!configured) {
     MB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::SMEM_BYTES));
@@ -355,14 +650,17 @@ void launch2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N
   const int total = tiles_m * tiles_n * k_splits;
   int clusters = sm_count() / 2;
   if (total < clusters) clusters = total;
-  kern<<<clusters * 2, T_THREADS, Cfg2::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, k_splits, epi,
+  kern<<<clusters * 2, cta_threads<FUSE>(), Cfg2::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, k_splits, epi,
                                                               vec_ok, alpha, status, scatter, n_scatter, rows_per_rank,
-                                                              slot_off);
+                                                              slot_off, fz);
   count_launch();
   check_launch();
 }
 
 }  // namespace
+
+namespace { int g_coalesced_epilogue = 1; }
+void set_gemm_coalesced_epilogue(int on) { g_coalesced_epilogue = on; }
 
 // Relative cost estimate (in 256-wide tile-waves) of the paired kernel; used by the dispatcher.
 double gemm_2cta_waves(int M, int N, int sms) {
@@ -374,6 +672,81 @@ double gemm_2cta_waves(int M, int N, int sms) {
 void gemm_bf16_2cta(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
                     long long ldc, int M, int N, int K, int epi, float alpha, int* status, cudaStream_t stream) {
   gemm_bf16_2cta_scatter(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, epi, alpha, status, stream, nullptr, 0, 0, 0);
+}
+
+namespace {
+void kmajor_map_dims(uint64_t* dims, uint32_t* box, int rows, int K) {
+  dims[0] = K; dims[1] = rows; box[0] = T_BK; box[1] = 128;
+}
+}  // namespace
+
+void gemm_swiglu_fwd(const void* x, long long ldx, const void* w_gate_up, long long ldw, void* gate_up, long long ld_gu,
+                     void* h, long long ld_h, int M, int F, int K, int* status, cudaStream_t stream) {
+  MB_REQUIRE(M > 0 && F > 0 && K > 0, "gemm_swiglu_fwd: empty problem");
+  MB_REQUIRE(F % 128 == 0, "gemm_swiglu_fwd: the ffn width must be a multiple of 128");
+  MB_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && ld_h % 8 == 0 && (gate_up == nullptr || ld_gu % 8 == 0),
+             "gemm_swiglu_fwd: row strides must be multiples of 8 elements");
+  MB_REQUIRE((reinterpret_cast<uintptr_t>(h) & 15) == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0,
+             "gemm_swiglu_fwd: outputs must be 16-byte aligned");
+  uint64_t adims[2], astr[1] = {(uint64_t)ldx * 2}, bdims[2], bstr[1] = {(uint64_t)ldw * 2};
+  uint32_t abox[2], bbox[2];
+  kmajor_map_dims(adims, abox, M, K);
+  kmajor_map_dims(bdims, bbox, 2 * F, K);
+  const CUtensorMap ta = make_tensor_map(x, TmaDType::BF16, 2, adims, astr, abox, true);
+  const CUtensorMap tb = make_tensor_map(w_gate_up, TmaDType::BF16, 2, bdims, bstr, bbox, true);
+  EpiFuse fz{};
+  fz.F = F;
+  fz.out2 = reinterpret_cast<__nv_bfloat16*>(h);
+  fz.ld_out2 = ld_h;
+  // N = 2F: one 256-column tile is 128 gate + 128 up columns, so tiles_n = F / 128
+  launch2<false, false, FUSE_SWIGLU_FWD>(ta, tb, gate_up, M, 2 * F, K, ld_gu, 1, EPI_BF16, 1, 1.f, status, stream,
+                                         PeerPtrs{}, 0, 0, 0, fz);
+}
+
+void gemm_swiglu_bwd(const void* dy, long long ld_dy, const void* w_down, long long ldw, const void* gate_up,
+                     long long ld_gu, void* d_gate_up, long long ld_dgu, int M, int F, int K, int* status,
+                     cudaStream_t stream) {
+  MB_REQUIRE(M > 0 && F > 0 && K > 0, "gemm_swiglu_bwd: empty problem");
+  MB_REQUIRE(F % 64 == 0, "gemm_swiglu_bwd: the ffn width must be a multiple of 64");
+  MB_REQUIRE(ld_dy % 8 == 0 && ldw % 8 == 0 && ld_gu % 8 == 0 && ld_dgu % 8 == 0,
+             "gemm_swiglu_bwd: row strides must be multiples of 8 elements");
+  MB_REQUIRE((reinterpret_cast<uintptr_t>(gate_up) & 15) == 0 && (reinterpret_cast<uintptr_t>(d_gate_up) & 15) == 0,
+             "gemm_swiglu_bwd: pre-activation buffers must be 16-byte aligned");
+  // dh[M, F] = dy[M, K] @ W_down[K, F]: A K-major, B MN-major
+  uint64_t adims[2], astr[1] = {(uint64_t)ld_dy * 2}, bdims[2] = {(uint64_t)F, (uint64_t)K}, bstr[1] = {(uint64_t)ldw * 2};
+  uint32_t abox[2], bbox[2] = {64, T_BK};
+  kmajor_map_dims(adims, abox, M, K);
+  const CUtensorMap ta = make_tensor_map(dy, TmaDType::BF16, 2, adims, astr, abox, true);
+  const CUtensorMap tb = make_tensor_map(w_down, TmaDType::BF16, 2, bdims, bstr, bbox, true);
+  EpiFuse fz{};
+  fz.F = F;
+  fz.aux = reinterpret_cast<const __nv_bfloat16*>(gate_up);
+  fz.ld_aux = ld_gu;
+  launch2<false, true, FUSE_SWIGLU_BWD>(ta, tb, d_gate_up, M, F, K, ld_dgu, 1, EPI_BF16, 1, 1.f, status, stream,
+                                        PeerPtrs{}, 0, 0, 0, fz);
+}
+
+void gemm_rope(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int M, int N, int K,
+               const int* pos, const float* cos_sin, int max_pos, int rope_cols, int* status, cudaStream_t stream) {
+  MB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_rope: empty problem");
+  MB_REQUIRE(N % 128 == 0 && rope_cols % 128 == 0 && rope_cols <= N, "gemm_rope: heads of 128 columns");
+  MB_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(cos_sin) & 15) == 0,
+             "gemm_rope: alignment");
+  MB_REQUIRE(pos != nullptr && cos_sin != nullptr && max_pos > 0, "gemm_rope: positions and table");
+  uint64_t adims[2], astr[1] = {(uint64_t)ldx * 2}, bdims[2], bstr[1] = {(uint64_t)ldw * 2};
+  uint32_t abox[2], bbox[2];
+  kmajor_map_dims(adims, abox, M, K);
+  kmajor_map_dims(bdims, bbox, N, K);
+  const CUtensorMap ta = make_tensor_map(x, TmaDType::BF16, 2, adims, astr, abox, true);
+  const CUtensorMap tb = make_tensor_map(w, TmaDType::BF16, 2, bdims, bstr, bbox, true);
+  EpiFuse fz{};
+  fz.pos = pos;
+  fz.cs = reinterpret_cast<const float2*>(cos_sin);
+  fz.max_pos = max_pos;
+  fz.rope_cols = rope_cols;
+  launch2<false, false, FUSE_ROPE>(ta, tb, out, M, N, K, ldo, 1, EPI_BF16, 1, 1.f, status, stream, PeerPtrs{}, 0, 0, 0,
+                                   fz);
 }
 
 void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,
@@ -393,7 +766,9 @@ void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void*
   MB_REQUIRE(!(a_mn && !b_mn), "gemm: MN-major A with K-major B is not instantiated");
   MB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: operand row strides must be multiples of 8 elements");
   const int esz = (epi == EPI_BF16) ? 2 : 4;
-  const int vec_ok = ((ldc * esz) % 16 == 0 && (n_scatter > 0 || (reinterpret_cast<uintptr_t>(C) & 15) == 0)) ? 1 : 0;
+  // 2 = vector accesses through the shared-memory transpose, 1 = vector accesses straight from registers
+  const int vec_ok = ((ldc * esz) % 16 == 0 && (n_scatter > 0 || (reinterpret_cast<uintptr_t>(C) & 15) == 0))
+                         ? (g_coalesced_epilogue && n_scatter == 0 ? 2 : 1) : 0;
   const int kblocks = (K + T_BK - 1) / T_BK;
   int k_splits = 1;
   if (epi == EPI_F32_ATOMIC) {

@@ -63,7 +63,7 @@ template <int NC>
 __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ rstd,
                                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma_partial, int rows,
-                                   int dim) {
+                                   int dim, const __nv_bfloat16* __restrict__ dres) {
   __shared__ float scratch[32];
   const int nchunk = dim >> 3;
   float g[NC][8], dg[NC][8];
@@ -102,6 +102,12 @@ __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* _
         float o[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = rs * (dyg[c][i] - xh[c][i] * dot);
+        if (dres) {  // gradient arriving through the residual stream, added here instead of in a second pass
+          float e[8];
+          unpack8(ldg8(dres, row * dim + ch * 8), e);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += e[i];
+        }
         stg8(dx, row * dim + ch * 8, pack8(o));
       }
     }
@@ -206,13 +212,14 @@ void rmsnorm_fwd(const void* x, const void* residual, const void* gamma, void* y
 }
 
 void rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, void* dx, float* dgamma_partial,
-                 int rows, int dim, int n_partial, cudaStream_t stream) {
+                 int rows, int dim, int n_partial, cudaStream_t stream, const void* dres) {
   if (rows == 0) return;
+  MB_REQUIRE(dres != dx, "rmsnorm_bwd: the residual gradient must not alias dx");
   const int th = norm_threads(dim, 512);  // the backward keeps four row-sized arrays in registers
   MB_NORM_DISPATCH(norm_nc(dim, th), rmsnorm_bwd_kernel,
                    <<<n_partial, th, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                   (const __nv_bfloat16*)gamma, rstd, (__nv_bfloat16*)dx,
-                                                  dgamma_partial, rows, dim));
+                                                  dgamma_partial, rows, dim, (const __nv_bfloat16*)dres));
   count_launch();
   check_launch();
 }

@@ -160,8 +160,16 @@ class Attention(nn.Module):
 
     def forward(self, x, pos):
         cfg = self.cfg
-        qkv = self.qkv_proj(x)
-        o = F.attention_qkv(qkv, pos, cfg.num_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta, True)
+        w = self.qkv_proj.compute_weight() if type(self.qkv_proj) is OILLinear else None   # not an adapter wrapper
+        if w is not None and F.fused_rope_ok(x, w, cfg.head_dim, cfg.rope_theta) and x.shape[-2] <= cfg.max_seq_len:
+            # RoPE in the epilogue of the projection GEMM; positions are below max_seq_len
+            qkv = F.linear_rope(x, w, getattr(self.qkv_proj.weight, "main_grad", None), pos, cfg.rope_theta,
+                                cfg.q_dim + cfg.kv_dim, cfg.max_seq_len)
+            o = F.attention_qkv(qkv, pos, cfg.num_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta, True,
+                                rope_applied=True)
+        else:
+            qkv = self.qkv_proj(x)
+            o = F.attention_qkv(qkv, pos, cfg.num_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta, True)
         return self.o_proj(o)
 
 
@@ -183,6 +191,11 @@ class FFN(nn.Module):
                                    init_std=0.02 / math.sqrt(2 * cfg.num_layers))
 
     def forward(self, x):
+        if self.gated and self.act != "relu2" and type(self.up_proj) is OILLinear and type(self.down_proj) is OILLinear:
+            w_gu, w_down = self.up_proj.compute_weight(), self.down_proj.compute_weight()
+            if F.fused_ffn_ok(x, w_gu, w_down):
+                return F.swiglu_ffn(x, w_gu, w_down, getattr(self.up_proj.weight, "main_grad", None),
+                                    getattr(self.down_proj.weight, "main_grad", None))
         u = self.up_proj(x)
         if self.gated:
             if self.act == "relu2":

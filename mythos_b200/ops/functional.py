@@ -16,12 +16,15 @@ extension raises.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
 from . import native, reference as ref
 
 EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_F32_ATOMIC = 0, 1, 2, 3
+# MYTHOS_FUSED_EPILOGUES=0 runs SwiGLU / RoPE as separate kernels (for A/B timing of the fusion)
+FUSED_EPILOGUES = os.environ.get("MYTHOS_FUSED_EPILOGUES", "1") != "0"
 
 
 def _C():
@@ -73,6 +76,119 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, None
 
 
+_ROPE_TABLES: dict = {}
+
+
+def rope_table(theta: float, max_pos: int, device, head_dim: int = 128):
+    """[max_pos, head_dim/2, 2] fp32 (cos, sin) of angle ``pos * theta^(-2j/head_dim)``; cached."""
+    key = (float(theta), int(max_pos), str(device), head_dim)
+    t = _ROPE_TABLES.get(key)
+    if t is None:
+        j = torch.arange(head_dim // 2, device=device, dtype=torch.float32)
+        inv = torch.exp2(-2.0 * j / head_dim * math.log2(theta))
+        ang = torch.arange(max_pos, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+        t = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+        _ROPE_TABLES[key] = t
+    return t
+
+
+class _LinearRopeFn(torch.autograd.Function):
+    """y = x W^T with the rotary embedding of the q and k heads applied in the GEMM epilogue. The
+    gradient handed back by the attention function is already rotated back (it is the gradient of
+    the un-rotated projection), so the backward pass is the one of a plain linear layer."""
+
+    @staticmethod
+    def forward(ctx, x, w, grad_target, pos, table, rope_cols):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = torch.empty(x2.shape[0], w.shape[0], device=x.device, dtype=torch.bfloat16)
+        _C().gemm_rope(x2, w, y, pos, table, rope_cols, native.status_word(x.device))
+        ctx.save_for_backward(x2, w)
+        ctx.grad_target = grad_target
+        ctx.x_shape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, dw, _ = _LinearFn.backward(ctx, dy)
+        return dx, dw, None, None, None, None
+
+
+def fused_rope_ok(x, w, head_dim: int, theta: float) -> bool:
+    """The epilogue rotation covers heads of 128 on the paired-SM GEMM (>= 256 rows and columns)."""
+    rows = x.numel() // x.shape[-1]
+    return (FUSED_EPILOGUES and x.is_cuda and head_dim == 128 and theta > 0 and rows >= 256 and w.shape[0] >= 256
+            and w.shape[0] % 128 == 0 and x.shape[-1] % 8 == 0)
+
+
+def linear_rope(x, w, grad_target, pos, theta: float, rope_cols: int, max_pos: int):
+    """``x @ w.T`` followed by RoPE on columns [0, rope_cols) (heads of 128), in one kernel. ``pos``
+    values must be below ``max_pos``. Pair with ``attention_qkv(..., rope_applied=True)``."""
+    table = rope_table(theta, max_pos, x.device)
+    return _LinearRopeFn.apply(x, w, grad_target, pos, table, rope_cols)
+
+
+class _FusedFFNFn(torch.autograd.Function):
+    """SwiGLU FFN ``down(silu(gate(x)) * up(x))`` in two GEMM launches forward and four backward:
+    the activation runs in the epilogue of the gate/up GEMM, its derivative in the epilogue of the
+    down-projection dgrad GEMM (dL/dh is never written)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down, gt_gu, gt_down):
+        C = _C()
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        M, F2 = x2.shape[0], w_gu.shape[0]
+        st = native.status_word(x.device)
+        gu = torch.empty(M, F2, device=x.device, dtype=torch.bfloat16)
+        h = torch.empty(M, F2 // 2, device=x.device, dtype=torch.bfloat16)
+        C.gemm_swiglu_fwd(x2, w_gu, gu, h, st)
+        y = gemm(h, w_down)
+        ctx.save_for_backward(x2, w_gu, w_down, gu, h)
+        ctx.gts = (gt_gu, gt_down)
+        ctx.x_shape = x.shape
+        return y.reshape(*x.shape[:-1], w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _C()
+        x2, w_gu, w_down, gu, h = ctx.saved_tensors
+        gt_gu, gt_down = ctx.gts
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dgu = torch.empty_like(gu)
+        C.gemm_swiglu_bwd(dy2, w_down, gu, dgu, native.status_word(dy.device))
+        dw_down = dw_gu = None
+        if gt_down is not None:
+            gemm(dy2, h, a_mn=True, b_mn=True, out=gt_down, epi=EPI_F32_ACC)
+        elif ctx.needs_input_grad[2]:
+            dw_down = gemm(dy2, h, a_mn=True, b_mn=True, epi=EPI_F32).to(w_down.dtype)
+        dx = gemm(dgu, w_gu, b_mn=True).reshape(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        if gt_gu is not None:
+            gemm(dgu, x2, a_mn=True, b_mn=True, out=gt_gu, epi=EPI_F32_ACC)
+        elif ctx.needs_input_grad[1]:
+            dw_gu = gemm(dgu, x2, a_mn=True, b_mn=True, epi=EPI_F32).to(w_gu.dtype)
+        return dx, dw_gu, dw_down, None, None
+
+
+def fused_ffn_ok(x, w_gu, w_down) -> bool:
+    rows = x.numel() // x.shape[-1]
+    f = w_gu.shape[0] // 2
+    return (FUSED_EPILOGUES and x.is_cuda and rows >= 256 and f % 128 == 0 and f >= 256 and x.shape[-1] % 8 == 0
+            and w_down.shape[0] >= 256 and w_down.shape[1] == f)
+
+
+def swiglu_ffn(x, w_gu, w_down, gt_gu=None, gt_down=None):
+    """``(silu(x Wg^T) * (x Wu^T)) Wd^T`` with ``w_gu`` = [Wg; Wu] ([2F, d]) and ``w_down`` [d, F].
+    CUDA with F a multiple of 128: the fused-epilogue GEMMs; otherwise linear -> swiglu -> linear."""
+    if fused_ffn_ok(x, w_gu, w_down):
+        return _FusedFFNFn.apply(x, w_gu, w_down, gt_gu, gt_down)
+    return linear(swiglu(linear(x, w_gu, gt_gu)), w_down, gt_down)
+
+
 def linear(x, w, grad_target=None):
     """``x @ w.T``. CUDA: tcgen05 GEMMs (bf16). CPU: torch matmul in the weight's dtype."""
     if x.is_cuda:
@@ -117,15 +233,15 @@ class _RMSNormFn(torch.autograd.Function):
         dx = torch.empty_like(h)
         npart = _n_partial(rows, h.device)
         partial = torch.empty(npart, dim, device=h.device, dtype=torch.float32)
+        # the gradient that arrives through the residual stream is added inside the kernel
+        dres = dh.contiguous() if (ctx.has_residual and dh is not None) else None
         if ctx.grad_target is not None:
-            C.rmsnorm_bwd(dy.contiguous(), h, gamma, rstd, dx, partial, ctx.grad_target, True)
+            C.rmsnorm_bwd(dy.contiguous(), h, gamma, rstd, dx, partial, ctx.grad_target, True, dres)
             dgamma = None
         else:
             dg = torch.empty(dim, device=h.device, dtype=torch.float32)
-            C.rmsnorm_bwd(dy.contiguous(), h, gamma, rstd, dx, partial, dg, False)
+            C.rmsnorm_bwd(dy.contiguous(), h, gamma, rstd, dx, partial, dg, False, dres)
             dgamma = dg.to(gamma.dtype)
-        if ctx.has_residual and dh is not None:
-            C.add(dx, dh.contiguous(), dx)
         return dx, (dx if ctx.has_residual else None), dgamma, None, None
 
 
@@ -166,14 +282,14 @@ class _AttentionFn(torch.autograd.Function):
     qkv: [B, S, (H + 2*Hkv) * D] bf16, laid out q | k | v along the last dimension."""
 
     @staticmethod
-    def forward(ctx, qkv, pos, H, Hkv, D, theta, causal, scale):
+    def forward(ctx, qkv, pos, H, Hkv, D, theta, causal, scale, rope_applied=False):
         C = _C()
         B, S, W = qkv.shape
         assert W == (H + 2 * Hkv) * D and qkv.is_contiguous()
         flat = qkv.view(B * S, W)
         q = flat[:, : H * D].unflatten(-1, (H, D))
         k = flat[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
-        if theta > 0:
+        if theta > 0 and not rope_applied:
             C.rope(q, pos, theta, False)
             C.rope(k, pos, theta, False)
         q4 = qkv[..., : H * D].unflatten(-1, (H, D))
@@ -223,17 +339,20 @@ class _AttentionFn(torch.autograd.Function):
             flat = dqkv.view(B * S, W)
             C.rope(flat[:, : H * D].unflatten(-1, (H, D)), pos, theta, True)
             C.rope(flat[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D)), pos, theta, True)
-        return dqkv, None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None
 
 
 def attention_qkv(qkv, pos, n_heads: int, n_kv_heads: int, head_dim: int, theta: float = 10000.0,
-                  causal: bool = True, scale: float | None = None):
+                  causal: bool = True, scale: float | None = None, rope_applied: bool = False):
     """Self-attention over a fused projection ``qkv`` = [B, S, (H+2Hkv)*D] (q | k | v). RoPE with
     half-split pairs is applied to q and k at positions ``pos`` ([B*S] int32); ``theta <= 0``
-    disables it. Returns [B, S, H*D]. On CUDA the projection buffer is rotated in place."""
+    disables it. Returns [B, S, H*D]. On CUDA the projection buffer is rotated in place.
+    ``rope_applied``: q and k arrive rotated (``linear_rope``); the forward pass then skips the
+    rotation, the backward pass still rotates the gradient back (CUDA only)."""
     scale = (1.0 / math.sqrt(head_dim)) if scale is None else scale
     if qkv.is_cuda:
-        return _AttentionFn.apply(qkv, pos, n_heads, n_kv_heads, head_dim, theta, causal, scale)
+        return _AttentionFn.apply(qkv, pos, n_heads, n_kv_heads, head_dim, theta, causal, scale, rope_applied)
+    assert not rope_applied
     B, S, _ = qkv.shape
     H, Hkv, D = n_heads, n_kv_heads, head_dim
     q = qkv[..., : H * D].reshape(B * S, H, D)

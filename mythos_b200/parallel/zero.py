@@ -179,3 +179,12 @@ class ZeroEngine:
 
     def barrier(self) -> None:
         dist.barrier(group=self.group)
+
+    def release(self) -> None:
+        """Drop the symmetric gradient / compute buffers and the shard state (collective: every rank
+        calls it at the same point, with no kernel of the engine in flight)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for name in ("grad_buf", "compute_buf", "barrier_obj", "gshard", "store", "cb8", "cb4", "seg_fmt", "seg_cb"):
+            if hasattr(self, name):
+                setattr(self, name, None)

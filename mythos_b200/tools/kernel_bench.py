@@ -98,6 +98,60 @@ def bench_gemm(t: Timer, M, N, K, layout="kk", epi=0):
     return ms, 2.0 * M * N * K / ms / 1e9, "TFLOP/s"
 
 
+def bench_fused_epilogues(t: Timer, M: int, d: int, F: int, heads: int, only: str = "", unfused: bool = True):
+    """The fused-epilogue GEMMs against the launches they replace (same shapes as one layer of the
+    1.3B model): gate/up GEMM + SwiGLU, down dgrad GEMM + SwiGLU backward, QKV GEMM + RoPE on q and k.
+    Returns [(name, ms fused, ms unfused)]."""
+    from mythos_b200.ops import functional as Fn, native
+
+    C = native.require()
+    st = native.status_word("cuda")
+    x = torch.randn(M, d, device="cuda").to(torch.bfloat16)
+    w_gu = (torch.randn(2 * F, d, device="cuda") * 0.02).to(torch.bfloat16)
+    w_dn = (torch.randn(d, F, device="cuda") * 0.02).to(torch.bfloat16)
+    gu = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
+    h = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    dgu = torch.empty_like(gu)
+    dh = torch.empty_like(h)
+    dy = torch.randn(M, d, device="cuda").to(torch.bfloat16)
+    out = []
+    skip = (lambda fn: 0.0) if not unfused else t        # profiling runs time the fused launch only
+
+    def unfused_fwd():
+        Fn.gemm(x, w_gu, out=gu)
+        C.swiglu_fused_fwd(gu, h)
+
+    if only in ("", "fwd"):
+        out.append(("gate_up+swiglu_fwd", t(lambda: C.gemm_swiglu_fwd(x, w_gu, gu, h, st)), skip(unfused_fwd),
+                    2.0 * M * 2 * F * d))
+
+    def unfused_bwd():
+        Fn.gemm(dy, w_dn, b_mn=True, out=dh)
+        C.swiglu_fused_bwd(gu, dh, dgu)
+
+    if only in ("", "bwd"):
+        gu.normal_()
+        out.append(("down_dgrad+swiglu_bwd", t(lambda: C.gemm_swiglu_bwd(dy, w_dn, gu, dgu, st)), skip(unfused_bwd),
+                    2.0 * M * F * d))
+    if only not in ("", "rope"):
+        return out
+    D = 128
+    N = 3 * heads * D
+    w_qkv = (torch.randn(N, d, device="cuda") * 0.02).to(torch.bfloat16)
+    qkv = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    pos = (torch.arange(M, device="cuda") % 2048).to(torch.int32)
+    table = Fn.rope_table(10000.0, 2048, x.device)
+
+    def unfused_rope():
+        Fn.gemm(x, w_qkv, out=qkv)
+        C.rope(qkv[:, : heads * D].unflatten(-1, (heads, D)), pos, 10000.0, False)
+        C.rope(qkv[:, heads * D: 2 * heads * D].unflatten(-1, (heads, D)), pos, 10000.0, False)
+
+    out.append(("qkv+rope", t(lambda: C.gemm_rope(x, w_qkv, qkv, pos, table, 2 * heads * D, st)), skip(unfused_rope),
+                2.0 * M * N * d))
+    return out
+
+
 def bench_attn(t: Timer, B, S, H, Hkv, D, backward=False):
     from mythos_b200.ops import functional as F
 
@@ -236,11 +290,14 @@ def main():
     ap.add_argument("--fmt", default="oil8", choices=["oil8", "oil4", "i2s"])
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--splits", type=int, default=0, help="KV splits of paged_decode (0 = the engine's choice)")
+    ap.add_argument("--coalesced-epilogue", type=int, default=1,
+                    help="paired GEMM: 1 stores through a shared-memory transpose, 0 straight from registers")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 single-CTA kernel, 2 paired-SM kernel")
     args = ap.parse_args()
     from mythos_b200.ops import native
 
     native.require().set_gemm_mode(args.gemm_mode)
+    native.require().set_gemm_coalesced_epilogue(args.coalesced_epilogue)
     tf_peak, bw_peak, src = _peaks()
     t = Timer(args.iters, args.warmup, not args.no_flush)
     hkv = args.kv_heads or args.heads
@@ -254,7 +311,7 @@ def main():
         print(json.dumps(rows[-1]), flush=True)
 
     k = args.kernel
-    if k in ("gemm", "all"):
+    if k in ("gemm", "gemm_set", "all"):
         if k == "gemm":
             report(f"gemm_{args.layout}_{args.m}x{args.n}x{args.k}_epi{args.epi}",
                    bench_gemm(t, args.m, args.n, args.k, args.layout, args.epi))
@@ -266,6 +323,12 @@ def main():
                                         (11008, 2048, 16384, "mnmn", 2), (2048, 5504, 16384, "mnmn", 2),
                                         (32000, 2048, 16384, "mnmn", 2), (8192, 8192, 8192, "kk", 0)]:
                 report(f"gemm_{lay}_{M}x{N}x{K}_epi{epi}", bench_gemm(t, M, N, K, lay, epi))
+    if k in ("fused_epilogue", "fused_swiglu_fwd", "fused_swiglu_bwd", "fused_rope", "all"):
+        only = {"fused_swiglu_fwd": "fwd", "fused_swiglu_bwd": "bwd", "fused_rope": "rope"}.get(k, "")
+        for name, ms_f, ms_u, flops in bench_fused_epilogues(t, args.m, 2048, 5504, 16, only, unfused=not only):
+            report(f"{name}_fused_m{args.m}", (ms_f, flops / ms_f / 1e9, "TFLOP/s"))
+            if ms_u > 0:
+                report(f"{name}_unfused_m{args.m}", (ms_u, flops / ms_u / 1e9, "TFLOP/s"))
     if k in ("attn_fwd", "all"):
         report(f"attn_fwd_b{args.batch}_s{args.seq}_h{args.heads}_d{args.head_dim}",
                bench_attn(t, args.batch, args.seq, args.heads, hkv, args.head_dim, False))

@@ -106,3 +106,100 @@ def test_gemm_paired_sm_kernel(M, N, K, layout):
     ref = _ref(a, b, a_mn, b_mn)
     _check(out, ref, K)
     _check(acc, ref + 1.0, K)
+
+
+@pytest.mark.parametrize("M,F,K", [(256, 256, 128), (512, 640, 256), (1000, 384, 200), (4096, 5504, 2048)])
+def test_gemm_swiglu_forward_epilogue(M, F, K):
+    """gate/up projection with silu(gate) * up computed in the GEMM epilogue, against fp32."""
+    from mythos_b200.ops import native
+
+    C = native.require()
+    torch.manual_seed(M + F)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    gu = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
+    h = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    C.gemm_swiglu_fwd(x, w, gu, h, native.status_word(x.device))
+    ref = x.float() @ w.float().t()
+    _check(gu, ref, K)
+    g, u = ref[:, :F], ref[:, F:]
+    _check(h, g * torch.sigmoid(g) * u, K)
+    h2 = torch.empty_like(h)
+    C.gemm_swiglu_fwd(x, w, None, h2, native.status_word(x.device))      # without the pre-activation output
+    assert torch.equal(h, h2)
+
+
+@pytest.mark.parametrize("M,F,K", [(256, 256, 256), (520, 640, 320), (4096, 5504, 2048)])
+def test_gemm_swiglu_backward_epilogue(M, F, K):
+    """down-projection dgrad with the SwiGLU derivative in the epilogue, against fp32 autograd."""
+    from mythos_b200.ops import native
+
+    C = native.require()
+    torch.manual_seed(M + F + 1)
+    dy = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w_down = (torch.randn(K, F, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    gu = torch.randn(M, 2 * F, device="cuda").to(torch.bfloat16)
+    dgu = torch.empty_like(gu)
+    C.gemm_swiglu_bwd(dy, w_down, gu, dgu, native.status_word(dy.device))
+    guf = gu.float().requires_grad_()
+    hh = torch.nn.functional.silu(guf[:, :F]) * guf[:, F:]
+    hh.backward(dy.float() @ w_down.float())
+    _check(dgu, guf.grad, K)
+
+
+@pytest.mark.parametrize("M,heads,kv_heads,K", [(256, 2, 2, 128), (600, 3, 1, 256), (4096, 16, 16, 2048)])
+def test_gemm_rope_epilogue(M, heads, kv_heads, K):
+    """QKV projection with the rotary embedding of the q and k heads in the epilogue; v untouched."""
+    from mythos_b200.ops import functional as Fn, native, reference as ref
+
+    C = native.require()
+    torch.manual_seed(M + heads)
+    D = 128
+    N = (heads + 2 * kv_heads) * D
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    pos = torch.randint(0, 512, (M,), device="cuda", dtype=torch.int32)
+    table = Fn.rope_table(10000.0, 512, x.device)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    C.gemm_rope(x, w, out, pos, table, (heads + kv_heads) * D, native.status_word(x.device))
+    y = x.float() @ w.float().t()
+    nr = heads + kv_heads
+    rot = ref.rope(y[:, : nr * D].reshape(M, nr, D), pos, 10000.0).reshape(M, nr * D)
+    _check(out[:, : nr * D], rot, K)
+    _check(out[:, nr * D:], y[:, nr * D:], K)
+
+
+def test_fused_ffn_and_rope_layers_match_unfused_autograd():
+    """The fused FFN / QKV+RoPE functions give the gradients of the unfused operator chain."""
+    from mythos_b200.ops import functional as Fn
+
+    torch.manual_seed(3)
+    M, d, F = 512, 256, 384
+    x = torch.randn(M, d, device="cuda").to(torch.bfloat16).requires_grad_()
+    w_gu = (torch.randn(2 * F, d, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    w_dn = (torch.randn(d, F, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(M, d, device="cuda").to(torch.bfloat16)
+    assert Fn.fused_ffn_ok(x, w_gu, w_dn)
+    y = Fn.swiglu_ffn(x, w_gu, w_dn)
+    y.backward(dy)
+    got = (y.detach().float(), x.grad.float(), w_gu.grad.float(), w_dn.grad.float())
+    xf, wg, wd = (t.detach().float().requires_grad_() for t in (x, w_gu, w_dn))
+    u = xf @ wg.t()
+    yr = (torch.nn.functional.silu(u[:, :F]) * u[:, F:]) @ wd.t()
+    yr.backward(dy.float())
+    for a, b in zip(got, (yr.detach(), xf.grad, wg.grad, wd.grad)):
+        assert (a - b).abs().max().item() <= 3e-2 * b.abs().max().item() + 1e-3
+    # residual-gradient add inside the RMSNorm backward
+    hdn = torch.randn(M, d, device="cuda").to(torch.bfloat16).requires_grad_()
+    res = torch.randn(M, d, device="cuda").to(torch.bfloat16).requires_grad_()
+    gamma = (1 + 0.1 * torch.randn(d, device="cuda")).to(torch.bfloat16).requires_grad_()
+    yn, hs = Fn.rmsnorm(hdn, gamma, 1e-5, res)
+    g1, g2 = torch.randn_like(yn), torch.randn_like(hs)
+    torch.autograd.backward([yn, hs], [g1, g2])
+    hf, rf, gf = (t.detach().float().requires_grad_() for t in (hdn, res, gamma))
+    s = hf + rf
+    ynr = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * gf
+    torch.autograd.backward([ynr, s], [g1.float(), g2.float()])
+    assert (hdn.grad.float() - hf.grad).abs().max().item() <= 5e-2
+    assert torch.equal(hdn.grad, res.grad)
+    assert (gamma.grad.float() - gf.grad).abs().max().item() <= 3e-2 * gf.grad.abs().max().item() + 1e-2
