@@ -313,10 +313,11 @@ void gemm_bf16(const void* A, long long lda, bool a_mn, const void* B, long long
   if (epi == EPI_F32_ATOMIC) {
     double best = 1e30;
     for (int s = 1; s <= 8; ++s) {
-      if (kblocks / s < 8 && s > 1) break;
-      const double waves = (double)((tiles * s + sms - 1) / sms) / s;
+      if (s > 1 && (kblocks / s < 8 || tiles >= 6LL * sms)) break;
+      const double waves = (double)((tiles * s + sms - 1) / sms) / s * (1.0 + 0.02 * (s - 1));
       if (waves < best * 0.97) { best = waves; k_splits = s; }
     }
+    if (k_splits == 1) epi = EPI_F32_ACC;  // one tile per output block: same sum, no atomic traffic
   }
   uint64_t adims[2], astr[1], bdims[2], bstr[1];
   uint32_t abox[2], bbox[2];

@@ -774,13 +774,18 @@ void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void*
   if (epi == EPI_F32_ATOMIC) {
     const int clusters = sm_count() / 2;
     const long long tiles = (long long)((M + T_BM - 1) / T_BM) * ((N + T_BN - 1) / T_BN);
+    // Split K only where whole waves of tiles leave SM pairs idle (few tiles per pair); every extra
+    // split adds a pass of atomic traffic over C, charged here as 2 % of a wave (with many tiles per
+    // pair, e.g. a vocabulary-sized wgrad, splitting measured 25 % slower).
     double best = 1e30;
     for (int s = 1; s <= 8; ++s) {
-      if (kblocks / s < 8 && s > 1) break;
-      const double waves = (double)((tiles * s + clusters - 1) / clusters) / s;
+      if (s > 1 && (kblocks / s < 8 || tiles >= 6LL * clusters)) break;
+      const double waves = (double)((tiles * s + clusters - 1) / clusters) / s * (1.0 + 0.02 * (s - 1));
       if (waves < best * 0.97) { best = waves; k_splits = s; }
     }
   }
+  // one tile per output block: the plain read-add-store gives the same sum without atomic traffic
+  if (epi == EPI_F32_ATOMIC && k_splits == 1) epi = EPI_F32_ACC;
   uint64_t adims[2], astr[1], bdims[2], bstr[1];
   uint32_t abox[2], bbox[2];
   if (!a_mn) { adims[0] = K; adims[1] = M; abox[0] = T_BK; abox[1] = 128; }

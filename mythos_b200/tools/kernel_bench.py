@@ -323,6 +323,13 @@ def main():
                                         (11008, 2048, 16384, "mnmn", 2), (2048, 5504, 16384, "mnmn", 2),
                                         (32000, 2048, 16384, "mnmn", 2), (8192, 8192, 8192, "kk", 0)]:
                 report(f"gemm_{lay}_{M}x{N}x{K}_epi{epi}", bench_gemm(t, M, N, K, lay, epi))
+    if k == "wgrad_set":
+        # weight-gradient shapes of the 1.3B model at 8 and 32 sequences per pass: read-add-store
+        # epilogue (one tile per output block) against split-K with atomic adds
+        for K in (16384, 65536):
+            for (M, N) in [(6144, 2048), (11008, 2048), (2048, 5504), (2048, 2048), (32000, 2048)]:
+                for epi in (2, 3):
+                    report(f"gemm_mnmn_{M}x{N}x{K}_epi{epi}", bench_gemm(t, M, N, K, "mnmn", epi))
     if k in ("fused_epilogue", "fused_swiglu_fwd", "fused_swiglu_bwd", "fused_rope", "all"):
         only = {"fused_swiglu_fwd": "fwd", "fused_swiglu_bwd": "bwd", "fused_rope": "rope"}.get(k, "")
         for name, ms_f, ms_u, flops in bench_fused_epilogues(t, args.m, 2048, 5504, 16, only, unfused=not only):
