@@ -174,6 +174,8 @@ def main() -> int:
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"],
                     help="data-parallel gradient path: fused peer-memory kernels or plain NCCL collectives")
+    ap.add_argument("--activation-checkpointing", action="store_true",
+                    help="recompute block activations in the backward pass (memory for one extra forward)")
     ap.add_argument("--no-decode", action="store_true", help="skip the tensor-parallel decode measurement")
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--decode-prompt", type=int, default=1024)
@@ -215,7 +217,8 @@ def main() -> int:
     with torch.device(device):
         model = DenseModel(cfg)
     tcfg = TrainConfig(batch_size=args.per_gpu_batch, micro_batch_size=args.micro_batch, seq_length=SEQ, lr=3e-4,
-                       warmup_steps=100, max_steps=10000, max_grad_norm=1.0, codebook_ema_interval=0)
+                       warmup_steps=100, max_steps=10000, max_grad_norm=1.0, codebook_ema_interval=0,
+                       activation_checkpointing=args.activation_checkpointing)
     trainer = Trainer(model, tcfg, device=device, dp=dp)
     stream = ZipfStream(cfg.vocab_size, args.per_gpu_batch, SEQ, s=1.1, seed=100 + rank, pin=True)
 
@@ -305,6 +308,7 @@ def main() -> int:
             "config": {"model": "dense-1.3B (24L d2048 16h ffn5504 v32000) OIL8 STE on all linear weights",
                        "global_batch": args.per_gpu_batch * world, "seq_len": SEQ,
                        "micro_batch": args.micro_batch,
+                       "activation_checkpointing": bool(args.activation_checkpointing),
                        "parallelism": f"dp{world}-zero" + (f"-{args.dp_mode}" if world > 1 else ""),
                        "l2": "working set (weights 2.6 GB + activations) far exceeds the 126 MB L2; no flush needed",
                        "optimizer": "AdamW fp32 master, global-norm clip 1.0, every step inside the timed region"},

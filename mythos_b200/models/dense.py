@@ -18,6 +18,9 @@ class DenseModel(nn.Module):
     def __init__(self, cfg: TransformerConfig):
         super().__init__()
         self.cfg = cfg
+        # recompute every block's activations in the backward pass instead of keeping them
+        # (memory of one block's activations + one [B, S, d] pair per block; one extra forward)
+        self.activation_checkpointing = False
         self.tok_embeddings = Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList([self._make_block(i) for i in range(cfg.num_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.norm_eps)
@@ -39,7 +42,10 @@ class DenseModel(nn.Module):
         x = self.tok_embeddings(ids)
         branch, stream = x, None
         for blk in self.layers:
-            branch, stream = blk(branch, stream, pos)
+            if self.activation_checkpointing and self.training:
+                branch, stream = F.checkpoint(blk, branch, stream, pos)
+            else:
+                branch, stream = blk(branch, stream, pos)
         h, _ = self.norm(branch, stream)
         return h
 

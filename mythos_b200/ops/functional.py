@@ -36,6 +36,55 @@ def _C():
     return native.require()
 
 
+# --------------------------------------------------------------------------------------- recompute
+class _CheckpointFn(torch.autograd.Function):
+    """Keeps only the inputs of ``fn``; the backward pass runs ``fn`` again to rebuild what its
+    operators need (the reference's ``CheckpointFn``, include/oil/autograd.h:23-44, and the
+    checkpoint flag of its engine, src/autograd.cpp:1226-1244, 1288-1290)."""
+
+    @staticmethod
+    def forward(ctx, fn, *args):
+        ctx.fn = fn
+        ctx.is_tensor = [torch.is_tensor(a) for a in args]
+        ctx.others = [None if torch.is_tensor(a) else a for a in args]
+        ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
+        with torch.no_grad():
+            out = fn(*args)
+        ctx.single = torch.is_tensor(out)
+        return out if ctx.single else tuple(out)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        saved = list(ctx.saved_tensors)
+        args, leaves = [], []
+        for is_t, other in zip(ctx.is_tensor, ctx.others):
+            if is_t:
+                t = saved.pop(0).detach()
+                if t.is_floating_point():
+                    t.requires_grad_()
+                leaves.append(t)
+                args.append(t)
+            else:
+                leaves.append(None)
+                args.append(other)
+        with torch.enable_grad():
+            out = ctx.fn(*args)
+        outs = [out] if torch.is_tensor(out) else list(out)
+        pairs = [(o, g) for o, g in zip(outs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
+        if pairs:
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        return (None,) + tuple(None if t is None else t.grad for t in leaves)
+
+
+def checkpoint(fn, *args):
+    """``fn(*args)`` with activation recomputation: intermediate activations are dropped after the
+    forward pass and rebuilt in the backward pass (one extra forward of ``fn``). Parameters reached
+    through ``fn`` receive their gradients as usual. Without autograd it is a plain call."""
+    if not torch.is_grad_enabled() or not any(torch.is_tensor(a) and a.requires_grad for a in args):
+        return fn(*args)
+    return _CheckpointFn.apply(fn, *args)
+
+
 # --------------------------------------------------------------------------------------- GEMM
 def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, epi: int = EPI_BF16, alpha: float = 1.0):
     """``out[M,N] (+)= alpha * A @ B^T`` on tcgen05. ``a_mn``/``b_mn``: the operand is stored

@@ -49,6 +49,7 @@ class TrainConfig:
     warmup_steps: int = 100
     schedule: str = "warmup_cosine"
     max_grad_norm: float = 1.0     # 0 disables clipping
+    activation_checkpointing: bool = False   # recompute block activations in backward (less memory, +1 forward)
     codebook_ema_interval: int = 100
     codebook_ema_decay: float = 0.999
     log_interval: int = 10
@@ -85,6 +86,8 @@ class Trainer:
         else:
             self.store = ParamStore(model, self.device, world)
         self.model = model
+        if cfg.activation_checkpointing and hasattr(model, "activation_checkpointing"):
+            model.activation_checkpointing = True
         n = self.store.shard
         self.m = torch.zeros(n, device=self.device, dtype=torch.float32)
         self.v = torch.zeros(n, device=self.device, dtype=torch.float32)

@@ -64,3 +64,35 @@ def test_short_training_run_reduces_loss():
     assert native.launch_count() > before
     assert losses[-1] < losses[0] - 0.3, losses
     assert all(l == l for l in losses)
+
+
+def test_activation_checkpointing_same_update_less_memory():
+    """Recomputing block activations in the backward pass gives the same loss and gradients on the
+    native path and a lower peak of allocated memory."""
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.train.param_store import ParamStore
+
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=6, num_heads=2, head_dim=128,
+                            ffn_hidden_size=512, max_seq_len=512, oil_block_size=64, weight_format="oil8")
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = DenseModel(cfg).train()
+    store = ParamStore(model, "cuda")
+    store.refresh_compute()
+    ids = torch.randint(0, cfg.vocab_size, (8, 512), dtype=torch.int32, device="cuda")
+    tg = torch.randint(0, cfg.vocab_size, (8, 512), dtype=torch.int32, device="cuda")
+    res = []
+    for ckpt in (False, True):
+        model.activation_checkpointing = ckpt
+        store.zero_grad()
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        loss = model(ids, tg)
+        loss.backward()
+        torch.cuda.synchronize()
+        res.append((loss.item(), store.grad.clone(), torch.cuda.max_memory_allocated() - base))
+        del loss
+    assert res[0][0] == res[1][0]
+    assert torch.allclose(res[0][1], res[1][1], rtol=1e-3, atol=1e-5)
+    assert res[1][2] < 0.7 * res[0][2], (res[0][2], res[1][2])

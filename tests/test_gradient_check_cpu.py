@@ -68,3 +68,25 @@ def test_ste_passes_gradients_straight_through():
     for name, p in model.named_parameters():
         if name.endswith("proj.weight"):
             assert torch.isfinite(p.grad).all() and float(p.grad.abs().sum()) > 0, name
+
+
+def test_activation_checkpointing_gives_the_same_gradients():
+    """Blocks recomputed in the backward pass produce the gradients of the stored-activation run."""
+    from mythos_b200.models import DenseModel, TransformerConfig
+
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=3, num_heads=2, head_dim=16, ffn_hidden_size=64,
+                            max_seq_len=16, oil_block_size=32)
+    torch.manual_seed(0)
+    model = DenseModel(cfg).train()
+    ids = torch.randint(0, 64, (2, 16), dtype=torch.int32)
+    tg = torch.randint(0, 64, (2, 16), dtype=torch.int32)
+    grads = []
+    for ckpt in (False, True):
+        model.activation_checkpointing = ckpt
+        model.zero_grad()
+        loss = model(ids, tg)
+        loss.backward()
+        grads.append((float(loss), [p.grad.clone() for p in model.parameters()]))
+    assert grads[0][0] == grads[1][0]
+    for a, b in zip(grads[0][1], grads[1][1]):
+        assert torch.allclose(a, b, atol=1e-7)
