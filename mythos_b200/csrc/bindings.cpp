@@ -849,6 +849,123 @@ void moe_combine(const std::vector<int64_t>& ybuf_ptrs, const Tensor& topk_idx, 
                   (int)dim, (int)experts_per_rank, (int)rank, cap, cur_stream());
 }
 
+// logits: bf16 [T, ld >= E]. Fills probs [T,E] f32, topk_idx / slot [T,k] i32, w [T,k] f32; adds into counts [E] i32, psum [E] f32.
+void moe_route(const Tensor& logits, int64_t E, Tensor& probs, Tensor& topk_idx, Tensor& slot, Tensor& w, Tensor& counts,
+               Tensor& psum) {
+  chk(logits, BF16, "logits");
+  chk_c(probs, F32, "probs");
+  chk_c(topk_idx, I32, "topk_idx");
+  chk_c(slot, I32, "slot");
+  chk_c(w, F32, "w");
+  chk_c(counts, I32, "counts");
+  chk_c(psum, F32, "psum");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.size(1) >= E, "moe_route: logits [T, >= E]");
+  const int64_t T = logits.size(0), k = topk_idx.size(1);
+  TORCH_CHECK(probs.numel() == T * E && topk_idx.size(0) == T && slot.numel() == T * k && w.numel() == T * k &&
+                  counts.numel() >= E && psum.numel() >= E, "moe_route: output shapes");
+  c10::cuda::CUDAGuard guard(logits.device());
+  mb::moe_route(logits.data_ptr(), (int)logits.stride(0), (int)T, (int)E, (int)k, probs.data_ptr<float>(),
+                topk_idx.data_ptr<int>(), slot.data_ptr<int>(), w.data_ptr<float>(), counts.data_ptr<int>(),
+                psum.data_ptr<float>(), cur_stream());
+}
+void moe_route_bwd(const Tensor& probs, const Tensor& topk_idx, const Tensor& dw, const OptTensor& coef, Tensor& dlogits) {
+  chk_c(probs, F32, "probs");
+  chk_c(topk_idx, I32, "topk_idx");
+  chk_c(dw, F32, "dw");
+  chk_c(dlogits, BF16, "dlogits");
+  const int64_t T = probs.size(0), E = probs.size(1), k = topk_idx.size(1);
+  TORCH_CHECK(dw.numel() == T * k && dlogits.size(0) == T && dlogits.size(1) >= E, "moe_route_bwd: shapes");
+  if (coef.has_value()) chk_c(*coef, F32, "coef");
+  c10::cuda::CUDAGuard guard(probs.device());
+  mb::moe_route_bwd(probs.data_ptr<float>(), topk_idx.data_ptr<int>(), dw.data_ptr<float>(),
+                    coef.has_value() ? coef->data_ptr<float>() : nullptr, (int)T, (int)E, (int)k, dlogits.data_ptr(),
+                    (int)dlogits.size(1), cur_stream());
+}
+void moe_publish_counts(const Tensor& counts, const std::vector<int64_t>& table_ptrs, int64_t E, int64_t rank) {
+  chk_c(counts, I32, "counts");
+  c10::cuda::CUDAGuard guard(counts.device());
+  mb::moe_publish_counts(counts.data_ptr<int>(), to_peers(table_ptrs), (int)table_ptrs.size(), (int)E, (int)rank, cur_stream());
+}
+void moe_offsets(const Tensor& all_counts, int64_t world, int64_t E, int64_t rank, int64_t cap, Tensor& seg_start,
+                 Tensor& seg_rows, Tensor& send_base, const OptTensor& status) {
+  chk_c(all_counts, I32, "all_counts");
+  chk_c(seg_start, I32, "seg_start");
+  chk_c(seg_rows, I32, "seg_rows");
+  chk_c(send_base, I32, "send_base");
+  TORCH_CHECK(all_counts.numel() >= world * E && send_base.numel() >= E && seg_start.numel() >= E / world &&
+                  seg_rows.numel() >= E / world, "moe_offsets: shapes");
+  c10::cuda::CUDAGuard guard(all_counts.device());
+  mb::moe_offsets(all_counts.data_ptr<int>(), (int)world, (int)E, (int)rank, (int)cap, seg_start.data_ptr<int>(),
+                  seg_rows.data_ptr<int>(), send_base.data_ptr<int>(), status_ptr(status), cur_stream());
+}
+void moe_zero_pad(const Tensor& seg_start, const Tensor& seg_rows, int64_t n_seg, OptTensor a, OptTensor b) {
+  chk_c(seg_start, I32, "seg_start");
+  chk_c(seg_rows, I32, "seg_rows");
+  TORCH_CHECK(a.has_value(), "moe_zero_pad: need a buffer");
+  chk_c(*a, BF16, "a");
+  if (b.has_value()) {
+    chk_c(*b, BF16, "b");
+    TORCH_CHECK(b->sizes() == a->sizes(), "moe_zero_pad: buffers must have one shape");
+  }
+  TORCH_CHECK(a->dim() == 2, "moe_zero_pad: [rows, dim] buffers");
+  c10::cuda::CUDAGuard guard(a->device());
+  mb::moe_zero_pad(seg_start.data_ptr<int>(), seg_rows.data_ptr<int>(), (int)n_seg, (int)a->size(1), mptr(a), mptr(b),
+                   (int)a->size(0), cur_stream());
+}
+
+// Grouped GEMM over row segments: out[rows of e] = a[rows of e] @ weights[e]^T (weights[e]: [N, K], or [K, N] with b_mn).
+void gemm_grouped_rows(const Tensor& a, const std::vector<Tensor>& weights, bool b_mn, OptTensor out, const Tensor& seg_start,
+                       const Tensor& seg_rows, int64_t fuse, const OptTensor& aux, OptTensor out2, const OptTensor& status) {
+  chk(a, BF16, "a");
+  chk_c(seg_start, I32, "seg_start");
+  chk_c(seg_rows, I32, "seg_rows");
+  TORCH_CHECK(a.dim() == 2 && a.stride(1) == 1 && !weights.empty(), "gemm_grouped_rows: a [rows, K] and weights");
+  const int64_t K = a.size(1);
+  const int64_t N = b_mn ? weights[0].size(1) : weights[0].size(0);
+  std::vector<const void*> bp;
+  for (const auto& wt : weights) {
+    chk(wt, BF16, "weight");
+    TORCH_CHECK(wt.dim() == 2 && wt.stride(1) == 1 && wt.stride(0) == weights[0].stride(0) && wt.sizes() == weights[0].sizes(),
+                "gemm_grouped_rows: weights must share one shape");
+    TORCH_CHECK((b_mn ? wt.size(0) : wt.size(1)) == K, "gemm_grouped_rows: contraction sizes differ");
+    bp.push_back(wt.data_ptr());
+  }
+  TORCH_CHECK((int64_t)bp.size() <= seg_start.numel() && (int64_t)bp.size() <= seg_rows.numel(), "gemm_grouped_rows: segments");
+  if (out.has_value()) {
+    chk(*out, BF16, "out");
+    TORCH_CHECK(out->dim() == 2 && out->stride(1) == 1 && out->size(0) == a.size(0), "gemm_grouped_rows: out rows");
+  }
+  if (aux.has_value()) chk(*aux, BF16, "aux");
+  if (out2.has_value()) chk(*out2, BF16, "out2");
+  c10::cuda::CUDAGuard guard(a.device());
+  mb::gemm_grouped_rows(a.data_ptr(), a.stride(0), (int)a.size(0), bp.data(), weights[0].stride(0), b_mn, mptr(out),
+                        out.has_value() ? out->stride(0) : (fuse == mb::FUSE_SWIGLU_FWD ? N : 0), (int)N, (int)K,
+                        seg_start.data_ptr<int>(), seg_rows.data_ptr<int>(), (int)bp.size(), (int)fuse, cptr(aux),
+                        aux.has_value() ? aux->stride(0) : 0, mptr(out2), out2.has_value() ? out2->stride(0) : 0,
+                        status_ptr(status), cur_stream());
+}
+// Grouped weight gradients: grads[e] [M, N] (fp32) += a[rows of e, 0:M]^T @ b[rows of e, 0:N].
+void gemm_grouped_k(const Tensor& a, const Tensor& b, const std::vector<Tensor>& grads, const Tensor& seg_start,
+                    const Tensor& seg_rows, const OptTensor& status) {
+  chk(a, BF16, "a");
+  chk(b, BF16, "b");
+  chk_c(seg_start, I32, "seg_start");
+  chk_c(seg_rows, I32, "seg_rows");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && a.size(0) == b.size(0) && !grads.empty(),
+              "gemm_grouped_k: a [rows, M], b [rows, N]");
+  std::vector<float*> cp;
+  for (const auto& g : grads) {
+    chk(g, F32, "grad");
+    TORCH_CHECK(g.dim() == 2 && g.stride(1) == 1 && g.size(0) == a.size(1) && g.size(1) == b.size(1) &&
+                    g.stride(0) == grads[0].stride(0), "gemm_grouped_k: grads must be [M, N] with one stride");
+    cp.push_back(g.data_ptr<float>());
+  }
+  c10::cuda::CUDAGuard guard(a.device());
+  mb::gemm_grouped_k(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), cp.data(), grads[0].stride(0), (int)a.size(1),
+                     (int)b.size(1), (int)a.size(0), seg_start.data_ptr<int>(), seg_rows.data_ptr<int>(), (int)cp.size(),
+                     status_ptr(status), cur_stream());
+}
+
 int64_t launch_count() { return mb::launch_count(); }
 
 }  // namespace
@@ -921,6 +1038,13 @@ PYBIND11_MODULE(_C, m) {
   m.def("symm_barrier", &symm_barrier);
   m.def("zero_reduce_scatter", &zero_reduce_scatter);
   m.def("zero_adamw_ste_allgather", &zero_adamw_ste_allgather);
+  m.def("moe_route", &moe_route);
+  m.def("moe_route_bwd", &moe_route_bwd);
+  m.def("moe_publish_counts", &moe_publish_counts);
+  m.def("moe_offsets", &moe_offsets);
+  m.def("moe_zero_pad", &moe_zero_pad);
+  m.def("gemm_grouped_rows", &gemm_grouped_rows);
+  m.def("gemm_grouped_k", &gemm_grouped_k);
   m.def("set_gemm_coalesced_epilogue", [](int64_t on) { mb::set_gemm_coalesced_epilogue((int)on); });
   m.def("set_gemm_mode", [](int64_t mode) { mb::set_gemm_mode((int)mode); });
   m.def("get_gemm_mode", []() { return (int64_t)mb::get_gemm_mode(); });

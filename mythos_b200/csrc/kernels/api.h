@@ -54,6 +54,21 @@ void gemm_swiglu_bwd(const void* dy, long long ld_dy, const void* w_down, long l
 // each) in columns [0, rope_cols); cos_sin is the [max_pos, 64, 2] fp32 table.
 void gemm_rope(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int M, int N, int K,
                const int* pos, const float* cos_sin, int max_pos, int rope_cols, int* status, cudaStream_t stream);
+// Grouped (ragged) GEMMs on the paired kernel: one launch over up to 16 segments of a row-indexed buffer
+// (the tokens routed to each local expert). seg_start / seg_rows are DEVICE arrays of n_seg ints; starts
+// are multiples of 256 and the rows from a segment's end up to the next multiple of 256 must hold zeros.
+//   rows: C[rows of e, 0:N] = A[rows of e, 0:K] * B[e]^T with B[e] = [N, K] (or [K, N] with b_mn). `fuse`:
+//         FUSE_NONE, FUSE_SWIGLU_FWD (N = 2F; C = pre-activations or null, out2 = h[rows, F]) or
+//         FUSE_SWIGLU_BWD (B[e] = [K, F] read MN-major, aux = pre-activations, C = d pre-activations [rows, 2F]).
+//   k:    C[e][M, N] += A[rows of e, 0:M]^T * B[rows of e, 0:N] in fp32 (weight gradients).
+// B / C are HOST arrays of device pointers.
+void gemm_grouped_rows(const void* A, long long lda, int total_rows, const void* const* B, long long ldb, bool b_mn,
+                       void* C, long long ldc, int N, int K, const int* seg_start, const int* seg_rows, int n_seg,
+                       int fuse, const void* aux, long long ld_aux, void* out2, long long ld_out2, int* status,
+                       cudaStream_t stream);
+void gemm_grouped_k(const void* A, long long lda, const void* B, long long ldb, float* const* C, long long ldc, int M,
+                    int N, int total_rows, const int* seg_start, const int* seg_rows, int n_seg, int* status,
+                    cudaStream_t stream);
 double gemm_2cta_waves(int M, int N, int sms);
 // 1 (default): the paired kernel's plain epilogues store through a shared-memory transpose; 0: from registers.
 void set_gemm_coalesced_epilogue(int on);
@@ -277,6 +292,18 @@ void sample_tokens(const void* logits, long long ld, int rows, int vocab, const 
 void i2s_gemv(const void* x, const DequantWeights& w, void* y, cudaStream_t stream);
 
 // ---- mixture of experts: routing, dispatch / combine exchange (moe.cu)
+// Device-side router (no host round trip): softmax + top-k + slots + combine weights + load statistics;
+// its backward; the exchange of per-expert counts between ranks; segment offsets of the receive buffer
+// (starts aligned to 256 rows for the grouped GEMMs) and zeroing of the alignment padding.
+void moe_route(const void* logits, int ld, int T, int E, int k, float* probs, int* topk_idx, int* slot, float* w,
+               int* counts, float* psum, cudaStream_t stream);
+void moe_route_bwd(const float* probs, const int* topk_idx, const float* dw, const float* coef, int T, int E, int k,
+                   void* dlogits, int ld, cudaStream_t stream);
+void moe_publish_counts(const int* counts, const PeerPtrs& tables, int world, int E, int rank, cudaStream_t stream);
+void moe_offsets(const int* all_counts, int world, int E, int rank, int cap, int* seg_start, int* seg_rows,
+                 int* send_base, int* status, cudaStream_t stream);
+void moe_zero_pad(const int* seg_start, const int* seg_rows, int n_seg, int dim, void* a, void* b, int cap,
+                  cudaStream_t stream);
 void moe_topk(const float* probs, int T, int E, int k, int* topk_idx, int* slot, int* counts, cudaStream_t stream);
 // Row (t, j) goes to recv[owner(e)] at row rank*cap + send_off[e] + slot[t, j] (optionally scaled).
 void moe_dispatch(const void* x, const int* topk_idx, const int* slot, const int* send_off, const float* row_scale,

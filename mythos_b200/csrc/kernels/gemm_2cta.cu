@@ -33,7 +33,8 @@ struct Cfg2 {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = T_STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * T_STAGES + 4;
-  static constexpr int EPI_STAGE_OFFSET = BAR_OFFSET + 256;       // [up to 8 epilogue warps][32 rows][128 B]
+  static constexpr int SEG_OFFSET = BAR_OFFSET + 256;             // grouped GEMM: segment starts / rows (2 x 16 ints)
+  static constexpr int EPI_STAGE_OFFSET = BAR_OFFSET + 512;       // [up to 8 epilogue warps][32 rows][128 B]
   static constexpr int SMEM_BYTES = EPI_STAGE_OFFSET + 8 * 4096 + 1024;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
   static_assert(NUM_BARS * 8 + 16 <= 256, "barrier region");
@@ -81,6 +82,33 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 
 struct Work2 {
   int m0, n0, kb0, kb1;
+  int e = 0;      // grouped GEMM: segment (expert) of this tile
+  int kofs = 0;   // grouped GEMM over K: first row of the segment (added to every K coordinate)
+};
+
+// Grouped (ragged) GEMM. One launch covers several segments of one row-indexed buffer, e.g. the
+// tokens routed to each local expert; segment starts and row counts live in device memory (they come
+// from the router kernel, the host never sees them). Segment starts are multiples of 256 rows and the
+// rows between a segment's end and the next multiple of 256 hold zeros.
+//   GROUP_ROWS  C[rows of segment e, :] = A[rows of segment e, :] * B_e^T   (ragged M; B per segment)
+//   GROUP_K     C_e (+)= A[rows of e, :]^T * B[rows of e, :]                (ragged K; C per segment)
+constexpr int MAX_GROUPS = 16;
+enum : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_K = 2 };
+template <int G>
+struct GroupArgsT {};
+template <>
+struct GroupArgsT<GROUP_ROWS> {
+  const int* seg_start;
+  const int* seg_rows;
+  int n_seg;
+  CUtensorMap bmaps[MAX_GROUPS];
+};
+template <>
+struct GroupArgsT<GROUP_K> {
+  const int* seg_start;
+  const int* seg_rows;
+  int n_seg;
+  void* cptrs[MAX_GROUPS];
 };
 __device__ __forceinline__ Work2 decode2(int w, int tiles_m, int tiles_n, int k_splits, int kblocks) {
   const int tiles = tiles_m * tiles_n;
@@ -140,12 +168,48 @@ template <int FUSE>
 __host__ __device__ constexpr int cta_threads() { return 64 + 32 * epi_warps<FUSE>(); }
 static_assert(cta_threads<FUSE_NONE>() == T_THREADS, "plain kernel: producer + MMA + four epilogue warps");
 
-template <bool A_MN, bool B_MN, int FUSE>
+// Tile list of a grouped launch: segment-major; s_seg = [starts | rows] in shared memory.
+template <int GROUP>
+__device__ __forceinline__ int group_total(const int* s_seg, int n_seg, int tiles_m, int tiles_n) {
+  int total = 0;
+  for (int e = 0; e < n_seg; ++e) {
+    const int rows = s_seg[MAX_GROUPS + e];
+    if (rows > 0) total += (GROUP == GROUP_ROWS ? (rows + T_BM - 1) / T_BM : tiles_m) * tiles_n;
+  }
+  return total;
+}
+template <int GROUP>
+__device__ __forceinline__ Work2 group_decode(int w, const int* s_seg, int n_seg, int tiles_m, int tiles_n, int kblocks) {
+  Work2 wi{0, 0, 0, 0, 0, 0};
+  for (int e = 0; e < n_seg; ++e) {
+    const int rows = s_seg[MAX_GROUPS + e];
+    if (rows <= 0) continue;
+    const int tm_e = GROUP == GROUP_ROWS ? (rows + T_BM - 1) / T_BM : tiles_m;
+    const int n_e = tm_e * tiles_n;
+    if (w < n_e) {
+      wi = decode2(w, tm_e, tiles_n, 1, kblocks);
+      wi.e = e;
+      if (GROUP == GROUP_ROWS) {
+        wi.m0 += s_seg[e];
+      } else {
+        wi.kofs = s_seg[e];
+        wi.kb0 = 0;
+        wi.kb1 = (rows + T_BK - 1) / T_BK;
+      }
+      return wi;
+    }
+    w -= n_e;
+  }
+  return wi;
+}
+
+template <bool A_MN, bool B_MN, int FUSE, int GROUP = GROUP_NONE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(cta_threads<FUSE>(), 1)
 gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Cout, int M, int N, int K, long long ldc, int tiles_m, int tiles_n, int k_splits,
                  int epi, int vec_ok, float alpha, int* status, PeerPtrs scatter, int n_scatter,
-                 long long rows_per_rank, long long slot_off, EpiFuse fz) {
+                 long long rows_per_rank, long long slot_off, EpiFuse fz,
+                 const __grid_constant__ GroupArgsT<GROUP> ga) {
   using Cfg = Cfg2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -160,8 +224,23 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t cta = cluster_ctarank();
   const bool leader = cta == 0;
   const int kblocks = (K + T_BK - 1) / T_BK;
-  const int total = tiles_m * tiles_n * k_splits;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  int* s_seg = reinterpret_cast<int*>(smem + Cfg::SEG_OFFSET);
+  int n_seg = 0;
+  if constexpr (GROUP != GROUP_NONE) {
+    n_seg = ga.n_seg;
+    if (threadIdx.x < MAX_GROUPS) {
+      const bool in = (int)threadIdx.x < n_seg;
+      s_seg[threadIdx.x] = in ? ga.seg_start[threadIdx.x] : 0;
+      s_seg[MAX_GROUPS + threadIdx.x] = in ? ga.seg_rows[threadIdx.x] : 0;
+    }
+    __syncthreads();
+  }
+  const int total = GROUP != GROUP_NONE ? group_total<GROUP>(s_seg, n_seg, tiles_m, tiles_n) : tiles_m * tiles_n * k_splits;
+  auto get_work = [&](int w) -> Work2 {
+    if constexpr (GROUP != GROUP_NONE) return group_decode<GROUP>(w, s_seg, n_seg, tiles_m, tiles_n, kblocks);
+    else return decode2(w, tiles_m, tiles_n, k_splits, kblocks);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T_STAGES; ++s) {
@@ -197,26 +276,29 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int w = cluster_id; w < total && ok; w += n_clusters) {
-        const Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
+        const Work2 wi = get_work(w);
         const int my_m = wi.m0 + (int)cta * 128;
         const int my_n = (FUSE == FUSE_SWIGLU_FWD) ? (wi.n0 >> 1) + (int)cta * fz.F : wi.n0 + (int)cta * 128;
+        const CUtensorMap* map_b = &tma_b;
+        if constexpr (GROUP == GROUP_ROWS) map_b = &ga.bmaps[wi.e];
         for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, status, 51)) { ok = false; break; }
           const uint32_t lbar = map_to_cta(smem_u32(&full[stage]), 0);
           if (leader) mbar_arrive_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
+          const int kc = wi.kofs + kb * T_BK;
           if (!A_MN) {
-            tma_load_2d_pair(sa, &tma_a, lbar, kb * T_BK, my_m);
+            tma_load_2d_pair(sa, &tma_a, lbar, kc, my_m);
           } else {
-            tma_load_2d_pair(sa, &tma_a, lbar, my_m, kb * T_BK);
-            tma_load_2d_pair(sa + 8192, &tma_a, lbar, my_m + 64, kb * T_BK);
+            tma_load_2d_pair(sa, &tma_a, lbar, my_m, kc);
+            tma_load_2d_pair(sa + 8192, &tma_a, lbar, my_m + 64, kc);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sb, &tma_b, lbar, kb * T_BK, my_n);
+            tma_load_2d_pair(sb, map_b, lbar, kc, my_n);
           } else {
-            tma_load_2d_pair(sb, &tma_b, lbar, my_n, kb * T_BK);
-            tma_load_2d_pair(sb + 8192, &tma_b, lbar, my_n + 64, kb * T_BK);
+            tma_load_2d_pair(sb, map_b, lbar, my_n, kc);
+            tma_load_2d_pair(sb + 8192, map_b, lbar, my_n + 64, kc);
           }
           if (++stage == T_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -230,7 +312,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int w = cluster_id; w < total && ok; w += n_clusters) {
-        const Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
+        const Work2 wi = get_work(w);
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, status, 52)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * T_BN;
@@ -266,7 +348,9 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int w = cluster_id; w < total; w += n_clusters) {
-      const Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
+      const Work2 wi = get_work(w);
+      void* Cw = Cout;                                   // output of this tile (per segment when K is ragged)
+      if constexpr (GROUP == GROUP_K) Cw = ga.cptrs[wi.e];
       bool ok = mbar_wait(&tfull[acc], acc_phase, abort_flag, status, 54);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -282,7 +366,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int row0 = wi.m0 + (int)cta * 128 + q * 32;
         const int crow = lane >> 2, cpiece = lane & 3;
         const int colg0 = wi.n0 >> 1;
-        __nv_bfloat16* gu_base = reinterpret_cast<__nv_bfloat16*>(Cout);
+        __nv_bfloat16* gu_base = reinterpret_cast<__nv_bfloat16*>(Cw);
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t rg[32], ru[32];
@@ -363,7 +447,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           // the demand loads above then pay an L2 hit instead of a loaded-DRAM round trip.
           const int w2 = w + n_clusters;
           if (w2 < total) {
-            const Work2 nx = decode2(w2, tiles_m, tiles_n, k_splits, kblocks);
+            const Work2 nx = get_work(w2);
             const int tid = (warp - 2) * 32 + lane;             // 256 threads, 1024 lines of 128 bytes
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -425,7 +509,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             const int rr = it * 8 + crow;
             if (row0 + rr < M) {
               const uint32_t off = rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4);
-              __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)(row0 + rr) * ldc + col;
+              __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cw) + (long long)(row0 + rr) * ldc + col;
               *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(sA + off);
               *reinterpret_cast<uint4*>(p + fz.F) = *reinterpret_cast<const uint4*>(sB + off);
             }
@@ -433,7 +517,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           __syncwarp();
         }
       } else if (FUSE == FUSE_ROPE) {
-        __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc;
+        __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(Cw) + (long long)row * ldc;
         int p = (row < M) ? fz.pos[row] : 0;
         p = min(max(p, 0), fz.max_pos - 1);
         const float4* cs_row = reinterpret_cast<const float4*>(fz.cs + (long long)p * 64);
@@ -536,7 +620,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int it = 0; it < 4; ++it) {
               const int rr = it * 8 + crow;
               if (row0 + rr < M)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)(row0 + rr) * ldc + col +
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(Cw) + (long long)(row0 + rr) * ldc + col +
                                           cpiece * 8) =
                     *reinterpret_cast<const uint4*>(sbuf + rr * 64 + ((cpiece ^ ((rr >> 1) & 3)) << 4));
             }
@@ -554,7 +638,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               const int rr = it * 4 + crow;
               if (row0 + rr < M) {
                 float4 v = *reinterpret_cast<const float4*>(stage + rr * 128 + ((cpiece ^ (rr & 7)) << 4));
-                float4* gp = reinterpret_cast<float4*>(reinterpret_cast<float*>(Cout) + (long long)(row0 + rr) * ldc + col +
+                float4* gp = reinterpret_cast<float4*>(reinterpret_cast<float*>(Cw) + (long long)(row0 + rr) * ldc + col +
                                                        cpiece * 4);
                 if (epi == EPI_F32_ACC) {
                   const float4 o = *gp;
@@ -570,7 +654,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (row < M && col < N) {
           const int ncols = min(32, N - col);
           if (epi == EPI_BF16) {
-            __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc + col;
+            __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(Cw) + (long long)row * ldc + col;
             if (ncols == 32 && vec_ok) {
               uint4* p4 = reinterpret_cast<uint4*>(p);
 #pragma unroll
@@ -586,7 +670,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < ncols; ++j) p[j] = __float2bfloat16(alpha * __uint_as_float(r[j]));
             }
           } else {
-            float* p = reinterpret_cast<float*>(Cout) + (long long)row * ldc + col;
+            float* p = reinterpret_cast<float*>(Cw) + (long long)row * ldc + col;
             if (ncols == 32 && vec_ok) {
               float4* p4 = reinterpret_cast<float4*>(p);
 #pragma unroll
@@ -636,11 +720,12 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  : "memory");
 }
 
-template <bool A_MN, bool B_MN, int FUSE = FUSE_NONE>
+template <bool A_MN, bool B_MN, int FUSE = FUSE_NONE, int GROUP = GROUP_NONE>
 void launch2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, long long ldc, int k_splits,
              int epi, int vec_ok, float alpha, int* status, cudaStream_t stream, const PeerPtrs& scatter,
-             int n_scatter, long long rows_per_rank, long long slot_off, const EpiFuse& fz = EpiFuse{}) {
-  auto kern = gemm_2cta_kernel<A_MN, B_MN, FUSE>;
+             int n_scatter, long long rows_per_rank, long long slot_off, const EpiFuse& fz = EpiFuse{},
+             const GroupArgsT<GROUP>& ga = GroupArgsT<GROUP>{}) {
+  auto kern = gemm_2cta_kernel<A_MN, B_MN, FUSE, GROUP>;
   static bool configured = false;
   if (!configured) {
     MB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::SMEM_BYTES));
@@ -649,10 +734,10 @@ void launch2(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N
   const int tiles_m = (M + T_BM - 1) / T_BM, tiles_n = (N + T_BN - 1) / T_BN;
   const int total = tiles_m * tiles_n * k_splits;
   int clusters = sm_count() / 2;
-  if (total < clusters) clusters = total;
+  if (GROUP == GROUP_NONE && total < clusters) clusters = total;   // grouped: the tile count is known on the device only
   kern<<<clusters * 2, cta_threads<FUSE>(), Cfg2::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, tiles_m, tiles_n, k_splits, epi,
                                                               vec_ok, alpha, status, scatter, n_scatter, rows_per_rank,
-                                                              slot_off, fz);
+                                                              slot_off, fz, ga);
   count_launch();
   check_launch();
 }
@@ -747,6 +832,89 @@ void gemm_rope(const void* x, long long ldx, const void* w, long long ldw, void*
   fz.rope_cols = rope_cols;
   launch2<false, false, FUSE_ROPE>(ta, tb, out, M, N, K, ldo, 1, EPI_BF16, 1, 1.f, status, stream, PeerPtrs{}, 0, 0, 0,
                                    fz);
+}
+
+// ---------------------------------------------------------------------------- grouped launches
+void gemm_grouped_rows(const void* A, long long lda, int total_rows, const void* const* B, long long ldb, bool b_mn,
+                       void* C, long long ldc, int N, int K, const int* seg_start, const int* seg_rows, int n_seg,
+                       int fuse, const void* aux, long long ld_aux, void* out2, long long ld_out2, int* status,
+                       cudaStream_t stream) {
+  MB_REQUIRE(n_seg >= 1 && n_seg <= MAX_GROUPS, "gemm_grouped_rows: 1..16 segments per launch");
+  MB_REQUIRE(total_rows > 0 && N > 0 && K > 0, "gemm_grouped_rows: empty problem");
+  MB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0, "gemm_grouped_rows: row strides must be multiples of 8 elements");
+  MB_REQUIRE(fuse == FUSE_NONE || fuse == FUSE_SWIGLU_FWD || fuse == FUSE_SWIGLU_BWD, "gemm_grouped_rows: bad fusion id");
+  MB_REQUIRE(!(fuse == FUSE_SWIGLU_FWD && b_mn) && !(fuse == FUSE_SWIGLU_BWD && !b_mn),
+             "gemm_grouped_rows: SwiGLU forward takes K-major weights, SwiGLU backward MN-major weights");
+  uint64_t adims[2], astr[1] = {(uint64_t)lda * 2};
+  uint32_t abox[2];
+  kmajor_map_dims(adims, abox, total_rows, K);
+  const CUtensorMap ta = make_tensor_map(A, TmaDType::BF16, 2, adims, astr, abox, true);
+  GroupArgsT<GROUP_ROWS> ga{};
+  ga.seg_start = seg_start;
+  ga.seg_rows = seg_rows;
+  ga.n_seg = n_seg;
+  EpiFuse fz{};
+  // N is the number of weight rows of one segment: 2F for the fused gate/up projection
+  const int F = fuse == FUSE_SWIGLU_FWD ? N / 2 : N;
+  if (fuse != FUSE_NONE) {
+    MB_REQUIRE(F % 128 == 0, "gemm_grouped_rows: the ffn width must be a multiple of 128");
+    fz.F = F;
+    fz.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
+    fz.ld_aux = ld_aux;
+    fz.out2 = reinterpret_cast<__nv_bfloat16*>(out2);
+    fz.ld_out2 = ld_out2;
+    MB_REQUIRE(fuse != FUSE_SWIGLU_FWD || (out2 != nullptr && ld_out2 % 8 == 0), "gemm_grouped_rows: h output");
+    MB_REQUIRE(fuse != FUSE_SWIGLU_BWD || (aux != nullptr && ld_aux % 8 == 0), "gemm_grouped_rows: pre-activations");
+  }
+  for (int e = 0; e < n_seg; ++e) {
+    uint64_t bdims[2], bstr[1] = {(uint64_t)ldb * 2};
+    uint32_t bbox[2];
+    if (!b_mn) { kmajor_map_dims(bdims, bbox, N, K); }
+    else { bdims[0] = (uint64_t)N; bdims[1] = (uint64_t)K; bbox[0] = 64; bbox[1] = T_BK; }
+    ga.bmaps[e] = make_tensor_map(B[e], TmaDType::BF16, 2, bdims, bstr, bbox, true);
+  }
+  const int vec_ok = (reinterpret_cast<uintptr_t>(C) & 15) == 0 ? 2 : 0;
+  MB_REQUIRE(vec_ok || fuse == FUSE_NONE, "gemm_grouped_rows: fused outputs must be 16-byte aligned");
+  // the kernel's N: output columns of the accumulator tiles (2F for the fused forward, whose tiles hold
+  // 128 gate + 128 up columns; F for the fused backward, whose output buffer is [rows, 2F])
+  const PeerPtrs none{};
+  if (fuse == FUSE_SWIGLU_FWD)
+    launch2<false, false, FUSE_SWIGLU_FWD, GROUP_ROWS>(ta, ga.bmaps[0], C, total_rows, N, K, ldc, 1, EPI_BF16, 1, 1.f,
+                                                       status, stream, none, 0, 0, 0, fz, ga);
+  else if (fuse == FUSE_SWIGLU_BWD)
+    launch2<false, true, FUSE_SWIGLU_BWD, GROUP_ROWS>(ta, ga.bmaps[0], C, total_rows, N, K, ldc, 1, EPI_BF16, 1, 1.f,
+                                                      status, stream, none, 0, 0, 0, fz, ga);
+  else if (!b_mn)
+    launch2<false, false, FUSE_NONE, GROUP_ROWS>(ta, ga.bmaps[0], C, total_rows, N, K, ldc, 1, EPI_BF16, vec_ok, 1.f,
+                                                 status, stream, none, 0, 0, 0, fz, ga);
+  else
+    launch2<false, true, FUSE_NONE, GROUP_ROWS>(ta, ga.bmaps[0], C, total_rows, N, K, ldc, 1, EPI_BF16, vec_ok, 1.f,
+                                                status, stream, none, 0, 0, 0, fz, ga);
+}
+
+void gemm_grouped_k(const void* A, long long lda, const void* B, long long ldb, float* const* C, long long ldc, int M,
+                    int N, int total_rows, const int* seg_start, const int* seg_rows, int n_seg, int* status,
+                    cudaStream_t stream) {
+  MB_REQUIRE(n_seg >= 1 && n_seg <= MAX_GROUPS, "gemm_grouped_k: 1..16 segments per launch");
+  MB_REQUIRE(total_rows > 0 && M > 0 && N > 0, "gemm_grouped_k: empty problem");
+  MB_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldc % 4 == 0, "gemm_grouped_k: strides");
+  // both operands are row-indexed buffers read transposed: A [rows, M], B [rows, N] (MN-major)
+  uint64_t adims[2] = {(uint64_t)M, (uint64_t)total_rows}, astr[1] = {(uint64_t)lda * 2};
+  uint64_t bdims[2] = {(uint64_t)N, (uint64_t)total_rows}, bstr[1] = {(uint64_t)ldb * 2};
+  uint32_t box[2] = {64, T_BK};
+  const CUtensorMap ta = make_tensor_map(A, TmaDType::BF16, 2, adims, astr, box, true);
+  const CUtensorMap tb = make_tensor_map(B, TmaDType::BF16, 2, bdims, bstr, box, true);
+  GroupArgsT<GROUP_K> ga{};
+  ga.seg_start = seg_start;
+  ga.seg_rows = seg_rows;
+  ga.n_seg = n_seg;
+  int vec_ok = 2;
+  for (int e = 0; e < n_seg; ++e) {
+    ga.cptrs[e] = C[e];
+    if (reinterpret_cast<uintptr_t>(C[e]) & 15) vec_ok = 0;
+  }
+  launch2<true, true, FUSE_NONE, GROUP_K>(ta, tb, nullptr, M, N, total_rows, ldc, 1, EPI_F32_ACC, vec_ok, 1.f, status,
+                                          stream, PeerPtrs{}, 0, 0, 0, EpiFuse{}, ga);
 }
 
 void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void* B, long long ldb, bool b_mn, void* C,

@@ -9,12 +9,15 @@ choice, dense / soft mixtures, gating dropout, router z-loss and the load-balanc
 ``E * sum_e f_e P_e``. Router weights are the softmax probabilities over all experts, used without
 renormalising over the chosen k (src/moe_variants.cpp:46-58).
 
-CUDA path: probabilities -> ``moe_topk`` (top-k + slot per expert) -> ``moe_dispatch`` (permute and
-send rows to the expert's owner) -> per (source rank, expert) tcgen05 GEMMs -> ``moe_combine``
-(gather from the owners and weight). With expert parallelism the dispatch and combine kernels read
-and write the other ranks' buffers directly (symmetric memory); only the per-expert counts (a few
-integers) travel through a library all-gather. CPU path: the same arithmetic in plain PyTorch (the
-oracle of the kernel tests).
+CUDA path, with no host round trip inside a layer: router GEMM -> ``moe_route`` (softmax, top-k,
+slot per expert, combine weights, load statistics in one kernel) -> per-expert counts exchanged
+between ranks through symmetric memory -> ``moe_offsets`` (segment of every local expert in the
+receive buffer, computed on the device) -> ``moe_dispatch`` (permute and store rows straight into
+the owner rank's buffer) -> two grouped tcgen05 GEMM launches over all local experts (ragged M,
+SwiGLU in the first epilogue) -> ``moe_combine`` (gather from the owners and weight). The backward
+pass reuses the exchange kernels in the opposite direction and adds two ragged-K grouped GEMMs for
+the weight gradients. CPU path and the other routing families: the same arithmetic in plain
+PyTorch (the oracle of the kernel tests).
 """
 from __future__ import annotations
 
@@ -28,8 +31,15 @@ from .dense import DenseModel
 from .layers import FFN, OILLinear, TransformerBlock
 
 
+MAX_LOCAL_EXPERTS = 16      # segments one grouped GEMM launch covers
+SEG_ALIGN = 256             # segment starts are multiples of the paired GEMM's tile height
+
+
 class ExpertParallel:
-    """Expert-parallel context: symmetric receive/return buffers and a flag barrier."""
+    """Expert-parallel context: symmetric receive / return buffers, the table through which the ranks
+    exchange their per-expert token counts, and a flag barrier. ``cap_rows`` is the number of
+    (token, expert) rows one rank may send per layer call; a rank can receive ``world * cap_rows``
+    rows (every token of every rank routed to its experts), plus alignment padding per expert."""
 
     def __init__(self, group, device, cap_rows: int, dim: int):
         import torch.distributed as dist
@@ -38,28 +48,31 @@ class ExpertParallel:
 
         self.group, self.device = group, torch.device(device)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.cap = cap_rows
-        n = self.world * cap_rows * dim
+        self.cap = self.world * cap_rows + SEG_ALIGN * MAX_LOCAL_EXPERTS
+        self.dim = dim
+        n = self.cap * dim
         self.bufs = {k: symm.make_buffer(n, torch.bfloat16, device, group) for k in ("x", "y", "dy", "dx")}
+        self.count_table = symm.make_buffer(self.world * 64, torch.int32, device, group).zero_()
         self.barrier = symm.FlagBarrier(device, group)
+        self.shared = True      # one set of buffers serves every layer: saved rows are copied out
 
-    def all_counts(self, counts: torch.Tensor) -> torch.Tensor:
-        import torch.distributed as dist
-
-        out = torch.empty(self.world, counts.numel(), device=counts.device, dtype=counts.dtype)
-        dist.all_gather_into_tensor(out, counts, group=self.group)
-        return out
+    def ensure(self, rows: int, dim: int, device):
+        if rows > self.cap or dim != self.dim:
+            raise ValueError(f"expert-parallel buffers hold {self.cap} rows of {self.dim}; this call needs {rows} x {dim}")
 
 
 class _LocalExchange:
-    """Single-rank stand-in for :class:`ExpertParallel` (buffers are ordinary tensors)."""
+    """Single-rank stand-in for :class:`ExpertParallel` (buffers are ordinary tensors, one set per
+    layer, so the rows of a layer stay valid until its backward pass)."""
 
     rank, world = 0, 1
+    shared = False
 
     def __init__(self):
         self.bufs = {}
         self.cap = 0
         self.barrier = None
+        self.count_table = None
 
     def ensure(self, rows: int, dim: int, device):
         if self.cap < rows or not self.bufs or next(iter(self.bufs.values())).tensor.shape[0] < rows * dim:
@@ -68,79 +81,142 @@ class _LocalExchange:
             self.cap = rows
             self.bufs = {k: LocalBuffer(rows * dim, torch.bfloat16, device) for k in ("x", "y", "dy", "dx")}
 
-    def all_counts(self, counts):
-        return counts[None]
+
+class _RouteFn(torch.autograd.Function):
+    """Router on the device in one kernel: softmax over the expert logits, top-k, a slot in each
+    chosen expert's batch, combine weights (the probabilities of the chosen experts, not
+    renormalised: src/moe_variants.cpp:46-58) and the statistics of the load-balance loss
+    ``coef * E * sum_e f_e P_e`` (engines/trainer/moe/moe.cpp:47-153). Nothing returns to the host."""
+
+    @staticmethod
+    def forward(ctx, logits, E, k, aux_coef):
+        C = native.require()
+        T = logits.shape[0]
+        dev = logits.device
+        probs = torch.empty(T, E, device=dev, dtype=torch.float32)
+        topk_idx = torch.empty(T, k, device=dev, dtype=torch.int32)
+        slot = torch.empty(T, k, device=dev, dtype=torch.int32)
+        w = torch.empty(T, k, device=dev, dtype=torch.float32)
+        counts = torch.zeros(E, device=dev, dtype=torch.int32)
+        psum = torch.zeros(E, device=dev, dtype=torch.float32)
+        C.moe_route(logits, E, probs, topk_idx, slot, w, counts, psum)
+        f = counts.float() / float(T * k)
+        aux = (aux_coef * E) * (f * (psum / float(T))).sum()
+        ctx.save_for_backward(probs, topk_idx, f)
+        ctx.meta = (E, k, aux_coef, T, logits.shape[1])
+        ctx.mark_non_differentiable(topk_idx, slot, counts)
+        return w, aux, topk_idx, slot, counts
+
+    @staticmethod
+    def backward(ctx, dw, daux, *_):
+        C = native.require()
+        probs, topk_idx, f = ctx.saved_tensors
+        E, k, aux_coef, T, ld = ctx.meta
+        if dw is None:
+            dw = torch.zeros(T, k, device=probs.device, dtype=torch.float32)
+        coef = None
+        if daux is not None:            # d aux / d p[t, e] = coef * E * f_e / T (f is piecewise constant)
+            coef = (f * (aux_coef * E / float(T))) * daux.float()
+        dlogits = torch.empty(T, ld, device=probs.device, dtype=torch.bfloat16)
+        C.moe_route_bwd(probs, topk_idx, dw.contiguous().float(), coef, dlogits)
+        return dlogits, None, None, None
 
 
 class _MoEFn(torch.autograd.Function):
-    """dispatch -> expert FFNs -> combine, with a hand-written backward that reuses the same two
-    exchange kernels in the opposite direction."""
+    """dispatch -> grouped expert FFN -> combine without a host round trip. The receive buffer holds
+    one segment per local expert (start aligned to 256 rows, tokens of all source ranks in rank
+    order); segment starts and sizes are computed on the device from the exchanged counts and read
+    by the grouped GEMMs' tile scheduler. Expert FFN: gate/up GEMM with SwiGLU in the epilogue,
+    down GEMM; backward: down dgrad with the SwiGLU derivative in the epilogue, up dgrad, and two
+    ragged-K weight-gradient GEMMs accumulating in fp32 into the experts' gradient buffers."""
 
     @staticmethod
-    def forward(ctx, x, w, moe, topk_idx, slot, send_off, groups):
+    def forward(ctx, x, w, moe, topk_idx, slot, counts):
         C = native.require()
         ex = moe.exchange
         T, d = x.shape
+        E = moe.num_experts
         k = topk_idx.shape[1]
-        epr = moe.num_experts // ex.world
+        epr = E // ex.world
+        dev = x.device
+        st = native.status_word(dev)
+        rows = T * k + SEG_ALIGN * epr if ex.world == 1 else ex.cap
+        ex.ensure(rows, d, dev)
+        cap = ex.cap
+        if ex.world > 1:
+            C.moe_publish_counts(counts, ex.count_table.ptrs, E, ex.rank)
+            ex.barrier.sync()
+            table = ex.count_table.tensor
+        else:
+            table = counts
+        seg_start = torch.empty(epr, device=dev, dtype=torch.int32)
+        seg_rows = torch.empty(epr, device=dev, dtype=torch.int32)
+        send_base = torch.empty(E, device=dev, dtype=torch.int32)
+        C.moe_offsets(table, ex.world, E, ex.rank, cap, seg_start, seg_rows, send_base, st)
         xbuf, ybuf = ex.bufs["x"], ex.bufs["y"]
-        C.moe_dispatch(x, topk_idx, slot, send_off, None, xbuf.ptrs, epr, ex.rank, ex.cap)
+        xs = xbuf.tensor.view(-1, d)[:cap]
+        ys = ybuf.tensor.view(-1, d)[:cap]
+        C.moe_zero_pad(seg_start, seg_rows, epr, xs, None)
+        C.moe_dispatch(x, topk_idx, slot, send_base, None, xbuf.ptrs, epr, 0, 0)
         if ex.barrier is not None:
             ex.barrier.sync()
-        xs = xbuf.tensor.view(-1, d)
-        ys = ybuf.tensor.view(-1, d)
-        saved_h = []
-        for (le, a, b) in groups:
-            up, down = moe.experts_up[ex.rank * epr + le], moe.experts_down[ex.rank * epr + le]
-            u = F.gemm(xs[a:b], up.weight.compute)
-            h = torch.empty(b - a, u.shape[1] // 2, device=x.device, dtype=x.dtype)
-            C.swiglu_fused_fwd(u, h)
-            F.gemm(h, down.weight.compute, out=ys[a:b])
-            saved_h.append((u, h))
+        lo = ex.rank * epr
+        ups = [moe.experts_up[lo + i].weight.compute for i in range(epr)]
+        downs = [moe.experts_down[lo + i].weight.compute for i in range(epr)]
+        f2 = ups[0].shape[0]
+        gu = torch.empty(cap, f2, device=dev, dtype=torch.bfloat16)
+        h = torch.empty(cap, f2 // 2, device=dev, dtype=torch.bfloat16)
+        C.gemm_grouped_rows(xs, ups, False, gu, seg_start, seg_rows, 1, None, h, st)      # + SwiGLU forward
+        C.gemm_grouped_rows(h, downs, False, ys, seg_start, seg_rows, 0, None, None, st)
         if ex.barrier is not None:
             ex.barrier.sync()
         out = torch.empty_like(x)
-        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_off, w, None, out, None, d, epr, ex.rank, ex.cap)
-        ctx.moe, ctx.groups, ctx.saved_h = moe, groups, saved_h
-        ctx.save_for_backward(x, w, topk_idx, slot, send_off, xs.clone() if ex.world > 1 else xs, ys.clone())
+        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_base, w, None, out, None, d, epr, 0, 0)
+        ctx.moe = moe
+        keep_x, keep_y = (xs.clone(), ys.clone()) if ex.shared else (xs, ys)
+        ctx.save_for_backward(x, w, topk_idx, slot, send_base, seg_start, seg_rows, keep_x, keep_y, gu, h)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         C = native.require()
         moe, ex = ctx.moe, ctx.moe.exchange
-        x, w, topk_idx, slot, send_off, xs, ys = ctx.saved_tensors
+        x, w, topk_idx, slot, send_base, seg_start, seg_rows, xs, ys, gu, h = ctx.saved_tensors
         T, d = x.shape
         k = topk_idx.shape[1]
         epr = moe.num_experts // ex.world
+        dev = x.device
+        st = native.status_word(dev)
+        cap = ex.cap
         dout = dout.contiguous()
-        # dw[t,j] = <dout[t], y row>; needs the forward's expert outputs where the combine reads them
+        # dw[t, j] = <dout[t], y row of (t, j)>: the forward's expert outputs, where the combine reads them
         ybuf = ex.bufs["y"]
-        ybuf.tensor.view(-1, d)[: ys.shape[0]].copy_(ys)
-        if ex.barrier is not None:
+        if ex.shared:
+            ybuf.tensor.view(-1, d)[:cap].copy_(ys)
             ex.barrier.sync()
-        dw = torch.empty(T, k, device=x.device, dtype=torch.float32)
-        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_off, None, dout, None, dw, d, epr, ex.rank, ex.cap)
+        dw = torch.empty(T, k, device=dev, dtype=torch.float32)
+        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_base, None, dout, None, dw, d, epr, 0, 0)
         # dy rows = w * dout[t], sent to the owners
         dybuf, dxbuf = ex.bufs["dy"], ex.bufs["dx"]
-        C.moe_dispatch(dout, topk_idx, slot, send_off, w.contiguous(), dybuf.ptrs, epr, ex.rank, ex.cap)
+        dys = dybuf.tensor.view(-1, d)[:cap]
+        dxs = dxbuf.tensor.view(-1, d)[:cap]
+        C.moe_zero_pad(seg_start, seg_rows, epr, dys, None)
+        C.moe_dispatch(dout, topk_idx, slot, send_base, w.contiguous(), dybuf.ptrs, epr, 0, 0)
         if ex.barrier is not None:
             ex.barrier.sync()
-        dys = dybuf.tensor.view(-1, d)
-        dxs = dxbuf.tensor.view(-1, d)
-        for (le, a, b), (u, h) in zip(ctx.groups, ctx.saved_h):
-            up, down = moe.experts_up[ex.rank * epr + le], moe.experts_down[ex.rank * epr + le]
-            dh = F.gemm(dys[a:b], down.weight.compute, b_mn=True)
-            F.gemm(dys[a:b], h, a_mn=True, b_mn=True, out=down.weight.main_grad, epi=F.EPI_F32_ACC)
-            du = torch.empty_like(u)
-            C.swiglu_fused_bwd(u, dh, du)
-            F.gemm(du, up.weight.compute, b_mn=True, out=dxs[a:b])
-            F.gemm(du, xs[a:b], a_mn=True, b_mn=True, out=up.weight.main_grad, epi=F.EPI_F32_ACC)
+        lo = ex.rank * epr
+        ups = [moe.experts_up[lo + i].weight for i in range(epr)]
+        downs = [moe.experts_down[lo + i].weight for i in range(epr)]
+        dgu = torch.empty_like(gu)
+        C.gemm_grouped_rows(dys, [p.compute for p in downs], True, dgu, seg_start, seg_rows, 2, gu, None, st)  # + SwiGLU backward
+        C.gemm_grouped_k(dys, h, [p.main_grad for p in downs], seg_start, seg_rows, st)
+        C.gemm_grouped_rows(dgu, [p.compute for p in ups], True, dxs, seg_start, seg_rows, 0, None, None, st)
+        C.gemm_grouped_k(dgu, xs, [p.main_grad for p in ups], seg_start, seg_rows, st)
         if ex.barrier is not None:
             ex.barrier.sync()
         dx = torch.empty_like(x)
-        C.moe_combine(dxbuf.ptrs, topk_idx, slot, send_off, None, None, dx, None, d, epr, ex.rank, ex.cap)
-        return dx, dw, None, None, None, None, None
+        C.moe_combine(dxbuf.ptrs, topk_idx, slot, send_base, None, None, dx, None, d, epr, 0, 0)
+        return dx, dw, None, None, None, None
 
 
 class MoEFFN(nn.Module):
@@ -212,15 +288,14 @@ class MoEFFN(nn.Module):
             probs = torch.softmax(self.router(x2)[:, :E].float(), dim=-1)
             out = sum(probs[:, e:e + 1].to(x2.dtype) * self._expert(e, x2) for e in range(E))
             self.last_aux = torch.zeros((), device=x.device)
+        elif self._native_ok(x2):
+            out = self._forward_native(x2)
         else:
             probs, idx, w, aux = self._route(x2)
             self.last_aux = aux
             if self.capacity_factor > 0:
                 idx, w = self._apply_capacity(idx, w, T)
-            native_ok = x2.is_cuda and getattr(self.experts_up[0].weight, "compute", None) is not None \
-                and self.routing == "topk" and self.capacity_factor == 0 and self.cfg.gated_ffn \
-                and self.cfg.activation != "relu2"
-            out = self._forward_native(x2, probs, w) if native_ok else self._forward_reference(x2, idx, w)
+            out = self._forward_reference(x2, idx, w)
             kept = idx.reshape(-1)
             counts = torch.bincount(kept[kept >= 0], minlength=E).float()
             self.last_stats.update({"tokens_per_expert": counts,
@@ -264,34 +339,25 @@ class MoEFFN(nn.Module):
             out = torch.where(dropped[:, None], x2, out)
         return out
 
-    def _forward_native(self, x2, probs, w_unused):
-        C = native.require()
-        ex = self.exchange
-        T, d = x2.shape
-        E, k = self.num_experts, self.top_k
-        dev = x2.device
-        topk_idx = torch.empty(T, k, device=dev, dtype=torch.int32)
-        slot = torch.empty(T, k, device=dev, dtype=torch.int32)
-        counts = torch.zeros(E, device=dev, dtype=torch.int32)
-        C.moe_topk(probs.detach().contiguous(), k, topk_idx, slot, counts)
-        w = probs.gather(1, topk_idx.long())
-        epr = E // ex.world
-        if isinstance(ex, _LocalExchange):
-            ex.ensure(T * k, d, dev)
-        all_counts = ex.all_counts(counts).cpu()            # [world, E] (one small host sync per layer)
-        send_off = torch.zeros(E, dtype=torch.int32)
-        for r in range(ex.world):                             # my rows inside each owner's segment
-            send_off[r * epr:(r + 1) * epr] = torch.cumsum(all_counts[ex.rank, r * epr:(r + 1) * epr], 0) - \
-                all_counts[ex.rank, r * epr:(r + 1) * epr]
-        groups = []
-        for s in range(ex.world):                             # what every source sent to my experts
-            off = 0
-            for le in range(epr):
-                c = int(all_counts[s, ex.rank * epr + le])
-                if c > 0:
-                    groups.append((le, s * ex.cap + off, s * ex.cap + off + c))
-                off += c
-        return _MoEFn.apply(x2.contiguous(), w, self, topk_idx, slot, send_off.to(dev), groups)
+    def _native_ok(self, x2) -> bool:
+        """The device-side path: plain top-k routing without capacity limit, SwiGLU experts whose width
+        is a multiple of 128, weights bound to a parameter store, at most 16 experts per rank."""
+        cfg = self.cfg
+        f = cfg.moe_ffn_hidden_size or cfg.ffn_hidden_size
+        return (x2.is_cuda and getattr(self.experts_up[0].weight, "compute", None) is not None
+                and getattr(self.router.weight, "compute", None) is not None
+                and self.routing == "topk" and self.capacity_factor == 0 and cfg.gated_ffn and cfg.activation != "relu2"
+                and cfg.moe_z_coef == 0 and not (self.training and self.gating_dropout > 0)
+                and f % 128 == 0 and cfg.hidden_size % 8 == 0 and cfg.hidden_size >= 256
+                and self.num_experts % self.exchange.world == 0
+                and self.num_experts // self.exchange.world <= MAX_LOCAL_EXPERTS)
+
+    def _forward_native(self, x2):
+        logits = self.router(x2)                                     # bf16 [T, E padded to 8]
+        w, aux, topk_idx, slot, counts = _RouteFn.apply(logits, self.num_experts, self.top_k, float(self.cfg.moe_aux_coef))
+        self.last_aux = aux
+        self.last_stats.update({"tokens_per_expert": counts})        # device tensor; no host read here
+        return _MoEFn.apply(x2.contiguous(), w, self, topk_idx, slot, counts)
 
 
 class MoEBlock(TransformerBlock):

@@ -203,3 +203,47 @@ def test_fused_ffn_and_rope_layers_match_unfused_autograd():
     assert (hdn.grad.float() - hf.grad).abs().max().item() <= 5e-2
     assert torch.equal(hdn.grad, res.grad)
     assert (gamma.grad.float() - gf.grad).abs().max().item() <= 3e-2 * gf.grad.abs().max().item() + 1e-2
+
+
+def test_grouped_gemms_over_ragged_segments():
+    """Ragged-M and ragged-K grouped GEMMs (segments described by device arrays, 256-aligned starts,
+    zero padding rows) against per-segment fp32 products."""
+    from mythos_b200.ops import native
+
+    C = native.require()
+    torch.manual_seed(5)
+    rows = [300, 0, 77, 512]
+    K, N = 256, 384
+    starts, off = [], 0
+    for r in rows:
+        starts.append(off)
+        off += (r + 255) // 256 * 256
+    cap = off + 256
+    a = torch.zeros(cap, K, device="cuda", dtype=torch.bfloat16)
+    for s0, r in zip(starts, rows):
+        a[s0:s0 + r] = torch.randn(r, K, device="cuda").to(torch.bfloat16)
+    ws = [(torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16) for _ in rows]
+    seg_start = torch.tensor(starts, device="cuda", dtype=torch.int32)
+    seg_rows = torch.tensor(rows, device="cuda", dtype=torch.int32)
+    st = native.status_word(a.device)
+    out = torch.full((cap, N), 7.0, device="cuda", dtype=torch.bfloat16)
+    C.gemm_grouped_rows(a, ws, False, out, seg_start, seg_rows, 0, None, None, st)
+    for s0, r, w in zip(starts, rows, ws):
+        if r:
+            _check(out[s0:s0 + r], a[s0:s0 + r].float() @ w.float().t(), K)
+    # MN-major weights (the dgrad form): out = a @ w with w [K, N]
+    wt = [w.t().contiguous() for w in ws]
+    out2 = torch.empty(cap, N, device="cuda", dtype=torch.bfloat16)
+    C.gemm_grouped_rows(a, wt, True, out2, seg_start, seg_rows, 0, None, None, st)
+    for s0, r, w in zip(starts, rows, ws):
+        if r:
+            _check(out2[s0:s0 + r], a[s0:s0 + r].float() @ w.float().t(), K)
+    # ragged K: grads[e] += a[rows of e]^T @ b[rows of e]
+    b = torch.zeros(cap, N, device="cuda", dtype=torch.bfloat16)
+    for s0, r in zip(starts, rows):
+        b[s0:s0 + r] = torch.randn(r, N, device="cuda").to(torch.bfloat16)
+    grads = [torch.ones(K, N, device="cuda") for _ in rows]
+    C.gemm_grouped_k(a, b, grads, seg_start, seg_rows, st)
+    for s0, r, g in zip(starts, rows, grads):
+        ref = 1.0 + a[s0:s0 + r].float().t() @ b[s0:s0 + r].float()
+        _check(g, ref, max(r, 1))

@@ -32,6 +32,7 @@ def test_moe_native_matches_reference_forward_and_backward():
     dy = torch.randn_like(yr)
     (yr * dy).sum().backward()
     xg = x.cuda().to(torch.bfloat16).requires_grad_()
+    assert nat._native_ok(xg)                 # device router + grouped GEMMs, not the per-expert loop
     yg = nat(xg)
     (yg.float() * dy.cuda()).sum().backward()
     torch.cuda.synchronize()
