@@ -1038,6 +1038,11 @@ PYBIND11_MODULE(_C, m) {
   m.def("symm_barrier", &symm_barrier);
   m.def("zero_reduce_scatter", &zero_reduce_scatter);
   m.def("zero_adamw_ste_allgather", &zero_adamw_ste_allgather);
+  m.def("comm_set_abort_word", [](const Tensor& status) {
+    chk_c(status, I32, "status");
+    c10::cuda::CUDAGuard guard(status.device());
+    mb::comm_set_abort_word(status.data_ptr<int>());
+  });
   m.def("moe_route", &moe_route);
   m.def("moe_route_bwd", &moe_route_bwd);
   m.def("moe_publish_counts", &moe_publish_counts);

@@ -213,6 +213,10 @@ struct ZeroFusedArgs {
 // With epoch_ptr != null the epoch is read from (and advanced in) device memory instead of `epoch`.
 void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* send_val, int rank, int world, int epoch,
                   int* epoch_ptr, long long limit_cycles, int* status, cudaStream_t stream);
+// Registers the status word of the current device: the kernels below that consume data guarded by a
+// flag barrier (zero_reduce_scatter, zero_adamw_ste_allgather, tp_reduce_slots, tp_reduce_slots_bcast,
+// tp_allreduce_pull) return without writing once the word is non-zero (a bounded wait expired).
+void comm_set_abort_word(const int* status);
 void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,
                          cudaStream_t stream);
 void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream);

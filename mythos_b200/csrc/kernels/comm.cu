@@ -26,6 +26,20 @@
 namespace mb {
 namespace {
 
+const int* g_abort_word[64] = {nullptr};
+const int* abort_word_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return g_abort_word[dev];
+}
+
+// A kernel that consumes what a barrier guarded reads the status word first: once a bounded wait
+// has expired somewhere on this device the data may be incomplete, so the kernel returns without
+// writing anything (no poisoned update is applied or broadcast); the host sees the word afterwards.
+__device__ __forceinline__ bool aborted(const int* abort_word) {
+  return abort_word != nullptr && *reinterpret_cast<const volatile int*>(abort_word) != 0;
+}
+
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -60,8 +74,9 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, PeerPtrs slots, const float*
 }
 
 __global__ void zero_reduce_scatter_kernel(PeerPtrs grads, float* __restrict__ out, long long shard_off, long long n,
-                                           int world, float* __restrict__ sumsq) {
+                                           int world, float* __restrict__ sumsq, const int* abort_word) {
   __shared__ float scratch[32];
+  if (aborted(abort_word)) return;
   float ss = 0.f;
   const long long n4 = n >> 2;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
@@ -94,7 +109,8 @@ __device__ __forceinline__ int nearest_sorted_dev(const float* cb, float w) {
 }
 
 // One warp per 256-element segment of the local shard.
-__global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a) {
+__global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a, const int* abort_word) {
+  if (aborted(abort_word)) return;
   extern __shared__ float cb_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
   float* cb = cb_smem + warp * 256;
@@ -199,7 +215,8 @@ void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off,
   long long grid = (n / 4 + 255) / 256;
   const long long cap = (long long)sm_count() * 8;
   if (grid > cap) grid = cap;
-  zero_reduce_scatter_kernel<<<(int)grid, 256, 0, stream>>>(grads, out, shard_off, n, world, sumsq);
+  zero_reduce_scatter_kernel<<<(int)grid, 256, 0, stream>>>(grads, out, shard_off, n, world, sumsq,
+                                                            abort_word_for_current_device());
   count_launch();
   check_launch();
 }
@@ -211,7 +228,8 @@ void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream) {
   long long grid = ((a.n >> 8) + wpb - 1) / wpb;
   const long long cap = (long long)sm_count() * 8;
   if (grid > cap) grid = cap;
-  zero_adamw_ste_allgather_kernel<<<(int)grid, threads, wpb * 256 * sizeof(float), stream>>>(a);
+  zero_adamw_ste_allgather_kernel<<<(int)grid, threads, wpb * 256 * sizeof(float), stream>>>(
+      a, abort_word_for_current_device());
   count_launch();
   check_launch();
 }
@@ -275,7 +293,8 @@ __device__ __forceinline__ bf16x8 ld_l2_8(const void* base, long long elem_index
 // out[i] = bf16(sum_s staging[s * slot_stride + i] (+ residual[i]))
 __global__ void tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, int slots, long long slot_stride,
                                        const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
-                                       long long n8) {
+                                       long long n8, const int* abort_word) {
+  if (aborted(abort_word)) return;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bf16x8 v[MAX_PEERS];
@@ -302,7 +321,9 @@ __global__ void tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging
 
 // out_p[out_off + i] = bf16(sum_s staging[s * slot_stride + i]) for every peer p.
 __global__ void tp_reduce_slots_bcast_kernel(const __nv_bfloat16* __restrict__ staging, int slots, long long slot_stride,
-                                             PeerPtrs out, int n_peers, int rank, long long out_off, long long n8) {
+                                             PeerPtrs out, int n_peers, int rank, long long out_off, long long n8,
+                                             const int* abort_word) {
+  if (aborted(abort_word)) return;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bf16x8 v[MAX_PEERS];
@@ -325,7 +346,8 @@ __global__ void tp_reduce_slots_bcast_kernel(const __nv_bfloat16* __restrict__ s
 // Elements [begin8, end8) (units of 8) are this rank's slice: out_p[i] = bf16(sum_q part_q[i]) for
 // every p. Partials are summed in rank order, so the value does not depend on which rank owns it.
 __global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peers, int rank, long long begin8,
-                                         long long end8) {
+                                         long long end8, const int* abort_word) {
+  if (aborted(abort_word)) return;
   for (long long i = begin8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end8;
        i += (long long)gridDim.x * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -347,6 +369,13 @@ __global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peer
 }
 
 }  // namespace
+
+void comm_set_abort_word(const int* status) {
+  int dev = 0;
+  MB_CUDA_CHECK(cudaGetDevice(&dev));
+  MB_REQUIRE(dev >= 0 && dev < 64, "comm_set_abort_word: device index out of range");
+  g_abort_word[dev] = status;
+}
 
 void peer_add_f32(const float* part, const PeerPtrs& dst, int n_peers, long long n, cudaStream_t stream) {
   MB_REQUIRE(n % 4 == 0, "peer_add_f32: element count must be a multiple of 4");
@@ -391,7 +420,8 @@ void tp_reduce_slots(const void* staging, int slots, long long slot_stride, cons
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;
   tp_reduce_slots_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)staging, slots, slot_stride,
-                                                     (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n / 8);
+                                                     (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n / 8,
+                                                     abort_word_for_current_device());
   count_launch();
   check_launch();
 }
@@ -405,7 +435,8 @@ void tp_reduce_slots_bcast(const void* staging, int slots, long long slot_stride
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;
   tp_reduce_slots_bcast_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)staging, slots, slot_stride, out,
-                                                           n_peers, rank, out_off, n / 8);
+                                                           n_peers, rank, out_off, n / 8,
+                                                           abort_word_for_current_device());
   count_launch();
   check_launch();
 }
@@ -422,7 +453,8 @@ void tp_allreduce_pull(const PeerPtrs& part, const PeerPtrs& out, int n_peers, i
   long long g = (end - begin + 255) / 256;
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;
-  tp_allreduce_pull_kernel<<<(int)g, 256, 0, stream>>>(part, out, n_peers, rank, begin, end);
+  tp_allreduce_pull_kernel<<<(int)g, 256, 0, stream>>>(part, out, n_peers, rank, begin, end,
+                                                       abort_word_for_current_device());
   count_launch();
   check_launch();
 }

@@ -62,6 +62,9 @@ def status_word(device) -> torch.Tensor:
     if t is None:
         t = torch.zeros(1, dtype=torch.int32, device=dev)
         _status[key] = t
+        ext = _load()
+        if dev.type == "cuda" and ext is not None and hasattr(ext, "comm_set_abort_word"):
+            ext.comm_set_abort_word(t)    # collective kernels stop writing once a bounded wait has expired
     return t
 
 

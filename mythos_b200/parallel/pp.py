@@ -94,7 +94,11 @@ class PipelineStage:
                 logits = x
                 from ..ops import functional as F
 
-                loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets[i].to(device).reshape(-1)) / M
+                rows = logits.numel() // logits.shape[-1]
+                # the 1/M of the micro-batch mean goes into the loss scale: the fused CUDA loss writes
+                # its (scaled) gradient in the forward pass and expects an upstream gradient of 1
+                loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets[i].to(device).reshape(-1),
+                                       1.0 / (rows * M))
                 outputs.append(loss)
                 losses.append(loss.detach())
             else:

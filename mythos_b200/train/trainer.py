@@ -113,6 +113,8 @@ class Trainer:
         token loss of the step as a 0-d device tensor (read it with ``.item()`` when needed)."""
         cfg, st = self.cfg, self.store
         cuda = self.device.type == "cuda"
+        if cuda:
+            self._check_posted_status()
         B = ids.shape[0]
         mb = cfg.micro_batch_size or B
         n_micro = (B + mb - 1) // mb
@@ -147,9 +149,33 @@ class Trainer:
         self._stale = True
         if cfg.codebook_ema_interval and self.step % cfg.codebook_ema_interval == 0:
             self.update_codebooks()
-        if cuda and self.step % 50 == 0:
-            native.check_status(self.device)
+        if cuda:
+            self._post_status_read()
         return total
+
+    def _post_status_read(self):
+        """Copies the device status word to pinned host memory without waiting; the next step looks
+        at it before launching anything. Kernels that consume barrier-guarded data refuse to write
+        once the word is set, so a step whose barrier timed out changes no weights, and the step
+        after it raises here."""
+        if getattr(self, "_status_host", None) is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(native.status_word(self.device), non_blocking=True)
+        self._status_event.record()
+
+    def _check_posted_status(self):
+        ev = getattr(self, "_status_event", None)
+        if ev is None:
+            return
+        ev.synchronize()
+        code = int(self._status_host[0])
+        if code != 0:
+            native.status_word(self.device).zero_()
+            self._status_host.zero_()
+            raise RuntimeError(f"the previous training step reported kernel status {code & 0xffff} at wait site "
+                               f"{code >> 16} (1 = a bounded wait expired, e.g. a rank did not reach a barrier); "
+                               "its optimizer update was not applied")
 
     def _refresh(self):
         if self.dp is not None:

@@ -98,3 +98,52 @@ def test_flag_barrier_single_rank_and_timeout():
         native.check_status("cuda")
     native.check_status("cuda")  # cleared
     assert fb[0].item() == 1  # the signal to the peer was still delivered
+
+
+def test_timeout_stops_the_consuming_kernels_and_the_next_step():
+    """A flag nobody sets makes the bounded barrier wait expire (status word set). The kernels that
+    would consume the guarded data then return without writing, and the trainer raises at the
+    start of the next step instead of training on."""
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.ops import native
+    from mythos_b200.train.data import ZipfStream
+    from mythos_b200.train.trainer import TrainConfig, Trainer
+
+    C = native.require()
+    st = native.status_word("cuda")
+    fa = torch.zeros(64, dtype=torch.int32, device="cuda")
+    fb = torch.zeros(64, dtype=torch.int32, device="cuda")
+    sl = torch.zeros(64, device="cuda")
+    C.symm_barrier([fa.data_ptr(), fb.data_ptr()], [sl.data_ptr(), sl.data_ptr()], None, 0, 1, 2_000_000, st, None)
+    torch.cuda.synchronize()
+    assert int(st.item()) != 0
+    # reduce-scatter and pull all-reduce after the expired wait: outputs stay as they were
+    g = torch.ones(1024, device="cuda")
+    out = torch.full((1024,), 7.0, device="cuda")
+    ss = torch.zeros(1, device="cuda")
+    C.zero_reduce_scatter([g.data_ptr()], out, 0, ss)
+    part = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    res = torch.full((1024,), 5.0, device="cuda", dtype=torch.bfloat16)
+    C.tp_allreduce_pull([part.data_ptr()], [res.data_ptr()], 0, 1024)
+    torch.cuda.synchronize()
+    assert torch.all(out == 7.0) and float(ss) == 0.0 and torch.all(res == 5.0)
+    with pytest.raises(RuntimeError, match="status 1"):
+        native.check_status("cuda")
+    C.zero_reduce_scatter([g.data_ptr()], out, 0, ss)                  # cleared: the kernels work again
+    torch.cuda.synchronize()
+    assert torch.all(out == 1.0)
+
+    cfg = TransformerConfig(vocab_size=256, hidden_size=256, num_layers=1, num_heads=2, head_dim=128,
+                            ffn_hidden_size=256, max_seq_len=128, oil_block_size=64)
+    with torch.device("cuda"):
+        model = DenseModel(cfg)
+    tr = Trainer(model, TrainConfig(batch_size=2, seq_length=128, lr=1e-3, warmup_steps=0), device="cuda")
+    data = ZipfStream(cfg.vocab_size, 2, 128, seed=0)
+    tr.train_step(*data.next_batch())
+    st.fill_(1 | (40 << 16))                                           # as an expired barrier wait would leave it
+    tr.train_step(*data.next_batch())                                   # posts the word to the host
+    with pytest.raises(RuntimeError, match="bounded wait expired"):
+        tr.train_step(*data.next_batch())
+    tr.train_step(*data.next_batch())                                   # cleared; training continues
+    torch.cuda.synchronize()
+    native.check_status("cuda")

@@ -1,6 +1,8 @@
-"""Multi-GPU data parallelism: the fused peer-memory path must produce the same training
-trajectory as the NCCL baseline path. Runs as child processes (one per GPU) when at least two
-GPUs are visible; NVLS is disabled in NCCL for these runs."""
+"""Multi-GPU checks, run as child processes (one per GPU) at every world size in {2, 4, 8} that the
+machine offers: fused ZeRO data parallelism against the NCCL path (and against itself, bit for
+bit), tensor-parallel inference against the single-GPU engine (logits), expert-parallel MoE and the
+vocabulary-parallel loss against fp32 references, and the 1F1B pipeline over NCCL p2p against the
+unsplit model. NVLS is disabled in NCCL for these runs."""
 import json
 import os
 import subprocess
@@ -11,8 +13,24 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
+N_GPUS = torch.cuda.device_count() if torch.cuda.is_available() else 0
+WORLD_SIZES = [n for n in (2, 4, 8) if n <= N_GPUS] or [2]
+needs_two = pytest.mark.skipif(N_GPUS < 2, reason="needs at least 2 GPUs")
+
+
+def _launch(worker: str, n: int, port: int, args=(), extra_env=None, timeout=900):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, REPO_ROOT=root, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), "--no-python", sys.executable, "-c", worker, *args]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
 WORKER = r'''
-import json, os, sys, torch, torch.distributed as dist
+import hashlib, json, os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["REPO_ROOT"])
 from mythos_b200.models import DenseModel, TransformerConfig
 from mythos_b200.parallel.zero import ZeroEngine
@@ -32,38 +50,56 @@ with torch.device(dev):
 dp = ZeroEngine(dist.group.WORLD, dev, mode=mode)
 tr = Trainer(model, TrainConfig(batch_size=4, micro_batch_size=2, seq_length=256, lr=1e-3, warmup_steps=2,
                                 codebook_ema_interval=0), device=dev, dp=dp)
+# the fused exchange alone, twice from the same state and the same (seeded) gradients: reduce-scatter in
+# fixed rank order + AdamW + STE + all-gather must reproduce every bit of the shard and of the image
+repeat = []
+if dp.mode == "fused":
+    st = tr.store
+    tr._refresh()
+    snap = [t.clone() for t in (st.master, tr.m, tr.v)]
+    gsrc = torch.randn(st.total, generator=torch.Generator(device=dev).manual_seed(100 + rank), device=dev) * 1e-3
+    lo = rank * st.shard
+    for rep in range(2):
+        for t, c in zip((st.master, tr.m, tr.v), snap):
+            t.copy_(c)
+        st.grad[: st.total].copy_(gsrc)
+        tr.step = 1
+        dp.step(tr, 1e-3)
+        torch.cuda.synchronize()
+        blob = st.master[lo:lo + st.shard].cpu().numpy().tobytes() + st.compute[: st.total].view(torch.int16).cpu().numpy().tobytes()
+        repeat.append(hashlib.sha256(blob).hexdigest())
+    for t, c in zip((st.master, tr.m, tr.v), snap):
+        t.copy_(c)
+    tr.step = 0
+    tr._stale = True
+    tr._force_refresh = True
+    allrep = [None] * dist.get_world_size()
+    dist.all_gather_object(allrep, repeat)
+    repeat = allrep
 data = ZipfStream(cfg.vocab_size, 4, 256, seed=11 + rank)
 losses = [tr.train_step(*data.next_batch()).item() for _ in range(6)]
 torch.cuda.synchronize(); native.check_status(dev)
 dp.gather_master()
 digest = float(tr.store.master.double().abs().sum())
+sha = hashlib.sha256(tr.store.master.cpu().numpy().tobytes()).hexdigest()
 if rank == 0:
-    print("RESULT " + json.dumps({"mode": dp.mode, "losses": losses, "digest": digest}))
+    print("RESULT " + json.dumps({"mode": dp.mode, "losses": losses, "digest": digest, "sha": sha, "repeat": repeat}))
 dist.destroy_process_group()
 '''
 
 
-def _run(mode: str, n: int):
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, REPO_ROOT=root, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", "29611", "--no-python", sys.executable, "-c", WORKER, mode]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    line = [l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1]
-    return json.loads(line[len("RESULT "):])
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_fused_zero_matches_nccl_baseline():
-    n = 2
-    fused = _run("fused", n)
-    base = _run("nccl", n)
+@needs_two
+@pytest.mark.parametrize("n", WORLD_SIZES)
+def test_fused_zero_matches_nccl_baseline_and_itself_bit_for_bit(n):
+    fused = _launch(WORKER, n, 29611 + n, ("fused",))
+    base = _launch(WORKER, n, 29611 + n, ("nccl",))
     assert fused["mode"] == "fused" and base["mode"] == "nccl"
     for a, b in zip(fused["losses"], base["losses"]):
         assert abs(a - b) < 5e-2, (fused["losses"], base["losses"])
     assert fused["losses"][-1] < fused["losses"][0]
     assert abs(fused["digest"] - base["digest"]) < 1e-3 * base["digest"]
+    # the fused exchange sums in fixed rank order: a re-run from the same state reproduces every bit
+    assert len(fused["repeat"]) == n and all(len(r) == 2 and r[0] == r[1] for r in fused["repeat"]), fused["repeat"]
 
 
 TP_WORKER = r'''
@@ -77,8 +113,8 @@ torch.cuda.set_device(local)
 dev = torch.device("cuda", local)
 dist.init_process_group("nccl", device_id=dev)
 torch.manual_seed(3)
-cfg = TransformerConfig(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=4, head_dim=128, num_kv_heads=2,
-                        ffn_hidden_size=1024, max_seq_len=256, oil_block_size=256, codebook_group=2,
+cfg = TransformerConfig(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, head_dim=128, num_kv_heads=8,
+                        ffn_hidden_size=1024, max_seq_len=256, oil_block_size=64, codebook_group=2,
                         weight_format="oil8", attn_format="oil4")
 with torch.device(dev):
     model = DenseModel(cfg)
@@ -93,29 +129,35 @@ tp = TPContext(dist.group.WORLD, dev, max_tokens=B * S, hidden=cfg.hidden_size, 
 eng = InferenceEngine.from_model(model, device=dev, max_batch=4, max_seq_len=256, tp=tp)
 out = eng.generate(prompts, max_new_tokens=new, use_graph=False)
 out_g = eng.generate(prompts, max_new_tokens=new, use_graph=True)
+# logits of the last prompt token and of one decode step, tensor-parallel against single GPU
+single.reset_context(); eng.reset_context()
+diffs = []
+for b in range(B):
+    ids = prompts[b].tolist()
+    s0, l0 = single.start_sequence(ids, reuse_prefix=False)
+    s1, l1 = eng.start_sequence(ids, reuse_prefix=False)
+    scale = float(l0.float().abs().max())
+    diffs.append(float((l0.float() - l1.float()).abs().max()) / scale)
+    tok = int(l0.float().argmax())
+    d0 = single.decode([s0], [tok]); d1 = eng.decode([s1], [tok])
+    diffs.append(float((d0.float() - d1.float()).abs().max()) / float(d0.float().abs().max()))
+    single.release(s0); eng.release(s1)
 torch.cuda.synchronize(); native.check_status(dev)
 if rank == 0:
-    print("RESULT " + json.dumps({"ref": ref.tokens, "tp": out.tokens, "tp_graph": out_g.tokens}))
+    print("RESULT " + json.dumps({"ref": ref.tokens, "tp": out.tokens, "tp_graph": out_g.tokens, "logit_diff": diffs}))
 dist.destroy_process_group()
 '''
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+@needs_two
+@pytest.mark.parametrize("n", WORLD_SIZES)
 @pytest.mark.parametrize("row_flags", ["0", "1"])
-def test_tensor_parallel_engine_matches_single_gpu(row_flags):
+def test_tensor_parallel_engine_matches_single_gpu_logits(n, row_flags):
     """row_flags = 1: decode-sized sums run as the single-launch kernel with per-row flags."""
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, REPO_ROOT=root, NCCL_NVLS_ENABLE="0", MYTHOS_TP_ROW_FLAGS=row_flags)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29621", "--no-python", sys.executable, "-c", TP_WORKER]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    r = json.loads([l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    r = _launch(TP_WORKER, n, 29621 + n, extra_env={"MYTHOS_TP_ROW_FLAGS": row_flags})
     assert r["tp"] == r["tp_graph"]
-    same = sum(int(a == b) for x, y in zip(r["ref"], r["tp"]) for a, b in zip(x, y))
-    total = sum(len(x) for x in r["ref"])
-    # sharded accumulation order differs from the single-GPU order; greedy paths may split at a near-tie
-    assert same >= 0.7 * total, r
+    # the same packed weights, sharded: logits differ only by the bf16 rounding of the partial sums
+    assert max(r["logit_diff"]) < 4e-2, r["logit_diff"]
     assert [x[0] for x in r["ref"]] == [x[0] for x in r["tp"]]
 
 
@@ -132,7 +174,7 @@ torch.cuda.set_device(local)
 dev = torch.device("cuda", local)
 dist.init_process_group("nccl", device_id=dev)
 cfg = TransformerConfig(vocab_size=256, hidden_size=256, num_layers=1, num_heads=2, head_dim=128, ffn_hidden_size=256,
-                        max_seq_len=128, oil_block_size=64, weight_format="fp32", num_experts=4, moe_top_k=2,
+                        max_seq_len=128, oil_block_size=64, weight_format="fp32", num_experts=max(4, world), moe_top_k=2,
                         moe_ffn_hidden_size=256)
 T = 96
 torch.manual_seed(0)                      # the same expert weights on every rank
@@ -148,6 +190,7 @@ xr = torch.cat(xs).requires_grad_()
 yr = ref(xr)
 (yr * torch.cat(dys)).sum().backward()
 xg = xs[rank].to(dev).to(torch.bfloat16).requires_grad_()
+assert nat._native_ok(xg)
 yg = nat(xg)
 (yg.float() * dys[rank].to(dev)).sum().backward()
 torch.cuda.synchronize(); native.check_status(dev)
@@ -184,18 +227,84 @@ dist.destroy_process_group()
 '''
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_expert_parallel_moe_and_vocab_parallel_loss_on_two_gpus():
+@needs_two
+@pytest.mark.parametrize("n", WORLD_SIZES)
+def test_expert_parallel_moe_and_vocab_parallel_loss(n):
     """Expert parallelism: every rank routes its own tokens, expert FFNs run on the owner rank over
-    peer-memory dispatch / combine; outputs, input gradients and the local experts' weight
-    gradients must match all experts applied to all tokens in fp32. Then the sharded loss."""
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, REPO_ROOT=root, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29631", "--no-python", sys.executable, "-c", EP_WORKER]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    ranks = json.loads([l for l in res.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    peer-memory dispatch / combine (device router, counts through symmetric memory, grouped GEMMs);
+    outputs, input gradients and the local experts' weight gradients must match all experts applied
+    to all tokens in fp32. Then the sharded loss."""
+    ranks = _launch(EP_WORKER, n, 29631 + n)
     for r in ranks:
         assert r["y"] < 5e-2 and r["dx"] < 8e-2 and r["dw_local"] < 8e-2, ranks
         assert r["ce_loss"] < 5e-3 and r["ce_grad"] < 5e-2, ranks
+
+
+PP_WORKER = r'''
+import json, os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from mythos_b200.models import DenseModel, TransformerConfig
+from mythos_b200.ops import native
+from mythos_b200.parallel.pp import PipelineStage, split_layers
+from mythos_b200.train.param_store import ParamStore
+rank = int(os.environ["RANK"]); local = int(os.environ["LOCAL_RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(local)
+dev = torch.device("cuda", local)
+dist.init_process_group("nccl", device_id=dev)
+cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=8, num_heads=2, head_dim=128, ffn_hidden_size=512,
+                        max_seq_len=128, oil_block_size=64, weight_format="oil8")
+torch.manual_seed(0)                       # identical weights on every rank
+model = DenseModel(cfg)
+ref = DenseModel(cfg); ref.load_state_dict(model.state_dict())
+store = ParamStore(model, dev); store.refresh_compute()
+rstore = ParamStore(ref, dev); rstore.refresh_compute()
+M, mb, S = 4, 2, 128
+g = torch.Generator().manual_seed(1)
+ids = torch.randint(0, 512, (M, mb, S), generator=g, dtype=torch.int32)
+tg = torch.randint(0, 512, (M, mb, S), generator=g, dtype=torch.int32)
+stage = PipelineStage(model, None, micro_batches=M)
+ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+loss = stage.train_step(ids, tg, hidden_shape=(mb, S, cfg.hidden_size), dtype=torch.bfloat16, device=dev)   # warm-up
+store.zero_grad()
+torch.cuda.synchronize(); dist.barrier()
+ev0.record()
+loss = stage.train_step(ids, tg, hidden_shape=(mb, S, cfg.hidden_size), dtype=torch.bfloat16, device=dev)
+ev1.record()
+torch.cuda.synchronize(); native.check_status(dev)
+# the unsplit model on this GPU
+total = 0.0
+for i in range(M):
+    l = ref(ids[i].to(dev), tg[i].to(dev), loss_scale=1.0 / (mb * S * M))
+    l.backward(); total += float(l)
+torch.cuda.synchronize()
+lo, hi = split_layers(cfg.num_layers, world)[rank]
+worst = 0.0
+for k in range(lo, hi):
+    for (n, p), (_, q) in zip(model.layers[k].named_parameters(), ref.layers[k].named_parameters()):
+        a, b = p.main_grad.float(), q.main_grad.float()
+        worst = max(worst, float((a - b).norm() / (b.norm() + 1e-9)))
+res = {"grad_err": worst, "ms": ev0.elapsed_time(ev1)}
+if rank == world - 1:
+    res["loss_err"] = abs(float(loss) - total)
+    a, b = model.lm_head.weight.main_grad, ref.lm_head.weight.main_grad
+    res["head_err"] = float((a - b).norm() / (b.norm() + 1e-9))
+if rank == 0:
+    a, b = model.tok_embeddings.weight.main_grad, ref.tok_embeddings.weight.main_grad
+    res["emb_err"] = float((a - b).norm() / (b.norm() + 1e-9))
+out = [None] * world
+dist.all_gather_object(out, res)
+if rank == 0:
+    print("RESULT " + json.dumps(out))
+dist.destroy_process_group()
+'''
+
+
+@needs_two
+@pytest.mark.parametrize("n", [w for w in WORLD_SIZES if w <= 4])
+def test_pipeline_1f1b_over_nccl_matches_unsplit_model(n):
+    """1F1B over NCCL p2p on n GPUs (native kernels, bf16 activations): the gradients each stage
+    accumulates for its layers equal those of the whole model run on one GPU."""
+    ranks = _launch(PP_WORKER, n, 29641 + n)
+    for r in ranks:
+        assert r["grad_err"] < 3e-2, ranks
+    assert ranks[-1]["loss_err"] < 2e-2 and ranks[-1]["head_err"] < 3e-2 and ranks[0]["emb_err"] < 3e-2, ranks
