@@ -425,12 +425,20 @@ void symm_barrier(const std::vector<int64_t>& flag_ptrs, const std::vector<int64
                    status_ptr(status), cur_stream());
 }
 
-void zero_reduce_scatter(const std::vector<int64_t>& grad_ptrs, Tensor& out, int64_t shard_off, Tensor& sumsq) {
+void zero_reduce_scatter(const std::vector<int64_t>& grad_ptrs, Tensor& out, int64_t shard_off, Tensor& sumsq,
+                         int64_t multicast_ptr, int64_t max_blocks, OptTensor scratch) {
   chk_c(out, F32, "out");
   chk_c(sumsq, F32, "sumsq");
+  if (scratch.has_value()) chk_c(*scratch, F32, "scratch");
   c10::cuda::CUDAGuard guard(out.device());
   mb::zero_reduce_scatter(to_peers(grad_ptrs), out.data_ptr<float>(), shard_off, out.numel(), (int)grad_ptrs.size(),
-                          sumsq.data_ptr<float>(), cur_stream());
+                          sumsq.data_ptr<float>(), cur_stream(), reinterpret_cast<const float*>(multicast_ptr),
+                          (int)max_blocks, scratch.has_value() ? scratch->data_ptr<float>() : nullptr,
+                          scratch.has_value() ? scratch->numel() : 0);
+}
+void tp_allreduce_multimem(int64_t part_mc, int64_t out_mc, int64_t n_peers, int64_t rank, int64_t n) {
+  mb::tp_allreduce_multimem(reinterpret_cast<const void*>(part_mc), reinterpret_cast<void*>(out_mc), (int)n_peers, (int)rank,
+                            n, cur_stream());
 }
 
 void zero_adamw_ste_allgather(Tensor& p, Tensor& m, Tensor& v, const Tensor& g,
@@ -438,7 +446,7 @@ void zero_adamw_ste_allgather(Tensor& p, Tensor& m, Tensor& v, const Tensor& g,
                               const OptTensor& seg_cb, const OptTensor& codebooks8, const OptTensor& codebooks4,
                               const Tensor& norm_partials, OptTensor grad_norm_out, double max_norm, double lr,
                               double beta1, double beta2, double eps, double weight_decay, int64_t step,
-                              double grad_scale, int64_t rank) {
+                              double grad_scale, int64_t rank, int64_t compute_multicast_ptr) {
   chk_c(p, F32, "p");
   chk_c(m, F32, "m");
   chk_c(v, F32, "v");
@@ -450,6 +458,7 @@ void zero_adamw_ste_allgather(Tensor& p, Tensor& m, Tensor& v, const Tensor& g,
   a.v = v.data_ptr<float>();
   a.g = g.data_ptr<float>();
   a.compute = to_peers(compute_ptrs);
+  a.compute_mc = reinterpret_cast<void*>(compute_multicast_ptr);
   a.shard_off = shard_off;
   a.n = p.numel();
   a.seg_fmt = seg_fmt.has_value() ? seg_fmt->data_ptr<uint8_t>() : nullptr;
@@ -1036,7 +1045,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("peer_add_f32", &peer_add_f32);
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);
-  m.def("zero_reduce_scatter", &zero_reduce_scatter);
+  m.def("zero_reduce_scatter", &zero_reduce_scatter, py::arg("grad_ptrs"), py::arg("out"), py::arg("shard_off"),
+        py::arg("sumsq"), py::arg("multicast_ptr") = 0, py::arg("max_blocks") = 0, py::arg("scratch") = py::none());
+  m.def("tp_allreduce_multimem", &tp_allreduce_multimem);
   m.def("zero_adamw_ste_allgather", &zero_adamw_ste_allgather);
   m.def("comm_set_abort_word", [](const Tensor& status) {
     chk_c(status, I32, "status");

@@ -197,6 +197,7 @@ struct ZeroFusedArgs {
   float *p, *m, *v;            // local fp32 shard of master weights and Adam moments, n elements
   const float* g;              // local reduced gradient shard
   PeerPtrs compute;            // every rank's full bf16 compute buffer
+  void* compute_mc = nullptr;  // NVLS multicast address of the compute buffers (null: plain peer stores)
   long long shard_off, n;      // element offset of the shard in the flat buffer; shard length
   const uint8_t* seg_fmt;      // per 256-element segment of the flat buffer: ZERO_FMT_*
   const int* seg_cb;           // per segment: codebook row in codebooks8 / codebooks4
@@ -217,8 +218,16 @@ void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* sen
 // flag barrier (zero_reduce_scatter, zero_adamw_ste_allgather, tp_reduce_slots, tp_reduce_slots_bcast,
 // tp_allreduce_pull) return without writing once the word is non-zero (a bounded wait expired).
 void comm_set_abort_word(const int* status);
+// block_partials (zeroed fp32 scratch of n_block_partials >= 2 words, not shared by launches that can run at
+// the same time): the sum of squares is then added in a fixed order and is bit-reproducible.
+// grads_multicast: NVLS multicast address of the gradient buffers (the sum is then formed inside the
+// NVSwitch by multimem.ld_reduce; null: one peer load per rank, added in rank order). max_blocks > 0 caps the grid.
 void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,
-                         cudaStream_t stream);
+                         cudaStream_t stream, const float* grads_multicast = nullptr, int max_blocks = 0,
+                         float* block_partials = nullptr, long long n_block_partials = 0);
+// All-reduce of bf16 partials through NVLS (multimem.ld_reduce + multimem.st on multicast addresses):
+// this rank handles slice `rank` of n elements; barriers before and after are the caller's.
+void tp_allreduce_multimem(const void* part_mc, void* out_mc, int n_peers, int rank, long long n, cudaStream_t stream);
 void zero_adamw_ste_allgather(const ZeroFusedArgs& a, cudaStream_t stream);
 // dst_r[i] += part[i] on every rank r (fp32 peer reductions).
 void peer_add_f32(const float* part, const PeerPtrs& dst, int n_peers, long long n, cudaStream_t stream);

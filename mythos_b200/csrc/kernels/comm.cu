@@ -26,6 +26,11 @@
 namespace mb {
 namespace {
 
+// Two-shot all-reduce through NVLS: this rank's slice is summed inside the switch (one multicast load
+// per 16 bytes) and broadcast to every rank with one multicast store.
+__global__ void tp_allreduce_mc_kernel(const __nv_bfloat16* part_mc, __nv_bfloat16* out_mc, long long begin8,
+                                       long long end8, const int* abort_word);
+
 const int* g_abort_word[64] = {nullptr};
 const int* abort_word_for_current_device() {
   int dev = 0;
@@ -73,24 +78,72 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, PeerPtrs slots, const float*
   }
 }
 
+// NVLS: one load from the multicast address of a symmetric buffer returns the sum over every rank's
+// copy, added inside the NVSwitch (fp32), so a rank receives one value per element instead of one per peer.
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// NVLS: one store to the multicast address writes the 16 bytes into every rank's copy.
+__device__ __forceinline__ void multimem_st_b128(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+// Sum of bf16 pairs over every rank's copy, accumulated in fp32 inside the switch.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+
 __global__ void zero_reduce_scatter_kernel(PeerPtrs grads, float* __restrict__ out, long long shard_off, long long n,
-                                           int world, float* __restrict__ sumsq, const int* abort_word) {
+                                           int world, float* __restrict__ sumsq, const int* abort_word,
+                                           const float* mc, float* __restrict__ block_partials) {
   __shared__ float scratch[32];
   if (aborted(abort_word)) return;
   float ss = 0.f;
   const long long n4 = n >> 2;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (mc != nullptr) {
+      acc = multimem_ld_reduce_f32x4(mc + shard_off + 4 * i);
+    } else {
 #pragma unroll 8
-    for (int r = 0; r < world; ++r) {
-      const float4 v = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + shard_off) + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      for (int r = 0; r < world; ++r) {
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + shard_off) + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
     }
     reinterpret_cast<float4*>(out)[i] = acc;
     ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
   }
   ss = block_sum(ss, scratch);
-  if (threadIdx.x == 0 && sumsq) atomicAdd(sumsq, ss);
+  if (threadIdx.x == 0 && sumsq) {
+    if (block_partials == nullptr) {
+      atomicAdd(sumsq, ss);                      // order of the additions varies from launch to launch
+    } else {
+      // bit-reproducible norm: every block leaves its partial, the block that finishes last adds them
+      // in index order (the ticket lives behind the partials and is reset for the next launch)
+      unsigned* ticket = reinterpret_cast<unsigned*>(block_partials + gridDim.x);
+      block_partials[blockIdx.x] = ss;
+      __threadfence();
+      if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+        __threadfence();
+        float tot = 0.f;
+        for (unsigned b = 0; b < gridDim.x; ++b) tot += reinterpret_cast<volatile float*>(block_partials)[b];
+        atomicAdd(sumsq, tot);
+        *ticket = 0u;
+      }
+    }
+  }
 }
 
 template <int CB>
@@ -191,9 +244,14 @@ __global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a, const int* abor
     }
     const bf16x8 packed = pack8(q);
     const long long gelem = a.shard_off + base;
-    for (int r = 0; r < a.world; ++r) {
-      const int dst = (a.rank + r) % a.world;  // start with the local copy, then fan out
-      stg8(a.compute.p[dst], gelem, packed);
+    if (a.compute_mc != nullptr) {
+      // one multicast store reaches every rank's compute buffer (this rank's own included)
+      multimem_st_b128(reinterpret_cast<__nv_bfloat16*>(a.compute_mc) + gelem, *reinterpret_cast<const uint4*>(&packed));
+    } else {
+      for (int r = 0; r < a.world; ++r) {
+        const int dst = (a.rank + r) % a.world;  // start with the local copy, then fan out
+        stg8(a.compute.p[dst], gelem, packed);
+      }
     }
   }
 }
@@ -209,14 +267,19 @@ void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* sen
 }
 
 void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const float* grads_multicast, int max_blocks, float* block_partials,
+                         long long n_block_partials) {
   MB_REQUIRE(n % 4 == 0 && shard_off % 4 == 0, "zero_reduce_scatter: shard must be a multiple of 4 elements");
   if (n == 0) return;
   long long grid = (n / 4 + 255) / 256;
-  const long long cap = (long long)sm_count() * 8;
+  long long cap = (long long)sm_count() * 8;
+  if (max_blocks > 0 && max_blocks < cap) cap = max_blocks;   // a small grid when it runs beside the backward pass
   if (grid > cap) grid = cap;
+  if (block_partials != nullptr && grid + 1 > n_block_partials) grid = n_block_partials - 1;
+  MB_REQUIRE(grid >= 1, "zero_reduce_scatter: scratch for the block partials is too small");
   zero_reduce_scatter_kernel<<<(int)grid, 256, 0, stream>>>(grads, out, shard_off, n, world, sumsq,
-                                                            abort_word_for_current_device());
+                                                            abort_word_for_current_device(), grads_multicast,
+                                                            block_partials);
   count_launch();
   check_launch();
 }
@@ -368,7 +431,32 @@ __global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peer
   }
 }
 
+__global__ void tp_allreduce_mc_kernel(const __nv_bfloat16* part_mc, __nv_bfloat16* out_mc, long long begin8,
+                                       long long end8, const int* abort_word) {
+  if (aborted(abort_word)) return;
+  for (long long i = begin8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = multimem_ld_reduce_bf16x8(part_mc + i * 8);
+    multimem_st_b128(out_mc + i * 8, v);
+  }
+}
+
 }  // namespace
+
+void tp_allreduce_multimem(const void* part_mc, void* out_mc, int n_peers, int rank, long long n, cudaStream_t stream) {
+  MB_REQUIRE(n % 8 == 0 && n_peers >= 1 && part_mc != nullptr && out_mc != nullptr, "tp_allreduce_multimem: bad arguments");
+  const long long n8 = n / 8;
+  const long long per = (n8 + n_peers - 1) / n_peers;
+  const long long begin = per * rank, end = begin + per < n8 ? begin + per : n8;
+  if (begin >= end) return;
+  long long g = (end - begin + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  tp_allreduce_mc_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)part_mc, (__nv_bfloat16*)out_mc, begin, end,
+                                                     abort_word_for_current_device());
+  count_launch();
+  check_launch();
+}
 
 void comm_set_abort_word(const int* status) {
   int dev = 0;

@@ -21,6 +21,9 @@ class DenseModel(nn.Module):
         # recompute every block's activations in the backward pass instead of keeping them
         # (memory of one block's activations + one [B, S, d] pair per block; one extra forward)
         self.activation_checkpointing = False
+        # set by the data-parallel engine around the last backward pass of a step: called with i when
+        # the gradients of every parameter in blocks >= i (and of the final norm / head) are complete
+        self.grad_ready_callback = None
         self.tok_embeddings = Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList([self._make_block(i) for i in range(cfg.num_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.norm_eps)
@@ -41,11 +44,17 @@ class DenseModel(nn.Module):
             pos = torch.arange(S, device=ids.device, dtype=torch.int32).repeat(B)
         x = self.tok_embeddings(ids)
         branch, stream = x, None
-        for blk in self.layers:
+        cb = self.grad_ready_callback if torch.is_grad_enabled() else None
+        for i, blk in enumerate(self.layers):
+            if cb is not None and branch.requires_grad:
+                # the gradient of block i's input exists once block i (and everything after it) is done
+                branch.register_hook(lambda g, i=i: cb(i))
             if self.activation_checkpointing and self.training:
                 branch, stream = F.checkpoint(blk, branch, stream, pos)
             else:
                 branch, stream = blk(branch, stream, pos)
+        if cb is not None and branch.requires_grad:
+            branch.register_hook(lambda g, i=len(self.layers): cb(i))
         h, _ = self.norm(branch, stream)
         return h
 

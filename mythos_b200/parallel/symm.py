@@ -32,6 +32,12 @@ class SymmBuffer:
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.rank = self.handle.rank
         self.world_size = self.handle.world_size
+        # NVLS: address at which every rank's copy is mapped as one multicast object (0 when the
+        # allocator could not bind one); multimem.ld_reduce / multimem.st go through it
+        try:
+            self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        except Exception:
+            self.multicast_ptr = 0
 
     def zero_(self):
         self.tensor.zero_()
@@ -45,10 +51,20 @@ class LocalBuffer:
         self.tensor = torch.zeros(numel, dtype=dtype, device=device)
         self.ptrs = [self.tensor.data_ptr()]
         self.rank, self.world_size = 0, 1
+        self.multicast_ptr = 0
 
     def zero_(self):
         self.tensor.zero_()
         return self
+
+
+def nvls_enabled() -> bool:
+    """In-switch reductions and multicast stores (``multimem`` on NVLS multicast mappings) are opt-in:
+    ``MYTHOS_NVLS=1``. The default, and what the failure tests use, is plain peer loads and stores: a
+    rank that dies while its memory is bound to a multicast object can fault its peers' GPUs."""
+    import os
+
+    return os.environ.get("MYTHOS_NVLS", "0") == "1"
 
 
 def make_buffer(numel: int, dtype, device, group=None):

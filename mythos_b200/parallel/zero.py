@@ -13,6 +13,13 @@ Two implementations:
     this framework do everything with peer loads/stores over NVLink
     (``csrc/kernels/comm.cu``): flag barrier -> reduce-scatter + norm partial -> flag barrier that
     also exchanges the norm partials -> clip + AdamW + fake-quant + all-gather -> flag barrier.
+    With ``MYTHOS_NVLS=1`` the reduce-scatter reads through the NVLS multicast mapping of the
+    gradient buffers (``multimem.ld_reduce``: the sum is formed inside the NVSwitch) and the
+    all-gather is one ``multimem.st`` per 16 bytes. The reduce-scatter is overlapped with the
+    backward pass of the last micro-batch: as soon as a layer's gradients are complete (a hook on
+    the layer's input gradient) a side stream runs barrier + reduce-scatter for that layer's slice
+    of the flat buffer, so only the embedding's slice, the norm exchange and the optimizer kernel
+    remain after the backward pass.
 ``nccl`` (the baseline it is measured against): ``reduce_scatter_tensor``, ``all_reduce`` of the
     norm, the single-GPU AdamW kernel, ``all_gather_into_tensor`` of the master slice and a local
     re-quantisation.
@@ -62,6 +69,15 @@ class ZeroEngine:
             store = ParamStore(model, device, self.world_size, self.grad_buf.tensor, self.compute_buf.tensor)
             self._build_tables(store)
             self.part = torch.zeros(1, device=self.device, dtype=torch.float32)
+            use_mc = symm.nvls_enabled() and self.world_size > 1
+            self.grad_mc = self.grad_buf.multicast_ptr if use_mc else 0
+            self.compute_mc = self.compute_buf.multicast_ptr if use_mc else 0
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            # per-block partials of the gradient norm (+ a ticket word): added in a fixed order
+            self.rs_scratch = torch.zeros(sms * 8 + 2, device=self.device, dtype=torch.float32)
+            self._plan_buckets(model, store)
+            self._reduced: list[tuple[int, int]] = []   # slices of the flat buffer already reduce-scattered this step
         else:
             store = ParamStore(model, device, self.world_size)
         self.gshard = torch.zeros(store.shard, device=self.device, dtype=torch.float32)
@@ -71,6 +87,62 @@ class ZeroEngine:
         # every rank starts from rank 0's weights
         dist.broadcast(store.master, src=dist.get_global_rank(self.group, 0), group=self.group)
         return store
+
+    # ------------------------------------------------------------------ overlap with the backward pass
+    def _plan_buckets(self, model, store: ParamStore) -> None:
+        """One bucket per transformer block (its contiguous slice of the flat buffer) plus one for
+        everything after the last block (final norm, head). ``bucket[i]`` is complete when the
+        gradient of block i's input has been computed."""
+        self.buckets: dict[int, tuple[int, int]] = {}
+        layers = getattr(model, "layers", None)
+        if layers is None or not hasattr(model, "grad_ready_callback"):
+            return
+        by_param = {id(s.param): s for s in store.slots}
+        spans = []
+        for blk in layers:
+            sl = [by_param[id(p)] for p in blk.parameters() if id(p) in by_param]
+            if not sl:
+                return
+            spans.append((min(x.offset for x in sl), max(x.offset + (x.numel + ALIGN - 1) // ALIGN * ALIGN for x in sl)))
+        if any(a >= b for a, b in spans) or any(spans[i][1] > spans[i + 1][0] for i in range(len(spans) - 1)):
+            return                                  # blocks are not laid out one after another: no overlap
+        for i, sp in enumerate(spans):
+            self.buckets[i] = sp
+        if spans[-1][1] < store.total:
+            self.buckets[len(spans)] = (spans[-1][1], store.total)
+
+    def arm_overlap(self, model) -> None:
+        """Call before the backward pass of the step's LAST micro-batch."""
+        if self.mode != "fused" or not self.buckets or self.world_size == 1:
+            return
+        self.part.zero_()
+        self._reduced = []
+        model.grad_ready_callback = self._on_bucket_ready
+
+    def disarm_overlap(self, model) -> None:
+        if hasattr(model, "grad_ready_callback"):
+            model.grad_ready_callback = None
+
+    def _on_bucket_ready(self, index: int) -> None:
+        span = self.buckets.get(index)
+        if span is None:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(ev)
+            self.barrier_obj.sync()                      # every rank has finished this bucket's gradients
+            self._reduce_span(span[0], span[1], max_blocks=64)
+        self._reduced.append(span)
+
+    def _reduce_span(self, a: int, b: int, max_blocks: int = 0) -> None:
+        """Reduce-scatter of flat elements [a, b): this rank sums the part that lies in its shard."""
+        lo = self.rank * self.store.shard
+        s0, e0 = max(a, lo), min(b, lo + self.store.shard)
+        if s0 >= e0:
+            return
+        native.require().zero_reduce_scatter(self.grad_buf.ptrs, self.gshard[s0 - lo:e0 - lo], s0, self.part,
+                                             self.grad_mc, max_blocks, self.rs_scratch)
 
     @staticmethod
     def _fusable(slots) -> bool:
@@ -141,14 +213,24 @@ class ZeroEngine:
         lo = self.rank * st.shard
         if self.mode == "fused":
             C = native.require()
-            self.part.zero_()
+            done = sorted(getattr(self, "_reduced", []))
+            if done:
+                torch.cuda.current_stream().wait_stream(self.comm_stream)   # the overlapped buckets have landed
+            else:
+                self.part.zero_()
+            self._reduced = []
             self.barrier_obj.sync()                                   # every rank's gradients are complete
-            C.zero_reduce_scatter(self.grad_buf.ptrs, self.gshard, lo, self.part)
+            pos = 0
+            for a, b in done + [(st.total, st.total)]:                # whatever the backward pass did not cover
+                if a > pos:
+                    self._reduce_span(pos, a)
+                pos = max(pos, b)
             self.barrier_obj.sync(self.part)                          # norm partials exchanged; peers done reading
             C.zero_adamw_ste_allgather(st.master[lo:lo + st.shard], trainer.m, trainer.v, self.gshard,
                                        self.compute_buf.ptrs, lo, self.seg_fmt, self.seg_cb, self.cb8, self.cb4,
                                        self.barrier_obj.slots, trainer._last_grad_norm, c.max_grad_norm, lr,
-                                       c.beta1, c.beta2, c.eps, c.weight_decay, trainer.step, 1.0, self.rank)
+                                       c.beta1, c.beta2, c.eps, c.weight_decay, trainer.step, 1.0, self.rank,
+                                       self.compute_mc)
             self.barrier_obj.sync()                                   # every rank's compute image is complete
         else:
             dist.reduce_scatter_tensor(self.gshard, st.grad[: st.total], op=dist.ReduceOp.SUM, group=self.group)
@@ -185,6 +267,7 @@ class ZeroEngine:
         calls it at the same point, with no kernel of the engine in flight)."""
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
+        self.grad_mc = self.compute_mc = 0
         for name in ("grad_buf", "compute_buf", "barrier_obj", "gshard", "store", "cb8", "cb4", "seg_fmt", "seg_cb"):
             if hasattr(self, name):
                 setattr(self, name, None)

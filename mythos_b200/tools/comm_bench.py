@@ -82,6 +82,7 @@ def main(argv=None) -> int:
             print(json.dumps(row), flush=True)
 
     bar = symm.FlagBarrier(dev, group)
+    use_mc = symm.nvls_enabled()          # MYTHOS_NVLS=1: also time the multimem (in-switch) variants
 
     # ---------------------------------------------------------------- ZeRO reduce-scatter + norm
     n = a.params // (256 * W) * (256 * W)
@@ -104,6 +105,22 @@ def main(argv=None) -> int:
     t_f, t_n = _time(rs_fused, group, a.iters, a.warmup), _time(rs_nccl, group, a.iters, a.warmup)
     # local memory: this rank's slice is read by every rank (W reads) and the result written once
     report("zero_reduce_scatter_norm_fp32", t_f, shard * 4.0 * (W - 1), baseline_ms=t_n, hbm_bytes=shard * 4.0 * (W + 1))
+    if use_mc and gbuf.multicast_ptr:
+        want = gshard.clone()
+        gmc = torch.empty_like(gshard)
+
+        def rs_nvls():
+            bar.sync()
+            C.zero_reduce_scatter(gbuf.ptrs, gmc, rank * shard, part, gbuf.multicast_ptr, 0)
+            bar.sync(part)
+
+        t_m = _time(rs_nvls, group, a.iters, a.warmup)
+        err = float((gmc - want).abs().max() / want.abs().max())
+        assert err < 1e-5, f"multimem reduce-scatter differs from the peer-load sum: {err}"
+        report("zero_reduce_scatter_norm_fp32_nvls", t_m, shard * 4.0 * (W - 1), baseline_ms=t_n,
+               hbm_bytes=shard * 4.0 * (W + 1))
+    elif use_mc and rank == 0:
+        print(json.dumps({"note": "MYTHOS_NVLS=1 but the symmetric allocation has no multicast mapping"}), flush=True)
 
     # ---------------------------------------------------------------- ZeRO AdamW + STE + all-gather
     cbuf = symm.make_buffer(n, torch.bfloat16, dev, group)
@@ -118,9 +135,9 @@ def main(argv=None) -> int:
     cb4 = torch.zeros(1, 16, device=dev)
     gnorm = torch.zeros(1, device=dev)
 
-    def ag_fused():
+    def ag_fused(mc=0):
         C.zero_adamw_ste_allgather(master, m, v, gshard, cbuf.ptrs, rank * shard, seg_fmt, seg_cb, cb8, cb4, bar.slots,
-                                   gnorm, 1.0, 1e-4, 0.9, 0.95, 1e-8, 0.1, 10, 1.0, rank)
+                                   gnorm, 1.0, 1e-4, 0.9, 0.95, 1e-8, 0.1, 10, 1.0, rank, mc)
         bar.sync()
 
     full = torch.empty(n, device=dev)
@@ -137,6 +154,15 @@ def main(argv=None) -> int:
     # local memory: p, m, v, g read and p, m, v written in fp32, plus the bf16 image written by all W ranks
     report("zero_adamw_ste_allgather_bf16", t_f, shard * 2.0 * (W - 1), baseline_ms=t_n,
            hbm_bytes=shard * (28.0 + 2.0 * W))
+    if use_mc and cbuf.multicast_ptr:
+        t_m = _time(lambda: ag_fused(cbuf.multicast_ptr), group, a.iters, a.warmup)
+        # every rank's image must be identical after a multicast all-gather
+        digest = cbuf.tensor.view(torch.int16).long().sum().reshape(1)
+        digs = [torch.zeros_like(digest) for _ in range(W)]
+        dist.all_gather(digs, digest, group=group)
+        assert all(int(d) == int(digs[0]) for d in digs), "multicast all-gather left different images on the ranks"
+        report("zero_adamw_ste_allgather_bf16_nvls", t_m, shard * 2.0 * (W - 1), baseline_ms=t_n,
+               hbm_bytes=shard * (28.0 + 2.0 * W))
     del gbuf, cbuf, full, qout
     torch.cuda.empty_cache()
 
@@ -224,6 +250,21 @@ def main(argv=None) -> int:
 
     t_f, t_n = _time(tp_fused_gemm, group, a.iters, a.warmup), _time(tp_gemm_nccl, group, a.iters, a.warmup)
     t_p = _time(tp_gemm_pull, group, a.iters, a.warmup)
+    if use_mc and partc.multicast_ptr and outb.multicast_ptr:
+        want = outb.tensor.clone()
+
+        def tp_gemm_nvls():    # local GEMM, then the all-reduce inside the switch: multimem.ld_reduce + multimem.st
+            F.gemm(x, w, out=partc.tensor.view(Tp, N))
+            fbar.sync()
+            C.tp_allreduce_multimem(partc.multicast_ptr, outb.multicast_ptr, W, rank, Tp * N)
+            fbar.sync()
+
+        t_m = _time(tp_gemm_nvls, group, a.iters, a.warmup)
+        err = float((outb.tensor.float() - want.float()).abs().max() / want.float().abs().max())
+        assert err < 2e-2, f"multimem all-reduce differs from the pull all-reduce: {err}"
+        # in-switch reduction: each direction carries the output once ((W-1)/W up, the same down)
+        report(f"tp_gemm_then_nvls_allreduce_{Tp}x{N}x{K}", t_m, Tp * N * 2.0 * (W - 1) / W * 1.0 + Tp * N * 2.0 / W,
+               flops=2.0 * Tp * N * K, baseline_ms=t_n)
     t_g = _time(lambda: F.gemm(x, w, out=yb), group, a.iters, a.warmup)
     report(f"tp_gemm_then_pull_allreduce_{Tp}x{N}x{K}", t_p, 2.0 * Tp * N * 2.0 * (W - 1) / W, flops=2.0 * Tp * N * K,
            baseline_ms=t_n)

@@ -133,8 +133,13 @@ class Trainer:
                 ti = ti.to(self.device, non_blocking=True)
             with trace.span("forward", self.device):
                 loss = self.model(xi, ti, loss_scale=loss_scale)
+            overlap = self.dp is not None and i == n_micro - 1 and hasattr(self.dp, "arm_overlap")
+            if overlap:
+                self.dp.arm_overlap(self.model)      # gradient reduce-scatter per layer, under this backward pass
             with trace.span("backward", self.device):
                 loss.backward()
+            if overlap:
+                self.dp.disarm_overlap(self.model)
             if not st.bound:
                 st.gather_autograd_grads()
             total = loss.detach() if total is None else total + loss.detach()

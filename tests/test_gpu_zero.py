@@ -49,7 +49,7 @@ def test_reduce_scatter_adamw_ste_allgather_emulated_ranks():
     for r in range(world):
         C.zero_adamw_ste_allgather(masters[r][r * shard:(r + 1) * shard], ms[r], vs[r], gsh[r],
                                    [c.data_ptr() for c in compute], r * shard, seg_fmt, seg_cb, cb8, cb4, parts, gn,
-                                   max_norm, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, r)
+                                   max_norm, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, r, 0)
     torch.cuda.synchronize()
     assert abs(gn.item() - gsum.norm().item()) < 1e-3 * gsum.norm().item()
     # reference: AdamW on the clipped summed gradient, then per-segment quantisation

@@ -15,6 +15,8 @@ pytestmark = pytest.mark.gpu
 
 N_GPUS = torch.cuda.device_count() if torch.cuda.is_available() else 0
 WORLD_SIZES = [n for n in (2, 4, 8) if n <= N_GPUS] or [2]
+if os.environ.get("MYTHOS_TEST_WORLD_SIZES"):          # e.g. "8": only these sizes (each launch costs GPU time)
+    WORLD_SIZES = [int(x) for x in os.environ["MYTHOS_TEST_WORLD_SIZES"].split(",") if int(x) <= max(N_GPUS, 2)]
 needs_two = pytest.mark.skipif(N_GPUS < 2, reason="needs at least 2 GPUs")
 
 
