@@ -734,6 +734,32 @@ void paged_attn_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
                         status_ptr(status), cur_stream(), q.stride(0));
 }
 
+// q: [total_q, heads, head_dim] (new tokens of all sequences, packed; token stride free); caches [pages, 16, kv_heads, D].
+void flash_attn_paged_prefill(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
+                              const Tensor& cu_q, const Tensor& kv_lens, Tensor& out, int64_t max_q_len, double scale,
+                              const OptTensor& status) {
+  chk(q, BF16, "q");
+  chk_c(k_cache, BF16, "k_cache");
+  chk_c(v_cache, BF16, "v_cache");
+  chk_c(block_table, I32, "block_table");
+  chk_c(cu_q, I32, "cu_q");
+  chk_c(kv_lens, I32, "kv_lens");
+  chk(out, BF16, "out");
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q.stride(1) == q.size(2), "paged prefill: q must be [tokens, heads, head_dim]");
+  TORCH_CHECK(out.dim() == 3 && out.stride(2) == 1 && out.stride(1) == out.size(2) && out.size(0) == q.size(0) &&
+                  out.size(1) == q.size(1) && out.size(2) == q.size(2), "paged prefill: out must match q");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(1) == 16 && k_cache.size(3) == q.size(2) && v_cache.sizes() == k_cache.sizes(),
+              "paged prefill: caches must be [pages, 16, kv_heads, head_dim]");
+  const int64_t B = kv_lens.numel();
+  TORCH_CHECK(cu_q.numel() == B + 1 && block_table.dim() == 2 && block_table.size(0) >= B, "paged prefill: batch metadata");
+  c10::cuda::CUDAGuard guard(q.device());
+  mb::flash_attn_paged_prefill(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), (int)k_cache.size(0),
+                               block_table.data_ptr<int>(), (int)block_table.size(1), cu_q.data_ptr<int>(),
+                               kv_lens.data_ptr<int>(), out.data_ptr(), out.stride(0), (int)B, (int)q.size(0),
+                               (int)max_q_len, (int)q.size(1), (int)k_cache.size(2), (int)q.size(2), (float)scale,
+                               status_ptr(status), cur_stream());
+}
+
 void kv_append_int8(const Tensor& k, const Tensor& v, Tensor& k_cache, Tensor& v_cache, Tensor& k_scale, Tensor& v_scale,
                     const Tensor& block_table, const Tensor& positions, const Tensor& seq_ids) {
   chk(k, BF16, "k");
@@ -1054,6 +1080,7 @@ PYBIND11_MODULE(_C, m) {
     c10::cuda::CUDAGuard guard(status.device());
     mb::comm_set_abort_word(status.data_ptr<int>());
   });
+  m.def("flash_attn_paged_prefill", &flash_attn_paged_prefill);
   m.def("moe_route", &moe_route);
   m.def("moe_route_bwd", &moe_route_bwd);
   m.def("moe_publish_counts", &moe_publish_counts);

@@ -155,6 +155,14 @@ void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float*
 void flash_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq,
                             int heads, int kv_heads, int head_dim, long long q_tok_stride, long long kv_tok_stride,
                             long long o_tok_stride, bool causal, float scale, int* status, cudaStream_t stream);
+// Prefill attention over the paged KV cache (tcgen05, causal): q holds the NEW tokens of `batch` sequences
+// packed back to back (sequence b = rows cu_q[b] .. cu_q[b+1]); k_cache / v_cache are bf16 pages
+// [n_pages, 16, kv_heads, head_dim] addressed through block_table [batch, table_stride]; kv_lens[b] counts the
+// keys the last query of b sees (cached prefix + new tokens, which must already be in the pages).
+void flash_attn_paged_prefill(const void* q, long long q_tok_stride, const void* k_cache, const void* v_cache,
+                              int n_pages, const int* block_table, int table_stride, const int* cu_q, const int* kv_lens,
+                              void* o, long long o_tok_stride, int batch, int total_q, int max_q_len, int heads,
+                              int kv_heads, int head_dim, float scale, int* status, cudaStream_t stream);
 void flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                     void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch, int seq, int heads,
                     int kv_heads, int head_dim, bool causal, float scale, int* status, cudaStream_t stream);

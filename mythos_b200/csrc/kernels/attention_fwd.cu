@@ -40,11 +40,26 @@ struct FaFwdCfg {
   static constexpr int COL_O = 128;  // O0 at 128, O1 at 128 + D
 };
 
-template <int D>
+// PAGED: prefill attention whose K/V live in the paged cache. Queries are the new tokens of each
+// sequence, packed one sequence after another ([total_q, heads, D], sequence b = rows cu_q[b] ..
+// cu_q[b+1]); keys / values are read page by page (16 tokens each) through the block table, one TMA
+// box per page and 64-wide chunk, landing in the same swizzled tiles as the contiguous loads. The
+// first query of sequence b sits at position kv_lens[b] - q_len, so the kernel serves a whole prompt
+// (offset 0), one chunk of a long prompt, the remainder after a cached prefix, and ragged batches.
+struct PagedPrefillArgs {
+  const int* block_table;   // [batch, table_stride] page ids
+  const int* cu_q;          // [batch + 1] first query row of every sequence
+  const int* kv_lens;       // [batch] keys visible to the LAST query of the sequence (prefix + new tokens)
+  int table_stride;
+};
+constexpr int FA_PAGE = 16;
+
+template <int D, bool PAGED>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, __nv_bfloat16* __restrict__ o, float* __restrict__ lse,
-              int seq, int heads, int kv_heads, long long o_tok_stride, int causal, float scale_log2, int* status) {
+              int seq, int heads, int kv_heads, long long o_tok_stride, int causal, float scale_log2, int* status,
+              PagedPrefillArgs pa) {
   using Cfg = FaFwdCfg<D>;
   constexpr int DC = D / 64;  // 64-wide chunks of head_dim
   extern __shared__ uint8_t smem_raw[];
@@ -64,11 +79,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int h = blockIdx.y, b = blockIdx.z;
   const int hkv = h / (heads / kv_heads);
   const int q0 = qblk * 2 * FA_BM;
-  const int n_qt = (q0 + FA_BM < seq) ? 2 : 1;
+  // q_len queries (rows q_row0 .. of the query tensor) see kv_len keys; query i sits at position q_off + i
+  int q_len = seq, kv_len = seq, q_off = 0, q_row0 = 0;
+  if constexpr (PAGED) {
+    q_row0 = pa.cu_q[b];
+    q_len = pa.cu_q[b + 1] - q_row0;
+    kv_len = pa.kv_lens[b];
+    q_off = kv_len - q_len;
+    if (q0 >= q_len) return;                     // uniform over the CTA, before any barrier exists
+  }
+  const int n_qt = (q0 + FA_BM < q_len) ? 2 : 1;
   int J[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int hi = causal ? min(seq, q0 + (t + 1) * FA_BM) : seq;
+    const int hi = causal ? min(kv_len, q_off + min(q_len, q0 + (t + 1) * FA_BM)) : kv_len;
     J[t] = (t < n_qt) ? (hi + FA_BN - 1) / FA_BN : 0;
   }
   const int Jmax = max(J[0], J[1]);
@@ -106,7 +130,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       for (int t = 0; t < 2; ++t)
         for (int c = 0; c < DC; ++c)
           tma_load_4d(smem + Cfg::OFF_Q + t * Cfg::Q_BYTES + c * (FA_BM * 128), &tm_q, q_full, c * 64, h,
-                      q0 + t * FA_BM, b);
+                      q_row0 + q0 + t * FA_BM, PAGED ? 0 : b);
       for (int j = 0; j < Jmax; ++j) {
         const int st = j % FA_STAGES;
         const uint32_t ph = (j / FA_STAGES) & 1;
@@ -114,9 +138,25 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         mbar_arrive_expect_tx(&kv_full[st], Cfg::STAGE_BYTES);
         uint8_t* sk = smem + Cfg::OFF_KV + st * Cfg::STAGE_BYTES;
         uint8_t* sv = sk + Cfg::KV_BYTES;
-        for (int c = 0; c < DC; ++c) {
-          tma_load_4d(sk + c * (FA_BN * 128), &tm_k, &kv_full[st], c * 64, hkv, j * FA_BN, b);
-          tma_load_4d(sv + c * (FA_BN * 128), &tm_v, &kv_full[st], c * 64, hkv, j * FA_BN, b);
+        if constexpr (PAGED) {
+          // four pages of 16 tokens per kv tile; pages past the sequence's end (never visible: the
+          // causal limit masks them) read page 0 so that the transaction count stays fixed
+          const int* row = pa.block_table + (long long)b * pa.table_stride;
+#pragma unroll
+          for (int p = 0; p < FA_BN / FA_PAGE; ++p) {
+            const int lp = j * (FA_BN / FA_PAGE) + p;
+            int page = (lp * FA_PAGE < kv_len && lp < pa.table_stride) ? row[lp] : 0;
+            if (page < 0) page = 0;
+            for (int c = 0; c < DC; ++c) {
+              tma_load_4d(sk + c * (FA_BN * 128) + p * (FA_PAGE * 128), &tm_k, &kv_full[st], c * 64, hkv, 0, page);
+              tma_load_4d(sv + c * (FA_BN * 128) + p * (FA_PAGE * 128), &tm_v, &kv_full[st], c * 64, hkv, 0, page);
+            }
+          }
+        } else {
+          for (int c = 0; c < DC; ++c) {
+            tma_load_4d(sk + c * (FA_BN * 128), &tm_k, &kv_full[st], c * 64, hkv, j * FA_BN, b);
+            tma_load_4d(sv + c * (FA_BN * 128), &tm_v, &kv_full[st], c * 64, hkv, j * FA_BN, b);
+          }
         }
       }
     }
@@ -183,7 +223,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int t = (warp - 2) >> 2;  // tile of this warpgroup
     const int quarter = warp & 3;   // TMEM lane quarter this warp may access
     const int r = quarter * 32 + lane;
-    const int q_row = q0 + t * FA_BM + r;
+    const int q_row = q0 + t * FA_BM + r;      // row within the sequence's queries
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const uint32_t t_s = tmem_base + Cfg::COL_S + t * FA_BN + lane_sel;
     const uint32_t t_o = tmem_base + Cfg::COL_O + t * D + lane_sel;
@@ -201,7 +241,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tmem_ld_wait();
       float* s = reinterpret_cast<float*>(&sr[0][0]);
       const int kv0 = j * FA_BN;
-      const int limit = causal ? min(seq - 1, q_row) : seq - 1;  // last visible kv index
+      const int limit = causal ? min(kv_len - 1, q_off + q_row) : kv_len - 1;  // last visible kv index
       if (kv0 + FA_BN - 1 > limit) {
 #pragma unroll
         for (int i = 0; i < FA_BN; ++i)
@@ -267,13 +307,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) {
         tc_fence_after();
         const float inv_l = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* orow = o + ((long long)b * seq + q_row) * o_tok_stride + (long long)h * D;
+        __nv_bfloat16* orow = o + (PAGED ? (long long)(q_row0 + q_row) : (long long)b * seq + q_row) * o_tok_stride +
+                              (long long)h * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t orr[32];
           tmem_ld32(t_o + c * 32, orr);
           tmem_ld_wait();
-          if (q_row < seq) {
+          if (q_row < q_len) {
             uint4* p4 = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -286,7 +327,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             }
           }
         }
-        if (q_row < seq && lse) lse[((long long)b * heads + h) * seq + q_row] = m_ref * 0.6931471805599453f + logf(l);
+        if (q_row < q_len && lse && !PAGED)
+          lse[((long long)b * heads + h) * seq + q_row] = m_ref * 0.6931471805599453f + logf(l);
       }
     }
   }
@@ -329,21 +371,68 @@ void flash_attn_fwd_strided(const void* q, const void* k, const void* v, void* o
   if (head_dim == 128) {
     static bool configured = false;
     if (!configured) {
-      MB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      MB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FaFwdCfg<128>::SMEM_BYTES));
       configured = true;
     }
-    fa_fwd_kernel<128><<<grid, FA_THREADS, FaFwdCfg<128>::SMEM_BYTES, stream>>>(
-        tq, tk, tv, (__nv_bfloat16*)o, lse, seq, heads, kv_heads, o_tok_stride, causal ? 1 : 0, scale_log2, status);
+    fa_fwd_kernel<128, false><<<grid, FA_THREADS, FaFwdCfg<128>::SMEM_BYTES, stream>>>(
+        tq, tk, tv, (__nv_bfloat16*)o, lse, seq, heads, kv_heads, o_tok_stride, causal ? 1 : 0, scale_log2, status,
+        PagedPrefillArgs{});
   } else {
     static bool configured = false;
     if (!configured) {
-      MB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      MB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FaFwdCfg<64>::SMEM_BYTES));
       configured = true;
     }
-    fa_fwd_kernel<64><<<grid, FA_THREADS, FaFwdCfg<64>::SMEM_BYTES, stream>>>(
-        tq, tk, tv, (__nv_bfloat16*)o, lse, seq, heads, kv_heads, o_tok_stride, causal ? 1 : 0, scale_log2, status);
+    fa_fwd_kernel<64, false><<<grid, FA_THREADS, FaFwdCfg<64>::SMEM_BYTES, stream>>>(
+        tq, tk, tv, (__nv_bfloat16*)o, lse, seq, heads, kv_heads, o_tok_stride, causal ? 1 : 0, scale_log2, status,
+        PagedPrefillArgs{});
+  }
+  count_launch();
+  check_launch();
+}
+
+void flash_attn_paged_prefill(const void* q, long long q_tok_stride, const void* k_cache, const void* v_cache,
+                              int n_pages, const int* block_table, int table_stride, const int* cu_q, const int* kv_lens,
+                              void* o, long long o_tok_stride, int batch, int total_q, int max_q_len, int heads,
+                              int kv_heads, int head_dim, float scale, int* status, cudaStream_t stream) {
+  MB_REQUIRE(head_dim == 64 || head_dim == 128, "flash_attn_paged_prefill: head_dim must be 64 or 128");
+  MB_REQUIRE(heads % kv_heads == 0, "flash_attn_paged_prefill: heads must be a multiple of kv_heads");
+  MB_REQUIRE(q_tok_stride % 8 == 0 && o_tok_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0,
+             "flash_attn_paged_prefill: strides / alignment");
+  if (batch == 0 || total_q == 0 || max_q_len == 0) return;
+  const CUtensorMap tq = make_bshd_map(q, 1, total_q, heads, head_dim, q_tok_stride, FA_BM);
+  // pages: [n_pages, 16 tokens, kv_heads, head_dim]; one box = 16 tokens x 64 columns of one head
+  auto page_map = [&](const void* base) {
+    uint64_t dims[4] = {(uint64_t)head_dim, (uint64_t)kv_heads, (uint64_t)FA_PAGE, (uint64_t)n_pages};
+    uint64_t strides[3] = {(uint64_t)head_dim * 2, (uint64_t)kv_heads * head_dim * 2,
+                           (uint64_t)FA_PAGE * kv_heads * head_dim * 2};
+    uint32_t box[4] = {64, 1, (uint32_t)FA_PAGE, 1};
+    return make_tensor_map(base, TmaDType::BF16, 4, dims, strides, box, true);
+  };
+  const CUtensorMap tk = page_map(k_cache), tv = page_map(v_cache);
+  const dim3 grid((max_q_len + 2 * FA_BM - 1) / (2 * FA_BM), heads, batch);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  PagedPrefillArgs pa{block_table, cu_q, kv_lens, table_stride};
+  if (head_dim == 128) {
+    static bool configured = false;
+    if (!configured) {
+      MB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FaFwdCfg<128>::SMEM_BYTES));
+      configured = true;
+    }
+    fa_fwd_kernel<128, true><<<grid, FA_THREADS, FaFwdCfg<128>::SMEM_BYTES, stream>>>(
+        tq, tk, tv, (__nv_bfloat16*)o, nullptr, total_q, heads, kv_heads, o_tok_stride, 1, scale_log2, status, pa);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      MB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FaFwdCfg<64>::SMEM_BYTES));
+      configured = true;
+    }
+    fa_fwd_kernel<64, true><<<grid, FA_THREADS, FaFwdCfg<64>::SMEM_BYTES, stream>>>(
+        tq, tk, tv, (__nv_bfloat16*)o, nullptr, total_q, heads, kv_heads, o_tok_stride, 1, scale_log2, status, pa);
   }
   count_launch();
   check_launch();

@@ -75,6 +75,7 @@ class TPContext:
         self.slot_stride = ONESHOT_MAX_TOKENS * hidden
         self.staging = [symm.make_buffer(self.world * self.slot_stride, torch.bfloat16, device, group).zero_()
                         for _ in range(2)]
+        self.max_tokens = max_tokens
         big = max(max_tokens, ONESHOT_MAX_TOKENS) * hidden
         self.part = symm.make_buffer(big, torch.bfloat16, device, group)
         self.out = [symm.make_buffer(big, torch.bfloat16, device, group) for _ in range(2)]
@@ -170,6 +171,11 @@ class InferenceEngine:
         self._scratch = None
         self._counters = None
         self.fused_decode = True     # decode steps use the fused epilogue kernels when the model allows
+        # tokens per pass of the chunked paged prefill (all sequences of the pass together); under tensor
+        # parallelism a pass must also fit the symmetric all-reduce buffers
+        self.prefill_chunk = 8192 if tp is None else min(8192, getattr(tp, "max_tokens", 8192))
+        # generate(): equal-length batches above this many prompt tokens are prefilled in chunks
+        self.prefill_chunk_threshold = 1 << 30
         self.last_prefix_hit = 0     # tokens of the latest start_sequence that came from shared pages
 
     # ------------------------------------------------------------------ weights
@@ -407,9 +413,12 @@ class InferenceEngine:
             n, stream = self._row_parallel_norm(L.down, h, gamma, stream)
         return n
 
-    def _forward(self, ids, pos, seq_ids, ctx_lens, prefill_shape=None):
-        """ids/pos/seq_ids: int32 [T]; ctx_lens int32 [B] (decode). Returns final hidden [T, d]."""
-        if prefill_shape is None and self.fused_decode and self._fused_decode_ok(ids.numel()):
+    def _forward(self, ids, pos, seq_ids, ctx_lens, prefill_shape=None, paged=None):
+        """ids/pos/seq_ids: int32 [T]; ctx_lens int32 [B] (decode). Returns final hidden [T, d].
+        ``paged`` = (cu_q, kv_lens, table_rows, max_q_len): the tokens are new tokens of several
+        sequences, packed; their K/V go to the pages first and attention is the tcgen05 prefill kernel
+        over the paged cache (prefix + new tokens)."""
+        if prefill_shape is None and paged is None and self.fused_decode and self._fused_decode_ok(ids.numel()):
             return self._forward_decode(ids, pos, seq_ids, ctx_lens)
         cfg, C = self.cfg, native.require()
         D, H, Hkv = cfg.head_dim, self.h_local, self.hkv_local
@@ -432,7 +441,13 @@ class InferenceEngine:
                                  self.cache.v_scale[li], table, pos, seq_ids)
             else:
                 C.kv_append(k, v, self.cache.k[li], self.cache.v[li], table, pos, seq_ids)
-            if prefill_shape is not None:
+            if paged is not None:
+                cu_q, kv_lens, rows, max_q = paged
+                o = torch.empty(T, H, D, device=self.device, dtype=torch.bfloat16)
+                C.flash_attn_paged_prefill(q, self.cache.k[li], self.cache.v[li], rows, cu_q, kv_lens, o, max_q, scale,
+                                           native.status_word(self.device))
+                o = o.view(T, H * D)
+            elif prefill_shape is not None:
                 B, S = prefill_shape
                 o = torch.empty(B, S, H, D, device=self.device, dtype=torch.bfloat16)
                 lse = torch.empty(B, H, S, device=self.device, dtype=torch.float32)
@@ -473,6 +488,54 @@ class InferenceEngine:
             return lg
         return _gather_columns(lg, self.tp)
 
+    # ------------------------------------------------------------------ paged / chunked prefill
+    def _paged_prefill_ok(self) -> bool:
+        return not self.cache.int8 and self.cfg.head_dim in (64, 128) and self.cache.page_size == 16
+
+    @torch.no_grad()
+    def _prefill_paged(self, seqs, token_lists, bases):
+        """Run the new tokens ``token_lists[i]`` of sequence ``seqs[i]`` (which already holds
+        ``bases[i]`` tokens; pages reserved) in one pass. Returns the hidden states of all new
+        tokens, packed in the order given, and the row offsets of the sequences."""
+        dev = self.device
+        lens = [len(t) for t in token_lists]
+        ids = torch.tensor([x for t in token_lists for x in t], dtype=torch.int32, device=dev)
+        pos = torch.cat([torch.arange(b, b + n, dtype=torch.int32) for b, n in zip(bases, lens)]).to(dev)
+        sid = torch.cat([torch.full((n,), s, dtype=torch.int32) for s, n in zip(seqs, lens)]).to(dev)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        cu_q = torch.tensor(cu, dtype=torch.int32, device=dev)
+        kv_lens = torch.tensor([b + n for b, n in zip(bases, lens)], dtype=torch.int32, device=dev)
+        rows = self.cache.block_table.index_select(0, torch.tensor(seqs, dtype=torch.long, device=dev)).contiguous()
+        h = self._forward(ids, pos, sid, None, paged=(cu_q, kv_lens, rows, max(lens)))
+        return h, cu
+
+    @torch.no_grad()
+    def _prefill_chunked(self, seqs, token_lists, bases=None):
+        """Prefill through the paged kernel in passes of at most ``prefill_chunk`` tokens: any mix of
+        prompt lengths, prompts longer than one pass, prompts that continue a cached prefix
+        (``bases``). Advances the sequences; returns the hidden state of each sequence's last token."""
+        cache = self.cache
+        B = len(seqs)
+        done = list(bases) if bases is not None else [0] * B
+        start = list(done)
+        total = [start[i] + len(token_lists[i]) for i in range(B)]
+        last = [None] * B
+        budget = max(16, getattr(self, "prefill_chunk", 8192))
+        while any(done[i] < total[i] for i in range(B)):
+            active = [i for i in range(B) if done[i] < total[i]]
+            per = max(16, budget // len(active))
+            part = [token_lists[i][done[i] - start[i]: done[i] - start[i] + per] for i in active]
+            h, cu = self._prefill_paged([seqs[i] for i in active], part, [done[i] for i in active])
+            for j, i in enumerate(active):
+                n = len(part[j])
+                cache.advance(seqs[i], n)
+                done[i] += n
+                if done[i] == total[i]:
+                    last[i] = h[cu[j + 1] - 1]
+        return torch.stack(last)
+
     def _prepare_decode_scratch(self, batch: int, max_ctx: int):
         pairs = max(1, batch * self.hkv_local)
         splits = max(1, min(32, (6 * self._sms + pairs - 1) // pairs, (max_ctx + 255) // 256))
@@ -488,32 +551,54 @@ class InferenceEngine:
     @torch.no_grad()
     def generate(self, prompts, max_new_tokens: int = 32, sampler: SamplerConfig | None = None, stream_callback=None,
                  eos_id: int | None = None, use_graph: bool = True) -> GenerationResult:
-        """prompts: list of equal-length token lists (or an int tensor [B, S])."""
+        """prompts: an int tensor [B, S] or a list of token lists, which may differ in length.
+        Equal-length prompts that fit one pass run the contiguous flash-attention prefill; ragged
+        batches and prompts longer than ``prefill_chunk`` tokens per pass go through the paged
+        prefill kernel in chunks."""
         sampler = sampler or SamplerConfig(temperature=0.0)
-        ids = torch.as_tensor(prompts, dtype=torch.int32)
-        B, S = ids.shape
-        if B > self.max_batch or S + max_new_tokens > self.max_seq_len:
+        if torch.is_tensor(prompts):
+            lists = [[int(x) for x in row] for row in prompts.tolist()]
+        else:
+            lists = [[int(x) for x in row] for row in prompts]
+        lens = [len(t) for t in lists]
+        B, S = len(lists), max(lens)
+        if B > self.max_batch or S + max_new_tokens > self.max_seq_len or min(lens) < 1:
             raise ValueError("batch or sequence length exceeds the engine's limits")
+        ragged = len(set(lens)) > 1
         cache = self.cache
         seqs = [cache.new_sequence() for _ in range(B)]
-        for s in seqs:
-            cache.reserve(s, S + max_new_tokens)
+        for s, n in zip(seqs, lens):
+            cache.reserve(s, n + max_new_tokens)
         cache.sync_tables()
         dev = self.device
         seq_t = torch.tensor(seqs, dtype=torch.int32, device=dev)
-        stats = GenerationStats(prompt_tokens=B * S)
+        stats = GenerationStats(prompt_tokens=sum(lens))
         self._prepare_decode_scratch(B, S + max_new_tokens)
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         # ---- prefill
-        ids_d = ids.to(dev).reshape(-1)
-        pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
+        chunked = (ragged or B * S > getattr(self, "prefill_chunk_threshold", 1 << 30)) and self._paged_prefill_ok()
         with trace.span("prefill", dev):
-            h = self._forward(ids_d, pos, seq_t.repeat_interleave(S), None, prefill_shape=(B, S))
-            last = h.view(B, S, -1)[:, -1, :].contiguous()
-            tok = sample(self._logits(last), sampler, step=0)
-        for s in seqs:
-            cache.advance(s, S)
+            if chunked:
+                last = self._prefill_chunked(seqs, lists)
+            elif ragged:          # int8 pages: one contiguous prefill per sequence
+                rows = []
+                for s, t in zip(seqs, lists):
+                    n = len(t)
+                    hh = self._forward(torch.tensor(t, dtype=torch.int32, device=dev),
+                                       torch.arange(n, device=dev, dtype=torch.int32),
+                                       torch.full((n,), s, device=dev, dtype=torch.int32), None, prefill_shape=(1, n))
+                    cache.advance(s, n)
+                    rows.append(hh[-1])
+                last = torch.stack(rows)
+            else:
+                ids_d = torch.tensor(lists, dtype=torch.int32).to(dev).reshape(-1)
+                pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
+                h = self._forward(ids_d, pos, seq_t.repeat_interleave(S), None, prefill_shape=(B, S))
+                last = h.view(B, S, -1)[:, -1, :].contiguous()
+                for s in seqs:
+                    cache.advance(s, S)
+            tok = sample(self._logits(last.contiguous()), sampler, step=0)
         torch.cuda.synchronize(dev)
         stats.ttft_s = time.perf_counter() - t0
         out = [tok.clone()]
@@ -521,8 +606,8 @@ class InferenceEngine:
             stream_callback(0, tok)
         # ---- decode
         cur = tok.clone()
-        posd = torch.full((B,), S, device=dev, dtype=torch.int32)
-        ctx = torch.full((B,), S + 1, device=dev, dtype=torch.int32)
+        posd = torch.tensor(lens, device=dev, dtype=torch.int32)
+        ctx = posd + 1
         graph = None
         graph_ok = use_graph and sampler.greedy and stream_callback is None and eos_id is None
 
@@ -668,19 +753,21 @@ class InferenceEngine:
         """Prefill one request. Returns ``(seq, logits)`` with the logits of the last prompt token
         ([1, V]). With ``reuse_prefix`` the full pages of an earlier prompt with the same head are
         mapped into the new sequence (their reference counts go up) and only the remaining tokens
-        are computed: their K/V are appended to fresh pages and their queries attend over the paged
-        cache (shared prefix + the new tokens before them) in chunks of at most ``max_batch``
-        tokens. Without a cached prefix, or when the hit covers less than half of the prompt, the
-        whole prompt runs through the flash-attention prefill."""
+        are computed: their K/V are appended to fresh pages and the tcgen05 prefill kernel attends
+        over the paged cache (shared prefix + the new tokens before them). Prompts longer than
+        ``prefill_chunk`` tokens run in several such passes. With int8 pages the remainder goes
+        through the decode kernel instead, and a hit below half of the prompt is not used."""
         ids = [int(t) for t in prompt_ids]
         cache = self.cache
         seq = cache.new_sequence()
         S = len(ids)
         # at least the last token is always computed: its logits are the result
         covered = cache.share_prefix(seq, ids[:-1]) if reuse_prefix and S > 1 else 0
-        if 0 < covered < S // 2:
-            # A short hit is not worth it: the rest would go through the decode kernel in chunks of
-            # max_batch tokens, each chunk a full pass over the weights. Recompute the whole prompt.
+        paged_ok = self._paged_prefill_ok()
+        if 0 < covered < S // 2 and not paged_ok:
+            # Without the paged prefill kernel (int8 pages) the rest would go through the decode kernel
+            # in chunks of max_batch tokens, each a full pass over the weights: a short hit is not
+            # worth it. Recompute the whole prompt.
             cache.free_sequence(seq)
             seq = cache.new_sequence()
             covered = 0
@@ -689,13 +776,14 @@ class InferenceEngine:
         dev = self.device
         self._prepare_decode_scratch(self.max_batch, self.max_seq_len)
         self.last_prefix_hit = covered
-        if covered == 0:
+        if covered == 0 and not (paged_ok and S > getattr(self, "prefill_chunk", 8192)):
             t = torch.tensor(ids, dtype=torch.int32, device=dev)
             pos = torch.arange(S, device=dev, dtype=torch.int32)
             sid = torch.full((S,), seq, device=dev, dtype=torch.int32)
             h = self._forward(t, pos, sid, None, prefill_shape=(1, S))
             cache.advance(seq, S)
         else:
+            # remainder after a cached prefix, or a prompt longer than one pass: chunked paged prefill
             h = self._extend_sequence(seq, ids[covered:])
         if reuse_prefix:
             cache.publish_prefix(seq, ids)
@@ -708,6 +796,10 @@ class InferenceEngine:
         table row is the sequence's and whose context length is its own position + 1, so the paged
         decode kernel gives causal attention over prefix and chunk."""
         cache, dev = self.cache, self.device
+        if self._paged_prefill_ok():
+            # the tcgen05 prefill kernel over the paged cache (shared prefix + the new tokens), in
+            # passes of at most prefill_chunk tokens
+            return self._prefill_chunked([seq], [list(new_ids)], bases=[cache.lens[seq]])[-1:]
         step = max(1, min(self.max_batch, ONESHOT_MAX_TOKENS))
         h = None
         for lo in range(0, len(new_ids), step):

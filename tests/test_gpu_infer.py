@@ -637,3 +637,96 @@ def test_zero_padded_ffn_shard_equals_the_unpadded_one():
                                                  ffn_hidden_size=192, max_seq_len=64, weight_format="oil8",
                                                  oil_block_size=64), seed=1, device="cuda", max_batch=2, max_seq_len=64,
                                ffn_multiple=128)
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(4, 2, 128), (2, 2, 64)])
+def test_paged_prefill_attention_ragged_prefix_and_partial_pages(H, Hkv, D):
+    """tcgen05 prefill attention reading K/V from 16-token pages through the block table: ragged
+    batch, queries that start after a cached prefix, last pages partly filled; against the fp32
+    reference attention over prefix + chunk."""
+    from mythos_b200.ops import native, reference as ref
+
+    C = native.require()
+    torch.manual_seed(H * 10 + D)
+    prefix = [0, 37, 300, 16]                  # cached tokens before the new ones
+    new = [70, 300, 5, 129]                    # new (query) tokens per sequence
+    B = len(new)
+    pages_per = [(p + n + 15) // 16 for p, n in zip(prefix, new)]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages)[: sum(pages_per)].tolist()
+    table = torch.zeros(B, max(pages_per) + 2, dtype=torch.int32)
+    kc = torch.zeros(n_pages, 16, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    ks, vs, qs = [], [], []
+    it = iter(perm)
+    for b in range(B):
+        L = prefix[b] + new[b]
+        k = (torch.randn(L, Hkv, D) * 0.5).to(torch.bfloat16)
+        v = (torch.randn(L, Hkv, D) * 0.5).to(torch.bfloat16)
+        q = (torch.randn(new[b], H, D) * 0.5).to(torch.bfloat16)
+        for lp in range(pages_per[b]):
+            pg = next(it)
+            table[b, lp] = pg
+            n = min(16, L - lp * 16)
+            kc[pg, :n] = k[lp * 16: lp * 16 + n].cuda()
+            vc[pg, :n] = v[lp * 16: lp * 16 + n].cuda()
+        ks.append(k); vs.append(v); qs.append(q)
+    q_all = torch.cat(qs).cuda()
+    cu_q = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device="cuda")
+    kv_lens = torch.tensor([p + n for p, n in zip(prefix, new)], dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q_all)
+    C.flash_attn_paged_prefill(q_all, kc, vc, table.cuda(), cu_q, kv_lens, out, max(new), D ** -0.5,
+                               native.status_word("cuda"))
+    torch.cuda.synchronize()
+    off = 0
+    for b in range(B):
+        L, n = prefix[b] + new[b], new[b]
+        qf = torch.zeros(1, L, H, D)
+        qf[0, prefix[b]:] = qs[b].float()
+        o_ref, _ = ref.attention(qf, ks[b].float()[None], vs[b].float()[None], True, D ** -0.5)
+        got = out[off:off + n].float().cpu()
+        want = o_ref[0, prefix[b]:]
+        assert (got - want).abs().max() < 3e-2, (b, float((got - want).abs().max()))
+        off += n
+
+
+def test_chunked_paged_prefill_and_ragged_generate_match_contiguous_prefill():
+    """A prompt prefilled in chunks through the paged kernel, a prompt continued after a cached
+    prefix, and a ragged batch give the logits / first tokens of the contiguous one-pass prefill."""
+    from mythos_b200.infer.engine import InferenceEngine
+    from mythos_b200.models import DenseModel, TransformerConfig
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=2, head_dim=128,
+                            ffn_hidden_size=512, max_seq_len=512, oil_block_size=256, codebook_group=2)
+    with torch.device("cuda"):
+        model = DenseModel(cfg)
+    eng = InferenceEngine.from_model(model, device="cuda", max_batch=4, max_seq_len=512)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab_size, (200,), generator=g).tolist()
+    s0, l0 = eng.start_sequence(ids, reuse_prefix=False)            # contiguous flash-attention prefill
+    eng.prefill_chunk = 64                                           # 200 tokens -> four paged passes
+    s1, l1 = eng.start_sequence(ids, reuse_prefix=False)
+    scale = float(l0.float().abs().max())
+    assert float((l0.float() - l1.float()).abs().max()) < 3e-2 * scale
+    assert int(l0.float().argmax()) == int(l1.float().argmax())
+    # continuation after a cached prefix: 160 shared tokens (10 pages), 40 new ones through the prefill kernel
+    eng.reset_context()
+    eng.prefill_chunk = 8192
+    sa, _ = eng.start_sequence(ids[:170], reuse_prefix=True)
+    sb, lb = eng.start_sequence(ids, reuse_prefix=True)
+    assert eng.last_prefix_hit == 160
+    assert float((l0.float() - lb.float()).abs().max()) < 3e-2 * scale
+    # ragged batch: first generated token of every prompt equals the single-sequence result
+    eng.reset_context()
+    lens = [70, 128, 33]
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    want = []
+    for p in prompts:
+        s, lg = eng.start_sequence(p, reuse_prefix=False)
+        want.append(int(lg.float().argmax()))
+        eng.release(s)
+    res = eng.generate(prompts, max_new_tokens=4, use_graph=False)
+    assert [t[0] for t in res.tokens] == want
+    res_g = eng.generate(prompts, max_new_tokens=4, use_graph=True)
+    assert res_g.tokens == res.tokens
