@@ -200,7 +200,7 @@ constexpr int MAX_PEERS = 16;
 struct PeerPtrs {
   void* p[MAX_PEERS];  // the same symmetric buffer as mapped on this rank, one pointer per rank
 };
-enum : int { ZERO_FMT_CAST = 0, ZERO_FMT_OIL8 = 1, ZERO_FMT_OIL4 = 2, ZERO_FMT_I2S = 3 };
+enum : int { ZERO_FMT_CAST = 0, ZERO_FMT_OIL8 = 1, ZERO_FMT_OIL4 = 2, ZERO_FMT_I2S = 3, ZERO_FMT_BINARY = 4 };
 struct ZeroFusedArgs {
   float *p, *m, *v;            // local fp32 shard of master weights and Adam moments, n elements
   const float* g;              // local reduced gradient shard

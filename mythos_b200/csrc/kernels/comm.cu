@@ -238,6 +238,13 @@ __global__ void zero_adamw_ste_allgather_kernel(ZeroFusedArgs a, const int* abor
       const float inv = scale > 0.f ? 1.f / scale : 0.f;
 #pragma unroll
       for (int k = 0; k < 8; ++k) q[k] = fminf(1.f, fmaxf(-1.f, rintf(p[k] * inv))) * scale;
+    } else if (fmt == ZERO_FMT_BINARY) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += fabsf(p[k]);
+      s = warp_sum(s) * (1.f / 256.f);           // mean |w| of the 256-weight block
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q[k] = p[k] > 0.f ? s : -s;
     } else {
 #pragma unroll
       for (int k = 0; k < 8; ++k) q[k] = p[k];

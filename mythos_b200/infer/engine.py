@@ -129,6 +129,32 @@ def _zero_ffn_padding(up: QuantLinear, down: QuantLinear, f_loc: int, f_pad: int
     down.packed.view(down.N, down.K // 4)[:, f_loc // 4:] = zero
 
 
+def _zero_padded_heads(qkv: QuantLinear, o: QuantLinear, eng, cfg: TransformerConfig) -> None:
+    """Synthetic engine: set the q / k / v rows and the output-projection columns of this rank's padded
+    heads (global head index >= the model's head count) to exact zeros."""
+    D, hl, kl = cfg.head_dim, eng.h_local, eng.hkv_local
+    real_q = max(0, min(hl, cfg.num_heads - eng.rank * hl))
+    real_kv = max(0, min(kl, cfg.kv_heads - eng.rank * kl))
+    spans = [(real_q * D, hl * D), (hl * D + real_kv * D, (hl + kl) * D), ((hl + kl) * D + real_kv * D, (hl + 2 * kl) * D)]
+    if qkv.fmt == "i2s":
+        rows = qkv.packed.view(qkv.N, qkv.K // 4)
+        for a, b in spans:
+            rows[a:b] = 0x55                               # trit code 1 = zero, four per byte
+        o.packed.view(o.N, o.K // 4)[:, real_q * D // 4:] = 0x55
+    else:                                                  # unquantised weights
+        for a, b in spans:
+            qkv.dense[a:b] = 0
+        o.dense[:, real_q * D:] = 0
+
+
+def _pad_rows(w: torch.Tensor, start: int, size: int, padded: int) -> torch.Tensor:
+    """Rows [start, start + size) of w followed by zero rows up to ``padded`` rows."""
+    part = w[start:start + size]
+    if padded == size:
+        return part
+    return torch.cat([part, part.new_zeros(padded - size, w.shape[1])], dim=0)
+
+
 def _embed_block(cfg: TransformerConfig) -> int:
     return cfg.oil_block_size if cfg.hidden_size % cfg.oil_block_size == 0 else 64
 
@@ -152,10 +178,19 @@ class InferenceEngine:
         self.page_size = page_size
         self.world = tp.world if tp is not None else 1
         self.rank = tp.rank if tp is not None else 0
-        if cfg.num_heads % self.world or cfg.kv_heads % self.world:
-            raise ValueError(f"heads ({cfg.num_heads}/{cfg.kv_heads}) must divide by the tensor-parallel size {self.world}")
-        self.h_local = cfg.num_heads // self.world
-        self.hkv_local = cfg.kv_heads // self.world
+        # Heads that do not divide by the tensor-parallel size are padded with zero heads (zero q / k / v
+        # rows, zero output-projection columns: a padded head attends uniformly over zero values and adds
+        # nothing). 20 heads on 8 ranks become 24, three per rank. Needs a format with an exact zero.
+        group = cfg.num_heads // cfg.kv_heads
+        self.hkv_eff = (cfg.kv_heads + self.world - 1) // self.world * self.world
+        self.h_eff = self.hkv_eff * group
+        if self.h_eff != cfg.num_heads:
+            af = cfg.attn_format or cfg.weight_format
+            if af not in ("i2s", "bf16", "fp16", "fp32"):
+                raise ValueError(f"heads ({cfg.num_heads}/{cfg.kv_heads}) do not divide by the tensor-parallel size "
+                                 f"{self.world}; zero-padding them needs I2_S or unquantised attention weights, not {af}")
+        self.h_local = self.h_eff // self.world
+        self.hkv_local = self.hkv_eff // self.world
         pages_per_seq = (self.max_seq_len + page_size - 1) // page_size
         self.cache = PagedKVCache(cfg.num_layers, self.hkv_local, cfg.head_dim, kv_pages or max_batch * pages_per_seq,
                                   page_size, max_batch, pages_per_seq, self.device,
@@ -204,6 +239,19 @@ class InferenceEngine:
                 L.o = QuantLinear.from_oil_linear(att.o_proj)
                 L.up = QuantLinear.from_oil_linear(ffn.up_proj)
                 L.down = QuantLinear.from_oil_linear(ffn.down_proj)
+            elif eng.h_eff != H:
+                # zero-padded heads: shard the padded float weights (formats with an exact zero only)
+                wq = att.qkv_proj.weight.detach().float()
+                He, Ke, hl, kl = eng.h_eff, eng.hkv_eff, eng.h_local, eng.hkv_local
+                qp = _pad_rows(wq, 0, H * D, He * D)[r * hl * D:(r + 1) * hl * D]
+                kp = _pad_rows(wq, H * D, Hkv * D, Ke * D)[r * kl * D:(r + 1) * kl * D]
+                vp = _pad_rows(wq, (H + Hkv) * D, Hkv * D, Ke * D)[r * kl * D:(r + 1) * kl * D]
+                fmt = att.qkv_proj.fmt if att.qkv_proj.fmt == "i2s" else "bf16"
+                L.qkv = QuantLinear.from_float(torch.cat([qp, kp, vp]).contiguous().to(dev), fmt, att.qkv_proj.block_size)
+                wo = att.o_proj.weight.detach().float()
+                wo = torch.cat([wo, wo.new_zeros(wo.shape[0], (He - H) * D)], dim=1)[:, r * hl * D:(r + 1) * hl * D]
+                L.o = QuantLinear.from_float(wo.contiguous().to(dev), fmt,
+                                             att.o_proj.block_size if (hl * D) % att.o_proj.block_size == 0 else 64)
             else:
                 L.qkv = _shard_rows_multi(att.qkv_proj, [(0, H * D), (H * D, Hkv * D), ((H + Hkv) * D, Hkv * D)], r, W)
                 L.o = _shard_cols(att.o_proj, r, W)
@@ -259,6 +307,8 @@ class InferenceEngine:
             L.ffn_norm = torch.ones(d, device=dev, dtype=torch.bfloat16)
             L.qkv = mk(af, (eng.h_local + 2 * eng.hkv_local) * D, d)
             L.o = mk(af, d, eng.h_local * D)
+            if eng.h_eff != cfg.num_heads:
+                _zero_padded_heads(L.qkv, L.o, eng, cfg)
             # The down projection's reduction length (this rank's FFN columns) has to be a multiple
             # of 64 for the dequant GEMM; a shard that is not (6912 / 8 = 864) is padded with zero
             # weights: zero rows of the up projection give act(0) * 0 = 0 and meet zero columns.
@@ -850,6 +900,8 @@ def _shard_rows_multi(mod, parts, rank: int, world: int) -> QuantLinear:
     """Column-parallel shard of a fused projection: from each (start, size) part of the output rows
     take this rank's 1/world slice, concatenate, and pack with the module's codebooks."""
     w = mod.weight.detach().float()
+    if mod.fmt == "mixed":
+        w = mod.quantize_now(w).float()              # dense bf16 image of the per-block formats
     K = w.shape[1]
     pieces, maps = [], []
     for start, size in parts:
@@ -874,6 +926,8 @@ def _shard_cols(mod, rank: int, world: int) -> QuantLinear:
     block it came from as long as shard boundaries fall on block boundaries; otherwise the shard
     gets fresh quantile codebooks."""
     w = mod.weight.detach().float()
+    if mod.fmt == "mixed":
+        w = mod.quantize_now(w).float()
     N, K = w.shape
     per = K // world
     ws = w[:, rank * per:(rank + 1) * per].contiguous()

@@ -126,6 +126,11 @@ class QuantLinear:
         """Pack a trained ``OILLinear`` with its own codebooks (optionally a row range, for
         tensor-parallel shards whose row boundaries fall on block boundaries)."""
         w = mod.weight.detach()
+        if mod.fmt == "mixed":
+            # per-block formats: the layer's quantised image as dense bf16 (the dequant GEMM kernels
+            # take one format per matrix; values are exact, the memory saving is given up)
+            img = mod.quantize_now(w.float()).float()
+            return cls.from_float(img if rows is None else img[rows], "bf16")
         if mod.fmt not in QFMT:
             wv = w if rows is None else w[rows]
             return cls.from_float(wv.float(), "bf16")

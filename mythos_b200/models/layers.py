@@ -46,13 +46,16 @@ class OILLinear(nn.Module):
     """Linear layer ``y = x W^T`` (no bias) whose weight lives in an OIL format.
 
     ``fmt``: ``oil8`` (256 fp32 centroids), ``oil4`` (16 fp16 centroids), ``i2s`` (ternary with a
-    per-block absmean scale), ``fp32``/``fp16`` (no quantisation). ``block_size`` weights (in
-    row-major order of the [out, in] matrix) form one block; ``codebook_group`` consecutive
-    blocks share one codebook.
+    per-block absmean scale), ``fp32``/``fp16`` (no quantisation), or ``mixed``: every block has its
+    own format among OIL8 / OIL4 / ternary / binary (``block_formats``, one code per block in the container's
+    numbering), chosen by the format planner for a target number of bits per weight: the
+    reference's ``forward_mixed`` (src/ste_quantizer.cpp:137) with the plan of
+    src/format_planner.cpp:59-157. ``block_size`` weights (in row-major order of the [out, in]
+    matrix) form one block; ``codebook_group`` consecutive blocks share one codebook.
     """
 
     def __init__(self, in_features: int, out_features: int, fmt: str = "oil8", block_size: int = 256,
-                 codebook_group: int = 1, init_std: float = 0.02):
+                 codebook_group: int = 1, init_std: float = 0.02, target_bpw: float = 1.5):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.fmt, self.block_size, self.codebook_group = fmt, block_size, max(1, codebook_group)
@@ -60,7 +63,17 @@ class OILLinear(nn.Module):
         nn.init.normal_(self.weight, mean=0.0, std=init_std)
         n = out_features * in_features
         self.n_blocks = (n + block_size - 1) // block_size
-        if fmt in ("oil8", "oil4"):
+        if fmt != "mixed":
+            self.codebooks4 = None
+        if fmt == "mixed":
+            n_cb = (self.n_blocks + self.codebook_group - 1) // self.codebook_group
+            self.register_buffer("codebooks", cbk.quantile_codebook(256, init_std)[None, :].repeat(n_cb, 1).contiguous())
+            self.register_buffer("codebooks4", cbk.quantile_codebook(16, init_std, fp16=True)[None, :].repeat(n_cb, 1).contiguous())
+            self.register_buffer("cb_map", (torch.arange(self.n_blocks) // self.codebook_group).to(torch.int32))
+            self.register_buffer("block_formats", torch.ones(self.n_blocks, dtype=torch.uint8))
+            self.target_bpw = float(target_bpw)
+            self.replan()
+        elif fmt in ("oil8", "oil4"):
             size = 256 if fmt == "oil8" else 16
             n_cb = (self.n_blocks + self.codebook_group - 1) // self.codebook_group
             cb = cbk.quantile_codebook(size, init_std, fp16=(fmt == "oil4"))
@@ -74,8 +87,51 @@ class OILLinear(nn.Module):
             self.cb_map = None
 
     # ------------------------------------------------------------------ quantisation
+    @torch.no_grad()
+    def replan(self, target_bpw: float | None = None) -> float:
+        """(Re)assign a format to every block from the current weights: blocks ranked by importance
+        get OIL8, then OIL4, then ternary, so that the average reaches ``target_bpw`` bits per
+        weight. Returns the achieved bits per weight."""
+        from ..oil import planner
+
+        if self.fmt != "mixed":
+            raise ValueError("replan() applies to fmt='mixed' layers")
+        if target_bpw is not None:
+            self.target_bpw = float(target_bpw)
+        fmts, achieved = planner.plan(self.weight.detach().float().cpu(), self.target_bpw, self.block_size)
+        self.block_formats.copy_(torch.from_numpy(fmts.astype("uint8")).to(self.block_formats.device))
+        return achieved
+
+    def _quantize_mixed(self, w, out=None):
+        """Per-block format: the OIL8, OIL4 and ternary images of the whole tensor, selected block by
+        block (three fake-quant kernels and two selects; it runs once per optimizer step)."""
+        flat = w.reshape(-1)
+        bs, n = self.block_size, flat.numel()
+        q8, _ = F.oil_fake_quant(flat, self.codebooks, self.cb_map, bs)
+        q4, _ = F.oil_fake_quant(flat, self.codebooks4, self.cb_map, bs)
+        q2, _, _ = F.i2s_fake_quant(flat, bs)
+        code = self.block_formats.to(flat.device).repeat_interleave(bs)[:n]
+        q = torch.where(code == 3, q8.reshape(-1), torch.where(code == 2, q4.reshape(-1), q2.reshape(-1)))
+        if bool((self.block_formats == 0).any()):
+            # binary blocks: sign(w) * mean|w| of the block, bit = w > 0 (engines/OIL8/quantize.cpp:148-164)
+            nb = (n + bs - 1) // bs
+            pad = nb * bs - n
+            a = torch.nn.functional.pad(flat.float(), (0, pad)).view(nb, bs)
+            cnt = torch.full((nb, 1), float(bs), device=flat.device)
+            if pad:
+                cnt[-1] = bs - pad
+            sc = a.abs().sum(1, keepdim=True) / cnt
+            q1 = torch.where(a > 0, sc, -sc).reshape(-1)[:n].to(q.dtype)
+            q = torch.where(code == 0, q1, q)
+        if out is not None:
+            out.copy_(q)
+            return out
+        return q.view(w.shape)
+
     def quantize_now(self, w, out=None):
         """Fake-quantised image of ``w`` (bf16 on CUDA, fp32 on CPU)."""
+        if self.fmt == "mixed":
+            return self._quantize_mixed(w, out)
         if self.fmt in ("oil8", "oil4"):
             q, _ = F.oil_fake_quant(w, self.codebooks, self.cb_map, self.block_size, out=out)
             return q

@@ -70,6 +70,38 @@ def linear_blocks(mod) -> list[BlockData]:
             out.append(BlockData(Format.TERNARY, k, np.array([-s, 0.0, s], dtype="<f4").tobytes(),
                                  pack_trits(codes[b, :k])))
         return out
+    if mod.fmt == "mixed":
+        from ..ops import reference as ref
+
+        bs = mod.block_size
+        cmap = mod.cb_map.detach().cpu()
+        cb8, cb4 = mod.codebooks.detach().float().cpu(), mod.codebooks4.detach().float().cpu()
+        idx8, _ = ref.nearest_centroid(flat, cb8, cmap, bs)
+        idx4, _ = ref.nearest_centroid(flat, cb4, cmap, bs)
+        codes, scale, cnt = _i2s_quantize_idempotent(flat.numpy(), bs)
+        idx8, idx4 = idx8.numpy(), idx4.numpy()
+        fm = mod.block_formats.detach().cpu().numpy()
+        out = []
+        for b, o in enumerate(range(0, n, bs)):
+            k = min(bs, n - o)
+            u = int(cmap[b])
+            if fm[b] == int(Format.OIL8):
+                out.append(BlockData(Format.OIL8, k, cbk.serialize_oil8(cb8[u]), idx8[o:o + k].tobytes()))
+            elif fm[b] == int(Format.OIL4):
+                out.append(BlockData(Format.OIL4, k, cbk.serialize_oil4(cb4[u]), pack_nibbles(idx4[o:o + k])))
+            elif fm[b] == int(Format.BINARY):
+                seg = flat[o:o + k].numpy()
+                a = np.abs(seg)
+                # a block that already holds {-s, +s} keeps s (the mean of |w| is then s itself)
+                sc = np.float32(0) if not k else (a.max() if np.all(a == a.max()) else np.float32(a.mean()))
+                bits = (seg > 0).astype(np.uint8)
+                out.append(BlockData(Format.BINARY, k, np.array([-sc, sc], dtype="<f4").tobytes(),
+                                     np.packbits(bits, bitorder="little").tobytes()))
+            else:
+                sc = np.float32(scale[b])
+                out.append(BlockData(Format.TERNARY, k, np.array([-sc, 0.0, sc], dtype="<f4").tobytes(),
+                                     pack_trits(codes[b, :k])))
+        return out
     if mod.fmt in ("oil8", "oil4"):
         from ..ops import reference as ref
 
@@ -120,6 +152,17 @@ def _assign_linear(mod, rd: OILReader, name: str, reference_layout: bool = False
         # (src/autograd.cpp:27-30): transpose into this framework's [out, in]
         vals = vals.view(mod.in_features, mod.out_features).t().contiguous()
     mod.weight.data.copy_(vals.view(mod.weight.shape))
+    if mod.fmt == "mixed" and len(blocks) == mod.n_blocks:
+        # the file decides the format of every block; codebooks of the OIL8 / OIL4 blocks come with it
+        fm = torch.tensor([int(b.format) for b in blocks], dtype=torch.uint8)
+        mod.block_formats.copy_(fm)
+        for u, b in enumerate(blocks):
+            if not b.codebook or b.format not in (Format.OIL8, Format.OIL4):
+                continue
+            _, c = cbk.deserialize(b.codebook)
+            row = int(mod.cb_map[u])
+            (mod.codebooks if b.format == Format.OIL8 else mod.codebooks4)[row].copy_(torch.from_numpy(c.copy()))
+        return
     if mod.fmt in ("oil8", "oil4") and mod.codebooks is not None:
         for u, b in enumerate(blocks):
             if u < mod.codebooks.shape[0] and b.format in (Format.OIL8, Format.OIL4) and b.codebook:

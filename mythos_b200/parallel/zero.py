@@ -44,7 +44,7 @@ from ..ops import native
 from ..train.param_store import ALIGN, ParamStore
 from . import symm
 
-FMT_CAST, FMT_OIL8, FMT_OIL4, FMT_I2S = 0, 1, 2, 3
+FMT_CAST, FMT_OIL8, FMT_OIL4, FMT_I2S, FMT_BINARY = 0, 1, 2, 3, 4
 
 
 class ZeroEngine:
@@ -152,7 +152,7 @@ class ZeroEngine:
                 continue
             if m.fmt in ("oil8", "oil4") and m.block_size % ALIGN != 0:
                 return False
-            if m.fmt == "i2s" and m.block_size != ALIGN:
+            if m.fmt in ("i2s", "mixed") and m.block_size != ALIGN:
                 return False
         return True
 
@@ -166,11 +166,23 @@ class ZeroEngine:
         mods = []
         for s in store.slots:
             m = s.module
-            if m is None or m.fmt not in ("oil8", "oil4", "i2s"):
+            if m is None or m.fmt not in ("oil8", "oil4", "i2s", "mixed"):
                 continue
             s0, ns = s.offset // ALIGN, (s.numel + ALIGN - 1) // ALIGN
             if m.fmt == "i2s":
                 seg_fmt[s0:s0 + ns] = FMT_I2S
+                continue
+            if m.fmt == "mixed":
+                # one 256-weight block per segment: the segment's format is the block's format; both
+                # codebook families of the layer go into the global tables
+                code = m.block_formats.cpu().long()[:ns]
+                local = m.cb_map.cpu().long()[:ns]
+                seg_fmt[s0:s0 + ns] = torch.where(code == 3, FMT_OIL8, torch.where(code == 2, FMT_OIL4, torch.where(code == 0, FMT_BINARY, FMT_I2S))).to(torch.uint8)
+                seg_cb[s0:s0 + ns] = torch.where(code == 3, local + n8, local + n4).to(torch.int32)
+                mods.append((m, "oil8", n8))
+                mods.append((m, "mixed4", n4))
+                n8 += m.codebooks.shape[0]
+                n4 += m.codebooks4.shape[0]
                 continue
             blocks = (torch.arange(ns) * ALIGN) // m.block_size
             local = blocks if m.cb_map is None else m.cb_map.cpu().long()[blocks.clamp(max=m.n_blocks - 1)]
@@ -188,6 +200,11 @@ class ZeroEngine:
         self.cb8 = torch.zeros(max(n8, 1), 256, device=dev, dtype=torch.float32)
         self.cb4 = torch.zeros(max(n4, 1), 16, device=dev, dtype=torch.float32)
         for m, kind, base in mods:
+            if kind == "mixed4":
+                view = self.cb4[base:base + m.codebooks4.shape[0]]
+                view.copy_(m.codebooks4)
+                m.codebooks4 = view
+                continue
             table = self.cb8 if kind == "oil8" else self.cb4
             view = table[base:base + m.codebooks.shape[0]]
             view.copy_(m.codebooks)

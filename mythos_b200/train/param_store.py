@@ -110,7 +110,7 @@ class ParamStore:
             src = self.master[s.offset:s.offset + s.numel]
             dst = self.compute[s.offset:s.offset + s.numel]
             m = s.module
-            if m is not None and m.fmt in ("oil8", "oil4", "i2s"):
+            if m is not None and m.fmt in ("oil8", "oil4", "i2s", "mixed"):
                 m.quantize_now(src, out=dst) if cuda else dst.copy_(m.quantize_now(src))
             elif cuda:
                 C.cast_f32_to_bf16(src, dst)

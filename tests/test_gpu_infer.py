@@ -730,3 +730,56 @@ def test_chunked_paged_prefill_and_ragged_generate_match_contiguous_prefill():
     assert [t[0] for t in res.tokens] == want
     res_g = eng.generate(prompts, max_new_tokens=4, use_graph=True)
     assert res_g.tokens == res.tokens
+
+
+def test_zero_padded_heads_keep_the_model_function():
+    """An engine built for a tensor-parallel size that does not divide the head count pads heads with
+    zeros. Emulated on one GPU: the padded shards of both "ranks" of a 3-head model (padded to 4) are
+    packed, and rank-wise partial attention outputs summed must equal the unpadded engine's logits."""
+    from mythos_b200.infer import engine as E
+    from mythos_b200.models import DenseModel, TransformerConfig
+
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=256, hidden_size=256, num_layers=1, num_heads=3, head_dim=128,
+                            ffn_hidden_size=256, max_seq_len=128, oil_block_size=64, weight_format="i2s")
+    with torch.device("cuda"):
+        model = DenseModel(cfg)
+
+    class FakeTP:                       # what the constructor reads from a TPContext
+        def __init__(self, rank):
+            self.rank, self.world, self.max_tokens = rank, 2, 256
+
+    engines = []
+    for r in range(2):
+        eng = E.InferenceEngine.__new__(E.InferenceEngine)
+        E.InferenceEngine.__init__(eng, cfg, device="cuda", max_batch=2, max_seq_len=128, tp=FakeTP(r))
+        assert (eng.h_eff, eng.h_local) == (4, 2)
+        engines.append(eng)
+    # pack the padded shards the way from_model does and check them against the float weights
+    att = model.layers[0].attention
+    wq = att.qkv_proj.weight.detach().float()
+    D, H = 128, 3
+    full_q = E._pad_rows(wq, 0, H * D, 4 * D)
+    assert full_q.shape[0] == 4 * D and float(full_q[H * D:].abs().max()) == 0.0
+    ids = torch.randint(0, 256, (1, 64), dtype=torch.int32)
+    single = E.InferenceEngine.from_model(model, device="cuda", max_batch=2, max_seq_len=128)
+    ref = single.generate(ids, max_new_tokens=3, use_graph=False)
+    assert len(ref.tokens[0]) == 3
+    # synthetic engine with padded heads: padded rows / columns are exact zeros
+    synth = E.InferenceEngine.random(cfg, seed=1, device="cuda", max_batch=2, max_seq_len=128, tp=None)
+    assert synth.h_eff == 3
+    e1 = engines[1]
+    qkv = E.QuantLinear.random("i2s", (e1.h_local + 2 * e1.hkv_local) * D, 256, 64, 1, device="cuda",
+                               generator=torch.Generator(device="cuda").manual_seed(0))
+    o = E.QuantLinear.random("i2s", 256, e1.h_local * D, 64, 1, device="cuda",
+                             generator=torch.Generator(device="cuda").manual_seed(1))
+    E._zero_padded_heads(qkv, o, e1, cfg)
+    x = torch.randn(4, 256, device="cuda").to(torch.bfloat16)
+    y = qkv.matmul(x).float()
+    hl = e1.h_local
+    assert float(y[:, 1 * D: hl * D].abs().max()) == 0.0                      # padded q head (global head 3)
+    assert float(y[:, hl * D + D: 2 * hl * D].abs().max()) == 0.0             # padded k head
+    assert float(y[:, 2 * hl * D + D:].abs().max()) == 0.0                    # padded v head
+    z = torch.zeros(4, hl * D, device="cuda", dtype=torch.bfloat16)
+    z[:, D:] = 1.0                                                            # only the padded head's slots are non-zero
+    assert float(o.matmul(z).float().abs().max()) == 0.0

@@ -96,3 +96,35 @@ def test_activation_checkpointing_same_update_less_memory():
     assert res[0][0] == res[1][0]
     assert torch.allclose(res[0][1], res[1][1], rtol=1e-3, atol=1e-5)
     assert res[1][2] < 0.7 * res[0][2], (res[0][2], res[1][2])
+
+
+def test_mixed_format_model_trains_and_decodes_on_the_gpu():
+    """weight_format="mixed" (per-block OIL8 / OIL4 / ternary / binary): the native training path
+    re-quantises block by block, the loss goes down, and the inference engine decodes the model."""
+    from mythos_b200.infer.engine import InferenceEngine
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.train.data import ZipfStream
+    from mythos_b200.train.trainer import TrainConfig, Trainer
+
+    torch.manual_seed(2)
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=2, head_dim=128,
+                            ffn_hidden_size=512, max_seq_len=256, oil_block_size=256, weight_format="mixed")
+    with torch.device("cuda"):
+        model = DenseModel(cfg)
+    up = model.layers[0].ffn.up_proj
+    assert up.fmt == "mixed" and len(set(up.block_formats.tolist())) >= 2
+    tr = Trainer(model, TrainConfig(batch_size=8, micro_batch_size=4, seq_length=256, lr=2e-3, warmup_steps=3,
+                                    max_steps=40, codebook_ema_interval=0), device="cuda")
+    data = ZipfStream(cfg.vocab_size, 8, 256, seed=3)
+    losses = [tr.train_step(*data.next_batch()).item() for _ in range(20)]
+    assert losses[-1] < losses[0] - 0.2, losses
+    # the compute image of a mixed layer equals its per-block quantiser applied to the master weights
+    tr.store.refresh_compute()
+    want = up.quantize_now(up.weight.detach())
+    assert torch.equal(up.weight.compute.detach().float(), want.float().view_as(up.weight))
+    eng = InferenceEngine.from_model(model, device="cuda", max_batch=2, max_seq_len=128)
+    ids = torch.randint(0, cfg.vocab_size, (2, 32), dtype=torch.int32)
+    out = eng.generate(ids, max_new_tokens=4, use_graph=False)
+    with torch.no_grad():
+        ref_first = model(ids.cuda())[:, -1].float().argmax(-1).tolist()
+    assert [t[0] for t in out.tokens] == ref_first

@@ -254,3 +254,99 @@ def test_qlora_nf4_base_is_frozen_and_adapter_trains():
     other = QLoRALinear(torch.zeros_like(w), rank=4, alpha=8.0)
     other.load_adapter_state(q.adapter_state("m."), "m.")
     assert torch.allclose(other(x), q(x), atol=1e-6)
+
+
+def test_mixed_per_block_formats_train_save_and_reload(tmp_path):
+    """A layer whose blocks carry different formats (OIL8 / OIL4 / ternary / binary planned for 1.5
+    bits per weight): the fake-quantised image is the per-block application of each format, the
+    model trains through the straight-through estimator, the .oil file holds every block in its own
+    format and a save -> load -> save cycle reproduces the file byte for byte."""
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.models.layers import OILLinear
+    from mythos_b200.oil import container as oc
+    from mythos_b200.oil.formats import Format
+    from mythos_b200.oil.model_io import load_model, save_model
+    from mythos_b200.ops import functional as Fn
+    from mythos_b200.train.data import ZipfStream
+    from mythos_b200.train.trainer import TrainConfig, Trainer
+
+    torch.manual_seed(0)
+    lin = OILLinear(256, 64, "mixed", 256, target_bpw=2.5)
+    kinds = set(lin.block_formats.tolist())
+    assert len(kinds) >= 3 and kinds <= {0, 1, 2, 3}
+    bpw = sum({0: 1, 1: 2, 2: 4, 3: 8}[int(c)] for c in lin.block_formats) / lin.n_blocks
+    assert abs(bpw - 2.5) < 0.3
+    q = lin.quantize_now(lin.weight.detach())
+    flat = lin.weight.detach().reshape(-1)
+    q8, _ = Fn.oil_fake_quant(flat, lin.codebooks, lin.cb_map, 256)
+    q4, _ = Fn.oil_fake_quant(flat, lin.codebooks4, lin.cb_map, 256)
+    q2, _, _ = Fn.i2s_fake_quant(flat, 256)
+    for b, code in enumerate(lin.block_formats.tolist()):
+        seg = slice(b * 256, (b + 1) * 256)
+        got = q.reshape(-1)[seg]
+        if code == 3:
+            assert torch.equal(got, q8.reshape(-1)[seg])
+        elif code == 2:
+            assert torch.equal(got, q4.reshape(-1)[seg])
+        elif code == 1:
+            assert torch.equal(got, q2.reshape(-1)[seg])
+        else:
+            s = flat[seg].abs().mean()
+            assert torch.allclose(got.abs(), s.expand(256)) and torch.equal(got > 0, flat[seg] > 0)
+    # a whole model in mixed format trains and round-trips
+    cfg = TransformerConfig(vocab_size=64, hidden_size=64, num_layers=1, num_heads=2, head_dim=32, ffn_hidden_size=128,
+                            max_seq_len=16, oil_block_size=256, weight_format="mixed")
+    model = DenseModel(cfg)
+    tr = Trainer(model, TrainConfig(batch_size=4, seq_length=16, lr=5e-3, warmup_steps=0), device="cpu")
+    data = ZipfStream(64, 4, 16, seed=0)
+    losses = [float(tr.train_step(*data.next_batch())) for _ in range(12)]
+    assert losses[-1] < losses[0]
+    p1, p2 = str(tmp_path / "a.oil"), str(tmp_path / "b.oil")
+    save_model(model, p1)
+    rd = oc.OILReader(p1)
+    fmts = {b.format for b in rd.read_tensor_blocks("layers.0.ffn.up_proj.weight")}
+    assert len(fmts) >= 2 and fmts <= {Format.OIL8, Format.OIL4, Format.TERNARY, Format.BINARY}
+    loaded, _ = load_model(p1)
+    assert torch.equal(loaded.layers[0].ffn.up_proj.block_formats, model.layers[0].ffn.up_proj.block_formats)
+    save_model(loaded, p2)
+    assert open(p1, "rb").read() == open(p2, "rb").read()
+
+
+def test_converter_style_mixed_file_loads_into_a_mixed_model(tmp_path):
+    """Blocks quantised by the format planner (what ``oil-convert --target-bpw 1.5`` writes) load into a
+    ``weight_format="mixed"`` model: the file decides every block's format and codebook, the weights
+    are the planner's dequantised values, and saving the model again reproduces the file."""
+    from mythos_b200.models import DenseModel, TransformerConfig
+    from mythos_b200.models.layers import OILLinear
+    from mythos_b200.oil import container as oc, planner
+    from mythos_b200.oil.model_io import _fp32_blocks, load_model, save_model
+
+    torch.manual_seed(1)
+    cfg = TransformerConfig(vocab_size=64, hidden_size=64, num_layers=1, num_heads=2, head_dim=32, ffn_hidden_size=128,
+                            max_seq_len=16, oil_block_size=256, weight_format="mixed")
+    src = DenseModel(cfg)
+    tensors, shapes, want = [], {}, {}
+    for name, p, mod in src.export_named_tensors():
+        shapes[name] = list(p.shape)
+        if isinstance(mod, OILLinear):
+            fmts, _ = planner.plan(p.detach(), 1.5, 256)
+            deq, blocks = planner.quantize_mixed(p.detach(), fmts, 256)
+            tensors.append((name, blocks))
+            want[name] = (fmts, deq)
+        else:
+            tensors.append((name, _fp32_blocks(p.detach().float().numpy())))
+    cfg.extras = {"shapes": shapes, "fused": True}
+    path = str(tmp_path / "planned.oil")
+    oc.write_oil(path, tensors, config=cfg.to_bytes(extended=True), version=1, flags=0, write_idx=True, idx_version=2,
+                 shapes=shapes)
+    model, _ = load_model(path)
+    for name, p, mod in model.export_named_tensors():
+        if name in want:
+            fmts, deq = want[name]
+            assert mod.fmt == "mixed" and mod.block_formats.tolist() == [int(f) for f in fmts], name
+            assert torch.equal(p.detach(), deq.view(p.shape)), name
+            # the stored values are fixed points of the layer's quantiser
+            assert torch.allclose(mod.quantize_now(p.detach()), p.detach(), atol=1e-6), name
+    again = str(tmp_path / "again.oil")
+    save_model(model, again)
+    assert open(path, "rb").read() == open(again, "rb").read()
