@@ -1001,6 +1001,17 @@ void gemm_grouped_k(const Tensor& a, const Tensor& b, const std::vector<Tensor>&
                      status_ptr(status), cur_stream());
 }
 
+void tl_gemm(const Tensor& packed, const Tensor& x, Tensor& y, int64_t group) {
+  chk_c(packed, U8, "packed");
+  chk_c(x, F32, "x");
+  chk_c(y, F32, "y");
+  TORCH_CHECK(x.dim() == 2 && packed.dim() == 2 && packed.size(1) * 4 == x.size(1) && y.size(0) == x.size(0) &&
+                  y.size(1) == packed.size(0), "tl_gemm: x [M, K], packed [N, K/4], y [M, N]");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::tl_gemm(packed.data_ptr<uint8_t>(), x.data_ptr<float>(), y.data_ptr<float>(), (int)x.size(0), (int)packed.size(0),
+              (int)x.size(1), (int)group, cur_stream());
+}
+
 int64_t launch_count() { return mb::launch_count(); }
 
 }  // namespace
@@ -1081,6 +1092,7 @@ PYBIND11_MODULE(_C, m) {
     mb::comm_set_abort_word(status.data_ptr<int>());
   });
   m.def("flash_attn_paged_prefill", &flash_attn_paged_prefill);
+  m.def("tl_gemm", &tl_gemm);
   m.def("moe_route", &moe_route);
   m.def("moe_route_bwd", &moe_route_bwd);
   m.def("moe_publish_counts", &moe_publish_counts);

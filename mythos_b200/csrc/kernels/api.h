@@ -195,6 +195,10 @@ void qkv_rope_append(float* acc, const int* pos, const int* seq_ids, const int* 
 // acc fp32 [rows, 2 * ffn] (zeroed) -> act(gate) * up, bf16 [rows, ffn]; kind 0 SiLU, 1 squared ReLU.
 void finalize_gate(float* acc, void* out, long long rows, int ffn, int kind, cudaStream_t stream);
 
+// ---- ternary look-up-table GEMMs with int8 activations (ternary_lut.cu)
+// y[M, N] fp32 = TL1 (group 2) / TL2 (group 3) product of x[M, K] fp32 with packed trits [N, K / 4].
+void tl_gemm(const uint8_t* packed, const float* x, float* y, int M, int N, int K, int group, cudaStream_t stream);
+
 // ---- peer-memory collectives fused with compute (comm.cu)
 constexpr int MAX_PEERS = 16;
 struct PeerPtrs {

@@ -220,6 +220,12 @@ class QuantLinear:
         if M <= DECODE_MAX_TOKENS:
             if out is None:
                 out = torch.empty(M, self.N, device=x.device, dtype=torch.bfloat16)
+            if M == 1 and self.fmt == "i2s" and self.K % 64 == 0 and self.K * 4 <= 200 * 1024 and x.is_contiguous() \
+                    and out.is_contiguous():
+                # single-token ternary decode: one warp per output row over the packed trits, no tensor-core
+                # tile to fill (a 128 x 8 MMA tile would be 7/8 padding)
+                C.i2s_gemv(x.view(-1), self.packed, self.scales, self.N, self.K, self.block_size, out.view(-1))
+                return out
             # One CTA covers 128 output features. Too few of them to fill the GPU (narrow or
             # tensor-parallel layers): split K across CTAs into the fp32 accumulator instead.
             n_ctas = (self.N + 127) // 128

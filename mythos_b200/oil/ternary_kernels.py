@@ -7,8 +7,10 @@ All use a weight-shared layout ``W[N, K]`` (one packed row per output feature) a
 arithmetic of the reference kernels (src/kernel_tl.cpp:13-168, src/kernel_i2s.cpp:156-235). The
 reference indexes a distinct weight row per (m, n) output and its TL1 loop reads the 9-entry
 table with a single weight's 2-bit code; both are artefacts of its test harness and are not
-reproduced. Tensor code (CPU or GPU); the production ternary path is the I2_S dequant GEMM / GEMV
-on tensor cores (``csrc/kernels/dequant_gemm.cu``, ``paged_attn.cu``).
+reproduced. CUDA tensors run the table kernels of ``csrc/kernels/ternary_lut.cu`` (tables of the
+activation row in shared memory, one table read per weight pair / triple); CPU tensors run the same
+arithmetic as tensor code, which is the oracle of the kernel test. The production ternary path is
+the I2_S dequant GEMM / GEMV on tensor cores (``csrc/kernels/dequant_gemm.cu``, ``paged_attn.cu``).
 
 Packing: trits are stored as 2-bit codes ``t + 1`` (0 = -1, 1 = 0, 2 = +1), four per byte, first
 weight in bits 0-1: the I2_S / ``kernel_i2s`` encoding. TL1 reads them as pairs, TL2 as triples
@@ -58,6 +60,12 @@ def _group_index(trits: torch.Tensor, g: int) -> torch.Tensor:
 
 
 def _lut_gemm(packed: torch.Tensor, x: torch.Tensor, K: int, g: int) -> torch.Tensor:
+    if x.is_cuda:
+        from ..ops import native
+
+        y = torch.empty(x.shape[0], packed.shape[0], device=x.device, dtype=torch.float32)
+        native.require().tl_gemm(packed.contiguous(), x.float().contiguous(), y, g)
+        return y
     q, scale = quantize_activations_int8(x)
     lut = _group_lut(q, g)                                                  # [M, K/g, 3^g]
     idx = _group_index(unpack_trits(packed, K), g)                          # [N, K/g]

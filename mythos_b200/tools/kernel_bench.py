@@ -226,6 +226,28 @@ def bench_dequant_gemm(t: Timer, fmt: str, M: int, N: int, K: int, group: int = 
     return ms, q.packed.numel() / ms / 1e6, "GB/s"
 
 
+def bench_i2s_gemv(t: Timer, N: int, K: int):
+    """Single-token ternary GEMV (one warp per output row); reported as packed weight bytes per second."""
+    from mythos_b200.infer.quant_weights import QuantLinear
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q = QuantLinear.random("i2s", N, K, 256, 1, device="cuda", generator=g)
+    x = (torch.randn(1, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    out = torch.empty(1, N, device="cuda", dtype=torch.bfloat16)
+    ms = graph_time(t, lambda: q.matmul(x, out=out))
+    return ms, q.packed.numel() / ms / 1e6, "GB/s"
+
+
+def bench_sampler(t: Timer, B: int, V: int, greedy: bool):
+    """Sampling kernels over bf16 logits [B, V]: greedy arg-max, or temperature + top-k + top-p."""
+    from mythos_b200.infer.sampler import SamplerConfig, sample
+
+    logits = (torch.randn(B, V, device="cuda") * 3).to(torch.bfloat16)
+    cfg = SamplerConfig(temperature=0.0) if greedy else SamplerConfig(temperature=0.8, top_k=40, top_p=0.9, seed=1)
+    ms = graph_time(t, lambda: sample(logits, cfg, step=1)) if greedy else t(lambda: sample(logits, cfg, step=1))
+    return ms, logits.numel() * 2 / ms / 1e6, "GB/s"
+
+
 def bench_paged_decode(t: Timer, B: int, ctx: int, H: int, Hkv: int, D: int, splits: int = 0, int8: bool = False):
     """Split-KV decode attention over 16-token pages; reported as KV bytes per second (for int8
     pages: the int8 rows plus their fp32 scales)."""
@@ -348,6 +370,12 @@ def main():
         for fmt, M, N, K in [("oil8", 64, 28672, 4096), ("oil8", 64, 4096, 14336), ("oil4", 64, 6144, 4096),
                              ("oil4", 64, 4096, 4096), ("i2s", 8, 6912, 2560), ("oil8", 64, 128256, 4096)]:
             report(f"dequant_gemm_{fmt}_{M}x{N}x{K}", bench_dequant_gemm(t, fmt, M, N, K))
+    if k in ("i2s_gemv", "all"):
+        for N, K in [(6912 * 2, 2560), (2560, 6912), (128256, 2560)]:
+            report(f"i2s_gemv_1x{N}x{K}", bench_i2s_gemv(t, N, K))
+    if k in ("sampler", "all"):
+        report("sampler_greedy_b64_v128256", bench_sampler(t, 64, 128256, True))
+        report("sampler_topk_topp_b64_v128256", bench_sampler(t, 64, 128256, False))
     if k in ("paged_decode", "paged_decode_int8"):
         report(f"{k}_b{args.batch}_ctx{args.ctx}_h{args.heads}_kv{hkv}_d{args.head_dim}_splits{args.splits}",
                bench_paged_decode(t, args.batch, args.ctx, args.heads, hkv, args.head_dim, args.splits,

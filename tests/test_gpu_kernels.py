@@ -312,3 +312,23 @@ def test_kernel_c_abi_through_ctypes():
     rc = lib.mythos_gemm_bf16(a.data_ptr(), 255, 0, b.data_ptr(), 256, 0, c.data_ptr(), 64, 128, 64, 256, 0, 1.0,
                               None, stream)
     assert rc != 0 and len(lib.mythos_last_error()) > 0        # misaligned row stride is reported, not launched
+
+
+@pytest.mark.parametrize("group", [2, 3])
+def test_ternary_lut_gemm_kernels_match_integer_reference(group):
+    """TL1 / TL2 table kernels: int8 activations, exact int32 accumulation, against the direct integer
+    product and the CPU table formulation."""
+    from mythos_b200.oil import ternary_kernels as tk
+
+    torch.manual_seed(group)
+    M, N, K = 5, 300, 2556 if group == 3 else 2560
+    K = K // 12 * 12
+    trits = torch.randint(-1, 2, (N, K))
+    x = torch.randn(M, K)
+    packed = tk.pack_trits(trits)
+    fn = tk.tl1_gemm if group == 2 else tk.tl2_gemm
+    want = tk.ternary_reference(trits, x)
+    cpu = fn(packed, x, K)
+    got = fn(packed.cuda(), x.cuda(), K).cpu()
+    assert torch.allclose(cpu, want, rtol=1e-6, atol=1e-5)
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-4)
