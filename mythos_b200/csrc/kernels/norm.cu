@@ -74,17 +74,38 @@ __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* _
     for (int i = 0; i < 8; ++i) dg[c][i] = 0.f;
     if (ch < nchunk) unpack8(ldg8(gamma, ch * 8), g[c]);
   }
+  // The loads of the next row (x, dy, residual gradient, rstd) are issued before the current row is
+  // reduced, so a CTA always has one row in flight behind its block-wide sum: without this every row
+  // paid two dependent trips to memory (x / dy, then the residual gradient after the reduction).
+  bf16x8 nx[NC], ndy[NC], nres[NC];
+  float nrs = 0.f;
+  auto fetch = [&](long long row) {
+    nrs = rstd[row];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+        nx[c] = ldg8(x, row * dim + ch * 8);
+        ndy[c] = ldg8(dy, row * dim + ch * 8);
+        if (dres) nres[c] = ldg8(dres, row * dim + ch * 8);
+      }
+    }
+  };
+  constexpr bool AHEAD = NC <= 2;             // wide rows (NC = 4) would spill with a second row in registers
+  if (AHEAD && (long long)blockIdx.x < rows) fetch(blockIdx.x);
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float rs = rstd[row];
-    float xh[NC][8], dyg[NC][8];
+    if (!AHEAD) fetch(row);
+    const float rs = nrs;
+    float xh[NC][8], dyg[NC][8], er[NC][8];
     float dot = 0.f;
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int ch = threadIdx.x + c * blockDim.x;
       if (ch < nchunk) {
         float d[8];
-        unpack8(ldg8(x, row * dim + ch * 8), xh[c]);
-        unpack8(ldg8(dy, row * dim + ch * 8), d);
+        unpack8(nx[c], xh[c]);
+        unpack8(ndy[c], d);
+        if (dres) unpack8(nres[c], er[c]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[c][i] *= rs;
@@ -94,6 +115,7 @@ __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* _
         }
       }
     }
+    if (AHEAD && row + gridDim.x < rows) fetch(row + gridDim.x);
     dot = block_sum(dot, scratch) / dim;
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
@@ -103,10 +125,8 @@ __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const __nv_bfloat16* _
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = rs * (dyg[c][i] - xh[c][i] * dot);
         if (dres) {  // gradient arriving through the residual stream, added here instead of in a second pass
-          float e[8];
-          unpack8(ldg8(dres, row * dim + ch * 8), e);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) o[i] += e[i];
+          for (int i = 0; i < 8; ++i) o[i] += er[c][i];
         }
         stg8(dx, row * dim + ch * 8, pack8(o));
       }

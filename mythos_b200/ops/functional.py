@@ -253,7 +253,7 @@ def linear(x, w, grad_target=None):
 # --------------------------------------------------------------------------------------- RMSNorm
 def _n_partial(rows: int, device) -> int:
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return max(1, min(rows, sms * 2))
+    return max(1, min(rows, sms * 3))
 
 
 class _RMSNormFn(torch.autograd.Function):

@@ -226,6 +226,143 @@ def bench_dequant_gemm(t: Timer, fmt: str, M: int, N: int, K: int, group: int = 
     return ms, q.packed.numel() / ms / 1e6, "GB/s"
 
 
+def bench_misc(t: Timer, name: str):
+    """Single-kernel cases of the smaller kernels (also the programs behind their ncu summaries).
+    Multi-rank kernels run over two emulated ranks' buffers on this GPU, one launch after the other
+    (none of them waits on a peer). Returns (ms, GB/s of the bytes the kernel must move, unit)."""
+    from mythos_b200.ops import functional as Fn, native
+
+    C = native.require()
+    st = native.status_word("cuda")
+    bf = torch.bfloat16
+    if name == "rope":
+        T, H, D = 16384, 16, 128
+        x = torch.randn(T, H, D, device="cuda").to(bf)
+        pos = (torch.arange(T, device="cuda") % 2048).to(torch.int32)
+        return t(lambda: C.rope(x, pos, 10000.0, False)), 2.0 * x.numel() * 2, "GB/s"
+    if name == "rmsnorm_bwd":
+        rows, dim = 16384, 2048
+        x, dy, dres = (torch.randn(rows, dim, device="cuda").to(bf) for _ in range(3))
+        g = torch.ones(dim, device="cuda", dtype=bf)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-5).contiguous()
+        dx = torch.empty_like(x)
+        part = torch.empty(296, dim, device="cuda")
+        dg = torch.zeros(dim, device="cuda")
+        return t(lambda: C.rmsnorm_bwd(dy, x, g, rstd, dx, part, dg, True, dres)), 4.0 * x.numel() * 2, "GB/s"
+    if name in ("moe_route", "moe_dispatch", "moe_combine"):
+        T, E, k, d = 16384, 8, 2, 2048
+        logits = torch.randn(T, 8, device="cuda").to(bf)
+        probs = torch.empty(T, E, device="cuda")
+        idx = torch.empty(T, k, device="cuda", dtype=torch.int32)
+        slot = torch.empty_like(idx)
+        w = torch.empty(T, k, device="cuda")
+        counts = torch.zeros(E, device="cuda", dtype=torch.int32)
+        psum = torch.zeros(E, device="cuda")
+
+        def route():
+            counts.zero_()
+            C.moe_route(logits, E, probs, idx, slot, w, counts, psum)
+
+        if name == "moe_route":
+            return t(route), T * (8 * 2 + E * 4 + k * 12.0), "GB/s"
+        route()
+        cap = T * k + 256 * E
+        seg_start = torch.empty(E, device="cuda", dtype=torch.int32)
+        seg_rows = torch.empty(E, device="cuda", dtype=torch.int32)
+        send_base = torch.empty(E, device="cuda", dtype=torch.int32)
+        C.moe_offsets(counts, 1, E, 0, cap, seg_start, seg_rows, send_base, st)
+        x = torch.randn(T, d, device="cuda").to(bf)
+        buf = torch.zeros(cap, d, device="cuda", dtype=bf)
+        if name == "moe_dispatch":
+            return t(lambda: C.moe_dispatch(x, idx, slot, send_base, None, [buf.data_ptr()], E, 0, 0)), \
+                (1 + k) * T * d * 2.0, "GB/s"
+        C.moe_dispatch(x, idx, slot, send_base, None, [buf.data_ptr()], E, 0, 0)
+        out = torch.empty_like(x)
+        return t(lambda: C.moe_combine([buf.data_ptr()], idx, slot, send_base, w, None, out, None, d, E, 0, 0)), \
+            (1 + k) * T * d * 2.0, "GB/s"
+    if name in ("zero_rs", "zero_adamw"):
+        n = 64 << 20                                   # elements per emulated rank buffer
+        world, shard = 2, (64 << 20) // 2
+        grads = [torch.randn(n, device="cuda") * 1e-3 for _ in range(world)]
+        gsh = torch.empty(shard, device="cuda")
+        part = torch.zeros(1, device="cuda")
+        if name == "zero_rs":
+            return t(lambda: C.zero_reduce_scatter([g.data_ptr() for g in grads], gsh, 0, part)), \
+                shard * 4.0 * (world + 1), "GB/s"
+        from mythos_b200.oil.codebook import quantile_codebook
+
+        master = torch.randn(shard, device="cuda") * 0.02
+        m, v = torch.zeros(shard, device="cuda"), torch.zeros(shard, device="cuda")
+        comp = [torch.empty(n, device="cuda", dtype=bf) for _ in range(world)]
+        nseg = n // 256
+        seg_fmt = torch.ones(nseg, device="cuda", dtype=torch.uint8)
+        seg_cb = (torch.arange(nseg, device="cuda") // 128).to(torch.int32)
+        cb8 = quantile_codebook(256).cuda()[None].repeat((nseg + 127) // 128, 1).contiguous()
+        cb4 = torch.zeros(1, 16, device="cuda")
+        parts = torch.ones(world, device="cuda")
+        gn = torch.zeros(1, device="cuda")
+        gsh.normal_(0, 1e-3)
+        return t(lambda: C.zero_adamw_ste_allgather(master, m, v, gsh, [c.data_ptr() for c in comp], 0, seg_fmt, seg_cb,
+                                                    cb8, cb4, parts, gn, 1.0, 1e-4, 0.9, 0.95, 1e-8, 0.1, 10, 1.0, 0, 0)), \
+            shard * (28.0 + 2.0 * world), "GB/s"
+    if name == "tp_pull":
+        n = 16384 * 4096
+        parts = [torch.randn(n, device="cuda").to(bf) for _ in range(2)]
+        outs = [torch.empty(n, device="cuda", dtype=bf) for _ in range(2)]
+        return t(lambda: C.tp_allreduce_pull([p.data_ptr() for p in parts], [o.data_ptr() for o in outs], 0, n)), \
+            (n // 2) * 2.0 * 4, "GB/s"
+    if name == "qkv_rope_append":
+        T, H, Hkv, D = 64, 32, 8, 128
+        acc = torch.randn(T, (H + 2 * Hkv) * D, device="cuda")
+        pos = torch.full((T,), 100, device="cuda", dtype=torch.int32)
+        sid = torch.arange(T, device="cuda", dtype=torch.int32)
+        table = torch.arange(T * 8, device="cuda", dtype=torch.int32).view(T, 8)
+        q = torch.empty(T, H, D, device="cuda", dtype=bf)
+        kc = torch.zeros(T * 8, 16, Hkv, D, device="cuda", dtype=bf)
+        vc = torch.zeros_like(kc)
+
+        def run():
+            acc.normal_()
+            C.qkv_rope_append(acc, pos, sid, table, q, kc, vc, 500000.0, None, None)
+
+        return t(run), acc.numel() * 6.0, "GB/s"
+    if name == "paged_prefill":
+        B, S, H, Hkv, D = 8, 2048, 16, 16, 128
+        pages = B * S // 16
+        kc = (torch.randn(pages, 16, Hkv, D, device="cuda") * 0.5).to(bf)
+        vc = (torch.randn(pages, 16, Hkv, D, device="cuda") * 0.5).to(bf)
+        q = (torch.randn(B * S, H, D, device="cuda") * 0.5).to(bf)
+        table = torch.randperm(pages, device="cuda").to(torch.int32).view(B, S // 16)
+        cu = (torch.arange(B + 1, device="cuda") * S).to(torch.int32)
+        kv = torch.full((B,), S, device="cuda", dtype=torch.int32)
+        o = torch.empty_like(q)
+        ms = t(lambda: C.flash_attn_paged_prefill(q, kc, vc, table, cu, kv, o, S, D ** -0.5, st))
+        return ms, 4.0 * B * H * S * S * D * 0.5 / 1e3, "TFLOP/s"       # value below is divided by ms * 1e6
+    if name == "grouped_gemm":
+        E, rows_e, d, F2 = 8, 4096, 2048, 2 * 5632
+        cap = E * rows_e
+        a = torch.randn(cap, d, device="cuda").to(bf)
+        ws = [(torch.randn(F2, d, device="cuda") * 0.02).to(bf) for _ in range(E)]
+        seg_start = (torch.arange(E, device="cuda") * rows_e).to(torch.int32)
+        seg_rows = torch.full((E,), rows_e, device="cuda", dtype=torch.int32)
+        gu = torch.empty(cap, F2, device="cuda", dtype=bf)
+        h = torch.empty(cap, F2 // 2, device="cuda", dtype=bf)
+        ms = t(lambda: C.gemm_grouped_rows(a, ws, False, gu, seg_start, seg_rows, 1, None, h, st))
+        return ms, 2.0 * cap * F2 * d / 1e3, "TFLOP/s"
+    if name == "tl_gemm":
+        from mythos_b200.oil import ternary_kernels as tk
+
+        N, K = 6912, 2556 // 12 * 12
+        packed = tk.pack_trits(torch.randint(-1, 2, (N, K))).cuda()
+        x = torch.randn(8, K, device="cuda")
+        return t(lambda: tk.tl2_gemm(packed, x, K)), packed.numel() * 8.0, "GB/s"
+    raise ValueError(name)
+
+
+MISC_CASES = ("rope", "rmsnorm_bwd", "moe_route", "moe_dispatch", "moe_combine", "zero_rs", "zero_adamw", "tp_pull",
+              "qkv_rope_append", "paged_prefill", "grouped_gemm", "tl_gemm")
+
+
 def bench_i2s_gemv(t: Timer, N: int, K: int):
     """Single-token ternary GEMV (one warp per output row); reported as packed weight bytes per second."""
     from mythos_b200.infer.quant_weights import QuantLinear
@@ -370,6 +507,10 @@ def main():
         for fmt, M, N, K in [("oil8", 64, 28672, 4096), ("oil8", 64, 4096, 14336), ("oil4", 64, 6144, 4096),
                              ("oil4", 64, 4096, 4096), ("i2s", 8, 6912, 2560), ("oil8", 64, 128256, 4096)]:
             report(f"dequant_gemm_{fmt}_{M}x{N}x{K}", bench_dequant_gemm(t, fmt, M, N, K))
+    if k in MISC_CASES or k in ("misc", "all"):
+        for name in (MISC_CASES if k in ("misc", "all") else (k,)):
+            ms, nbytes, unit = bench_misc(t, name)
+            report(f"misc_{name}", (ms, nbytes / ms / 1e6, unit))
     if k in ("i2s_gemv", "all"):
         for N, K in [(6912 * 2, 2560), (2560, 6912), (128256, 2560)]:
             report(f"i2s_gemv_1x{N}x{K}", bench_i2s_gemv(t, N, K))
