@@ -1101,6 +1101,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("gemm_grouped_rows", &gemm_grouped_rows);
   m.def("gemm_grouped_k", &gemm_grouped_k);
   m.def("set_gemm_coalesced_epilogue", [](int64_t on) { mb::set_gemm_coalesced_epilogue((int)on); });
+  m.def("set_attn_fwd_mode", [](int64_t mode) { mb::set_attn_fwd_mode((int)mode); });
+  m.def("get_attn_fwd_mode", []() { return (int64_t)mb::get_attn_fwd_mode(); });
   m.def("set_gemm_mode", [](int64_t mode) { mb::set_gemm_mode((int)mode); });
   m.def("get_gemm_mode", []() { return (int64_t)mb::get_gemm_mode(); });
   m.def("launch_count", &launch_count);

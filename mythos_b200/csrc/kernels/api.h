@@ -155,6 +155,14 @@ void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float*
 void flash_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq,
                             int heads, int kv_heads, int head_dim, long long q_tok_stride, long long kv_tok_stride,
                             long long o_tok_stride, bool causal, float scale, int* status, cudaStream_t stream);
+// Second-generation forward for head_dim 128 (attention_fwd2.cu): persistent CTAs, 128 x 128 score tiles, P in
+// tensor memory. set_attn_fwd_mode(1) routes flash_attn_fwd / _strided to it where it applies (0: first kernel).
+bool flash_attn_fwd2_supported(int head_dim, int seq);
+void flash_attn_fwd2_strided(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq,
+                             int heads, int kv_heads, long long q_tok_stride, long long kv_tok_stride,
+                             long long o_tok_stride, bool causal, float scale, int* status, cudaStream_t stream);
+void set_attn_fwd_mode(int mode);
+int get_attn_fwd_mode();
 // Prefill attention over the paged KV cache (tcgen05, causal): q holds the NEW tokens of `batch` sequences
 // packed back to back (sequence b = rows cu_q[b] .. cu_q[b+1]); k_cache / v_cache are bf16 pages
 // [n_pages, 16, kv_heads, head_dim] addressed through block_table [batch, table_stride]; kv_lens[b] counts the

@@ -354,10 +354,19 @@ CUtensorMap make_bshd_map(const void* base, int batch, int seq, int nheads, int 
   return make_tensor_map(base, TmaDType::BF16, 4, dims, strides, box, true);
 }
 
+namespace { int g_attn_fwd_mode = 1; }   // 1: the persistent 128 x 128 kernel where it applies (head_dim 128)
+void set_attn_fwd_mode(int mode) { g_attn_fwd_mode = mode; }
+int get_attn_fwd_mode() { return g_attn_fwd_mode; }
+
 void flash_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int seq,
                             int heads, int kv_heads, int head_dim, long long q_tok_stride, long long kv_tok_stride,
                             long long o_tok_stride, bool causal, float scale, int* status, cudaStream_t stream) {
   MB_REQUIRE(head_dim == 64 || head_dim == 128, "flash_attn_fwd: head_dim must be 64 or 128");
+  if (g_attn_fwd_mode == 1 && flash_attn_fwd2_supported(head_dim, seq)) {
+    flash_attn_fwd2_strided(q, k, v, o, lse, batch, seq, heads, kv_heads, q_tok_stride, kv_tok_stride, o_tok_stride,
+                            causal, scale, status, stream);
+    return;
+  }
   MB_REQUIRE(heads % kv_heads == 0, "flash_attn_fwd: heads must be a multiple of kv_heads");
   MB_REQUIRE(q_tok_stride % 8 == 0 && kv_tok_stride % 8 == 0 && o_tok_stride % 8 == 0,
              "flash_attn_fwd: token strides must be multiples of 8 elements");

@@ -265,9 +265,14 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const vo
                : "memory");
 }
 
+// Two fp32 -> one bf16x2 word on the integer pipe: add half an ulp of bf16 to the magnitude bits and
+// keep the upper halves (round to nearest, ties away from zero; differs from round-to-nearest-even only
+// on exact ties). The conversion instruction (cvt.rn.bf16x2.f32) issues on the special-function pipe,
+// which the softmax and activation epilogues already saturate with exp2 / tanh: with it, that pipe read
+// 85-92 % busy in the attention and fused-epilogue kernels while the tensor pipe idled.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
+  const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
+  return __byte_perm(a, b, 0x7632);
 }
 
 }  // namespace mb

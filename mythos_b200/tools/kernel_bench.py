@@ -451,12 +451,15 @@ def main():
     ap.add_argument("--splits", type=int, default=0, help="KV splits of paged_decode (0 = the engine's choice)")
     ap.add_argument("--coalesced-epilogue", type=int, default=1,
                     help="paired GEMM: 1 stores through a shared-memory transpose, 0 straight from registers")
+    ap.add_argument("--attn-fwd-mode", type=int, default=-1, help="0 first forward kernel, 1 persistent 128x128 kernel")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 single-CTA kernel, 2 paired-SM kernel")
     args = ap.parse_args()
     from mythos_b200.ops import native
 
     native.require().set_gemm_mode(args.gemm_mode)
     native.require().set_gemm_coalesced_epilogue(args.coalesced_epilogue)
+    if args.attn_fwd_mode >= 0:
+        native.require().set_attn_fwd_mode(args.attn_fwd_mode)
     tf_peak, bw_peak, src = _peaks()
     t = Timer(args.iters, args.warmup, not args.no_flush)
     hkv = args.kv_heads or args.heads

@@ -208,15 +208,25 @@ def test_i2s_fake_quant():
 
 @pytest.mark.parametrize("B,S,H,Hkv,D,causal", [
     (1, 256, 2, 2, 128, True), (2, 512, 4, 2, 128, True), (1, 300, 2, 1, 128, True), (1, 384, 2, 2, 128, False),
-    (2, 256, 4, 4, 64, True), (1, 2048, 2, 2, 128, True)])
-def test_flash_attention_forward(B, S, H, Hkv, D, causal):
-    from mythos_b200.ops import functional as F, reference as ref
+    (2, 256, 4, 4, 64, True), (1, 2048, 2, 2, 128, True), (3, 1000, 5, 5, 128, True)])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_flash_attention_forward(B, S, H, Hkv, D, causal, mode):
+    """mode 0: the first forward kernel; mode 1: the persistent 128 x 128 kernel with P in tensor memory
+    (head_dim 128; other shapes fall back to the first kernel)."""
+    from mythos_b200.ops import functional as F, native, reference as ref
 
     torch.manual_seed(S + H)
     q = torch.randn(B, S, H, D, device="cuda").to(torch.bfloat16)
     k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
     v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16)
-    o, lse = F.flash_attention(q, k, v, causal)
+    C = native.require()
+    before = C.get_attn_fwd_mode()
+    C.set_attn_fwd_mode(mode)
+    try:
+        o, lse = F.flash_attention(q, k, v, causal)
+        torch.cuda.synchronize()
+    finally:
+        C.set_attn_fwd_mode(before)
     orf, lser = ref.attention(q, k, v, causal)
     _close(o, orf, atol=2e-2)
     assert torch.allclose(lse, lser, atol=2e-2, rtol=1e-3)
