@@ -21,6 +21,8 @@
 #include "host_util.h"
 #include "tc.cuh"
 
+#include <type_traits>
+
 namespace mb {
 
 CUtensorMap make_bshd_map(const void* base, int batch, int seq, int nheads, int head_dim, long long tok_stride,
@@ -227,21 +229,26 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     bool ok = true;
 
     float* dq_stage = reinterpret_cast<float*>(smem + Cfg::OFF_DQ) + cw * (BW_QH * 32);
-    auto drain_dq = [&](int n) {
-      // dQ^T of step n is in TMEM: lane = d, column = q. Each warp transposes its 32 d-rows x 32
-      // q-columns into a [32 q][32 d] fp32 tile in shared memory and adds it to the fp32 dQ buffer
-      // with one bulk tensor reduction (no per-element atomics).
-      const int h = hkv * group + n / per_head;
-      const int q0 = (i_start + n % per_head) * BW_Q;
-      uint32_t a[32];
-      tmem_ld32(tmem_base + Cfg::COL_DQT + wg * BW_QH + lane_sel, a);
+    // dQ^T of step n is in TMEM: lane = d, column = q. Draining it has two halves. fetch_dq copies this
+    // warp's 32 d-rows x 32 q-columns into registers and frees the accumulator (the MMA thread waits for
+    // that before the next dQ product); store_dq transposes them into a [32 q][32 d] fp32 tile in shared
+    // memory and adds it to the fp32 dQ buffer with one bulk tensor reduction (no per-element atomics).
+    // Only the first half sits between a step's arithmetic and its P / dS stores; the second runs after
+    // the stores, while the tensor pipe works on the step's products.
+    uint32_t dq_regs[32];
+    auto fetch_dq = [&]() {
+      tmem_ld32(tmem_base + Cfg::COL_DQT + wg * BW_QH + lane_sel, dq_regs);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_free);
+    };
+    auto store_dq = [&](int n) {
+      const int h = hkv * group + n / per_head;
+      const int q0 = (i_start + n % per_head) * BW_Q;
       if (lane == 0) tma_store_wait_read0();  // the previous reduction has finished reading the staging tile
       __syncwarp();
 #pragma unroll
-      for (int q = 0; q < BW_QH; ++q) dq_stage[q * 32 + lane] = __uint_as_float(a[q]);
+      for (int q = 0; q < BW_QH; ++q) dq_stage[q * 32 + lane] = __uint_as_float(dq_regs[q]);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && q0 + wg * BW_QH < seq) {   // a box wholly past the sequence end is not issued
@@ -250,26 +257,36 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     };
 
-    float nx_lse = INFINITY, nx_dl = 0.f;
-    if (N > 0) {
-      const int q1 = i_start * BW_Q + wg * BW_QH + lane;
-      const long long off1 = ((long long)b * heads + hkv * group) * seq;
-      nx_lse = (q1 < seq) ? __ldg(lse + off1 + q1) * LOG2E : INFINITY;
-      nx_dl = (q1 < seq) ? __ldg(delta + off1 + q1) : 0.f;
-    }
+    // lse and delta of a step's 32 query columns are the same for every thread of the warp: each thread
+    // reads them itself with eight uniform 16-byte loads per array (one L1 transaction per load, issued
+    // before the wait for the scores) instead of receiving them through 64 shuffles per step, which kept
+    // the shuffle unit busy for 512 cycles of a 1280-cycle step. delta arrives as -delta * scale.
+    const bool vec_rows = (seq & 3) == 0 && (reinterpret_cast<uintptr_t>(lse) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(delta) & 15) == 0;
+    const uint64_t sc2 = f32x2(scale_log2, scale_log2), s2 = f32x2(scale, scale);
+    const uint64_t nlog2 = f32x2(-LOG2E, -LOG2E);
     for (int n = 0; n < N && ok; ++n) {
       const int h = hkv * group + n / per_head;
       const int q0 = (i_start + n % per_head) * BW_Q;
-      // lane i holds lse / delta of query column i of this warpgroup's 32 columns; the loop below
-      // broadcasts them with shuffles. The values of the next step are fetched now, a step ahead.
       const int qc0 = q0 + wg * BW_QH;   // first query row of this warpgroup's columns
-      const float my_lse = nx_lse, my_dl = nx_dl;
-      if (n + 1 < N) {
-        const int h1 = hkv * group + (n + 1) / per_head;
-        const int q1 = (i_start + (n + 1) % per_head) * BW_Q + wg * BW_QH + lane;
-        const long long off1 = ((long long)b * heads + h1) * seq;
-        nx_lse = (q1 < seq) ? __ldg(lse + off1 + q1) * LOG2E : INFINITY;
-        nx_dl = (q1 < seq) ? __ldg(delta + off1 + q1) : 0.f;
+      const long long off = ((long long)b * heads + h) * seq + qc0;
+      const bool tail = qc0 + BW_QH > seq;
+      float nl[BW_QH], nd[BW_QH];        // -lse * log2(e) and -delta * scale of the 32 query columns
+      if (vec_rows && !tail) {
+#pragma unroll
+        for (int c = 0; c < BW_QH / 4; ++c) {
+          const float4 a = __ldg(reinterpret_cast<const float4*>(lse + off) + c);
+          const float4 g = __ldg(reinterpret_cast<const float4*>(delta + off) + c);
+          nl[4 * c] = a.x; nl[4 * c + 1] = a.y; nl[4 * c + 2] = a.z; nl[4 * c + 3] = a.w;
+          nd[4 * c] = g.x; nd[4 * c + 1] = g.y; nd[4 * c + 2] = g.z; nd[4 * c + 3] = g.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BW_QH; ++i) {
+          const bool in = qc0 + i < seq;
+          nl[i] = in ? __ldg(lse + off + i) : 0.f;
+          nd[i] = in ? __ldg(delta + off + i) : 0.f;
+        }
       }
 
       ok = mbar_wait(s_full, n & 1, abort_flag, status, 28);
@@ -284,21 +301,32 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_arrive(sp_free);
       float* s = reinterpret_cast<float*>(&sr[0]);
       float* d = reinterpret_cast<float*>(&dr[0]);
-      const bool diag = causal && (qc0 < kv0 + BW_KV);
+      // P = exp2(S c - lse log2 e), dS = P (dP scale - delta scale), on packed fp32 pairs.
+      const bool masked = tail || (causal && (qc0 < kv0 + BW_KV));
+      auto body = [&](auto mask_tag) {
+        constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll
-      for (int i = 0; i < BW_QH; ++i) {
-        const float e = fmaf(s[i], scale_log2, -__shfl_sync(0xffffffffu, my_lse, i));
-        float p = ((i & 3) == 3) ? poly_exp2(e) : fast_exp2(e);
-        if (diag && (kv_row > qc0 + i)) p = 0.f;
-        s[i] = p;
-        d[i] = p * (d[i] - __shfl_sync(0xffffffffu, my_dl, i)) * scale;
-      }
+        for (int i = 0; i < BW_QH; i += 2) {
+          float e0, e1;
+          f32x2_unpack(fma_f32x2(f32x2(s[i], s[i + 1]), sc2, mul_f32x2(f32x2(nl[i], nl[i + 1]), nlog2)), e0, e1);
+          float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
+          if (MASK) {
+            if ((causal && kv_row > qc0 + i) || qc0 + i >= seq) p0 = 0.f;
+            if ((causal && kv_row > qc0 + i + 1) || qc0 + i + 1 >= seq) p1 = 0.f;
+          }
+          const uint64_t dd = fma_f32x2(f32x2(d[i], d[i + 1]), s2, f32x2(nd[i], nd[i + 1]));
+          f32x2_unpack(mul_f32x2(f32x2(p0, p1), dd), d[i], d[i + 1]);
+          s[i] = p0;
+          s[i + 1] = p1;
+        }
+      };
+      if (masked) body(std::true_type{}); else body(std::false_type{});
       if (n > 0) {
         ok = mbar_wait(mma_done, (n - 1) & 1, abort_flag, status, 29);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        drain_dq(n - 1);
+        fetch_dq();
       }
       uint8_t* pt = smem + Cfg::OFF_PT;
       uint8_t* dst = smem + Cfg::OFF_DST;
@@ -319,13 +347,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_full);
+      if (n > 0) store_dq(n - 1);
     }
     if (ok && N > 0) {
       ok = mbar_wait(mma_done, (N - 1) & 1, abort_flag, status, 30);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
-        drain_dq(N - 1);
+        fetch_dq();
+        store_dq(N - 1);
         if (lane == 0) tma_store_wait0();  // all dQ reductions of this warp have landed
         // this thread's kv row of dV (warpgroup 0) or dK (warpgroup 1)
         const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
@@ -373,9 +403,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
-// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h) row.
+// delta[b,h,s] = -scale * sum_d dO[b,s,h,d] * O[b,s,h,d] (the form the main kernel adds to dP * scale);
+// one warp per (b,s,h) row.
 __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                    float* __restrict__ delta, long long rows, int seq, int heads, int head_dim) {
+                                    float* __restrict__ delta, long long rows, int seq, int heads, int head_dim,
+                                    float scale) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -392,7 +424,7 @@ __global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const _
     const long long bs = row / heads;  // b*seq + s
     const int h = (int)(row % heads);
     const long long bb = bs / seq, ss = bs % seq;
-    delta[(bb * heads + h) * seq + ss] = s;
+    delta[(bb * heads + h) * seq + ss] = -scale * s;
   }
 }
 
@@ -432,7 +464,7 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
   if (batch == 0 || seq == 0) return;
   const long long rows = (long long)batch * seq * heads;
   fa_bwd_delta_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
-                                                             delta, rows, seq, heads, head_dim);
+                                                             delta, rows, seq, heads, head_dim, scale);
   count_launch();
   check_launch();
   MB_CUDA_CHECK(cudaMemsetAsync(dq_accum, 0, rows * head_dim * sizeof(float), stream));

@@ -16,14 +16,11 @@
 //     TMEM set-up is paid once per SM instead of once per 256 query rows;
 //   * K and V travel in separate rings (2 and 3 stages of 32 KB), so a K tile is released as soon as
 //     both score products that read it were issued, one full step before its V tile.
-//   * two threads per query row: each of a tile's eight softmax warps owns 32 rows x 64 of the 128 score
-//     columns (the two halves of a row exchange their maxima through shared memory behind one named
-//     barrier per step). With one thread per row a tile's softmax was a single warp per scheduler,
-//     which cannot hide its own instruction latency (~4 cycles per dependent instruction): 900
-//     instructions took ~4000 cycles against 1024 cycles of tensor work per tile and step.
-// Warps: 0 = K/V loader, 1 = MMA issuer + TMEM owner, 2-9 = softmax of query tile 0, 10-17 = softmax of
-// tile 1, 18 = Q loader. Two 128-row query tiles per work item ping-pong as before: while one
-// tile's warps do their softmax the tensor pipe works for the other tile.
+// Warps: 0 = K/V loader, 1 = MMA issuer + TMEM owner, 2 = Q loader, 3 idle, 4-7 = softmax of query
+// tile 0, 8-11 = softmax of tile 1. Two 128-row query tiles per work item ping-pong as before: while one
+// tile's warpgroup does its softmax the tensor pipe works for the other tile. (Splitting every row over
+// two threads, 16 softmax warps with a named barrier per step, measured slower: 415 against
+// 625 TFLOP/s at batch 8, sequence 2048.)
 // TMEM (512 columns): S0 | S1 (128 fp32 columns each, P aliased on their first 64) | O0 | O1 (128 each).
 #include "api.h"
 #include "host_util.h"
@@ -36,21 +33,19 @@ CUtensorMap make_bshd_map(const void* base, int batch, int seq, int nheads, int 
 
 namespace {
 
-constexpr int F2_THREADS = 608;
+constexpr int F2_THREADS = 384;   // three warpgroups: service warps, softmax of tile 0, softmax of tile 1
 constexpr int F2_BM = 128;
 constexpr int F2_BN = 128;
 constexpr int F2_D = 128;
 constexpr int F2_KS = 2;   // K stages
-constexpr int F2_VS = 2;   // V stages
+constexpr int F2_VS = 3;   // V stages
 
 struct F2Cfg {
   static constexpr int TILE_BYTES = 128 * F2_D * 2;        // 32 KB: two 64-column chunks of [128 rows x 128 B]
   static constexpr int OFF_Q = 0;                          // two query tiles
   static constexpr int OFF_K = 2 * TILE_BYTES;
   static constexpr int OFF_V = OFF_K + F2_KS * TILE_BYTES;
-  static constexpr int OFF_X = OFF_V + F2_VS * TILE_BYTES;   // [2 tiles][2 halves][128 rows] floats: row maxima / sums
-  static constexpr int OFF_BAD = OFF_X + 2 * 2 * 128 * 4;    // [2] ints: a warp of the tile gave up a wait
-  static constexpr int OFF_BAR = OFF_BAD + 16;
+  static constexpr int OFF_BAR = OFF_V + F2_VS * TILE_BYTES;
   static constexpr int NUM_BARS = 4 + 2 * F2_KS + 2 * F2_VS + 6;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16 + 1024;
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory per CTA");
@@ -121,14 +116,12 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(&q_full[t], 1);
       mbar_init(&q_free[t], 1);
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 256);
+      mbar_init(&p_full[t], 128);
       mbar_init(&o_full[t], 1);
     }
     for (int s = 0; s < F2_KS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < F2_VS; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     *abort_flag = 0;
-    reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAD)[0] = 0;
-    reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAD)[1] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
@@ -143,7 +136,7 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
-  if (warp == 18) {
+  if (warp == 2) {
     // ------------------------------------------------------------------ Q loader
     if (lane == 0) {
       uint32_t n_q[2] = {0, 0};   // loads issued per tile (phase of q_free / q_full)
@@ -269,58 +262,52 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (it.J[t] > 0) ++n_q[t];
       }
     }
-  } else {
+  } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax + epilogue
-    const int sw = warp - 2;                 // 0..15
-    const int t = sw >> 3;                   // query tile
-    const int half = (sw >> 2) & 1;          // which 64 of the 128 score columns (and of the output columns)
+    const int sw = warp - 4;                 // 0..7
+    const int t = sw >> 2;                   // query tile
     const int quarter = warp & 3;            // TMEM lane quarter this warp may access
     const int r = quarter * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const uint32_t t_s = tmem_base + Cfg::COL_S + t * 128 + lane_sel;
-    const uint32_t t_o = tmem_base + Cfg::COL_O + t * 128 + half * 64 + lane_sel;
-    float* xch = reinterpret_cast<float*>(smem + Cfg::OFF_X) + t * 256;   // [2 halves][128 rows]
-    volatile int* tile_bad = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAD) + t;
+    const uint32_t t_o = tmem_base + Cfg::COL_O + t * 128 + lane_sel;
     uint32_t n_s = 0, n_o = 0;
     bool ok = true;
-    auto tile_sync = [&]() { asm volatile("bar.sync %0, 256;" ::"r"(1 + t) : "memory"); };
     for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
       const F2Item it = f2_item(w, n_qb, heads, batch, seq, causal);
       const int Jt = it.J[t];
       if (Jt == 0) continue;
       const int q_row = it.q0 + t * F2_BM + r;
-      float m_ref = 0.f, l = 0.f;            // l: sum over this thread's half of the columns
+      float m_ref = 0.f, l = 0.f;
       for (int j = 0; j < Jt && ok; ++j) {
         ok = mbar_wait(&s_full[t], n_s & 1, abort_flag, status, 89);
         ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         ++n_s;
         tc_fence_after();
-        uint32_t sr[2][32];
-        tmem_ld32(t_s + half * 64, sr[0]);
-        tmem_ld32(t_s + half * 64 + 32, sr[1]);
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sr[c]);
         tmem_ld_wait();
         float* s = reinterpret_cast<float*>(&sr[0][0]);
-        const int kv0 = j * F2_BN + half * 64;
+        const int kv0 = j * F2_BN;
         const int limit = causal ? min(seq - 1, q_row) : seq - 1;
-        if (kv0 + 63 > limit) {
+        if (kv0 + F2_BN - 1 > limit) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
+          for (int i = 0; i < 128; ++i)
             if (kv0 + i > limit) s[i] = -INFINITY;
         }
         float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-        for (int i = 4; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-        const float mloc = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        // Both halves of a row meet here: every thread of the tile has its scores in registers (so the
-        // P stores below may overwrite S columns of the other half) and the row maximum is exchanged.
-        // A warp whose wait was abandoned still reaches the barrier and tells the other seven, so that
-        // the whole tile leaves together and nobody is left waiting at a later barrier.
-        xch[half * 128 + r] = mloc;
-        if (!ok) *tile_bad = 1;
-        tile_sync();
-        ok = *tile_bad == 0;
-        if (!ok) break;
-        const float m_new = fmaxf(mloc, xch[(half ^ 1) * 128 + r]) * scale_log2;
+        for (int i = 4; i < 124; i += 8) {
+          mx4[0] = fmax3(mx4[0], s[i], s[i + 1]);
+          mx4[1] = fmax3(mx4[1], s[i + 2], s[i + 3]);
+          mx4[2] = fmax3(mx4[2], s[i + 4], s[i + 5]);
+          mx4[3] = fmax3(mx4[3], s[i + 6], s[i + 7]);
+        }
+        mx4[0] = fmax3(mx4[0], s[124], s[125]);
+        mx4[1] = fmax3(mx4[1], s[126], s[127]);
+        const float m_new = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
         float alpha = 1.f;
         bool need = false;
         if (j == 0) {
@@ -331,11 +318,10 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           m_ref = m_new;
         }
         // S_t(j) complete implies PV_t(j-1) complete (same issuing thread, commit covers earlier MMAs):
-        // O_t is quiescent until this tile's warps arrive on p_full, so a rescale can happen right here.
-        // Each half rescales its own 64 output columns; both halves take the same decision per row.
+        // O_t is quiescent until this warpgroup arrives on p_full, so a rescale can happen right here.
         if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < 4; ++c) {
             uint32_t orr[32];
             tmem_ld32(t_o + c * 32, orr);
             tmem_ld_wait();
@@ -344,19 +330,26 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tmem_st32(t_o + c * 32, orr);
           }
         }
-        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        // Packed fp32 pairs (fma.rn.f32x2 / add.rn.f32x2) halve the issue slots of the scale-and-shift
+        // and of the row sum; the exponentials themselves run at the special-function rate of 16 per
+        // clock per SM, which for two 128 x 128 tiles equals the tensor time of a step.
+        const uint64_t sc2 = f32x2(scale_log2, scale_log2), nm2 = f32x2(-m_ref, -m_ref);
+        uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};
         uint32_t* pk = &sr[0][0];         // packed in place: pair i lands in word i / 2, behind the read position
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float e0 = fmaf(s[i], scale_log2, -m_ref), e1 = fmaf(s[i + 1], scale_log2, -m_ref);
-          // three of four exponentials on the special-function unit, one on the FMA pipe
-          const float p0 = fast_exp2(e0);
-          const float p1 = ((i & 3) == 2) ? poly_exp2(e1) : fast_exp2(e1);
-          rs4[(i >> 1) & 3] += p0 + p1;
+        for (int i = 0; i < 128; i += 2) {
+          float e0, e1;
+          f32x2_unpack(fma_f32x2(f32x2(s[i], s[i + 1]), sc2, nm2), e0, e1);
+          const float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
+          rs2[(i >> 1) & 3] = add_f32x2(rs2[(i >> 1) & 3], f32x2(p0, p1));
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
-        l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
-        tmem_st32(t_s + half * 32, sr[0]);   // P_t: bf16 pairs over the first 64 columns of S_t
+        float rs[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) f32x2_unpack(rs2[q], rs[2 * q], rs[2 * q + 1]);
+        l = l * alpha + (((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7])));
+        tmem_st32(t_s, sr[0]);            // P_t: bf16 pairs over the first 64 columns of S_t
+        tmem_st32(t_s + 32, sr[1]);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_full[t]);
@@ -364,18 +357,13 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       ok = mbar_wait(&o_full[t], n_o & 1, abort_flag, status, 90);
       ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       ++n_o;
       tc_fence_after();
-      xch[half * 128 + r] = l;             // the row sum is the sum of both halves
-      if (!ok) *tile_bad = 1;
-      tile_sync();
-      ok = *tile_bad == 0;
-      if (!ok) break;
-      const float l_row = l + xch[(half ^ 1) * 128 + r];
-      const float inv_l = l_row > 0.f ? 1.f / l_row : 0.f;
-      __nv_bfloat16* orow = o + ((long long)it.b * seq + q_row) * o_tok_stride + (long long)it.h * F2_D + half * 64;
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = o + ((long long)it.b * seq + q_row) * o_tok_stride + (long long)it.h * F2_D;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t orr[32];
         tmem_ld32(t_o + c * 32, orr);
         tmem_ld_wait();
@@ -392,11 +380,9 @@ fa_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
-      if (half == 0 && q_row < seq && lse)
-        lse[((long long)it.b * heads + it.h) * seq + q_row] = m_ref * 0.6931471805599453f + logf(l_row);
+      if (q_row < seq && lse) lse[((long long)it.b * heads + it.h) * seq + q_row] = m_ref * 0.6931471805599453f + logf(l);
       // The TMEM loads above have completed (tmem_ld_wait); the next item's first PV product waits for
-      // this tile's next arrives on p_full, so O_t is not overwritten before it was read. The exchange
-      // slots are rewritten only after the next s_full wait, which follows every partner's read.
+      // this warpgroup's next arrives on p_full, so O_t is not overwritten before it was read.
       tc_fence_before();
     }
   }

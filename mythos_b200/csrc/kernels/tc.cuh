@@ -265,14 +265,46 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const vo
                : "memory");
 }
 
-// Two fp32 -> one bf16x2 word on the integer pipe: add half an ulp of bf16 to the magnitude bits and
-// keep the upper halves (round to nearest, ties away from zero; differs from round-to-nearest-even only
-// on exact ties). The conversion instruction (cvt.rn.bf16x2.f32) issues on the special-function pipe,
-// which the softmax and activation epilogues already saturate with exp2 / tanh: with it, that pipe read
-// 85-92 % busy in the attention and fused-epilogue kernels while the tensor pipe idled.
+// Two fp32 -> one bf16x2 word (round to nearest even). Measured on a B200: cvt.rn.bf16x2.f32 issues at
+// 64 lanes per clock per SM (not on the special-function unit, which runs ex2 / tanh at 16), so one
+// conversion costs less than the two integer adds and the byte permute that would replace it.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
-  return __byte_perm(a, b, 0x7632);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// max(a, b, c) in one instruction; a two-input max issues at the same half rate, so reductions over a
+// row of scores take half the issue slots this way.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Two fp32 values in one 64-bit register for the packed fp32 instructions of sm_100 (same arithmetic
+// rate as the scalar forms, half the issue slots).
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
 }
 
 }  // namespace mb
