@@ -242,11 +242,14 @@ def main() -> int:
     launches0 = native.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    native.require().comm_barrier_wait_stats(True)   # device-side wait counters of the flag barriers: cleared
     e0.record()
     for i in range(args.steps):
         ids, tg = dev_batches[i % 2]
         loss = trainer.train_step(ids, tg)
     e1.record()
+    torch.cuda.synchronize()
+    n_bar, wait_cycles, longest_cycles = native.require().comm_barrier_wait_stats(True)
     barrier()
     dev_ms = e0.elapsed_time(e1)
     launches = native.launch_count() - launches0
@@ -263,12 +266,22 @@ def main() -> int:
     clocks = sampler.stop()
     native.check_status(device)
 
-    t = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    # cycles between a rank's arrival at a flag barrier and the last peer's, converted with the SM clock
+    # sampled during the run: how long this rank sat waiting for the others, per step
+    mhz = float(clocks.get("sm_mhz") or 0) or 1700.0
+    wait_ms = wait_cycles / (mhz * 1e3) / max(1, args.steps)
+    longest_ms = longest_cycles / (mhz * 1e3)
+    t = torch.tensor([dev_ms, e2e_s * 1e3, wait_ms, longest_ms], device=device, dtype=torch.float64)
+    tsum = torch.tensor([wait_ms], device=device, dtype=torch.float64)
     if dp is not None:
         import torch.distributed as dist
 
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
+    barrier_wait = {"barriers_per_step": n_bar / max(1, args.steps), "mean_ms_per_step": float(tsum[0]) / world,
+                    "max_ms_per_step": float(t[2]), "longest_single_wait_ms": float(t[3]),
+                    "note": "device cycle counters in the flag-barrier kernel (arrival -> last peer), mean / max over ranks"}
     tokens_per_step = args.per_gpu_batch * SEQ * world
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
@@ -316,6 +329,7 @@ def main() -> int:
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": int(launches),
+            "barrier_wait": barrier_wait,
             "model_flops_per_token": flops_per_token,
             "fraction_of_measured_bf16_sustained": mfu,
             "final_loss": last,

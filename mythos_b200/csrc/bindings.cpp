@@ -212,6 +212,41 @@ void act_fwd(const Tensor& x, Tensor& out, int64_t kind) {
   c10::cuda::CUDAGuard guard(x.device());
   mb::act_fwd(x.data_ptr(), out.data_ptr(), x.numel(), (int)kind, cur_stream());
 }
+void act_bwd(const Tensor& x, const Tensor& dout, Tensor& dx, int64_t kind) {
+  chk_c(x, BF16, "x");
+  chk_c(dout, BF16, "dout");
+  chk_c(dx, BF16, "dx");
+  TORCH_CHECK(dout.numel() == x.numel() && dx.numel() == x.numel(), "act_bwd: shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::act_bwd(x.data_ptr(), dout.data_ptr(), dx.data_ptr(), x.numel(), (int)kind, cur_stream());
+}
+void softmax_rows_bwd(const Tensor& y, const Tensor& dy, Tensor& dx) {
+  chk_c(y, BF16, "y");
+  chk_c(dy, BF16, "dy");
+  chk_c(dx, BF16, "dx");
+  TORCH_CHECK(dy.numel() == y.numel() && dx.numel() == y.numel(), "softmax_rows_bwd: shape mismatch");
+  const int64_t cols = y.size(-1);
+  c10::cuda::CUDAGuard guard(y.device());
+  mb::softmax_rows_bwd(y.data_ptr(), dy.data_ptr(), dx.data_ptr(), (int)(y.numel() / cols), (int)cols, cur_stream());
+}
+void layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& gamma, Tensor& dx, Tensor& partial, Tensor& dgb,
+                   double eps) {
+  chk_c(dy, BF16, "dy");
+  chk_c(x, BF16, "x");
+  chk_c(gamma, BF16, "gamma");
+  chk_c(dx, BF16, "dx");
+  chk_c(partial, F32, "partial");
+  chk_c(dgb, F32, "dgb");
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  TORCH_CHECK(dy.numel() == x.numel() && dx.numel() == x.numel() && gamma.numel() == dim, "layernorm_bwd: shape mismatch");
+  TORCH_CHECK(partial.dim() == 2 && partial.size(1) == 2 * dim && dgb.numel() == 2 * dim,
+              "layernorm_bwd: partial must be [n, 2 * dim] and dgb [2 * dim]");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), dx.data_ptr(), partial.data_ptr<float>(),
+                    (int)partial.size(0), (int)rows, (int)dim, (float)eps, cur_stream());
+  mb::rmsnorm_bwd_reduce(partial.data_ptr<float>(), dgb.data_ptr<float>(), (int)partial.size(0), (int)(2 * dim), false,
+                         cur_stream());
+}
 void add(const Tensor& a, const Tensor& b, Tensor& out) {
   chk_c(a, BF16, "a");
   chk_c(b, BF16, "b");
@@ -378,7 +413,8 @@ void flash_attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o
 
 void flash_attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& dout,
                     const Tensor& lse, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& dq_accum, Tensor& delta,
-                    bool causal, double scale, const OptTensor& status) {
+                    bool causal, double scale, const OptTensor& status, const OptTensor& rope_pos,
+                    const OptTensor& rope_table) {
   chk(q, BF16, "q");
   chk(k, BF16, "k");
   chk(v, BF16, "v");
@@ -399,12 +435,26 @@ void flash_attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Ten
   TORCH_CHECK(k.stride(1) == v.stride(1) && dk.stride(1) == dv.stride(1),
               "flash_attn_bwd: k/v and dk/dv must share a token stride");
   TORCH_CHECK(dq_accum.numel() >= B * S * H * D && delta.numel() >= B * H * S, "flash_attn_bwd: scratch too small");
+  const int* pos_ptr = nullptr;
+  const float* cs_ptr = nullptr;
+  int max_pos = 0;
+  if (rope_table.has_value()) {
+    TORCH_CHECK(rope_pos.has_value(), "flash_attn_bwd: rope_table needs rope_pos");
+    chk_c(*rope_table, F32, "rope_table");
+    chk_c(*rope_pos, torch::kInt32, "rope_pos");
+    TORCH_CHECK(D == 128 && rope_table->dim() == 3 && rope_table->size(1) == 64 && rope_table->size(2) == 2,
+                "flash_attn_bwd: rope_table must be [max_pos, 64, 2] (head_dim 128)");
+    TORCH_CHECK(rope_pos->numel() == B * S, "flash_attn_bwd: rope_pos must have batch * seq entries");
+    pos_ptr = rope_pos->data_ptr<int>();
+    cs_ptr = rope_table->data_ptr<float>();
+    max_pos = (int)rope_table->size(0);
+  }
   c10::cuda::CUDAGuard guard(q.device());
   mb::flash_attn_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
                              lse.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                              dq_accum.data_ptr<float>(), delta.data_ptr<float>(), (int)B, (int)S, (int)H, (int)Hkv,
                              (int)D, q.stride(1), k.stride(1), dq.stride(1), dk.stride(1), causal, (float)scale,
-                             status_ptr(status), cur_stream());
+                             status_ptr(status), cur_stream(), pos_ptr, cs_ptr, max_pos);
 }
 
 mb::PeerPtrs to_peers(const std::vector<int64_t>& ptrs) {
@@ -423,6 +473,12 @@ void symm_barrier(const std::vector<int64_t>& flag_ptrs, const std::vector<int64
                    send_val.has_value() ? send_val->data_ptr<float>() : nullptr, (int)rank, (int)flag_ptrs.size(),
                    (int)epoch, epoch_dev.has_value() ? epoch_dev->data_ptr<int>() : nullptr, limit_cycles,
                    status_ptr(status), cur_stream());
+}
+
+std::vector<int64_t> comm_barrier_wait_stats(bool reset) {
+  unsigned long long v[3];
+  mb::comm_barrier_wait_stats(v, reset);
+  return {(int64_t)v[0], (int64_t)v[1], (int64_t)v[2]};
 }
 
 void zero_reduce_scatter(const std::vector<int64_t>& grad_ptrs, Tensor& out, int64_t shard_off, Tensor& sumsq,
@@ -1034,6 +1090,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("relu2_fwd", &relu2_fwd);
   m.def("relu2_bwd", &relu2_bwd);
   m.def("act_fwd", &act_fwd);
+  m.def("act_bwd", &act_bwd);
+  m.def("softmax_rows_bwd", &softmax_rows_bwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
   m.def("add", &add);
   m.def("softmax_rows", &softmax_rows);
   m.def("embedding_fwd", &embedding_fwd);
@@ -1050,7 +1109,10 @@ PYBIND11_MODULE(_C, m) {
   m.def("cast_bf16_to_f32", &cast_bf16_to_f32);
   m.def("oil_codebook_stats", &oil_codebook_stats);
   m.def("flash_attn_fwd", &flash_attn_fwd);
-  m.def("flash_attn_bwd", &flash_attn_bwd);
+  m.def("flash_attn_bwd", &flash_attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("dout"),
+        py::arg("lse"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("dq_accum"), py::arg("delta"),
+        py::arg("causal"), py::arg("scale"), py::arg("status") = py::none(), py::arg("rope_pos") = py::none(),
+        py::arg("rope_table") = py::none());
   m.def("dequant_gemm", &dequant_gemm, py::arg("x"), py::arg("packed"), py::arg("codebooks"), py::arg("cb_map"),
         py::arg("scales"), py::arg("fmt"), py::arg("N"), py::arg("K"), py::arg("block_size"), py::arg("out"),
         py::arg("peer_ptrs"), py::arg("k_splits"), py::arg("status"), py::arg("peer_bf16_offset") = -1);
@@ -1082,6 +1144,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("peer_add_f32", &peer_add_f32);
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);
+  m.def("comm_barrier_wait_stats", &comm_barrier_wait_stats, py::arg("reset") = true);
   m.def("zero_reduce_scatter", &zero_reduce_scatter, py::arg("grad_ptrs"), py::arg("out"), py::arg("shard_off"),
         py::arg("sumsq"), py::arg("multicast_ptr") = 0, py::arg("max_blocks") = 0, py::arg("scratch") = py::none());
   m.def("tp_allreduce_multimem", &tp_allreduce_multimem);

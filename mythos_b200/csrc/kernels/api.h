@@ -86,6 +86,9 @@ void rmsnorm_bwd_reduce(const float* dgamma_partial, float* dgamma, int n_partia
                         cudaStream_t stream);
 void layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, int rows, int dim, float eps,
                    cudaStream_t stream);
+// dx and per-CTA partials [n_partial, 2 * dim] = [dgamma | dbeta]; mean / rstd are recomputed from x.
+void layernorm_bwd(const void* dy, const void* x, const void* gamma, void* dx, float* partial, int n_partial, int rows,
+                   int dim, float eps, cudaStream_t stream);
 
 // ---- rotary embedding, half-split pairs (d, d + D/2) (rope.cu)
 // x: [tokens, heads, head_dim] bf16 in place; pos: [tokens] int32; inverse = backward pass.
@@ -104,8 +107,10 @@ void relu2_fwd(const void* x, void* out, long long n, cudaStream_t stream);
 void relu2_bwd(const void* x, const void* dout, void* dx, long long n, cudaStream_t stream);
 enum : int { ACT_RELU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SIGMOID = 4, ACT_TANH = 5 };
 void act_fwd(const void* x, void* out, long long n, int kind, cudaStream_t stream);
+void act_bwd(const void* x, const void* dout, void* dx, long long n, int kind, cudaStream_t stream);
 void add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
 void softmax_rows(const void* x, void* y, int rows, int cols, cudaStream_t stream);
+void softmax_rows_bwd(const void* y, const void* dy, void* dx, int rows, int cols, cudaStream_t stream);
 
 // ---- embedding (embed.cu)
 void embedding_fwd(const int* ids, const void* table, void* out, int tokens, int dim, int vocab, cudaStream_t stream);
@@ -178,7 +183,11 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
                             const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch,
                             int seq, int heads, int kv_heads, int head_dim, long long q_tok_stride,
                             long long kv_tok_stride, long long dq_tok_stride, long long dkv_tok_stride, bool causal,
-                            float scale, int* status, cudaStream_t stream);
+                            float scale, int* status, cudaStream_t stream, const int* rope_pos = nullptr,
+                            const float* rope_cs = nullptr, int rope_max_pos = 0);
+// rope_cs ([rope_max_pos, 64, 2] fp32 cos/sin) with rope_pos ([batch * seq] int32): q and k were rotated
+// before the forward pass, and dq / dk leave rotated back (dq in the fp32 -> bf16 conversion, dk in the
+// kernel's epilogue), i.e. as gradients of the un-rotated projection.
 
 // ---- fused decode epilogues (decode_fused.cu)
 // Exactly one of `acc` (fp32 [rows, dim], zeroed) / `slots` (n_slots bf16 partials, slot_stride apart) is summed,
@@ -234,6 +243,9 @@ struct ZeroFusedArgs {
 // With epoch_ptr != null the epoch is read from (and advanced in) device memory instead of `epoch`.
 void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* send_val, int rank, int world, int epoch,
                   int* epoch_ptr, long long limit_cycles, int* status, cudaStream_t stream);
+// out = {barriers launched, sum of wait cycles, longest wait in cycles} on the current device since the
+// last reset (SM clock cycles between a rank's arrival and the last peer's); synchronises the device.
+void comm_barrier_wait_stats(unsigned long long out[3], bool reset);
 // Registers the status word of the current device: the kernels below that consume data guarded by a
 // flag barrier (zero_reduce_scatter, zero_adamw_ste_allgather, tp_reduce_slots, tp_reduce_slots_bcast,
 // tp_allreduce_pull) return without writing once the word is non-zero (a bounded wait expired).

@@ -61,7 +61,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const __grid_constant__ CUtensorMap tm_dq, const float* __restrict__ lse,
               const float* __restrict__ delta,
               __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, long long dkv_tok_stride, int seq,
-              int heads, int kv_heads, int causal, float scale, float scale_log2, int* status) {
+              int heads, int kv_heads, int causal, float scale, float scale_log2, const int* __restrict__ rope_pos,
+              const float2* __restrict__ rope_cs, int rope_max_pos, int* status) {
   using Cfg = BwCfg;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -359,10 +360,39 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (lane == 0) tma_store_wait0();  // all dQ reductions of this warp have landed
         // this thread's kv row of dV (warpgroup 0) or dK (warpgroup 1)
         const long long row_off = ((long long)b * seq + kv_row) * dkv_tok_stride + (long long)hkv * BW_D;
-        {
-          const int which = wg;
-          __nv_bfloat16* out = (which == 0 ? dv : dk) + row_off;
-          const uint32_t col = which == 0 ? Cfg::COL_DV : Cfg::COL_DK;
+        const int which = wg;
+        __nv_bfloat16* out = (which == 0 ? dv : dk) + row_off;
+        const uint32_t col = which == 0 ? Cfg::COL_DV : Cfg::COL_DK;
+        if (which == 1 && rope_cs != nullptr) {
+          // dK leaves rotated back by the row's position (the gradient of the un-rotated projection):
+          // dx1 = dy1 cos + dy2 sin, dx2 = dy2 cos - dy1 sin for the pair (d, d + 64).
+          int p = kv_row < seq ? __ldg(rope_pos + (long long)b * seq + kv_row) : 0;
+          p = min(max(p, 0), rope_max_pos - 1);
+          const float4* cs_row = reinterpret_cast<const float4*>(rope_cs + (long long)p * 64);
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t lo[32], hi[32];
+            tmem_ld32(tmem_base + col + cc * 32 + lane_sel, lo);
+            tmem_ld32(tmem_base + col + 64 + cc * 32 + lane_sel, hi);
+            tmem_ld_wait();
+            if (kv_row < seq) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t a[4], c2[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                  const float4 t = __ldg(cs_row + ((cc * 32 + 8 * j + i) >> 1));  // (cos, sin) of two pairs
+                  const float x0 = __uint_as_float(lo[8 * j + i]), x1 = __uint_as_float(lo[8 * j + i + 1]);
+                  const float y0 = __uint_as_float(hi[8 * j + i]), y1 = __uint_as_float(hi[8 * j + i + 1]);
+                  a[i >> 1] = pack_bf16x2(x0 * t.x + y0 * t.y, x1 * t.z + y1 * t.w);
+                  c2[i >> 1] = pack_bf16x2(y0 * t.x - x0 * t.y, y1 * t.z - x1 * t.w);
+                }
+                *reinterpret_cast<uint4*>(out + cc * 32 + 8 * j) = make_uint4(a[0], a[1], a[2], a[3]);
+                *reinterpret_cast<uint4*>(out + 64 + cc * 32 + 8 * j) = make_uint4(c2[0], c2[1], c2[2], c2[3]);
+              }
+            }
+          }
+        } else {
 #pragma unroll 1
           for (int c = 0; c < BW_D / 32; ++c) {
             uint32_t a[32];
@@ -403,28 +433,49 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
-// delta[b,h,s] = -scale * sum_d dO[b,s,h,d] * O[b,s,h,d] (the form the main kernel adds to dP * scale);
-// one warp per (b,s,h) row.
-__global__ void fa_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                                    float* __restrict__ delta, long long rows, int seq, int heads, int head_dim,
-                                    float scale) {
-  const int lane = threadIdx.x & 31;
-  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  float s = 0.f;
-  for (int c = lane * 8; c < head_dim; c += 256) {
-    float a[8], g[8];
-    unpack8(ldg8(o, row * head_dim + c), a);
-    unpack8(ldg8(dout, row * head_dim + c), g);
+// Prologue of the backward pass, one pass over O and dO: delta[b,h,s] = -scale * sum_d dO[b,s,h,d] *
+// O[b,s,h,d] (the form the main kernel adds to dP * scale), and the fp32 dQ accumulator row of the same
+// (b,s,h) is zeroed (it used to be a separate memset). Sixteen lanes own one row of 128 columns, eight
+// columns each; every thread works on two rows so that four 16-byte loads are in flight.
+__global__ void __launch_bounds__(256)
+fa_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                   float* __restrict__ dq_accum, long long rows, int seq, int heads, float scale) {
+  const int sub = threadIdx.x & 15;
+  const long long r0 = ((long long)blockIdx.x * 16 + (threadIdx.x >> 4)) * 2;
+  float acc[2] = {0.f, 0.f};
+  bf16x8 ov[2], gv[2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s += a[i] * g[i];
+  for (int k = 0; k < 2; ++k) {
+    const long long row = r0 + k;
+    if (row < rows) {
+      ov[k] = ldg8(o, row * BW_D + sub * 8);
+      gv[k] = ldg8(dout, row * BW_D + sub * 8);
+    } else {
+      ov[k] = bf16x8{};
+      gv[k] = bf16x8{};
+    }
   }
-  s = warp_sum(s);
-  if (lane == 0) {
-    const long long bs = row / heads;  // b*seq + s
-    const int h = (int)(row % heads);
-    const long long bb = bs / seq, ss = bs % seq;
-    delta[(bb * heads + h) * seq + ss] = -scale * s;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const long long row = r0 + k;
+    float a[8], g[8];
+    unpack8(ov[k], a);
+    unpack8(gv[k], g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[k] += a[i] * g[i];
+#pragma unroll
+    for (int m = 8; m >= 1; m >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], m);
+    if (row < rows) {
+      float4* z = reinterpret_cast<float4*>(dq_accum + row * BW_D + sub * 8);
+      z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (sub == 0) {
+        const long long bs = row / heads;  // b*seq + s
+        const int h = (int)(row % heads);
+        const long long bb = bs / seq, ss = bs % seq;
+        delta[(bb * heads + h) * seq + ss] = -scale * acc[k];
+      }
+    }
   }
 }
 
@@ -444,6 +495,34 @@ __global__ void cast_rows_kernel(const float* __restrict__ src, __nv_bfloat16* _
   }
 }
 
+// The same conversion with the rotary embedding undone on the way (heads of 128, pairs (d, d + 64)):
+// dst = bf16(R(-pos[r]) src). One thread owns four pairs of one head.
+__global__ void cast_rows_rope_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows,
+                                      int heads, long long dst_stride, const int* __restrict__ pos,
+                                      const float2* __restrict__ cs, int max_pos) {
+  const int per_row = heads * 16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per_row;
+    const int w = (int)(i % per_row);
+    const int h = w >> 4, c = (w & 15) * 4;
+    const int p = min(max(__ldg(pos + r), 0), max_pos - 1);
+    const float4* t4 = reinterpret_cast<const float4*>(cs + (long long)p * 64 + c);
+    const float4 t0 = __ldg(t4), t1 = __ldg(t4 + 1);   // (cos, sin) of pairs c, c+1 | c+2, c+3
+    const float* s = src + (r * heads + h) * BW_D;
+    const float4 x = *reinterpret_cast<const float4*>(s + c);
+    const float4 y = *reinterpret_cast<const float4*>(s + 64 + c);
+    __nv_bfloat16* d = dst + r * dst_stride + h * BW_D;
+    uint2 lo, hi;
+    lo.x = pack_bf16x2(x.x * t0.x + y.x * t0.y, x.y * t0.z + y.y * t0.w);
+    lo.y = pack_bf16x2(x.z * t1.x + y.z * t1.y, x.w * t1.z + y.w * t1.w);
+    hi.x = pack_bf16x2(y.x * t0.x - x.x * t0.y, y.y * t0.z - x.y * t0.w);
+    hi.y = pack_bf16x2(y.z * t1.x - x.z * t1.y, y.w * t1.z - x.w * t1.w);
+    *reinterpret_cast<uint2*>(d + c) = lo;
+    *reinterpret_cast<uint2*>(d + 64 + c) = hi;
+  }
+}
+
 }  // namespace
 
 void flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
@@ -451,23 +530,24 @@ void flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, 
                     int kv_heads, int head_dim, bool causal, float scale, int* status, cudaStream_t stream) {
   flash_attn_bwd_strided(q, k, v, o, dout, lse, dq, dk, dv, dq_accum, delta, batch, seq, heads, kv_heads, head_dim,
                          (long long)heads * head_dim, (long long)kv_heads * head_dim, (long long)heads * head_dim,
-                         (long long)kv_heads * head_dim, causal, scale, status, stream);
+                         (long long)kv_heads * head_dim, causal, scale, status, stream, nullptr, nullptr, 0);
 }
 
 void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* dout,
                             const float* lse, void* dq, void* dk, void* dv, float* dq_accum, float* delta, int batch,
                             int seq, int heads, int kv_heads, int head_dim, long long q_tok_stride,
                             long long kv_tok_stride, long long dq_tok_stride, long long dkv_tok_stride, bool causal,
-                            float scale, int* status, cudaStream_t stream) {
+                            float scale, int* status, cudaStream_t stream, const int* rope_pos, const float* rope_cs,
+                            int rope_max_pos) {
   MB_REQUIRE(head_dim == 128, "flash_attn_bwd: head_dim must be 128");
   MB_REQUIRE(heads % kv_heads == 0, "flash_attn_bwd: heads must be a multiple of kv_heads");
   if (batch == 0 || seq == 0) return;
   const long long rows = (long long)batch * seq * heads;
-  fa_bwd_delta_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
-                                                             delta, rows, seq, heads, head_dim, scale);
+  MB_REQUIRE(rope_cs == nullptr || (rope_pos != nullptr && rope_max_pos > 0), "flash_attn_bwd: rope table without positions");
+  fa_bwd_prep_kernel<<<(unsigned)ceil_div(rows, 32), 256, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                                     delta, dq_accum, rows, seq, heads, scale);
   count_launch();
   check_launch();
-  MB_CUDA_CHECK(cudaMemsetAsync(dq_accum, 0, rows * head_dim * sizeof(float), stream));
   const CUtensorMap tq = make_bshd_map(q, batch, seq, heads, head_dim, q_tok_stride, BW_Q);
   const CUtensorMap tdo = make_bshd_map(dout, batch, seq, heads, head_dim, (long long)heads * head_dim, BW_Q);
   const CUtensorMap tk = make_bshd_map(k, batch, seq, kv_heads, head_dim, kv_tok_stride, BW_KV);
@@ -489,7 +569,8 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
   fa_bwd_kernel<<<grid, BW_THREADS, BwCfg::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, lse, delta,
                                                                  (__nv_bfloat16*)dk, (__nv_bfloat16*)dv,
                                                                  dkv_tok_stride, seq, heads, kv_heads, causal ? 1 : 0, scale,
-                                                                 scale * 1.4426950408889634f, status);
+                                                                 scale * 1.4426950408889634f, rope_pos,
+                                                                 reinterpret_cast<const float2*>(rope_cs), rope_max_pos, status);
   count_launch();
   check_launch();
   {
@@ -498,7 +579,11 @@ void flash_attn_bwd_strided(const void* q, const void* k, const void* v, const v
     long long g = (tok * (cols / 4) + 255) / 256;
     const long long cap = (long long)sm_count() * 16;
     if (g > cap) g = cap;
-    cast_rows_kernel<<<(int)g, 256, 0, stream>>>(dq_accum, (__nv_bfloat16*)dq, tok, cols, dq_tok_stride);
+    if (rope_cs != nullptr)
+      cast_rows_rope_kernel<<<(int)g, 256, 0, stream>>>(dq_accum, (__nv_bfloat16*)dq, tok, heads, dq_tok_stride, rope_pos,
+                                                        reinterpret_cast<const float2*>(rope_cs), rope_max_pos);
+    else
+      cast_rows_kernel<<<(int)g, 256, 0, stream>>>(dq_accum, (__nv_bfloat16*)dq, tok, cols, dq_tok_stride);
     count_launch();
     check_launch();
   }

@@ -54,6 +54,11 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   return v;
 }
 
+// Wait statistics of the flag barriers launched on this device: [0] number of barriers, [1] sum and
+// [2] maximum of the cycles between this rank's arrival and the last peer's (the slowest of the
+// per-peer waits of a launch). Read and cleared by comm_barrier_wait_stats.
+__device__ unsigned long long g_barrier_wait[3];
+
 // One thread per peer. flags[r] on every rank is an int array of `world` slots; slot s of rank r
 // holds the last epoch that rank s announced to rank r.
 __global__ void symm_barrier_kernel(PeerPtrs flags, PeerPtrs slots, const float* send_val, int rank, int world,
@@ -64,17 +69,27 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, PeerPtrs slots, const float*
   if (epoch_ptr) epoch = *epoch_ptr + 1;
   __syncwarp();
   if (p == 0 && epoch_ptr) *epoch_ptr = epoch;
-  if (p >= world) return;
-  __threadfence_system();
-  if (send_val) reinterpret_cast<float*>(slots.p[p])[rank] = *send_val;
-  st_release_sys(reinterpret_cast<int*>(flags.p[p]) + rank, epoch);
-  const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + p;
-  const long long t0 = clock64();
-  while (ld_acquire_sys(mine) < epoch) {
-    if (clock64() - t0 > limit_cycles) {
-      if (status) atomicCAS(status, 0, 1 | (40 << 16));
-      break;
+  long long waited = 0;
+  if (p < world) {
+    __threadfence_system();
+    if (send_val) reinterpret_cast<float*>(slots.p[p])[rank] = *send_val;
+    st_release_sys(reinterpret_cast<int*>(flags.p[p]) + rank, epoch);
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + p;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(mine) < epoch) {
+      if (clock64() - t0 > limit_cycles) {
+        if (status) atomicCAS(status, 0, 1 | (40 << 16));
+        break;
+      }
     }
+    waited = clock64() - t0;
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) waited = max(waited, __shfl_xor_sync(0xffffffffu, waited, m));
+  if (p == 0) {
+    atomicAdd(&g_barrier_wait[0], 1ull);
+    atomicAdd(&g_barrier_wait[1], (unsigned long long)waited);
+    atomicMax(&g_barrier_wait[2], (unsigned long long)waited);
   }
 }
 
@@ -271,6 +286,14 @@ void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* sen
   symm_barrier_kernel<<<1, 32, 0, stream>>>(flags, slots, send_val, rank, world, epoch, epoch_ptr, limit_cycles, status);
   count_launch();
   check_launch();
+}
+
+void comm_barrier_wait_stats(unsigned long long out[3], bool reset) {
+  MB_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_barrier_wait, 3 * sizeof(unsigned long long)));
+  if (reset) {
+    const unsigned long long zero[3] = {0ull, 0ull, 0ull};
+    MB_CUDA_CHECK(cudaMemcpyToSymbol(g_barrier_wait, zero, sizeof(zero)));
+  }
 }
 
 void zero_reduce_scatter(const PeerPtrs& grads, float* out, long long shard_off, long long n, int world, float* sumsq,

@@ -198,6 +198,95 @@ __global__ void __launch_bounds__(1024) layernorm_fwd_kernel(const __nv_bfloat16
   }
 }
 
+// LayerNorm backward. mean and rstd are recomputed from x (one extra reduction, no saved statistics):
+//   xhat = (x - mean) rstd,  a = gamma dy,  dx = rstd (a - mean(a) - xhat mean(a xhat)),
+//   dgamma += dy xhat,  dbeta += dy.
+// Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dgamma / dbeta partials in registers;
+// partial[blockIdx.x] = [dgamma | dbeta] (2 * dim floats), summed over CTAs by the column-sum kernel.
+template <int NC>
+__global__ void __launch_bounds__(512) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                     const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ dx,
+                                     float* __restrict__ partial, int rows, int dim, float eps) {
+  __shared__ float scratch[32];
+  const int nchunk = dim >> 3;
+  float g[NC][8], dg[NC][8], db[NC][8];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dg[c][i] = 0.f; db[c][i] = 0.f; g[c][i] = 0.f; }
+    if (ch < nchunk) unpack8(ldg8(gamma, ch * 8), g[c]);
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    float h[NC][8], d[NC][8];
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+        unpack8(ldg8(x, row * dim + ch * 8), h[c]);
+        unpack8(ldg8(dy, row * dim + ch * 8), d[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += h[c][i];
+      }
+    }
+    const float mean = block_sum(s, scratch) / dim;
+    float vs = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          h[c][i] -= mean;
+          vs += h[c][i] * h[c][i];
+        }
+      }
+    }
+    const float rstd = rsqrtf(block_sum(vs, scratch) / dim + eps);
+    float sa = 0.f, sax = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          h[c][i] *= rstd;                       // xhat
+          dg[c][i] += d[c][i] * h[c][i];
+          db[c][i] += d[c][i];
+          d[c][i] *= g[c][i];                    // a
+          sa += d[c][i];
+          sax += d[c][i] * h[c][i];
+        }
+      }
+    }
+    sa = block_sum(sa, scratch) / dim;
+    sax = block_sum(sax, scratch) / dim;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rstd * (d[c][i] - sa - h[c][i] * sax);
+        stg8(dx, row * dim + ch * 8, pack8(o));
+      }
+    }
+  }
+  float* pr = partial + (long long)blockIdx.x * 2 * dim;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        pr[ch * 8 + i] = dg[c][i];
+        pr[dim + ch * 8 + i] = db[c][i];
+      }
+    }
+  }
+}
+
 int norm_threads(int dim, int max_threads = 1024) {
   MB_REQUIRE(dim % 8 == 0, "norm: dim must be a multiple of 8");
   const int chunks = dim / 8;
@@ -258,6 +347,18 @@ void layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, 
   MB_NORM_DISPATCH(norm_nc(dim, th), layernorm_fwd_kernel,
                    <<<rows, th, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma,
                                              (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, dim, eps));
+  count_launch();
+  check_launch();
+}
+
+// partial: [n_partial, 2 * dim] fp32; sum it with rmsnorm_bwd_reduce(partial, dgamma_dbeta, n_partial, 2 * dim).
+void layernorm_bwd(const void* dy, const void* x, const void* gamma, void* dx, float* partial, int n_partial, int rows,
+                   int dim, float eps, cudaStream_t stream) {
+  MB_REQUIRE(n_partial > 0, "layernorm_bwd: needs at least one partial row");
+  const int th = norm_threads(dim, 512);
+  MB_NORM_DISPATCH(norm_nc(dim, th), layernorm_bwd_kernel,
+                   <<<n_partial, th, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                  (const __nv_bfloat16*)gamma, (__nv_bfloat16*)dx, partial, rows, dim, eps));
   count_launch();
   check_launch();
 }

@@ -140,6 +140,42 @@ __global__ void act_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* _
     stg8(out, i * 8, pack8(v));
   }
 }
+// d act(x) / dx for the same table of activations.
+__device__ __forceinline__ float act_grad(float x, int kind) {
+  switch (kind) {
+    case ACT_RELU: return x > 0.f ? 1.f : 0.f;
+    case ACT_GELU_ERF:   // Phi(x) + x phi(x)
+      return 0.5f * (1.f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+    case ACT_GELU_TANH: {
+      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      const float t = tanhf(u);
+      return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * 0.7978845608028654f * (1.f + 0.134145f * x * x);
+    }
+    case ACT_SILU: {
+      const float sg = sigmoid_f(x);
+      return sg * (1.f + x * (1.f - sg));
+    }
+    case ACT_SIGMOID: {
+      const float sg = sigmoid_f(x);
+      return sg * (1.f - sg);
+    }
+    default: {
+      const float t = tanhf(x);
+      return 1.f - t * t;
+    }
+  }
+}
+__global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dout,
+                               __nv_bfloat16* __restrict__ dx, long long n8, int kind) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float v[8], d[8];
+    unpack8(ldg8(x, i * 8), v);
+    unpack8(ldg8(dout, i * 8), d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = act_grad(v[k], kind) * d[k];
+    stg8(dx, i * 8, pack8(v));
+  }
+}
 __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                            __nv_bfloat16* __restrict__ out, long long n8) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
@@ -165,6 +201,18 @@ __global__ void softmax_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat1
   s = block_sum(s, scratch);
   const float inv = 1.f / s;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) yr[c] = __float2bfloat16(__expf(__bfloat162float(xr[c]) - m) * inv);
+}
+
+// dx = y * (dy - sum_c dy_c y_c), one CTA per row.
+__global__ void softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dy,
+                                   __nv_bfloat16* __restrict__ dx, int cols) {
+  __shared__ float scratch[32];
+  const long long base = (long long)blockIdx.x * cols;
+  float dot = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dot += __bfloat162float(y[base + c]) * __bfloat162float(dy[base + c]);
+  dot = block_sum(dot, scratch);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x)
+    dx[base + c] = __float2bfloat16(__bfloat162float(y[base + c]) * (__bfloat162float(dy[base + c]) - dot));
 }
 
 // ------------------------------------------------------------------------------ embedding
@@ -393,6 +441,20 @@ void add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t
   if (n == 0) return;
   add_kernel<<<ew_grid(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                                       (__nv_bfloat16*)out, n / 8);
+  count_launch();
+  check_launch();
+}
+void act_bwd(const void* x, const void* dout, void* dx, long long n, int kind, cudaStream_t stream) {
+  MB_REQUIRE(n % 8 == 0, "act: element count must be a multiple of 8");
+  if (n == 0) return;
+  act_bwd_kernel<<<ew_grid(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dout,
+                                                          (__nv_bfloat16*)dx, n / 8, kind);
+  count_launch();
+  check_launch();
+}
+void softmax_rows_bwd(const void* y, const void* dy, void* dx, int rows, int cols, cudaStream_t stream) {
+  if (rows == 0) return;
+  softmax_bwd_kernel<<<rows, 256, 0, stream>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, cols);
   count_launch();
   check_launch();
 }

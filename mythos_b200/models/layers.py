@@ -222,7 +222,7 @@ class Attention(nn.Module):
             qkv = F.linear_rope(x, w, getattr(self.qkv_proj.weight, "main_grad", None), pos, cfg.rope_theta,
                                 cfg.q_dim + cfg.kv_dim, cfg.max_seq_len)
             o = F.attention_qkv(qkv, pos, cfg.num_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta, True,
-                                rope_applied=True)
+                                rope_applied=True, rope_max_pos=cfg.max_seq_len)
         else:
             qkv = self.qkv_proj(x)
             o = F.attention_qkv(qkv, pos, cfg.num_heads, cfg.kv_heads, cfg.head_dim, cfg.rope_theta, True)

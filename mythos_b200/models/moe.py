@@ -39,16 +39,24 @@ class ExpertParallel:
     """Expert-parallel context: symmetric receive / return buffers, the table through which the ranks
     exchange their per-expert token counts, and a flag barrier. ``cap_rows`` is the number of
     (token, expert) rows one rank may send per layer call; a rank can receive ``world * cap_rows``
-    rows (every token of every rank routed to its experts), plus alignment padding per expert."""
+    rows (every token of every rank routed to its experts) unless ``receive_factor`` lowers the bound,
+    plus alignment padding per expert."""
 
-    def __init__(self, group, device, cap_rows: int, dim: int):
+    def __init__(self, group, device, cap_rows: int, dim: int, receive_factor: float | None = None):
+        import math
+
         import torch.distributed as dist
 
         from ..parallel import symm
 
         self.group, self.device = group, torch.device(device)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.cap = self.world * cap_rows + SEG_ALIGN * MAX_LOCAL_EXPERTS
+        # receive_factor bounds what one rank accepts per call to that multiple of a rank's own rows
+        # (perfect balance = 1); None keeps the worst case, every row of every rank. The buffers and the
+        # activations saved per layer scale with it. More rows than the bound raise the status word
+        # (nothing is dropped silently).
+        factor = self.world if receive_factor is None else min(float(self.world), max(1.0, float(receive_factor)))
+        self.cap = int(math.ceil(factor * cap_rows)) + SEG_ALIGN * MAX_LOCAL_EXPERTS
         self.dim = dim
         n = self.cap * dim
         self.bufs = {k: symm.make_buffer(n, torch.bfloat16, device, group) for k in ("x", "y", "dy", "dx")}

@@ -29,6 +29,9 @@ FUSED_EPILOGUES = os.environ.get("MYTHOS_FUSED_EPILOGUES", "1") != "0"
 # tile per output block, bit-reproducible). MYTHOS_WGRAD_SPLITK=1 lets the wgrad GEMM split K over SM
 # pairs and add with fp32 atomics instead: +5-15 % on some layer shapes of the 1.3B model in isolation,
 # no measurable change of the whole training step, and the order of the additions varies run to run.
+# MYTHOS_FUSED_ROPE_BWD=0: the attention backward leaves dq / dk rotated and two RoPE passes undo it
+# (for A/B timing of the in-kernel rotation)
+FUSED_ROPE_BWD = os.environ.get("MYTHOS_FUSED_ROPE_BWD", "1") != "0"
 WGRAD_EPI = EPI_F32_ATOMIC if os.environ.get("MYTHOS_WGRAD_SPLITK", "0") == "1" else EPI_F32_ACC
 
 
@@ -310,8 +313,35 @@ def rmsnorm(x, gamma, eps: float = 1e-5, residual=None, grad_target=None):
     return (h.float() * rstd * gamma.float()).to(x.dtype), h
 
 
+class _LayerNormFn(torch.autograd.Function):
+    """LayerNorm with native forward and backward kernels (the backward recomputes mean and rstd from
+    x; formula of the reference's layer-norm gradient, src/autograd.cpp)."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _C().layernorm_fwd(xc, gamma, beta, y, eps)
+        ctx.save_for_backward(xc, gamma)
+        ctx.eps, ctx.has_beta = eps, beta is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gamma = ctx.saved_tensors
+        dim = x.shape[-1]
+        dx = torch.empty_like(x)
+        n_partial = _n_partial(x.numel() // dim, x.device)
+        partial = torch.empty(n_partial, 2 * dim, device=x.device, dtype=torch.float32)
+        dgb = torch.empty(2 * dim, device=x.device, dtype=torch.float32)
+        _C().layernorm_bwd(dy.contiguous(), x, gamma, dx, partial, dgb, ctx.eps)
+        return dx, dgb[:dim].to(gamma.dtype), (dgb[dim:].to(gamma.dtype) if ctx.has_beta else None), None
+
+
 def layernorm(x, gamma, beta=None, eps: float = 1e-5):
-    if x.is_cuda and not torch.is_grad_enabled():
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        if torch.is_grad_enabled() and (x.requires_grad or gamma.requires_grad):
+            return _LayerNormFn.apply(x, gamma, beta, eps)
         y = torch.empty_like(x.contiguous())
         _C().layernorm_fwd(x.contiguous(), gamma, beta, y, eps)
         return y
@@ -336,7 +366,7 @@ class _AttentionFn(torch.autograd.Function):
     qkv: [B, S, (H + 2*Hkv) * D] bf16, laid out q | k | v along the last dimension."""
 
     @staticmethod
-    def forward(ctx, qkv, pos, H, Hkv, D, theta, causal, scale, rope_applied=False):
+    def forward(ctx, qkv, pos, H, Hkv, D, theta, causal, scale, rope_applied=False, rope_max_pos=0):
         C = _C()
         B, S, W = qkv.shape
         assert W == (H + 2 * Hkv) * D and qkv.is_contiguous()
@@ -353,14 +383,14 @@ class _AttentionFn(torch.autograd.Function):
         lse = torch.empty(B, H, S, device=qkv.device, dtype=torch.float32)
         C.flash_attn_fwd(q4, k4, v4, o, lse, causal, scale, native.status_word(qkv.device))
         ctx.save_for_backward(qkv, pos, o, lse)
-        ctx.cfg = (H, Hkv, D, theta, causal, scale)
+        ctx.cfg = (H, Hkv, D, theta, causal, scale, rope_max_pos)
         return o.view(B, S, H * D)
 
     @staticmethod
     def backward(ctx, do):
         C = _C()
         qkv, pos, o, lse = ctx.saved_tensors
-        H, Hkv, D, theta, causal, scale = ctx.cfg
+        H, Hkv, D, theta, causal, scale, rope_max_pos = ctx.cfg
         if D not in _SUPPORTED_BWD_HEAD_DIMS:
             raise NotImplementedError(f"flash attention backward supports head_dim {_SUPPORTED_BWD_HEAD_DIMS}, got {D}")
         B, S, W = qkv.shape
@@ -374,9 +404,13 @@ class _AttentionFn(torch.autograd.Function):
         dq_accum = torch.empty(B * S * H * D, device=qkv.device, dtype=torch.float32)
         delta = torch.empty(B * H * S, device=qkv.device, dtype=torch.float32)
         do4 = do.reshape(B, S, H, D).contiguous()
+        # With a position bound the kernel undoes the rotation itself (dq while converting the fp32
+        # accumulator, dk in its epilogue) from the same cos/sin table the fused projection used.
+        fused_rope = FUSED_ROPE_BWD and D == 128 and theta > 0 and rope_max_pos > 0
         if D == 128:
             C.flash_attn_bwd(q4, k4, v4, o, do4, lse, dq4, dk4, dv4, dq_accum, delta, causal, scale,
-                             native.status_word(qkv.device))
+                             native.status_word(qkv.device), pos if fused_rope else None,
+                             rope_table(theta, rope_max_pos, qkv.device) if fused_rope else None)
         else:
             # Zero columns change neither the scores nor o . do, so the padded problem has the same
             # lse and delta; the gradients of the padding columns come out zero and are dropped.
@@ -389,23 +423,27 @@ class _AttentionFn(torch.autograd.Function):
             dq4.copy_(dqp[..., :D])
             dk4.copy_(dkp[..., :D])
             dv4.copy_(dvp[..., :D])
-        if theta > 0:
+        if theta > 0 and not fused_rope:
             flat = dqkv.view(B * S, W)
             C.rope(flat[:, : H * D].unflatten(-1, (H, D)), pos, theta, True)
             C.rope(flat[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D)), pos, theta, True)
-        return dqkv, None, None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None, None
 
 
 def attention_qkv(qkv, pos, n_heads: int, n_kv_heads: int, head_dim: int, theta: float = 10000.0,
-                  causal: bool = True, scale: float | None = None, rope_applied: bool = False):
+                  causal: bool = True, scale: float | None = None, rope_applied: bool = False,
+                  rope_max_pos: int = 0):
     """Self-attention over a fused projection ``qkv`` = [B, S, (H+2Hkv)*D] (q | k | v). RoPE with
     half-split pairs is applied to q and k at positions ``pos`` ([B*S] int32); ``theta <= 0``
     disables it. Returns [B, S, H*D]. On CUDA the projection buffer is rotated in place.
     ``rope_applied``: q and k arrive rotated (``linear_rope``); the forward pass then skips the
-    rotation, the backward pass still rotates the gradient back (CUDA only)."""
+    rotation, the backward pass still rotates the gradient back (CUDA only). ``rope_max_pos`` > 0
+    promises positions below that bound: the backward kernel then rotates dq and dk back itself
+    (head_dim 128) instead of two extra passes over the gradient."""
     scale = (1.0 / math.sqrt(head_dim)) if scale is None else scale
     if qkv.is_cuda:
-        return _AttentionFn.apply(qkv, pos, n_heads, n_kv_heads, head_dim, theta, causal, scale, rope_applied)
+        return _AttentionFn.apply(qkv, pos, n_heads, n_kv_heads, head_dim, theta, causal, scale, rope_applied,
+                                  rope_max_pos)
     assert not rope_applied
     B, S, _ = qkv.shape
     H, Hkv, D = n_heads, n_kv_heads, head_dim
@@ -486,9 +524,54 @@ def relu2(x):
 _ACT_IDS = {"relu": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "sigmoid": 4, "tanh": 5}
 
 
+class _ActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, kind_id):
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        _C().act_fwd(xc, out, kind_id)
+        ctx.save_for_backward(xc)
+        ctx.kind_id = kind_id
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (x,) = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        _C().act_bwd(x, dout.contiguous(), dx, ctx.kind_id)
+        return dx, None
+
+
+class _SoftmaxFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _C().softmax_rows(xc, y)
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        dx = torch.empty_like(y)
+        _C().softmax_rows_bwd(y, dy.contiguous(), dx)
+        return dx
+
+
+def softmax(x):
+    """Softmax over the last dimension (native forward and backward on CUDA bf16)."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _SoftmaxFn.apply(x)
+    return torch.softmax(x.float(), dim=-1).to(x.dtype)
+
+
 def activation(x, kind: str):
-    """Inference-time pointwise activation (no autograd on the CUDA path)."""
-    if x.is_cuda and not torch.is_grad_enabled():
+    """Pointwise activation: relu, gelu (erf), gelu_tanh, silu, sigmoid, tanh. On CUDA bf16 tensors
+    whose element count is a multiple of 8 both directions run native kernels."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+        if torch.is_grad_enabled() and x.requires_grad:
+            return _ActFn.apply(x, _ACT_IDS[kind])
         xc = x.contiguous()
         out = torch.empty_like(xc)
         _C().act_fwd(xc, out, _ACT_IDS[kind])

@@ -40,6 +40,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--lora-rank", type=int, default=0, help="> 0: freeze the base and train rank-r adapters")
     ap.add_argument("--lora-targets", default="q,v")
+    ap.add_argument("--ep-receive-factor", type=float, default=2.0,
+                    help="expert parallel: rows a rank accepts per micro-batch, as a multiple of its own (0 = worst case)")
     a = ap.parse_args(argv)
     import os
 
@@ -68,9 +70,10 @@ def main(argv=None) -> int:
     if world > 1 and cfg.num_experts > 0:
         from ..models.moe import ExpertParallel
 
-        # every (token, expert) row of a micro-batch may land on one rank: no token is ever dropped
+        # a rank accepts up to --ep-receive-factor times its own (token, expert) rows per micro-batch
+        # (0 = every row of every rank); more than that raises the status word, nothing is dropped
         exchange = ExpertParallel(dist.group.WORLD, dev, cap_rows=a.micro_batch * a.seq * cfg.moe_top_k,
-                                  dim=cfg.hidden_size)
+                                  dim=cfg.hidden_size, receive_factor=a.ep_receive_factor or None)
     with torch.device(dev):
         model = Model(cfg, exchange=exchange) if cfg.num_experts > 0 else Model(cfg)
     if a.lora_rank > 0:

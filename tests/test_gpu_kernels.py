@@ -260,6 +260,92 @@ def test_attention_qkv_forward_backward(B, S, H, Hkv, D):
     _close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("B,S,H,Hkv", [(2, 320, 4, 2), (1, 200, 2, 2)])
+def test_attention_backward_undoes_rope_in_kernel(B, S, H, Hkv):
+    """With a position bound the backward kernel rotates dq (in the fp32 -> bf16 conversion) and dk (in
+    its epilogue) back itself; the gradients must match autograd of the naive fp32 form."""
+    from mythos_b200.ops import functional as F, reference as ref
+
+    D = 128
+    torch.manual_seed(S + 1)
+    W = (H + 2 * Hkv) * D
+    qkv = (torch.randn(B, S, W, device="cuda") * 0.5).to(torch.bfloat16)
+    pos = torch.arange(S, device="cuda", dtype=torch.int32).repeat(B)
+    x = qkv.clone().requires_grad_()
+    o = F.attention_qkv(x, pos, H, Hkv, D, 10000.0, True, rope_max_pos=S)
+    do = torch.randn_like(o)
+    o.backward(do)
+
+    xr = qkv.float().requires_grad_()
+    qf = xr[..., : H * D].reshape(B * S, H, D)
+    kf = xr[..., H * D:(H + Hkv) * D].reshape(B * S, Hkv, D)
+    vf = xr[..., (H + Hkv) * D:].reshape(B, S, Hkv, D)
+    qf, kf = ref.rope(qf, pos, 10000.0), ref.rope(kf, pos, 10000.0)
+    orf, _ = ref.attention(qf.reshape(B, S, H, D), kf.reshape(B, S, Hkv, D), vf, True)
+    orf.reshape(B, S, H * D).backward(do.float())
+    _close(x.grad, xr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("rows,dim,with_beta", [(33, 256, True), (700, 2048, False), (5, 6144, True)])
+def test_layernorm_forward_backward(rows, dim, with_beta):
+    from mythos_b200.ops import functional as F
+
+    torch.manual_seed(dim)
+    x = torch.randn(rows, dim, device="cuda").to(torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(dim, device="cuda")).to(torch.bfloat16)
+    b = (0.1 * torch.randn(dim, device="cuda")).to(torch.bfloat16) if with_beta else None
+    xs, gs = x.clone().requires_grad_(), g.clone().requires_grad_()
+    bs = b.clone().requires_grad_() if with_beta else None
+    y = F.layernorm(xs, gs, bs, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, gr = x.float().requires_grad_(), g.float().requires_grad_()
+    br = b.float().requires_grad_() if with_beta else None
+    yr = torch.nn.functional.layer_norm(xr, (dim,), gr, br, 1e-5)
+    yr.backward(dy.float())
+    _close(y, yr, atol=3e-2)
+    _close(xs.grad, xr.grad, rtol=3e-2, atol=3e-2)
+    _close(gs.grad, gr.grad, rtol=3e-2, atol=0.02 * max(1.0, rows ** 0.5))
+    if with_beta:
+        _close(bs.grad, br.grad, rtol=3e-2, atol=0.02 * max(1.0, rows ** 0.5))
+
+
+@pytest.mark.parametrize("kind", ["relu", "gelu", "gelu_tanh", "silu", "sigmoid", "tanh"])
+def test_activation_backward(kind):
+    from mythos_b200.ops import functional as F
+
+    torch.manual_seed(3)
+    x = (2 * torch.randn(64, 264, device="cuda")).to(torch.bfloat16)
+    xs = x.clone().requires_grad_()
+    y = F.activation(xs, kind)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.float().requires_grad_()
+    ref = {"relu": torch.relu, "gelu": torch.nn.functional.gelu,
+           "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+           "silu": torch.nn.functional.silu, "sigmoid": torch.sigmoid, "tanh": torch.tanh}[kind]
+    yr = ref(xr)
+    yr.backward(dy.float())
+    _close(y, yr, atol=2e-2)
+    _close(xs.grad, xr.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_softmax_forward_backward():
+    from mythos_b200.ops import functional as F
+
+    torch.manual_seed(4)
+    x = torch.randn(37, 1000, device="cuda").to(torch.bfloat16)
+    xs = x.clone().requires_grad_()
+    y = F.softmax(xs)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.float().requires_grad_()
+    yr = torch.softmax(xr, dim=-1)
+    yr.backward(dy.float())
+    _close(y, yr, atol=1e-3)
+    _close(xs.grad, xr.grad, rtol=3e-2, atol=1e-3)
+
+
 def test_b200_backend_surface_matches_host():
     from mythos_b200.utils import backend as bk
 
