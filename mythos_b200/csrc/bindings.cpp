@@ -475,6 +475,22 @@ void symm_barrier(const std::vector<int64_t>& flag_ptrs, const std::vector<int64
                    status_ptr(status), cur_stream());
 }
 
+// a_ptrs: every rank's [M, K] bf16 buffer as mapped here; w: [N, K]; out: [M, N]; tile_count: int32 [M / 256].
+void gemm_allgather_a(const std::vector<int64_t>& a_ptrs, int64_t M, int64_t K, const Tensor& w, Tensor& out,
+                      int64_t rank, Tensor& tile_count, int64_t call, int64_t copier_clusters, const OptTensor& status) {
+  chk(w, BF16, "w");
+  chk(out, BF16, "out");
+  chk_c(tile_count, torch::kInt32, "tile_count");
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == K && w.stride(1) == 1, "gemm_allgather_a: w must be [N, K] with unit inner stride");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == w.size(0) && out.stride(1) == 1,
+              "gemm_allgather_a: out must be [M, N]");
+  TORCH_CHECK(tile_count.numel() >= M / 256, "gemm_allgather_a: tile_count too small");
+  c10::cuda::CUDAGuard guard(w.device());
+  mb::gemm_allgather_a(to_peers(a_ptrs), K, w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), (int)M,
+                       (int)w.size(0), (int)K, (int)rank, (int)a_ptrs.size(), tile_count.data_ptr<int>(), (int)call,
+                       (int)copier_clusters, status_ptr(status), cur_stream());
+}
+
 std::vector<int64_t> comm_barrier_wait_stats(bool reset) {
   unsigned long long v[3];
   mb::comm_barrier_wait_stats(v, reset);
@@ -1144,6 +1160,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("peer_add_f32", &peer_add_f32);
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);
+  m.def("gemm_allgather_a", &gemm_allgather_a);
   m.def("comm_barrier_wait_stats", &comm_barrier_wait_stats, py::arg("reset") = true);
   m.def("zero_reduce_scatter", &zero_reduce_scatter, py::arg("grad_ptrs"), py::arg("out"), py::arg("shard_off"),
         py::arg("sumsq"), py::arg("multicast_ptr") = 0, py::arg("max_blocks") = 0, py::arg("scratch") = py::none());

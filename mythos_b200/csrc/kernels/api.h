@@ -246,6 +246,12 @@ void symm_barrier(const PeerPtrs& flags, const PeerPtrs& slots, const float* sen
 // out = {barriers launched, sum of wait cycles, longest wait in cycles} on the current device since the
 // last reset (SM clock cycles between a rank's arrival and the last peer's); synchronises the device.
 void comm_barrier_wait_stats(unsigned long long out[3], bool reset);
+// All-gather of a row-sharded A fused into the GEMM C = A B^T (gemm_2cta.cu, GROUP_GATHER): copier CTAs of
+// the same launch pull the peers' rows into a_bufs.p[rank] with non-multicast TMA copies while the other
+// SM pairs multiply, own rows first. M % (256 * world) == 0, K % 64 == 0, world <= 8.
+void gemm_allgather_a(const PeerPtrs& a_bufs, long long lda, const void* B, long long ldb, void* C, long long ldc, int M,
+                      int N, int K, int rank, int world, int* tile_count, int call, int copier_clusters, int* status,
+                      cudaStream_t stream);
 // Registers the status word of the current device: the kernels below that consume data guarded by a
 // flag barrier (zero_reduce_scatter, zero_adamw_ste_allgather, tp_reduce_slots, tp_reduce_slots_bcast,
 // tp_allreduce_pull) return without writing once the word is non-zero (a bounded wait expired).

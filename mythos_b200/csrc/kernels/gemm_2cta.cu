@@ -93,7 +93,8 @@ struct Work2 {
 //   GROUP_ROWS  C[rows of segment e, :] = A[rows of segment e, :] * B_e^T   (ragged M; B per segment)
 //   GROUP_K     C_e (+)= A[rows of e, :]^T * B[rows of e, :]                (ragged K; C per segment)
 constexpr int MAX_GROUPS = 16;
-enum : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_K = 2 };
+enum : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_K = 2, GROUP_GATHER = 3 };
+constexpr int AG_MAX_RANKS = 8;
 template <int G>
 struct GroupArgsT {};
 template <>
@@ -110,6 +111,35 @@ struct GroupArgsT<GROUP_K> {
   int n_seg;
   void* cptrs[MAX_GROUPS];
 };
+// All-gather fused into the GEMM (GROUP_GATHER). A = [M, K] is sharded by rows over the ranks: every rank
+// holds a full-size buffer in symmetric memory and has written only its own rows. A few SM pairs of the
+// launch do not compute: their CTAs copy the other ranks' rows into this rank's buffer, 128 x 64 pieces
+// through a shared-memory ring with non-multicast TMA loads from the peer's buffer and TMA stores into the
+// local one, 256-row tile by tile in the order in which the computing SM pairs consume them (own rows
+// first, then the rows of rank + 1, rank + 2, ...). When a copier has stored its pieces of a tile it adds
+// one to the tile's counter; the TMA producers of the computing CTAs wait (bounded) for the counter to
+// reach `target` before they load a tile that is not the rank's own. Every remote byte crosses NVLink
+// once, and the copy of the later tiles overlaps the products of the earlier ones.
+template <>
+struct GroupArgsT<GROUP_GATHER> {
+  CUtensorMap peer[AG_MAX_RANKS];  // the A buffer of every rank as mapped here; same shape and box as tma_a
+  int* tile_count;                 // [tiles_m], monotonic over calls
+  int target;                      // copier CTAs x calls so far (this one included)
+  int rank, world, tiles_per_rank, copier_clusters;
+};
+__device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ Work2 decode2(int w, int tiles_m, int tiles_n, int k_splits, int kblocks) {
   const int tiles = tiles_m * tiles_n;
   const int split = w / tiles;
@@ -224,10 +254,16 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t cta = cluster_ctarank();
   const bool leader = cta == 0;
   const int kblocks = (K + T_BK - 1) / T_BK;
-  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int cluster_id = blockIdx.x >> 1;
+  int n_clusters = gridDim.x >> 1;      // SM pairs that compute tiles
+  bool is_copier = false;
+  if constexpr (GROUP == GROUP_GATHER) {
+    n_clusters -= ga.copier_clusters;
+    is_copier = cluster_id >= n_clusters;
+  }
   int* s_seg = reinterpret_cast<int*>(smem + Cfg::SEG_OFFSET);
   int n_seg = 0;
-  if constexpr (GROUP != GROUP_NONE) {
+  if constexpr (GROUP == GROUP_ROWS || GROUP == GROUP_K) {
     n_seg = ga.n_seg;
     if (threadIdx.x < MAX_GROUPS) {
       const bool in = (int)threadIdx.x < n_seg;
@@ -236,10 +272,17 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     __syncthreads();
   }
-  const int total = GROUP != GROUP_NONE ? group_total<GROUP>(s_seg, n_seg, tiles_m, tiles_n) : tiles_m * tiles_n * k_splits;
+  constexpr bool SEGMENTED = GROUP == GROUP_ROWS || GROUP == GROUP_K;
+  const int total = SEGMENTED ? group_total<GROUP>(s_seg, n_seg, tiles_m, tiles_n) : tiles_m * tiles_n * k_splits;
   auto get_work = [&](int w) -> Work2 {
-    if constexpr (GROUP != GROUP_NONE) return group_decode<GROUP>(w, s_seg, n_seg, tiles_m, tiles_n, kblocks);
-    else return decode2(w, tiles_m, tiles_n, k_splits, kblocks);
+    if constexpr (SEGMENTED) {
+      return group_decode<GROUP>(w, s_seg, n_seg, tiles_m, tiles_n, kblocks);
+    } else {
+      Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
+      if constexpr (GROUP == GROUP_GATHER)   // this rank's own rows first, then the ranks after it
+        wi.m0 = ((wi.m0 / T_BM + ga.rank * ga.tiles_per_rank) % tiles_m) * T_BM;
+      return wi;
+    }
   };
 
   if (threadIdx.x == 0) {
@@ -269,7 +312,71 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
-  if (warp == 0) {
+  if (is_copier) {
+    // ------------------------------------------------------------------ all-gather copier CTAs
+    if constexpr (GROUP == GROUP_GATHER) {
+      constexpr int CS = 12, PIECE = 128 * T_BK * 2;   // twelve 16 KB pieces in flight per CTA
+      static_assert(CS * PIECE <= Cfg::BAR_OFFSET, "copier ring must fit into the stage area");
+      uint64_t* cfull = reinterpret_cast<uint64_t*>(smem + Cfg::EPI_STAGE_OFFSET);
+      uint64_t* cempty = cfull + CS;
+      const int ci = (cluster_id - n_clusters) * 2 + (int)cta, n_cop = ga.copier_clusters * 2;
+      if (threadIdx.x == 0) {
+        for (int i = 0; i < CS; ++i) {
+          mbar_init(&cfull[i], 1);
+          mbar_init(&cempty[i], 1);
+        }
+        fence_mbar_init();
+      }
+      __syncthreads();
+      const int n_remote = tiles_m - ga.tiles_per_rank;
+      const int pieces = 2 * kblocks;                  // two 128-row halves per k-block of a 256-row tile
+      if (warp == 0 && lane == 0) {
+        // loads: the owner's buffer -> ring
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int j = 0; j < n_remote && ok; ++j) {
+          const int mt = ((ga.rank + 1) * ga.tiles_per_rank + j) % tiles_m;
+          const CUtensorMap* src = &ga.peer[mt / ga.tiles_per_rank];
+          for (int p = ci; p < pieces; p += n_cop) {
+            if (!mbar_wait(&cempty[stage], phase ^ 1, abort_flag, status, 57)) { ok = false; break; }
+            mbar_arrive_expect_tx(&cfull[stage], PIECE);
+            tma_load_2d(smem + stage * PIECE, src, &cfull[stage], (p >> 1) * T_BK, mt * T_BM + (p & 1) * 128);
+            if (++stage == CS) { stage = 0; phase ^= 1; }
+          }
+        }
+      } else if (warp == 1 && lane == 0) {
+        // stores: ring -> this rank's buffer; a stage is handed back once its store has read it
+        int stage = 0, oldest = 0, pending = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int j = 0; j < n_remote && ok; ++j) {
+          const int mt = ((ga.rank + 1) * ga.tiles_per_rank + j) % tiles_m;
+          for (int p = ci; p < pieces; p += n_cop) {
+            if (!mbar_wait(&cfull[stage], phase, abort_flag, status, 58)) { ok = false; break; }
+            tma_store_2d(&tma_a, smem + stage * PIECE, (p >> 1) * T_BK, mt * T_BM + (p & 1) * 128);
+            tma_store_commit();
+            if (++stage == CS) { stage = 0; phase ^= 1; }
+            if (++pending > 4) {
+              bulk_wait_group_read<4>();
+              mbar_arrive(&cempty[oldest]);
+              if (++oldest == CS) oldest = 0;
+              --pending;
+            }
+          }
+          if (!ok) break;
+          tma_store_wait0();               // this copier's pieces of the tile are in memory
+          for (; pending > 0; --pending) {
+            mbar_arrive(&cempty[oldest]);
+            if (++oldest == CS) oldest = 0;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");   // completed bulk stores before the release below
+          red_release_gpu_add(ga.tile_count + mt, 1);
+        }
+        tma_store_wait0();
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0;
@@ -281,6 +388,23 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int my_n = (FUSE == FUSE_SWIGLU_FWD) ? (wi.n0 >> 1) + (int)cta * fz.F : wi.n0 + (int)cta * 128;
         const CUtensorMap* map_b = &tma_b;
         if constexpr (GROUP == GROUP_ROWS) map_b = &ga.bmaps[wi.e];
+        if constexpr (GROUP == GROUP_GATHER) {
+          const int tmi = wi.m0 / T_BM;
+          if (tmi / ga.tiles_per_rank != ga.rank) {     // rows of another rank: wait until the copiers have brought them
+            const long long t0 = clock64();
+            while (ld_acquire_gpu_s32(ga.tile_count + tmi) - ga.target < 0) {
+              if (*abort_flag) { ok = false; break; }
+              if (clock64() - t0 > MB_WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, ST_TIMEOUT | (59 << 16));
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");   // the copiers' bulk stores before this thread's bulk loads
+          }
+        }
         for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, status, 51)) { ok = false; break; }
           const uint32_t lbar = map_to_cta(smem_u32(&full[stage]), 0);
@@ -973,6 +1097,41 @@ void gemm_bf16_2cta_scatter(const void* A, long long lda, bool a_mn, const void*
   else
     launch2<true, true>(ta, tb, C, M, N, K, ldc, k_splits, epi, vec_ok, alpha, status, stream, sc, n_scatter,
                         rows_per_rank, slot_off);
+}
+
+// C[M, N] = A[M, K] * B[N, K]^T where A is sharded by rows over `world` ranks: a_bufs.p[r] is rank r's
+// full-size [M, K] buffer (symmetric memory, as mapped in this process) in which rank r has written only
+// its own rows [r * M / world, (r + 1) * M / world). The launch gathers the other ranks' rows into
+// a_bufs.p[rank] while it multiplies (see GROUP_GATHER above); afterwards the local buffer holds all of A.
+// The caller makes sure (flag barrier) that every rank has written its rows before any rank launches,
+// and that a buffer is not rewritten while a peer may still read it (alternate two buffers).
+// tile_count: [M / 256] int32 in local memory, zero before the first call; `call` counts the launches
+// that used this counter array so far, this one included.
+void gemm_allgather_a(const PeerPtrs& a_bufs, long long lda, const void* B, long long ldb, void* C, long long ldc, int M,
+                      int N, int K, int rank, int world, int* tile_count, int call, int copier_clusters, int* status,
+                      cudaStream_t stream) {
+  MB_REQUIRE(world >= 1 && world <= AG_MAX_RANKS && rank >= 0 && rank < world, "gemm_allgather_a: bad rank / world");
+  MB_REQUIRE(M > 0 && N > 0 && K > 0 && M % (T_BM * world) == 0, "gemm_allgather_a: M must be a multiple of 256 x world");
+  MB_REQUIRE(K % T_BK == 0 && lda % 8 == 0 && ldb % 8 == 0, "gemm_allgather_a: K % 64 == 0 and 16-byte row strides");
+  const int clusters = sm_count() / 2;
+  if (world == 1) copier_clusters = 0;
+  MB_REQUIRE(copier_clusters >= (world > 1 ? 1 : 0) && copier_clusters < clusters, "gemm_allgather_a: bad copier count");
+  const int vec_ok = ((ldc * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? (g_coalesced_epilogue ? 2 : 1) : 0;
+  uint64_t adims[2] = {(uint64_t)K, (uint64_t)M}, astr[1] = {(uint64_t)lda * 2};
+  uint64_t bdims[2] = {(uint64_t)K, (uint64_t)N}, bstr[1] = {(uint64_t)ldb * 2};
+  uint32_t box[2] = {T_BK, 128};
+  GroupArgsT<GROUP_GATHER> ga{};
+  for (int r = 0; r < world; ++r) ga.peer[r] = make_tensor_map(a_bufs.p[r], TmaDType::BF16, 2, adims, astr, box, true);
+  for (int r = world; r < AG_MAX_RANKS; ++r) ga.peer[r] = ga.peer[0];
+  ga.tile_count = tile_count;
+  ga.target = 2 * copier_clusters * call;
+  ga.rank = rank;
+  ga.world = world;
+  ga.tiles_per_rank = M / T_BM / world;
+  ga.copier_clusters = copier_clusters;
+  const CUtensorMap tb = make_tensor_map(B, TmaDType::BF16, 2, bdims, bstr, box, true);
+  launch2<false, false, FUSE_NONE, GROUP_GATHER>(ga.peer[rank], tb, C, M, N, K, ldc, 1, EPI_BF16, vec_ok, 1.f, status, stream,
+                                                PeerPtrs{}, 0, 0, 0, EpiFuse{}, ga);
 }
 
 }  // namespace mb

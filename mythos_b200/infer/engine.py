@@ -103,6 +103,21 @@ class TPContext:
         self.row_epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.row_arrive = torch.zeros(1, dtype=torch.int32, device=device)
         self.row_signalled = os.environ.get("MYTHOS_TP_ROW_FLAGS", "0") != "0"
+        # Sequence-parallel prefill (MYTHOS_TP_SEQ_PARALLEL=1): between the row-parallel and the next
+        # column-parallel projection every rank keeps T / world tokens. The row-parallel GEMM stores its
+        # tiles into the owner's slots (fused reduce-scatter), the owner sums them, adds the residual and
+        # normalises its tokens only, and the column-parallel GEMM gathers the normalised rows from the
+        # peers while it multiplies (all-gather fused into the GEMM, parallel/ag_gemm.py). No all-reduce,
+        # and residual / RMSNorm work is divided by the world size.
+        self.seq_parallel = os.environ.get("MYTHOS_TP_SEQ_PARALLEL", "0") != "0" and self.world > 1
+        self.ag = None
+        if self.seq_parallel and hidden % 64 == 0:
+            from ..parallel.ag_gemm import AllGatherGemm
+
+            cap = max_tokens // (256 * self.world) * (256 * self.world)
+            if cap > 0:
+                self.ag = AllGatherGemm(group, device, cap, hidden,
+                                        copier_clusters=int(os.environ.get("MYTHOS_AG_COPIERS", str(min(12, 2 * self.world)))))
         if self.world > 1:
             torch.cuda.synchronize(device)
             dist.barrier(group=group)      # every rank's flags are zero before anyone signals
@@ -470,6 +485,8 @@ class InferenceEngine:
         over the paged cache (prefix + new tokens)."""
         if prefill_shape is None and paged is None and self.fused_decode and self._fused_decode_ok(ids.numel()):
             return self._forward_decode(ids, pos, seq_ids, ctx_lens)
+        if (prefill_shape is not None or paged is not None) and self._seq_parallel_ok(ids.numel()):
+            return self._forward_prefill_sp(ids, pos, seq_ids, prefill_shape, paged)
         cfg, C = self.cfg, native.require()
         D, H, Hkv = cfg.head_dim, self.h_local, self.hkv_local
         scale = 1.0 / math.sqrt(D)
@@ -531,6 +548,99 @@ class InferenceEngine:
             branch = self._row_parallel(L.down, h)
         hfin, _ = F.rmsnorm(branch, self.final_norm, cfg.norm_eps, stream)
         return hfin
+
+    def _seq_parallel_ok(self, T: int) -> bool:
+        tp = self.tp
+        if tp is None or tp.ag is None or T % (tp.world * 256) != 0 or T > tp.ag.rows or T > tp.max_tokens:
+            return False
+        cfg = self.cfg
+        return (cfg.hidden_size >= 256 and cfg.hidden_size % 64 == 0
+                and all(m.K % 64 == 0 for L in self.layers for m in (L.qkv, L.up)))
+
+    def _attention_prefill(self, li, qkv, pos, seq_ids, prefill_shape, paged):
+        """RoPE, K/V append and prefill attention for all tokens over this rank's heads -> [T, H_local * D]."""
+        cfg, C = self.cfg, native.require()
+        D, H, Hkv = cfg.head_dim, self.h_local, self.hkv_local
+        scale = 1.0 / math.sqrt(D)
+        T = qkv.shape[0]
+        q = qkv[:, : H * D].unflatten(-1, (H, D))
+        k = qkv[:, H * D:(H + Hkv) * D].unflatten(-1, (Hkv, D))
+        v = qkv[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+        if cfg.rope_theta > 0:
+            C.rope(qkv[:, : (H + Hkv) * D].unflatten(-1, (H + Hkv, D)), pos, cfg.rope_theta, False)
+        table = self.cache.block_table
+        if self.cache.int8:
+            C.kv_append_int8(k, v, self.cache.k[li], self.cache.v[li], self.cache.k_scale[li], self.cache.v_scale[li],
+                             table, pos, seq_ids)
+        else:
+            C.kv_append(k, v, self.cache.k[li], self.cache.v[li], table, pos, seq_ids)
+        if paged is not None:
+            cu_q, kv_lens, rows, max_q = paged
+            o = torch.empty(T, H, D, device=self.device, dtype=torch.bfloat16)
+            C.flash_attn_paged_prefill(q, self.cache.k[li], self.cache.v[li], rows, cu_q, kv_lens, o, max_q, scale,
+                                       native.status_word(self.device))
+            return o.view(T, H * D)
+        B, S = prefill_shape
+        o = torch.empty(B, S, H, D, device=self.device, dtype=torch.bfloat16)
+        lse = torch.empty(B, H, S, device=self.device, dtype=torch.float32)
+        q4 = qkv.view(B, S, -1)[..., : H * D].unflatten(-1, (H, D))
+        k4 = qkv.view(B, S, -1)[..., H * D:(H + Hkv) * D].unflatten(-1, (Hkv, D))
+        v4 = qkv.view(B, S, -1)[..., (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+        C.flash_attn_fwd(q4, k4, v4, o, lse, True, scale, native.status_word(self.device))
+        return o.view(T, H * D)
+
+    def _row_parallel_scatter(self, lin: QuantLinear, x: torch.Tensor) -> torch.Tensor:
+        """x [T, K_local] @ W_shard^T summed over the ranks, this rank's T / world rows only: the GEMM's
+        epilogue stores every 256-row tile into the owner's slot, the owner sums its slots."""
+        tp, C = self.tp, native.require()
+        T = x.shape[0]
+        rows = T // tp.world
+        n_slot = rows * lin.N
+        w = lin.dense if lin.dense is not None else lin.dequantize()
+        C.gemm_reduce_scatter(x, w, tp.part.ptrs, tp.rank, rows, n_slot, native.status_word(x.device))
+        tp.barrier.sync()
+        out = torch.empty(rows, lin.N, device=x.device, dtype=torch.bfloat16)
+        C.tp_reduce_slots(tp.part.tensor, tp.world, n_slot, None, out)
+        return out
+
+    def _forward_prefill_sp(self, ids, pos, seq_ids, prefill_shape, paged):
+        """Prefill with sequence-sharded activations between the projections (see TPContext.seq_parallel).
+        The slots of ``tp.part`` written by one reduce-scatter are summed before the barrier inside the
+        next all-gather GEMM, so the next reduce-scatter cannot overwrite them early."""
+        import torch.distributed as dist
+
+        cfg, tp = self.cfg, self.tp
+        self.sp_passes = getattr(self, "sp_passes", 0) + 1
+        T = ids.numel()
+        sh = T // tp.world
+        lo = tp.rank * sh
+        x = torch.empty(sh, cfg.hidden_size, device=self.device, dtype=torch.bfloat16)
+        self._embed(ids[lo:lo + sh].contiguous(), x)
+        branch, stream = x, None
+        for li, L in enumerate(self.layers):
+            n, stream = F.rmsnorm(branch, L.attn_norm, cfg.norm_eps, stream)
+            tp.ag.shard(T).copy_(n)
+            wq = L.qkv.dense if L.qkv.dense is not None else L.qkv.dequantize()
+            qkv, _ = tp.ag.run(wq, rows=T)
+            o = self._attention_prefill(li, qkv, pos, seq_ids, prefill_shape, paged)
+            a = self._row_parallel_scatter(L.o, o)
+            n, stream = F.rmsnorm(a, L.ffn_norm, cfg.norm_eps, stream)
+            tp.ag.shard(T).copy_(n)
+            wu = L.up.dense if L.up.dense is not None else L.up.dequantize()
+            u, _ = tp.ag.run(wu, rows=T)
+            if cfg.gated_ffn:
+                if cfg.activation == "relu2":
+                    f = u.shape[-1] // 2
+                    h = F.relu2(u[:, :f].contiguous()) * u[:, f:]
+                else:
+                    h = F.swiglu(u)
+            else:
+                h = F.relu2(u) if cfg.activation == "relu2" else F.activation(u, cfg.activation)
+            branch = self._row_parallel_scatter(L.down, h)
+        hfin, _ = F.rmsnorm(branch, self.final_norm, cfg.norm_eps, stream)
+        full = torch.empty(T, cfg.hidden_size, device=self.device, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(full, hfin.contiguous(), group=tp.group)   # once per pass: plumbing, not a hot op
+        return full
 
     def _logits(self, h: torch.Tensor) -> torch.Tensor:
         lg = self.head.matmul(h)

@@ -80,7 +80,7 @@ def main(argv=None) -> int:
         print(json.dumps({"metric": "decode tok/s and p50 TTFT", "preset": a.preset, "tp": world, "batch": a.batch,
                           "prompt": a.prompt, "new_tokens": a.new, "layers": cfg.num_layers,
                           "full_depth": cfg.num_layers == NAMED_CONFIGS[a.preset]().num_layers, "decode_tok_s": max(rates), "decode_tok_s_runs": [round(r, 1) for r in rates],
-                          "p50_ttft_s": ttfts[len(ttfts) // 2],
+                          "p50_ttft_s": ttfts[len(ttfts) // 2], "ttft_s_runs": [round(t, 4) for t in ttfts],
                           "weight_bytes_per_rank": wbytes, "kv_bytes_per_rank": eng.cache.size_bytes(), "kv_dtype": a.kv_dtype,
                           "data": "random-init weights in format, uniform-random prompts, greedy"}))
     if world > 1:

@@ -40,6 +40,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--lora-rank", type=int, default=0, help="> 0: freeze the base and train rank-r adapters")
     ap.add_argument("--lora-targets", default="q,v")
+    ap.add_argument("--activation-checkpointing", action="store_true",
+                    help="keep only each block's input and recompute the block in the backward pass")
     ap.add_argument("--ep-receive-factor", type=float, default=2.0,
                     help="expert parallel: rows a rank accepts per micro-batch, as a multiple of its own (0 = worst case)")
     a = ap.parse_args(argv)
@@ -83,7 +85,8 @@ def main(argv=None) -> int:
     n_params = sum(p.numel() for p in model.parameters())
     n_train = sum(p.numel() for p in model.parameters() if p.requires_grad)
     tr = Trainer(model, TrainConfig(batch_size=a.batch, micro_batch_size=a.micro_batch, seq_length=a.seq, lr=3e-4,
-                                    warmup_steps=100, max_steps=10000, max_grad_norm=1.0, codebook_ema_interval=0),
+                                    warmup_steps=100, max_steps=10000, max_grad_norm=1.0, codebook_ema_interval=0,
+                                    activation_checkpointing=a.activation_checkpointing),
                  device=dev, dp=dp)
     stream = ZipfStream(cfg.vocab_size, a.batch, a.seq, s=1.1, seed=100 + rank)
     batches = [tuple(t.to(dev) for t in stream.next_batch()) for _ in range(2)]
@@ -108,7 +111,7 @@ def main(argv=None) -> int:
         print(json.dumps({"metric": "train tokens/s (whole job)", "preset": a.preset, "layers": cfg.num_layers,
                       "n_gpus": world, "parallelism": (f"ep{world}+zero-dp{world}" if exchange is not None else f"dp{world}"),
                       "value": world * a.batch * a.seq / (ms / 1e3), "ms_per_step": ms, "batch": a.batch,
-                      "micro_batch": a.micro_batch, "seq_len": a.seq, "steps": a.steps, "warmup": a.warmup,
+                      "micro_batch": a.micro_batch, "activation_checkpointing": a.activation_checkpointing, "seq_len": a.seq, "steps": a.steps, "warmup": a.warmup,
                       "parameters": n_params, "trainable_parameters": n_train, "lora_rank": a.lora_rank,
                       "gpu_launches_per_step": (native.launch_count() - l0) // a.steps, "loss": float(loss),
                       "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,

@@ -56,6 +56,8 @@ def main(argv=None) -> int:
     ap.add_argument("--params", type=int, default=256 << 20, help="flat parameter count of the ZeRO cases")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--only", default="", help="'ag_gemm': run only the fused all-gather GEMM case")
+    ap.add_argument("--copier-clusters", type=int, default=0, help="ag_gemm: SM pairs that copy (0 = sweep 2, 4, 6, 8)")
     a = ap.parse_args(argv)
     rank, local, W = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(local)
@@ -80,6 +82,50 @@ def main(argv=None) -> int:
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
+
+    def ag_gemm_case():
+        # ------------------------------------------------------------ all-gather fused into the GEMM (prefill, sequence-sharded)
+        from ..parallel.ag_gemm import AllGatherGemm
+
+        Ma, Ka, Na = 16384, 4096, 28672 // W            # Llama-3-8B gate/up projection, tensor parallel over W ranks
+        Ma = Ma // (256 * W) * (256 * W)
+        wa = (torch.randn(Na, Ka, device=dev) * 0.05).to(torch.bfloat16)
+        a_loc = (torch.randn(Ma // W, Ka, device=dev) * 0.5).to(torch.bfloat16)
+        a_all = torch.empty(Ma, Ka, device=dev, dtype=torch.bfloat16)
+        ca = torch.empty(Ma, Na, device=dev, dtype=torch.bfloat16)
+
+        def nccl_form():
+            dist.all_gather_into_tensor(a_all, a_loc, group=group)
+            F.gemm(a_all, wa, out=ca)
+
+        t_n = _time(nccl_form, group, a.iters, a.warmup)
+        want = ca.clone()
+        t_g = _time(lambda: F.gemm(a_all, wa, out=ca), group, a.iters, a.warmup)
+        report(f"gemm_alone_{Ma}x{Na}x{Ka}", t_g, 0.0, flops=2.0 * Ma * Na * Ka)
+        for cc in ([a.copier_clusters] if a.copier_clusters > 0 else [2, 4, 6, 8]):
+            ag = AllGatherGemm(group, dev, Ma, Ka, copier_clusters=cc)
+            out = torch.empty(Ma, Na, device=dev, dtype=torch.bfloat16)
+
+            def fused():
+                ag.shard().copy_(a_loc)                    # stands for the producer of the local rows (8 MB copy)
+                ag.run(wa, out)
+
+            t_f = _time(fused, group, a.iters, a.warmup)
+            native.check_status(dev)
+            err = float((out.float() - want.float()).abs().max() / want.float().abs().max())
+            assert err < 2e-2, f"fused all-gather GEMM differs from all_gather + GEMM: {err}"
+            report(f"allgather_gemm_fused_{Ma}x{Na}x{Ka}_copiers{cc}", t_f, Ma * Ka * 2.0 * (W - 1) / W,
+                   flops=2.0 * Ma * Na * Ka, baseline_ms=t_n)
+            del ag
+            torch.cuda.empty_cache()
+
+    if a.only == "ag_gemm":
+        ag_gemm_case()
+        if rank == 0:
+            print(json.dumps({"summary": rows}))
+        native.check_status(dev)
+        dist.destroy_process_group()
+        return 0
 
     bar = symm.FlagBarrier(dev, group)
     use_mc = symm.nvls_enabled()          # MYTHOS_NVLS=1: also time the multimem (in-switch) variants
@@ -274,6 +320,7 @@ def main(argv=None) -> int:
            flops=2.0 * Tp * N * K, baseline_ms=t_n)
     del partb, outb, partc
     torch.cuda.empty_cache()
+    ag_gemm_case()
 
     if rank == 0:
         print(json.dumps({"summary": rows}))
