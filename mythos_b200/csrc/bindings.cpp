@@ -931,9 +931,15 @@ void moe_topk(const Tensor& probs, int64_t k, Tensor& topk_idx, Tensor& slot, Te
   mb::moe_topk(probs.data_ptr<float>(), (int)probs.size(0), (int)probs.size(1), (int)k, topk_idx.data_ptr<int>(),
                slot.data_ptr<int>(), counts.data_ptr<int>(), cur_stream());
 }
+const int* limit_ptr(const OptTensor& send_limit, const Tensor& send_off) {
+  if (!send_limit.has_value()) return nullptr;
+  chk_c(*send_limit, I32, "send_limit");
+  TORCH_CHECK(send_limit->numel() >= send_off.numel(), "send_limit must have an entry per expert");
+  return send_limit->data_ptr<int>();
+}
 void moe_dispatch(const Tensor& x, const Tensor& topk_idx, const Tensor& slot, const Tensor& send_off,
                   const OptTensor& row_scale, const std::vector<int64_t>& recv_ptrs, int64_t experts_per_rank,
-                  int64_t rank, int64_t cap) {
+                  int64_t rank, int64_t cap, const OptTensor& send_limit) {
   chk_c(x, BF16, "x");
   chk_c(topk_idx, I32, "topk_idx");
   chk_c(slot, I32, "slot");
@@ -941,11 +947,12 @@ void moe_dispatch(const Tensor& x, const Tensor& topk_idx, const Tensor& slot, c
   c10::cuda::CUDAGuard guard(x.device());
   mb::moe_dispatch(x.data_ptr(), topk_idx.data_ptr<int>(), slot.data_ptr<int>(), send_off.data_ptr<int>(),
                    row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr, to_peers(recv_ptrs), (int)x.size(0),
-                   (int)topk_idx.size(1), (int)x.size(1), (int)experts_per_rank, (int)rank, cap, cur_stream());
+                   (int)topk_idx.size(1), (int)x.size(1), (int)experts_per_rank, (int)rank, cap, cur_stream(),
+                   limit_ptr(send_limit, send_off));
 }
 void moe_combine(const std::vector<int64_t>& ybuf_ptrs, const Tensor& topk_idx, const Tensor& slot,
                  const Tensor& send_off, const OptTensor& w, const OptTensor& dout, OptTensor out, OptTensor dw,
-                 int64_t dim, int64_t experts_per_rank, int64_t rank, int64_t cap) {
+                 int64_t dim, int64_t experts_per_rank, int64_t rank, int64_t cap, const OptTensor& send_limit) {
   chk_c(topk_idx, I32, "topk_idx");
   chk_c(slot, I32, "slot");
   chk_c(send_off, I32, "send_off");
@@ -953,7 +960,7 @@ void moe_combine(const std::vector<int64_t>& ybuf_ptrs, const Tensor& topk_idx, 
   mb::moe_combine(to_peers(ybuf_ptrs), topk_idx.data_ptr<int>(), slot.data_ptr<int>(), send_off.data_ptr<int>(),
                   w.has_value() ? w->data_ptr<float>() : nullptr, cptr(dout), mptr(out),
                   dw.has_value() ? dw->data_ptr<float>() : nullptr, (int)topk_idx.size(0), (int)topk_idx.size(1),
-                  (int)dim, (int)experts_per_rank, (int)rank, cap, cur_stream());
+                  (int)dim, (int)experts_per_rank, (int)rank, cap, cur_stream(), limit_ptr(send_limit, send_off));
 }
 
 // logits: bf16 [T, ld >= E]. Fills probs [T,E] f32, topk_idx / slot [T,k] i32, w [T,k] f32; adds into counts [E] i32, psum [E] f32.
@@ -994,7 +1001,7 @@ void moe_publish_counts(const Tensor& counts, const std::vector<int64_t>& table_
   mb::moe_publish_counts(counts.data_ptr<int>(), to_peers(table_ptrs), (int)table_ptrs.size(), (int)E, (int)rank, cur_stream());
 }
 void moe_offsets(const Tensor& all_counts, int64_t world, int64_t E, int64_t rank, int64_t cap, Tensor& seg_start,
-                 Tensor& seg_rows, Tensor& send_base, const OptTensor& status) {
+                 Tensor& seg_rows, Tensor& send_base, const OptTensor& status, OptTensor send_limit) {
   chk_c(all_counts, I32, "all_counts");
   chk_c(seg_start, I32, "seg_start");
   chk_c(seg_rows, I32, "seg_rows");
@@ -1003,7 +1010,8 @@ void moe_offsets(const Tensor& all_counts, int64_t world, int64_t E, int64_t ran
                   seg_rows.numel() >= E / world, "moe_offsets: shapes");
   c10::cuda::CUDAGuard guard(all_counts.device());
   mb::moe_offsets(all_counts.data_ptr<int>(), (int)world, (int)E, (int)rank, (int)cap, seg_start.data_ptr<int>(),
-                  seg_rows.data_ptr<int>(), send_base.data_ptr<int>(), status_ptr(status), cur_stream());
+                  seg_rows.data_ptr<int>(), send_base.data_ptr<int>(), status_ptr(status), cur_stream(),
+                  send_limit.has_value() ? send_limit->data_ptr<int>() : nullptr);
 }
 void moe_zero_pad(const Tensor& seg_start, const Tensor& seg_rows, int64_t n_seg, OptTensor a, OptTensor b) {
   chk_c(seg_start, I32, "seg_start");
@@ -1155,8 +1163,12 @@ PYBIND11_MODULE(_C, m) {
         py::arg("scratch"), py::arg("counters"), py::arg("splits"), py::arg("scale"), py::arg("status") = py::none());
   m.def("sample_tokens", &sample_tokens);
   m.def("moe_topk", &moe_topk);
-  m.def("moe_dispatch", &moe_dispatch);
-  m.def("moe_combine", &moe_combine);
+  m.def("moe_dispatch", &moe_dispatch, py::arg("x"), py::arg("topk_idx"), py::arg("slot"), py::arg("send_off"),
+        py::arg("row_scale"), py::arg("recv_ptrs"), py::arg("experts_per_rank"), py::arg("rank"), py::arg("cap"),
+        py::arg("send_limit") = py::none());
+  m.def("moe_combine", &moe_combine, py::arg("ybuf_ptrs"), py::arg("topk_idx"), py::arg("slot"), py::arg("send_off"),
+        py::arg("w"), py::arg("dout"), py::arg("out"), py::arg("dw"), py::arg("dim"), py::arg("experts_per_rank"),
+        py::arg("rank"), py::arg("cap"), py::arg("send_limit") = py::none());
   m.def("peer_add_f32", &peer_add_f32);
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);
@@ -1176,7 +1188,9 @@ PYBIND11_MODULE(_C, m) {
   m.def("moe_route", &moe_route);
   m.def("moe_route_bwd", &moe_route_bwd);
   m.def("moe_publish_counts", &moe_publish_counts);
-  m.def("moe_offsets", &moe_offsets);
+  m.def("moe_offsets", &moe_offsets, py::arg("all_counts"), py::arg("world"), py::arg("E"), py::arg("rank"), py::arg("cap"),
+        py::arg("seg_start"), py::arg("seg_rows"), py::arg("send_base"), py::arg("status") = py::none(),
+        py::arg("send_limit") = py::none());
   m.def("moe_zero_pad", &moe_zero_pad);
   m.def("gemm_grouped_rows", &gemm_grouped_rows);
   m.def("gemm_grouped_k", &gemm_grouped_k);

@@ -352,18 +352,21 @@ void moe_route_bwd(const float* probs, const int* topk_idx, const float* dw, con
                    void* dlogits, int ld, cudaStream_t stream);
 void moe_publish_counts(const int* counts, const PeerPtrs& tables, int world, int E, int rank, cudaStream_t stream);
 void moe_offsets(const int* all_counts, int world, int E, int rank, int cap, int* seg_start, int* seg_rows,
-                 int* send_base, int* status, cudaStream_t stream);
+                 int* send_base, int* status, cudaStream_t stream, int* send_limit = nullptr);
+// send_limit[e] (optional, from moe_offsets): first row of expert e's segment that does not fit into its
+// owner's buffer; dispatch skips and combine ignores rows at or past it, so a full buffer drops rows
+// (with the status word raised) instead of storing out of bounds.
 void moe_zero_pad(const int* seg_start, const int* seg_rows, int n_seg, int dim, void* a, void* b, int cap,
                   cudaStream_t stream);
 void moe_topk(const float* probs, int T, int E, int k, int* topk_idx, int* slot, int* counts, cudaStream_t stream);
 // Row (t, j) goes to recv[owner(e)] at row rank*cap + send_off[e] + slot[t, j] (optionally scaled).
 void moe_dispatch(const void* x, const int* topk_idx, const int* slot, const int* send_off, const float* row_scale,
                   const PeerPtrs& recv, int T, int k, int dim, int experts_per_rank, int rank, long long cap,
-                  cudaStream_t stream);
+                  cudaStream_t stream, const int* send_limit = nullptr);
 // out[t] = sum_j w[t,j] * ybuf[owner][row(t,j)] (w null = 1); with dw also dw[t,j] = <dout[t], y row>.
 void moe_combine(const PeerPtrs& ybuf, const int* topk_idx, const int* slot, const int* send_off, const float* w,
                  const void* dout, void* out, float* dw, int T, int k, int dim, int experts_per_rank, int rank,
-                 long long cap, cudaStream_t stream);
+                 long long cap, cudaStream_t stream, const int* send_limit = nullptr);
 
 long long launch_count();
 

@@ -48,7 +48,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ probs, int T, int E, i
 __global__ void moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx,
                                     const int* __restrict__ slot, const int* __restrict__ send_off,
                                     const float* __restrict__ row_scale, PeerPtrs recv, int T, int k, int dim,
-                                    int experts_per_rank, int rank, long long cap) {
+                                    int experts_per_rank, int rank, long long cap, const int* __restrict__ send_limit) {
   const int per_row = dim >> 3;
   const long long total = (long long)T * k * per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -58,6 +58,9 @@ __global__ void moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const i
     const int e = topk_idx[tk];
     const int owner = e / experts_per_rank;
     const long long row = (long long)rank * cap + send_off[e] + slot[tk];
+    // a row past the end of the expert's (clamped) segment does not fit into the owner's buffer: it is
+    // not sent (moe_offsets has raised the status word for this step)
+    if (send_limit != nullptr && send_off[e] + slot[tk] >= send_limit[e]) continue;
     bf16x8 v = ldg8(x, (long long)t * dim + c);
     if (row_scale) {
       float f[8];
@@ -76,7 +79,7 @@ __global__ void moe_combine_kernel(PeerPtrs ybuf, const int* __restrict__ topk_i
                                    const int* __restrict__ send_off, const float* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ out,
                                    float* __restrict__ dw, int T, int k, int dim, int experts_per_rank, int rank,
-                                   long long cap) {
+                                   long long cap, const int* __restrict__ send_limit) {
   const int lane = threadIdx.x & 31;
   const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -85,7 +88,8 @@ __global__ void moe_combine_kernel(PeerPtrs ybuf, const int* __restrict__ topk_i
   for (int j = 0; j < k; ++j) {
     const int e = topk_idx[t * k + j];
     const long long row = (long long)rank * cap + send_off[e] + slot[t * k + j];
-    rows[j] = reinterpret_cast<const __nv_bfloat16*>(ybuf.p[e / experts_per_rank]) + row * dim;
+    const bool fits = send_limit == nullptr || send_off[e] + slot[t * k + j] < send_limit[e];
+    rows[j] = fits ? reinterpret_cast<const __nv_bfloat16*>(ybuf.p[e / experts_per_rank]) + row * dim : nullptr;
     wk[j] = w ? w[t * k + j] : 1.f;
   }
   float dots[MOE_MAX_K];
@@ -98,6 +102,7 @@ __global__ void moe_combine_kernel(PeerPtrs ybuf, const int* __restrict__ topk_i
     if (dw) unpack8(ldg8(dout, t * dim + c), g);
     for (int j = 0; j < k; ++j) {
       float y[8];
+      if (rows[j] == nullptr) continue;    // the row was not sent (receive buffer full): contributes nothing
       unpack8(ldg8(rows[j], c), y);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -203,8 +208,9 @@ __global__ void moe_publish_counts_kernel(const int* __restrict__ counts, PeerPt
 // A segment that would not fit into `cap` rows raises the status word (routing is drop-free here).
 __global__ void moe_offsets_kernel(const int* __restrict__ all_counts, int world, int E, int epr, int rank, int cap,
                                    int* __restrict__ seg_start, int* __restrict__ seg_rows,
-                                   int* __restrict__ send_base, int* status) {
+                                   int* __restrict__ send_base, int* __restrict__ send_limit, int* status) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int cap256 = cap / 256 * 256;      // whole 256-row tiles only: the grouped GEMMs store full tiles
   for (int r = 0; r < world; ++r) {
     int start = 0;
     for (int le = 0; le < epr; ++le) {
@@ -214,14 +220,19 @@ __global__ void moe_offsets_kernel(const int* __restrict__ all_counts, int world
         if (s < rank) before += all_counts[s * E + e];
         rows += all_counts[s * E + e];
       }
+      // A segment is cut where the owner's buffer ends; senders skip the rows past that point, so a
+      // full buffer costs tokens (and raises the status word below) but never an out-of-bounds store.
+      const int room = start < cap256 ? cap256 - start : 0;
+      const int kept = rows < room ? rows : room;
       send_base[e] = start + before;
+      if (send_limit) send_limit[e] = start + kept;
       if (r == rank) {
-        seg_start[le] = start;
-        seg_rows[le] = rows;
+        seg_start[le] = start < cap256 ? start : 0;
+        seg_rows[le] = kept;
       }
       start += (rows + 255) / 256 * 256;
     }
-    if (start > cap && status) atomicCAS(status, 0, 2 | (60 << 16));  // bad argument, site 60;
+    if (start > cap256 && status) atomicCAS(status, 0, 2 | (60 << 16));  // bad argument, site 60;
   }
 }
 
@@ -273,9 +284,10 @@ void moe_publish_counts(const int* counts, const PeerPtrs& tables, int world, in
 }
 
 void moe_offsets(const int* all_counts, int world, int E, int rank, int cap, int* seg_start, int* seg_rows,
-                 int* send_base, int* status, cudaStream_t stream) {
+                 int* send_base, int* status, cudaStream_t stream, int* send_limit) {
   MB_REQUIRE(world >= 1 && E % world == 0 && E <= MOE_MAX_E, "moe_offsets: experts must divide over the ranks");
-  moe_offsets_kernel<<<1, 32, 0, stream>>>(all_counts, world, E, E / world, rank, cap, seg_start, seg_rows, send_base, status);
+  moe_offsets_kernel<<<1, 32, 0, stream>>>(all_counts, world, E, E / world, rank, cap, seg_start, seg_rows, send_base,
+                                           send_limit, status);
   count_launch();
   check_launch();
 }
@@ -299,28 +311,28 @@ void moe_topk(const float* probs, int T, int E, int k, int* topk_idx, int* slot,
 
 void moe_dispatch(const void* x, const int* topk_idx, const int* slot, const int* send_off, const float* row_scale,
                   const PeerPtrs& recv, int T, int k, int dim, int experts_per_rank, int rank, long long cap,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const int* send_limit) {
   MB_REQUIRE(dim % 8 == 0, "moe_dispatch: dim must be a multiple of 8");
   if (T == 0) return;
   long long g = ((long long)T * k * (dim / 8) + 255) / 256;
   const long long capg = (long long)sm_count() * 16;
   if (g > capg) g = capg;
   moe_dispatch_kernel<<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)x, topk_idx, slot, send_off, row_scale, recv, T,
-                                                  k, dim, experts_per_rank, rank, cap);
+                                                  k, dim, experts_per_rank, rank, cap, send_limit);
   count_launch();
   check_launch();
 }
 
 void moe_combine(const PeerPtrs& ybuf, const int* topk_idx, const int* slot, const int* send_off, const float* w,
                  const void* dout, void* out, float* dw, int T, int k, int dim, int experts_per_rank, int rank,
-                 long long cap, cudaStream_t stream) {
+                 long long cap, cudaStream_t stream, const int* send_limit) {
   MB_REQUIRE(dim % 8 == 0, "moe_combine: dim must be a multiple of 8");
   MB_REQUIRE(k <= MOE_MAX_K, "moe_combine: top-k too large");
   MB_REQUIRE(dw == nullptr || dout != nullptr, "moe_combine: dw needs dout");
   if (T == 0) return;
   moe_combine_kernel<<<ceil_div(T, 8), 256, 0, stream>>>(ybuf, topk_idx, slot, send_off, w, (const __nv_bfloat16*)dout,
                                                          (__nv_bfloat16*)out, dw, T, k, dim, experts_per_rank, rank,
-                                                         cap);
+                                                         cap, send_limit);
   count_launch();
   check_launch();
 }

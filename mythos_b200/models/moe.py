@@ -56,7 +56,7 @@ class ExpertParallel:
         # activations saved per layer scale with it. More rows than the bound raise the status word
         # (nothing is dropped silently).
         factor = self.world if receive_factor is None else min(float(self.world), max(1.0, float(receive_factor)))
-        self.cap = int(math.ceil(factor * cap_rows)) + SEG_ALIGN * MAX_LOCAL_EXPERTS
+        self.cap = (int(math.ceil(factor * cap_rows)) + SEG_ALIGN - 1) // SEG_ALIGN * SEG_ALIGN + SEG_ALIGN * MAX_LOCAL_EXPERTS
         self.dim = dim
         n = self.cap * dim
         self.bufs = {k: symm.make_buffer(n, torch.bfloat16, device, group) for k in ("x", "y", "dy", "dx")}
@@ -160,12 +160,13 @@ class _MoEFn(torch.autograd.Function):
         seg_start = torch.empty(epr, device=dev, dtype=torch.int32)
         seg_rows = torch.empty(epr, device=dev, dtype=torch.int32)
         send_base = torch.empty(E, device=dev, dtype=torch.int32)
-        C.moe_offsets(table, ex.world, E, ex.rank, cap, seg_start, seg_rows, send_base, st)
+        send_limit = torch.empty(E, device=dev, dtype=torch.int32)   # where each expert's segment ends on its owner
+        C.moe_offsets(table, ex.world, E, ex.rank, cap, seg_start, seg_rows, send_base, st, send_limit)
         xbuf, ybuf = ex.bufs["x"], ex.bufs["y"]
         xs = xbuf.tensor.view(-1, d)[:cap]
         ys = ybuf.tensor.view(-1, d)[:cap]
         C.moe_zero_pad(seg_start, seg_rows, epr, xs, None)
-        C.moe_dispatch(x, topk_idx, slot, send_base, None, xbuf.ptrs, epr, 0, 0)
+        C.moe_dispatch(x, topk_idx, slot, send_base, None, xbuf.ptrs, epr, 0, 0, send_limit)
         if ex.barrier is not None:
             ex.barrier.sync()
         lo = ex.rank * epr
@@ -179,17 +180,17 @@ class _MoEFn(torch.autograd.Function):
         if ex.barrier is not None:
             ex.barrier.sync()
         out = torch.empty_like(x)
-        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_base, w, None, out, None, d, epr, 0, 0)
+        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_base, w, None, out, None, d, epr, 0, 0, send_limit)
         ctx.moe = moe
         keep_x, keep_y = (xs.clone(), ys.clone()) if ex.shared else (xs, ys)
-        ctx.save_for_backward(x, w, topk_idx, slot, send_base, seg_start, seg_rows, keep_x, keep_y, gu, h)
+        ctx.save_for_backward(x, w, topk_idx, slot, send_base, seg_start, seg_rows, keep_x, keep_y, gu, h, send_limit)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         C = native.require()
         moe, ex = ctx.moe, ctx.moe.exchange
-        x, w, topk_idx, slot, send_base, seg_start, seg_rows, xs, ys, gu, h = ctx.saved_tensors
+        x, w, topk_idx, slot, send_base, seg_start, seg_rows, xs, ys, gu, h, send_limit = ctx.saved_tensors
         T, d = x.shape
         k = topk_idx.shape[1]
         epr = moe.num_experts // ex.world
@@ -203,13 +204,13 @@ class _MoEFn(torch.autograd.Function):
             ybuf.tensor.view(-1, d)[:cap].copy_(ys)
             ex.barrier.sync()
         dw = torch.empty(T, k, device=dev, dtype=torch.float32)
-        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_base, None, dout, None, dw, d, epr, 0, 0)
+        C.moe_combine(ybuf.ptrs, topk_idx, slot, send_base, None, dout, None, dw, d, epr, 0, 0, send_limit)
         # dy rows = w * dout[t], sent to the owners
         dybuf, dxbuf = ex.bufs["dy"], ex.bufs["dx"]
         dys = dybuf.tensor.view(-1, d)[:cap]
         dxs = dxbuf.tensor.view(-1, d)[:cap]
         C.moe_zero_pad(seg_start, seg_rows, epr, dys, None)
-        C.moe_dispatch(dout, topk_idx, slot, send_base, w.contiguous(), dybuf.ptrs, epr, 0, 0)
+        C.moe_dispatch(dout, topk_idx, slot, send_base, w.contiguous(), dybuf.ptrs, epr, 0, 0, send_limit)
         if ex.barrier is not None:
             ex.barrier.sync()
         lo = ex.rank * epr
@@ -223,7 +224,7 @@ class _MoEFn(torch.autograd.Function):
         if ex.barrier is not None:
             ex.barrier.sync()
         dx = torch.empty_like(x)
-        C.moe_combine(dxbuf.ptrs, topk_idx, slot, send_base, None, None, dx, None, d, epr, 0, 0)
+        C.moe_combine(dxbuf.ptrs, topk_idx, slot, send_base, None, None, dx, None, d, epr, 0, 0, send_limit)
         return dx, dw, None, None, None, None
 
 

@@ -277,6 +277,19 @@ want = torch.nn.functional.cross_entropy(fr, tg.long())
 want.backward()
 res["ce_loss"] = abs(loss.item() - want.item())
 res["ce_grad"] = float((shard.grad.float().cpu() - fr.grad[:, rank * v:(rank + 1) * v]).abs().max()) * rows
+
+# A receive buffer too small for the routed rows: the rows that do not fit are not sent, the status word
+# reports it, and nothing is stored out of bounds (the buffers are really larger than the bound set here).
+nat.exchange.cap = 256
+with torch.no_grad():
+    y_small = nat(xs[rank].to(dev).to(torch.bfloat16))
+torch.cuda.synchronize()
+try:
+    native.check_status(dev)
+    res["overflow_reported"] = False
+except RuntimeError as e:
+    res["overflow_reported"] = "status 2" in str(e)
+res["overflow_finite"] = bool(torch.isfinite(y_small.float()).all())
 out = [None] * world
 dist.all_gather_object(out, res)
 if rank == 0:
@@ -295,6 +308,7 @@ def test_expert_parallel_moe_and_vocab_parallel_loss(n):
     ranks = _launch(EP_WORKER, n, 29631 + n)
     for r in ranks:
         assert r["y"] < 5e-2 and r["dx"] < 8e-2 and r["dw_local"] < 8e-2, ranks
+        assert r["overflow_reported"] and r["overflow_finite"], ranks
         assert r["ce_loss"] < 5e-3 and r["ce_grad"] < 5e-2, ranks
 
 
