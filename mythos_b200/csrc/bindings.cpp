@@ -632,6 +632,13 @@ void tp_allreduce_pull(const std::vector<int64_t>& part_ptrs, const std::vector<
   mb::tp_allreduce_pull(to_peers(part_ptrs), to_peers(out_ptrs), (int)part_ptrs.size(), (int)rank, n, cur_stream());
 }
 
+void tp_reduce_scatter_pull(const std::vector<int64_t>& part_ptrs, int64_t rank, int64_t n, Tensor& out) {
+  chk_c(out, BF16, "out");
+  TORCH_CHECK(out.numel() * (int64_t)part_ptrs.size() == n, "tp_reduce_scatter_pull: out must hold n / ranks elements");
+  c10::cuda::CUDAGuard guard(out.device());
+  mb::tp_reduce_scatter_pull(to_peers(part_ptrs), (int)part_ptrs.size(), (int)rank, n, out.data_ptr(), cur_stream());
+}
+
 // x [M, K] @ w [N, K]^T with the output rows scattered to their owner ranks (fused reduce-scatter).
 void gemm_reduce_scatter(const Tensor& x, const Tensor& w, const std::vector<int64_t>& slot_ptrs, int64_t rank,
                          int64_t rows_per_rank, int64_t slot_stride, const OptTensor& status) {
@@ -1143,6 +1150,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("tp_push", &tp_push);
   m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("tp_allreduce_pull", &tp_allreduce_pull);
+  m.def("tp_reduce_scatter_pull", &tp_reduce_scatter_pull);
   m.def("sum_residual_rmsnorm", &sum_residual_rmsnorm);
   m.def("tp_sum_residual_rmsnorm", &tp_sum_residual_rmsnorm);
   m.def("qkv_rope_append", &qkv_rope_append, py::arg("acc"), py::arg("pos"), py::arg("seq_ids"), py::arg("block_table"),

@@ -277,6 +277,9 @@ void tp_reduce_slots(const void* staging, int slots, long long slot_stride, cons
                      long long n, cudaStream_t stream);
 void tp_allreduce_pull(const PeerPtrs& part, const PeerPtrs& out, int n_peers, int rank, long long n,
                        cudaStream_t stream);
+// Reduce-scatter by peer loads: out_local[0 : n / n_peers) = sum over ranks of part_q[rank * n / n_peers + i].
+void tp_reduce_scatter_pull(const PeerPtrs& part, int n_peers, int rank, long long n, void* out_local,
+                            cudaStream_t stream);
 // Second half of the fused GEMM -> reduce-scatter: sum the `slots` partials of this rank's rows
 // (local staging) and store the bf16 result at out_p + out_off for every peer p (all-gather by stores).
 void tp_reduce_slots_bcast(const void* staging, int slots, long long slot_stride, const PeerPtrs& out, int n_peers,

@@ -438,8 +438,10 @@ __global__ void tp_reduce_slots_bcast_kernel(const __nv_bfloat16* __restrict__ s
 
 // Elements [begin8, end8) (units of 8) are this rank's slice: out_p[i] = bf16(sum_q part_q[i]) for
 // every p. Partials are summed in rank order, so the value does not depend on which rank owns it.
+// With local_out the sum of the slice is stored there only (element 0 = first element of the slice): a
+// reduce-scatter by peer loads.
 __global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peers, int rank, long long begin8,
-                                         long long end8, const int* abort_word) {
+                                         long long end8, const int* abort_word, __nv_bfloat16* __restrict__ local_out) {
   if (aborted(abort_word)) return;
   for (long long i = begin8 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < end8;
        i += (long long)gridDim.x * blockDim.x) {
@@ -457,7 +459,11 @@ __global__ void tp_allreduce_pull_kernel(PeerPtrs part, PeerPtrs out, int n_peer
         for (int j = 0; j < 8; ++j) acc[j] += f[j];
       }
     const bf16x8 r = pack8(acc);
-    for (int p = 0; p < n_peers; ++p) stg8(out.p[(rank + p) % n_peers], i * 8, r);
+    if (local_out != nullptr) {
+      stg8(local_out, (i - begin8) * 8, r);
+    } else {
+      for (int p = 0; p < n_peers; ++p) stg8(out.p[(rank + p) % n_peers], i * 8, r);
+    }
   }
 }
 
@@ -572,7 +578,21 @@ void tp_allreduce_pull(const PeerPtrs& part, const PeerPtrs& out, int n_peers, i
   const long long cap = (long long)sm_count() * 8;
   if (g > cap) g = cap;
   tp_allreduce_pull_kernel<<<(int)g, 256, 0, stream>>>(part, out, n_peers, rank, begin, end,
-                                                       abort_word_for_current_device());
+                                                       abort_word_for_current_device(), nullptr);
+  count_launch();
+  check_launch();
+}
+
+void tp_reduce_scatter_pull(const PeerPtrs& part, int n_peers, int rank, long long n, void* out_local, cudaStream_t stream) {
+  MB_REQUIRE(n % (8LL * n_peers) == 0, "tp_reduce_scatter_pull: element count must be a multiple of 8 x ranks");
+  MB_REQUIRE(n_peers >= 1 && n_peers <= MAX_PEERS, "tp_reduce_scatter_pull: bad peer count");
+  const long long per = n / 8 / n_peers;
+  if (per == 0) return;
+  long long g = (per + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (g > cap) g = cap;
+  tp_allreduce_pull_kernel<<<(int)g, 256, 0, stream>>>(part, PeerPtrs{}, n_peers, rank, per * rank, per * (rank + 1),
+                                                       abort_word_for_current_device(), (__nv_bfloat16*)out_local);
   count_launch();
   check_launch();
 }

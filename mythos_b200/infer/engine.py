@@ -103,13 +103,16 @@ class TPContext:
         self.row_epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.row_arrive = torch.zeros(1, dtype=torch.int32, device=device)
         self.row_signalled = os.environ.get("MYTHOS_TP_ROW_FLAGS", "0") != "0"
-        # Sequence-parallel prefill (MYTHOS_TP_SEQ_PARALLEL=1): between the row-parallel and the next
-        # column-parallel projection every rank keeps T / world tokens. The row-parallel GEMM stores its
-        # tiles into the owner's slots (fused reduce-scatter), the owner sums them, adds the residual and
-        # normalises its tokens only, and the column-parallel GEMM gathers the normalised rows from the
-        # peers while it multiplies (all-gather fused into the GEMM, parallel/ag_gemm.py). No all-reduce,
-        # and residual / RMSNorm work is divided by the world size.
-        self.seq_parallel = os.environ.get("MYTHOS_TP_SEQ_PARALLEL", "0") != "0" and self.world > 1
+        # Sequence-parallel prefill: between the row-parallel and the next column-parallel projection every
+        # rank keeps T / world tokens. The row-parallel sum is a reduce-scatter (from the GEMM epilogue at 2
+        # ranks, by peer loads after a local GEMM above that), the owner adds the residual and normalises
+        # its tokens only, and the column-parallel GEMM gathers the normalised rows from the peers while it
+        # multiplies (all-gather fused into the GEMM, parallel/ag_gemm.py). No all-reduce, and residual /
+        # RMSNorm work is divided by the world size. Measured time to first token, Llama-3-8B shape, 64 x
+        # 1024 tokens at 8 ranks: 0.194 s against 0.223 s for the all-reduce path; at 2 ranks the two are
+        # equal (0.118 s), so it is the default above 2 ranks. MYTHOS_TP_SEQ_PARALLEL=0/1 overrides.
+        self.seq_parallel = os.environ.get("MYTHOS_TP_SEQ_PARALLEL", "1" if self.world > 2 else "0") != "0" \
+            and self.world > 1
         self.ag = None
         if self.seq_parallel and hidden % 64 == 0:
             from ..parallel.ag_gemm import AllGatherGemm
@@ -590,17 +593,25 @@ class InferenceEngine:
         return o.view(T, H * D)
 
     def _row_parallel_scatter(self, lin: QuantLinear, x: torch.Tensor) -> torch.Tensor:
-        """x [T, K_local] @ W_shard^T summed over the ranks, this rank's T / world rows only: the GEMM's
-        epilogue stores every 256-row tile into the owner's slot, the owner sums its slots."""
+        """x [T, K_local] @ W_shard^T summed over the ranks, this rank's T / world rows only. Two routes, as
+        for the all-reduce: the GEMM's epilogue stores every 256-row tile into the owner's slot and the
+        owner sums its slots (the faster one at 2 ranks), or a local GEMM into the symmetric partial
+        buffer, a barrier, and one kernel that pulls this rank's rows from every peer and sums them."""
         tp, C = self.tp, native.require()
         T = x.shape[0]
         rows = T // tp.world
-        n_slot = rows * lin.N
-        w = lin.dense if lin.dense is not None else lin.dequantize()
-        C.gemm_reduce_scatter(x, w, tp.part.ptrs, tp.rank, rows, n_slot, native.status_word(x.device))
-        tp.barrier.sync()
         out = torch.empty(rows, lin.N, device=x.device, dtype=torch.bfloat16)
-        C.tp_reduce_slots(tp.part.tensor, tp.world, n_slot, None, out)
+        if tp.fused_reduce_scatter and lin.N >= 256 and lin.N % 64 == 0:
+            n_slot = rows * lin.N
+            w = lin.dense if lin.dense is not None else lin.dequantize()
+            C.gemm_reduce_scatter(x, w, tp.part.ptrs, tp.rank, rows, n_slot, native.status_word(x.device))
+            tp.barrier.sync()
+            C.tp_reduce_slots(tp.part.tensor, tp.world, n_slot, None, out)
+            return out
+        n = T * lin.N
+        lin.matmul(x, out=tp.part.tensor[:n].view(T, lin.N))
+        tp.barrier.sync()
+        C.tp_reduce_scatter_pull(tp.part.ptrs, tp.rank, n, out)
         return out
 
     def _forward_prefill_sp(self, ids, pos, seq_ids, prefill_shape, paged):

@@ -200,10 +200,12 @@ dist.destroy_process_group()
 
 @needs_two
 @pytest.mark.parametrize("n", WORLD_SIZES)
-def test_sequence_parallel_prefill_matches_single_gpu(n):
-    """Prefill with sequence-sharded activations: fused reduce-scatter after the row-parallel GEMMs, the
-    all-gather fused into the column-parallel GEMMs. First tokens as on one GPU, reproducible."""
-    r = _launch(SP_WORKER, n, 29681 + n, extra_env={"MYTHOS_TP_SEQ_PARALLEL": "1"})
+@pytest.mark.parametrize("fused_rs", ["1", "0"])
+def test_sequence_parallel_prefill_matches_single_gpu(n, fused_rs):
+    """Prefill with sequence-sharded activations: reduce-scatter after the row-parallel GEMMs (from the GEMM
+    epilogue, or by peer loads after a local GEMM), the all-gather fused into the column-parallel GEMMs.
+    First tokens as on one GPU, reproducible."""
+    r = _launch(SP_WORKER, n, 29681 + n, extra_env={"MYTHOS_TP_SEQ_PARALLEL": "1", "MYTHOS_TP_FUSED_RS": fused_rs})
     assert r["sp_passes"] >= 2, r
     assert r["tp"] == r["tp2"]
     same = sum(a[0] == b[0] for a, b in zip(r["ref"], r["tp"]))
