@@ -53,19 +53,6 @@ struct F2Cfg {
   static constexpr int COL_O = 256;   // O_t at 256 + t * 128
 };
 
-// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (bf16 pairs packed in 32-bit columns, one row per
-// lane) is read from tensor memory.
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-      "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 struct F2Item {
   int b, h, q0, n_qt, J[2], Jmax;
 };
