@@ -25,7 +25,9 @@ LIBS = ["oil_trainer", "oil_tokenizer", "oil_model", "oil_inference", "oil_kerne
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--source", default=os.environ.get("MYTHOS_REFERENCE", "/root/reference"))
+    # default: $MYTHOS_REFERENCE, else a checkout named "reference" beside this repository
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    ap.add_argument("--source", default=os.environ.get("MYTHOS_REFERENCE", sibling))
     a = ap.parse_args()
     if not os.path.exists(os.path.join(a.source, "CMakeLists.txt")):
         print(f"no reference checkout at {a.source}", file=sys.stderr)
