@@ -491,6 +491,22 @@ void gemm_allgather_a(const std::vector<int64_t>& a_ptrs, int64_t M, int64_t K, 
                        (int)copier_clusters, status_ptr(status), cur_stream());
 }
 
+// x: [M, K]; w_ptrs: every rank's [N, K] bf16 weight buffer as mapped here; out: [M, N]; tile_count: int32 [N / 256].
+void gemm_allgather_b(const Tensor& x, const std::vector<int64_t>& w_ptrs, int64_t N, Tensor& out, int64_t rank,
+                      Tensor& tile_count, int64_t call, int64_t copier_clusters, const OptTensor& status) {
+  chk(x, BF16, "x");
+  chk(out, BF16, "out");
+  chk_c(tile_count, torch::kInt32, "tile_count");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "gemm_allgather_b: x must be [M, K] with unit inner stride");
+  const int64_t M = x.size(0), K = x.size(1);
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == N && out.stride(1) == 1, "gemm_allgather_b: out must be [M, N]");
+  TORCH_CHECK(tile_count.numel() >= N / 256, "gemm_allgather_b: tile_count too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  mb::gemm_allgather_b(x.data_ptr(), x.stride(0), to_peers(w_ptrs), K, out.data_ptr(), out.stride(0), (int)M, (int)N, (int)K,
+                       (int)rank, (int)w_ptrs.size(), tile_count.data_ptr<int>(), (int)call, (int)copier_clusters,
+                       status_ptr(status), cur_stream());
+}
+
 std::vector<int64_t> comm_barrier_wait_stats(bool reset) {
   unsigned long long v[3];
   mb::comm_barrier_wait_stats(v, reset);
@@ -1181,6 +1197,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("peer_gather_cols", &peer_gather_cols);
   m.def("symm_barrier", &symm_barrier);
   m.def("gemm_allgather_a", &gemm_allgather_a);
+  m.def("gemm_allgather_b", &gemm_allgather_b);
   m.def("comm_barrier_wait_stats", &comm_barrier_wait_stats, py::arg("reset") = true);
   m.def("zero_reduce_scatter", &zero_reduce_scatter, py::arg("grad_ptrs"), py::arg("out"), py::arg("shard_off"),
         py::arg("sumsq"), py::arg("multicast_ptr") = 0, py::arg("max_blocks") = 0, py::arg("scratch") = py::none());

@@ -252,6 +252,12 @@ void comm_barrier_wait_stats(unsigned long long out[3], bool reset);
 void gemm_allgather_a(const PeerPtrs& a_bufs, long long lda, const void* B, long long ldb, void* C, long long ldc, int M,
                       int N, int K, int rank, int world, int* tile_count, int call, int copier_clusters, int* status,
                       cudaStream_t stream);
+// The weight-side form: B [N, K] sharded by rows over the ranks (a sharded bf16 compute image), gathered into
+// b_bufs.p[rank] by copier CTAs of the launch while the other SM pairs multiply, own column block first.
+// N % (256 * world) == 0, K % 64 == 0, world <= 8.
+void gemm_allgather_b(const void* A, long long lda, const PeerPtrs& b_bufs, long long ldb, void* C, long long ldc, int M,
+                      int N, int K, int rank, int world, int* tile_count, int call, int copier_clusters, int* status,
+                      cudaStream_t stream);
 // Registers the status word of the current device: the kernels below that consume data guarded by a
 // flag barrier (zero_reduce_scatter, zero_adamw_ste_allgather, tp_reduce_slots, tp_reduce_slots_bcast,
 // tp_allreduce_pull) return without writing once the word is non-zero (a bounded wait expired).

@@ -122,10 +122,15 @@ struct GroupArgsT<GROUP_K> {
 // once, and the copy of the later tiles overlaps the products of the earlier ones.
 template <>
 struct GroupArgsT<GROUP_GATHER> {
-  CUtensorMap peer[AG_MAX_RANKS];  // the A buffer of every rank as mapped here; same shape and box as tma_a
-  int* tile_count;                 // [tiles_m], monotonic over calls
+  CUtensorMap peer[AG_MAX_RANKS];  // the gathered operand's buffer on every rank as mapped here; same shape and
+                                   // box as the launch's own map of that operand (tma_a or tma_b)
+  int* tile_count;                 // [256-row tiles of the gathered operand], monotonic over calls
   int target;                      // copier CTAs x calls so far (this one included)
   int rank, world, tiles_per_rank, copier_clusters;
+  int gather_b;                    // 0: A (activations sharded by tokens); 1: B (a weight sharded by output rows).
+                                   // With B the tiles are walked column block by column block (own columns first),
+                                   // all row tiles of a column block on neighbouring SM pairs, so that a gathered
+                                   // 256-row block of B is reused out of L2 while it is current.
 };
 __device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
   int v;
@@ -278,10 +283,16 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if constexpr (SEGMENTED) {
       return group_decode<GROUP>(w, s_seg, n_seg, tiles_m, tiles_n, kblocks);
     } else {
-      Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
-      if constexpr (GROUP == GROUP_GATHER)   // this rank's own rows first, then the ranks after it
+      if constexpr (GROUP == GROUP_GATHER) {   // this rank's own rows first, then the ranks after it
+        if (ga.gather_b) {
+          const int tn = w / tiles_m, tm = w - tn * tiles_m;
+          return Work2{tm * T_BM, ((tn + ga.rank * ga.tiles_per_rank) % tiles_n) * T_BN, 0, kblocks};
+        }
+        Work2 wi = decode2(w, tiles_m, tiles_n, k_splits, kblocks);
         wi.m0 = ((wi.m0 / T_BM + ga.rank * ga.tiles_per_rank) % tiles_m) * T_BM;
-      return wi;
+        return wi;
+      }
+      return decode2(w, tiles_m, tiles_n, k_splits, kblocks);
     }
   };
 
@@ -328,7 +339,9 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         fence_mbar_init();
       }
       __syncthreads();
-      const int n_remote = tiles_m - ga.tiles_per_rank;
+      const int tiles_g = ga.gather_b ? tiles_n : tiles_m;   // 256-row tiles of the gathered operand
+      const CUtensorMap* store_map = ga.gather_b ? &tma_b : &tma_a;
+      const int n_remote = tiles_g - ga.tiles_per_rank;
       const int pieces = 2 * kblocks;                  // two 128-row halves per k-block of a 256-row tile
       if (warp == 0 && lane == 0) {
         // loads: the owner's buffer -> ring
@@ -336,7 +349,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint32_t phase = 0;
         bool ok = true;
         for (int j = 0; j < n_remote && ok; ++j) {
-          const int mt = ((ga.rank + 1) * ga.tiles_per_rank + j) % tiles_m;
+          const int mt = ((ga.rank + 1) * ga.tiles_per_rank + j) % tiles_g;
           const CUtensorMap* src = &ga.peer[mt / ga.tiles_per_rank];
           for (int p = ci; p < pieces; p += n_cop) {
             if (!mbar_wait(&cempty[stage], phase ^ 1, abort_flag, status, 57)) { ok = false; break; }
@@ -351,10 +364,10 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint32_t phase = 0;
         bool ok = true;
         for (int j = 0; j < n_remote && ok; ++j) {
-          const int mt = ((ga.rank + 1) * ga.tiles_per_rank + j) % tiles_m;
+          const int mt = ((ga.rank + 1) * ga.tiles_per_rank + j) % tiles_g;
           for (int p = ci; p < pieces; p += n_cop) {
             if (!mbar_wait(&cfull[stage], phase, abort_flag, status, 58)) { ok = false; break; }
-            tma_store_2d(&tma_a, smem + stage * PIECE, (p >> 1) * T_BK, mt * T_BM + (p & 1) * 128);
+            tma_store_2d(store_map, smem + stage * PIECE, (p >> 1) * T_BK, mt * T_BM + (p & 1) * 128);
             tma_store_commit();
             if (++stage == CS) { stage = 0; phase ^= 1; }
             if (++pending > 4) {
@@ -389,7 +402,7 @@ gemm_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const CUtensorMap* map_b = &tma_b;
         if constexpr (GROUP == GROUP_ROWS) map_b = &ga.bmaps[wi.e];
         if constexpr (GROUP == GROUP_GATHER) {
-          const int tmi = wi.m0 / T_BM;
+          const int tmi = ga.gather_b ? wi.n0 / T_BN : wi.m0 / T_BM;
           if (tmi / ga.tiles_per_rank != ga.rank) {     // rows of another rank: wait until the copiers have brought them
             const long long t0 = clock64();
             while (ld_acquire_gpu_s32(ga.tile_count + tmi) - ga.target < 0) {
@@ -1129,8 +1142,42 @@ void gemm_allgather_a(const PeerPtrs& a_bufs, long long lda, const void* B, long
   ga.world = world;
   ga.tiles_per_rank = M / T_BM / world;
   ga.copier_clusters = copier_clusters;
+  ga.gather_b = 0;
   const CUtensorMap tb = make_tensor_map(B, TmaDType::BF16, 2, bdims, bstr, box, true);
   launch2<false, false, FUSE_NONE, GROUP_GATHER>(ga.peer[rank], tb, C, M, N, K, ldc, 1, EPI_BF16, vec_ok, 1.f, status, stream,
+                                                PeerPtrs{}, 0, 0, 0, EpiFuse{}, ga);
+}
+
+// The same with the roles of the operands exchanged: C[M, N] = A[M, K] * B[N, K]^T where the weight B is
+// sharded by output rows over the ranks (b_bufs.p[r] = rank r's full-size [N, K] buffer holding its own rows
+// [r * N / world, (r + 1) * N / world)). The launch gathers the other ranks' rows of B into b_bufs.p[rank]
+// while it multiplies, own column block first; afterwards the local buffer holds all of B (a later product
+// with the same weight, e.g. the data gradient, can read it from there). tile_count: [N / 256].
+void gemm_allgather_b(const void* A, long long lda, const PeerPtrs& b_bufs, long long ldb, void* C, long long ldc, int M,
+                      int N, int K, int rank, int world, int* tile_count, int call, int copier_clusters, int* status,
+                      cudaStream_t stream) {
+  MB_REQUIRE(world >= 1 && world <= AG_MAX_RANKS && rank >= 0 && rank < world, "gemm_allgather_b: bad rank / world");
+  MB_REQUIRE(M > 0 && N > 0 && K > 0 && N % (T_BN * world) == 0, "gemm_allgather_b: N must be a multiple of 256 x world");
+  MB_REQUIRE(K % T_BK == 0 && lda % 8 == 0 && ldb % 8 == 0, "gemm_allgather_b: K % 64 == 0 and 16-byte row strides");
+  const int clusters = sm_count() / 2;
+  if (world == 1) copier_clusters = 0;
+  MB_REQUIRE(copier_clusters >= (world > 1 ? 1 : 0) && copier_clusters < clusters, "gemm_allgather_b: bad copier count");
+  const int vec_ok = ((ldc * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? (g_coalesced_epilogue ? 2 : 1) : 0;
+  uint64_t adims[2] = {(uint64_t)K, (uint64_t)M}, astr[1] = {(uint64_t)lda * 2};
+  uint64_t bdims[2] = {(uint64_t)K, (uint64_t)N}, bstr[1] = {(uint64_t)ldb * 2};
+  uint32_t box[2] = {T_BK, 128};
+  GroupArgsT<GROUP_GATHER> ga{};
+  for (int r = 0; r < world; ++r) ga.peer[r] = make_tensor_map(b_bufs.p[r], TmaDType::BF16, 2, bdims, bstr, box, true);
+  for (int r = world; r < AG_MAX_RANKS; ++r) ga.peer[r] = ga.peer[0];
+  ga.tile_count = tile_count;
+  ga.target = 2 * copier_clusters * call;
+  ga.rank = rank;
+  ga.world = world;
+  ga.tiles_per_rank = N / T_BN / world;
+  ga.copier_clusters = copier_clusters;
+  ga.gather_b = 1;
+  const CUtensorMap ta = make_tensor_map(A, TmaDType::BF16, 2, adims, astr, box, true);
+  launch2<false, false, FUSE_NONE, GROUP_GATHER>(ta, ga.peer[rank], C, M, N, K, ldc, 1, EPI_BF16, vec_ok, 1.f, status, stream,
                                                 PeerPtrs{}, 0, 0, 0, EpiFuse{}, ga);
 }
 

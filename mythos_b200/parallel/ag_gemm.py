@@ -65,3 +65,50 @@ class AllGatherGemm:
                            self.copier_clusters, native.status_word(self.device))
         self.cur ^= 1
         return out, self.bufs[i].tensor[: rows * self.cols].view(rows, self.cols)
+
+
+class ShardedWeightGemm:
+    """``y = x @ W.T`` for a weight ``W`` [N, K] whose bf16 image is sharded by output rows over the ranks
+    (each rank keeps and updates ``N / world`` rows): the parameter all-gather fused into the first GEMM
+    that consumes the weight. Copier CTAs of the launch pull the peers' rows into this rank's full-size
+    buffer while the other SM pairs multiply, own column block first (``gemm_allgather_b``); afterwards
+    the buffer holds all of ``W`` until the next ``write_shard`` (the backward products can read it).
+    The reference gathers parameters with a library all-gather before the layer runs
+    (src/distributed.cpp:102-138)."""
+
+    def __init__(self, group, device, out_features: int, in_features: int, copier_clusters: int = 2):
+        import torch.distributed as dist
+
+        self.group, self.device = group, torch.device(device)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if out_features % (256 * self.world) != 0 or in_features % 64 != 0:
+            raise ValueError("ShardedWeightGemm: out_features must be a multiple of 256 x world, in_features of 64")
+        self.N, self.K = out_features, in_features
+        self.buf = symm.make_buffer(out_features * in_features, torch.bfloat16, device, group)
+        self.counts = torch.zeros(out_features // 256, device=device, dtype=torch.int32)
+        self.copier_clusters = copier_clusters if self.world > 1 else 0
+        self.barrier = symm.FlagBarrier(device, group) if self.world > 1 else None
+
+    def weight(self) -> torch.Tensor:
+        """The full [N, K] buffer (all rows valid after ``run``; before it only this rank's)."""
+        return self.buf.tensor.view(self.N, self.K)
+
+    def write_shard(self, rows: torch.Tensor) -> None:
+        """Replace this rank's rows (e.g. after an optimizer step). The barrier first makes sure that no
+        peer is still copying the previous values."""
+        if self.barrier is not None:
+            self.barrier.sync()
+        sh = self.N // self.world
+        self.weight()[self.rank * sh:(self.rank + 1) * sh].copy_(rows)
+
+    def run(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        C = native.require()
+        x2 = x.reshape(-1, self.K)
+        if out is None:
+            out = torch.empty(x2.shape[0], self.N, device=self.device, dtype=torch.bfloat16)
+        if self.barrier is not None:
+            self.barrier.sync()                       # every rank's rows are in its buffer
+        self.counts.zero_()
+        C.gemm_allgather_b(x2, self.buf.ptrs, self.N, out, self.rank, self.counts, 1, self.copier_clusters,
+                           native.status_word(self.device))
+        return out

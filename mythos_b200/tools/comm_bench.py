@@ -119,8 +119,41 @@ def main(argv=None) -> int:
             del ag
             torch.cuda.empty_cache()
 
+    def sharded_weight_case():
+        # ------------------------------------------------------------ parameter all-gather fused into the consuming GEMM
+        from ..parallel.ag_gemm import ShardedWeightGemm
+
+        Mw, Kw, Nw = 16384, 2048, 6144                 # QKV projection of the 1.3B model, weight sharded over W ranks
+        Nw = Nw // (256 * W) * (256 * W)
+        w_loc = (torch.randn(Nw // W, Kw, device=dev) * 0.05).to(torch.bfloat16)
+        w_all = torch.empty(Nw, Kw, device=dev, dtype=torch.bfloat16)
+        xw = (torch.randn(Mw, Kw, device=dev) * 0.5).to(torch.bfloat16)
+        yw = torch.empty(Mw, Nw, device=dev, dtype=torch.bfloat16)
+
+        def nccl_form():
+            dist.all_gather_into_tensor(w_all, w_loc, group=group)
+            F.gemm(xw, w_all, out=yw)
+
+        t_n = _time(nccl_form, group, a.iters, a.warmup)
+        want = yw.clone()
+        t_g = _time(lambda: F.gemm(xw, w_all, out=yw), group, a.iters, a.warmup)
+        report(f"gemm_alone_{Mw}x{Nw}x{Kw}", t_g, 0.0, flops=2.0 * Mw * Nw * Kw)
+        for cc in (1, 2, 4):
+            sw = ShardedWeightGemm(group, dev, Nw, Kw, copier_clusters=cc)
+            sw.write_shard(w_loc)
+            out = torch.empty(Mw, Nw, device=dev, dtype=torch.bfloat16)
+            t_f = _time(lambda: sw.run(xw, out), group, a.iters, a.warmup)
+            native.check_status(dev)
+            err = float((out.float() - want.float()).abs().max() / want.float().abs().max())
+            assert err < 2e-2, f"fused weight gather GEMM differs from all_gather + GEMM: {err}"
+            report(f"weight_allgather_gemm_fused_{Mw}x{Nw}x{Kw}_copiers{cc}", t_f, Nw * Kw * 2.0 * (W - 1) / W,
+                   flops=2.0 * Mw * Nw * Kw, baseline_ms=t_n)
+            del sw
+            torch.cuda.empty_cache()
+
     if a.only == "ag_gemm":
         ag_gemm_case()
+        sharded_weight_case()
         if rank == 0:
             print(json.dumps({"summary": rows}))
         native.check_status(dev)
@@ -321,6 +354,7 @@ def main(argv=None) -> int:
     del partb, outb, partc
     torch.cuda.empty_cache()
     ag_gemm_case()
+    sharded_weight_case()
 
     if rank == 0:
         print(json.dumps({"summary": rows}))

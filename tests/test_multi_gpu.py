@@ -336,6 +336,20 @@ for call in range(5):                      # alternates the two buffers; counter
     want = a_full.float() @ w.float().cpu().T
     errs.append(float((c.float().cpu() - want).abs().max() / want.abs().max()))
     errs.append(float((gathered.float().cpu() - a_full.float()).abs().max()))
+# the weight-side form: W sharded by output rows, gathered inside the GEMM, over two "optimizer steps"
+from mythos_b200.parallel.ag_gemm import ShardedWeightGemm
+Nw, Kw, Mw = 512 * world, 256, 640
+sw = ShardedWeightGemm(dist.group.WORLD, dev, Nw, Kw, copier_clusters=2)
+for step in range(3):
+    w_full = (torch.randn(Nw, Kw, generator=torch.Generator().manual_seed(300 + step)) * 0.1).to(torch.bfloat16)
+    xw = torch.randn(Mw, Kw, generator=torch.Generator().manual_seed(400 + step)).to(torch.bfloat16).to(dev)
+    shw = Nw // world
+    sw.write_shard(w_full[rank * shw:(rank + 1) * shw].to(dev))
+    y = sw.run(xw)
+    torch.cuda.synchronize(); native.check_status(dev)
+    want = xw.float().cpu() @ w_full.float().T
+    errs.append(float((y.float().cpu() - want).abs().max() / want.abs().max()))
+    errs.append(float((sw.weight().float().cpu() - w_full.float()).abs().max()))
 out = [None] * world
 dist.all_gather_object(out, errs)
 if rank == 0:
@@ -347,9 +361,10 @@ dist.destroy_process_group()
 @needs_two
 @pytest.mark.parametrize("n", WORLD_SIZES)
 def test_allgather_fused_into_gemm(n):
-    """Row-sharded A gathered over peer memory by copier CTAs of the GEMM launch itself: the product must
-    match the fp32 product of the full matrices on every rank, and the local buffer must end up holding
-    all of A, over several calls (buffer alternation, monotonic tile counters)."""
+    """Row-sharded A (activations) and row-sharded B (a weight whose image is sharded over the ranks)
+    gathered over peer memory by copier CTAs of the GEMM launch itself: the product must match the fp32
+    product of the full matrices on every rank, and the local buffer must end up holding the whole
+    operand, over several calls."""
     ranks = _launch(AG_WORKER, n, 29671 + n)
     for errs in ranks:
         assert all(e < 2e-2 for e in errs[0::2]) and all(e == 0.0 for e in errs[1::2]), ranks
