@@ -249,6 +249,29 @@ def bench_misc(t: Timer, name: str):
         part = torch.empty(296, dim, device="cuda")
         dg = torch.zeros(dim, device="cuda")
         return t(lambda: C.rmsnorm_bwd(dy, x, g, rstd, dx, part, dg, True, dres)), 4.0 * x.numel() * 2, "GB/s"
+    if name in ("layernorm_fwd", "layernorm_bwd"):
+        rows, dim = 16384, 2048
+        x, dy = (torch.randn(rows, dim, device="cuda").to(bf) for _ in range(2))
+        g = torch.ones(dim, device="cuda", dtype=bf)
+        b = torch.zeros(dim, device="cuda", dtype=bf)
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        if name == "layernorm_fwd":
+            return t(lambda: C.layernorm_fwd(x, g, b, y, 1e-5)), 2.0 * x.numel() * 2, "GB/s"
+        part = torch.empty(444, 2 * dim, device="cuda")
+        dgb = torch.empty(2 * dim, device="cuda")
+        return t(lambda: C.layernorm_bwd(dy, x, g, dx, part, dgb, 1e-5)), 3.0 * x.numel() * 2, "GB/s"
+    if name in ("gelu_fwd", "gelu_bwd", "softmax_fwd", "softmax_bwd"):
+        rows, dim = 16384, 4096
+        x, dy = (torch.randn(rows, dim, device="cuda").to(bf) for _ in range(2))
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        if name == "gelu_fwd":
+            return t(lambda: C.act_fwd(x, y, 1)), 2.0 * x.numel() * 2, "GB/s"
+        if name == "gelu_bwd":
+            return t(lambda: C.act_bwd(x, dy, dx, 1)), 3.0 * x.numel() * 2, "GB/s"
+        if name == "softmax_fwd":
+            return t(lambda: C.softmax_rows(x, y)), 2.0 * x.numel() * 2, "GB/s"
+        C.softmax_rows(x, y)
+        return t(lambda: C.softmax_rows_bwd(y, dy, dx)), 3.0 * x.numel() * 2, "GB/s"
     if name in ("moe_route", "moe_dispatch", "moe_combine"):
         T, E, k, d = 16384, 8, 2, 2048
         logits = torch.randn(T, 8, device="cuda").to(bf)
@@ -360,7 +383,8 @@ def bench_misc(t: Timer, name: str):
 
 
 MISC_CASES = ("rope", "rmsnorm_bwd", "moe_route", "moe_dispatch", "moe_combine", "zero_rs", "zero_adamw", "tp_pull",
-              "qkv_rope_append", "paged_prefill", "grouped_gemm", "tl_gemm")
+              "qkv_rope_append", "paged_prefill", "grouped_gemm", "tl_gemm", "layernorm_fwd", "layernorm_bwd",
+              "gelu_fwd", "gelu_bwd", "softmax_fwd", "softmax_bwd")
 
 
 def bench_i2s_gemv(t: Timer, N: int, K: int):
